@@ -1,0 +1,812 @@
+// libffai_cuda — C ABI over the sm_100a MoE kernels.  See include/ffai_cuda.h.
+#include "../../include/ffai_cuda.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "combine.cuh"
+#include "common.cuh"
+#include "expert_gemv.cuh"
+#include "plan.cuh"
+#include "router.cuh"
+
+using namespace ffai;
+
+// ───────────────────────────── layer object ─────────────────────────────
+
+struct ffai_moe_layer {
+    ffai_moe_config cfg{};
+    int device = -1;
+    int e_local = 0;  // experts held by this rank
+    bool weights_set = false;
+    ffai_moe_weights w{};  // device pointers
+    std::vector<void*> owned_weights;
+    std::vector<void*> owned_ws;
+    std::vector<void*> owned_pinned;
+
+    // workspace (device)
+    float* logits = nullptr;        // [T,E]
+    uint32_t* indices = nullptr;    // [T,k]
+    float* rweights = nullptr;      // [T,k]
+    uint32_t* counts = nullptr;     // [E]
+    uint32_t* offsets = nullptr;    // [E+1]
+    uint32_t* perm = nullptr;       // [M]
+    uint32_t* inv_perm = nullptr;   // [M]
+    uint32_t* block_hist = nullptr; // [nblocks,E]
+    float* inner = nullptr;         // [M,I]
+    float* y = nullptr;             // [M,H]
+    float* sh_inner = nullptr;      // [T,Is]
+    float* sh_y = nullptr;          // [T,H]
+    float* sh_gate = nullptr;       // [T]
+
+    // host-buffer entry point
+    cudaStream_t own_stream = nullptr;
+    uint16_t* pin_x = nullptr;
+    uint16_t* pin_out = nullptr;
+    uint16_t* pin_res = nullptr;
+    uint16_t* dev_x = nullptr;
+    uint16_t* dev_out = nullptr;
+    uint16_t* dev_res = nullptr;
+    void* pin_dbg = nullptr;
+    size_t pin_dbg_bytes = 0;
+
+    // stage timing
+    bool timing = false;
+    cudaEvent_t ev[FFAI_N_STAGES][2][2]{};  // [stage][segment][begin/end]
+    bool ev_made = false;
+    int ev_segments[FFAI_N_STAGES]{};
+    int launches = 0;
+    void* nccl_comm = nullptr;
+    std::string err;
+};
+
+namespace {
+
+int fail(ffai_moe_layer* L, int status, const char* fmt, ...) {
+    if (L) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        L->err = buf;
+    }
+    return status;
+}
+
+#define CUDA_TRY(L, expr)                                                                   \
+    do {                                                                                    \
+        cudaError_t _e = (expr);                                                            \
+        if (_e != cudaSuccess)                                                              \
+            return fail((L), FFAI_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+bool valid_bits(int b) { return b == 2 || b == 3 || b == 4 || b == 5 || b == 6 || b == 8; }
+bool valid_gs(int g) { return g == 32 || g == 64 || g == 128; }
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename T>
+int ws_alloc(ffai_moe_layer* L, T** out, size_t count) {
+    void* p = nullptr;
+    if (count == 0) count = 1;
+    CUDA_TRY(L, cudaMalloc(&p, count * sizeof(T)));
+    L->owned_ws.push_back(p);
+    *out = static_cast<T*>(p);
+    return FFAI_OK;
+}
+
+size_t qproj_weight_bytes(int n, int out_dim, int in_dim, int bits) {
+    return (size_t)n * out_dim * (size_t)(in_dim * bits / 32) * 4;
+}
+size_t qproj_group_bytes(int n, int out_dim, int in_dim, int gs) {
+    return (size_t)n * out_dim * (size_t)(in_dim / gs) * 2;
+}
+
+int upload(ffai_moe_layer* L, const void* src, size_t bytes, int location, const void** dst) {
+    *dst = nullptr;
+    if (!src) return FFAI_OK;
+    if (location == FFAI_MEM_DEVICE) {
+        *dst = src;
+        return FFAI_OK;
+    }
+    void* p = nullptr;
+    CUDA_TRY(L, cudaMalloc(&p, bytes ? bytes : 1));
+    L->owned_weights.push_back(p);
+    CUDA_TRY(L, cudaMemcpy(p, src, bytes, cudaMemcpyHostToDevice));
+    *dst = p;
+    return FFAI_OK;
+}
+
+int upload_qproj(ffai_moe_layer* L, const ffai_qproj& src, int n, int out_dim, int in_dim, int bits,
+                 int gs, int location, ffai_qproj* dst, const char* name) {
+    if (!src.weight || !src.scales || !src.biases)
+        return fail(L, FFAI_ERR_INVALID_ARG, "%s: weight/scales/biases must be non-null", name);
+    int rc;
+    if ((rc = upload(L, src.weight, qproj_weight_bytes(n, out_dim, in_dim, bits), location,
+                     (const void**)&dst->weight)))
+        return rc;
+    if ((rc = upload(L, src.scales, qproj_group_bytes(n, out_dim, in_dim, gs), location,
+                     (const void**)&dst->scales)))
+        return rc;
+    if ((rc = upload(L, src.biases, qproj_group_bytes(n, out_dim, in_dim, gs), location,
+                     (const void**)&dst->biases)))
+        return rc;
+    if ((rc = upload(L, src.row_bias, (size_t)n * out_dim * 2, location, (const void**)&dst->row_bias)))
+        return rc;
+    if (!aligned16(dst->weight) || !aligned16(dst->scales) || !aligned16(dst->biases))
+        return fail(L, FFAI_ERR_INVALID_ARG, "%s: device pointers must be 16-byte aligned", name);
+    return FFAI_OK;
+}
+
+int upload_linear(ffai_moe_layer* L, const ffai_linear& src, int kind, int out_dim, int in_dim,
+                  int bits, int gs, int location, ffai_linear* dst, const char* name) {
+    if (!src.weight) return fail(L, FFAI_ERR_INVALID_ARG, "%s: weight must be non-null", name);
+    size_t wbytes = 0;
+    if (kind == FFAI_LINEAR_F32) wbytes = (size_t)out_dim * in_dim * 4;
+    else if (kind == FFAI_LINEAR_BF16) wbytes = (size_t)out_dim * in_dim * 2;
+    else wbytes = qproj_weight_bytes(1, out_dim, in_dim, bits);
+    int rc;
+    if ((rc = upload(L, src.weight, wbytes, location, &dst->weight))) return rc;
+    if (kind == FFAI_LINEAR_AFFINE) {
+        if (!src.scales || !src.biases)
+            return fail(L, FFAI_ERR_INVALID_ARG, "%s: affine projection needs scales and biases", name);
+        if ((rc = upload(L, src.scales, qproj_group_bytes(1, out_dim, in_dim, gs), location,
+                         (const void**)&dst->scales)))
+            return rc;
+        if ((rc = upload(L, src.biases, qproj_group_bytes(1, out_dim, in_dim, gs), location,
+                         (const void**)&dst->biases)))
+            return rc;
+    }
+    if ((rc = upload(L, src.bias, (size_t)out_dim * 2, location, (const void**)&dst->bias))) return rc;
+    if (!aligned16(dst->weight))
+        return fail(L, FFAI_ERR_INVALID_ARG, "%s: device pointers must be 16-byte aligned", name);
+    return FFAI_OK;
+}
+
+void free_list(std::vector<void*>& v) {
+    for (void* p : v) cudaFree(p);
+    v.clear();
+}
+
+// ───────────────────────────── launch helpers ─────────────────────────────
+
+#define BITS_SWITCH(bits, ...)                                  \
+    switch (bits) {                                             \
+        case 2: { constexpr int B = 2; __VA_ARGS__; } break;    \
+        case 3: { constexpr int B = 3; __VA_ARGS__; } break;    \
+        case 4: { constexpr int B = 4; __VA_ARGS__; } break;    \
+        case 5: { constexpr int B = 5; __VA_ARGS__; } break;    \
+        case 6: { constexpr int B = 6; __VA_ARGS__; } break;    \
+        case 8: { constexpr int B = 8; __VA_ARGS__; } break;    \
+        default: return FFAI_ERR_INVALID_ARG;                   \
+    }
+
+template <typename TIn, typename TOut, bool FUSED>
+int launch_grouped_gemv(const GemvParams& p, int bits, const TIn* in, TOut* out, int expert_slots,
+                        cudaStream_t st) {
+    if (p.N <= 0 || p.n_rows <= 0) return FFAI_OK;
+    dim3 grid((p.N + 3) / 4, expert_slots), block(128);
+    BITS_SWITCH(bits, (grouped_gemv_kernel<B, TIn, TOut, FUSED><<<grid, block, 0, st>>>(p, in, out)));
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}
+
+template <int KIND>
+int launch_router_kind(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w,
+                       float* logits, cudaStream_t st) {
+    const int nchunks = (p.hidden + 63) / 64;
+    const size_t smem = ((size_t)p.n_experts * nchunks + 2 * (size_t)p.n_experts) * sizeof(float);
+    if (smem > 200 * 1024) return FFAI_ERR_UNSUPPORTED;
+    const int work = p.n_experts * nchunks;
+    int threads = work >= 512 ? 512 : ((work + 31) / 32) * 32;
+    if (threads < 32) threads = 32;
+    if (KIND == FFAI_LINEAR_AFFINE) {
+        BITS_SWITCH(p.bits, {
+            auto k = router_token_kernel<KIND, B>;
+            if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            k<<<T, threads, smem, st>>>(p, x, T, idx, w, logits);
+        });
+    } else {
+        auto k = router_token_kernel<KIND, 4>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k<<<T, threads, smem, st>>>(p, x, T, idx, w, logits);
+    }
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}
+
+int launch_router(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w,
+                  float* logits, cudaStream_t st) {
+    switch (p.kind) {
+        case FFAI_LINEAR_F32: return launch_router_kind<FFAI_LINEAR_F32>(p, x, T, idx, w, logits, st);
+        case FFAI_LINEAR_BF16: return launch_router_kind<FFAI_LINEAR_BF16>(p, x, T, idx, w, logits, st);
+        case FFAI_LINEAR_AFFINE: return launch_router_kind<FFAI_LINEAR_AFFINE>(p, x, T, idx, w, logits, st);
+    }
+    return FFAI_ERR_INVALID_ARG;
+}
+
+// returns number of launches, or -1 on error
+int launch_plan(const uint32_t* indices, int n_rows, int E, uint32_t* counts, uint32_t* offsets,
+                uint32_t* perm, uint32_t* inv_perm, uint32_t* block_hist, cudaStream_t st) {
+    if (n_rows <= PLAN_ENTRIES_PER_WARP) {
+        plan_small_kernel<<<1, 32, 2 * E * sizeof(uint32_t), st>>>(indices, n_rows, E, counts, offsets,
+                                                                  perm, inv_perm);
+        return cudaGetLastError() == cudaSuccess ? 1 : -1;
+    }
+    const int nb = plan_num_blocks(n_rows);
+    plan_count_kernel<<<nb, 32, E * sizeof(uint32_t), st>>>(indices, n_rows, E, block_hist);
+    plan_scan_kernel<<<1, 256, (E + 1) * sizeof(uint32_t), st>>>(block_hist, nb, E, counts, offsets);
+    plan_scatter_kernel<<<nb, 32, E * sizeof(uint32_t), st>>>(indices, n_rows, E, block_hist, perm, inv_perm);
+    return cudaGetLastError() == cudaSuccess ? 3 : -1;
+}
+
+// dense [1,H] projection per token (shared-expert gate stored as f32 / bf16)
+template <typename TW>
+__global__ void dense_rowdot_kernel(const TW* __restrict__ w, const uint16_t* __restrict__ x,
+                                    float* __restrict__ out, int n_tokens, int hidden) {
+    const int warps = blockDim.x / 32;
+    const int t = blockIdx.x * warps + threadIdx.x / 32;
+    if (t >= n_tokens) return;
+    const int lane = threadIdx.x & 31;
+    float acc = 0.0f;
+    for (int k = lane; k < hidden; k += 32) {
+        float wv;
+        if (sizeof(TW) == 4) wv = ((const float*)w)[k];
+        else wv = bf16_bits_to_f32(((const uint16_t*)w)[k]);
+        acc = fmaf(wv, bf16_bits_to_f32(x[(size_t)t * hidden + k]), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[t] = acc;
+}
+
+enum Stage { ST_ROUTER = 0, ST_PLAN, ST_GATHER, ST_GATE_UP, ST_DOWN, ST_COMBINE, ST_SHARED, ST_EXCHANGE };
+
+// A stage may run in up to two segments per forward (the exchange does).
+void stage_begin(ffai_moe_layer* L, int stage, cudaStream_t st) {
+    if (!L->timing || L->ev_segments[stage] >= 2) return;
+    cudaEventRecord(L->ev[stage][L->ev_segments[stage]][0], st);
+}
+void stage_end(ffai_moe_layer* L, int stage, cudaStream_t st) {
+    if (!L->timing || L->ev_segments[stage] >= 2) return;
+    cudaEventRecord(L->ev[stage][L->ev_segments[stage]][1], st);
+    L->ev_segments[stage] += 1;
+}
+
+int validate_config(const ffai_moe_config* c, ffai_moe_layer* L) {
+    if (c->struct_size != sizeof(ffai_moe_config))
+        return fail(L, FFAI_ERR_INVALID_ARG, "config.struct_size %u != %zu", c->struct_size, sizeof(ffai_moe_config));
+    if (c->hidden <= 0 || c->hidden % 64) return fail(L, FFAI_ERR_INVALID_ARG, "hidden must be a positive multiple of 64");
+    if (c->intermediate <= 0 || c->intermediate % 64) return fail(L, FFAI_ERR_INVALID_ARG, "intermediate must be a positive multiple of 64");
+    // MoERouter.init preconditions, MoELayer.swift:109-118
+    if (c->n_experts <= 0 || c->n_experts > FFAI_MAX_EXPERTS) return fail(L, FFAI_ERR_INVALID_ARG, "n_experts must be in 1..%d", FFAI_MAX_EXPERTS);
+    if (c->top_k <= 0 || c->top_k > c->n_experts || c->top_k > FFAI_MAX_TOP_K)
+        return fail(L, FFAI_ERR_INVALID_ARG, "top_k (%d) must be in 1..min(n_experts=%d, %d)", c->top_k, c->n_experts, FFAI_MAX_TOP_K);
+    if (c->gating_mode != FFAI_GATING_SOFTMAX_THEN_TOPK && c->gating_mode != FFAI_GATING_TOPK_THEN_SOFTMAX)
+        return fail(L, FFAI_ERR_INVALID_ARG, "unknown gating_mode %d", c->gating_mode);
+    if (c->activation < 0 || c->activation > FFAI_ACT_GELU_GLU) return fail(L, FFAI_ERR_INVALID_ARG, "unknown activation %d", c->activation);
+    if (c->router_kind < FFAI_LINEAR_F32 || c->router_kind > FFAI_LINEAR_AFFINE) return fail(L, FFAI_ERR_INVALID_ARG, "unknown router_kind %d", c->router_kind);
+    if (c->router_kind == FFAI_LINEAR_AFFINE && (!valid_bits(c->router_bits) || !valid_gs(c->router_group_size)))
+        return fail(L, FFAI_ERR_INVALID_ARG, "router bits/group_size (%d/%d) unsupported", c->router_bits, c->router_group_size);
+    if (!valid_bits(c->expert_bits) || !valid_gs(c->expert_group_size))
+        return fail(L, FFAI_ERR_INVALID_ARG, "expert bits/group_size (%d/%d) unsupported", c->expert_bits, c->expert_group_size);
+    if (c->shared_intermediate < 0 || c->shared_intermediate % 64) return fail(L, FFAI_ERR_INVALID_ARG, "shared_intermediate must be a multiple of 64");
+    if (c->shared_intermediate > 0) {
+        if (!valid_bits(c->shared_bits) || !valid_gs(c->shared_group_size))
+            return fail(L, FFAI_ERR_INVALID_ARG, "shared bits/group_size (%d/%d) unsupported", c->shared_bits, c->shared_group_size);
+        if (c->shared_gate_kind < FFAI_LINEAR_NONE || c->shared_gate_kind > FFAI_LINEAR_AFFINE)
+            return fail(L, FFAI_ERR_INVALID_ARG, "unknown shared_gate_kind %d", c->shared_gate_kind);
+        if (c->shared_gate_kind == FFAI_LINEAR_AFFINE && (!valid_bits(c->shared_gate_bits) || !valid_gs(c->shared_gate_group_size)))
+            return fail(L, FFAI_ERR_INVALID_ARG, "shared gate bits/group_size unsupported");
+    }
+    if (c->max_tokens <= 0) return fail(L, FFAI_ERR_INVALID_ARG, "max_tokens must be positive");
+    if ((int64_t)c->max_tokens * c->top_k > (int64_t)1 << 30) return fail(L, FFAI_ERR_INVALID_ARG, "max_tokens*top_k too large");
+    const int world = c->ep_world <= 1 ? 1 : c->ep_world;
+    if (c->n_experts % world) return fail(L, FFAI_ERR_INVALID_ARG, "n_experts must divide evenly over ep_world");
+    if (c->ep_rank < 0 || c->ep_rank >= world) return fail(L, FFAI_ERR_INVALID_ARG, "ep_rank out of range");
+    return FFAI_OK;
+}
+
+}  // namespace
+
+// ───────────────────────────── probes ─────────────────────────────
+
+extern "C" FFAI_API int ffai_cuda_abi_version(void) { return FFAI_CUDA_ABI_VERSION; }
+
+extern "C" FFAI_API int ffai_cuda_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+extern "C" FFAI_API const char* ffai_status_string(int status) {
+    switch (status) {
+        case FFAI_OK: return "ok";
+        case FFAI_ERR_INVALID_ARG: return "invalid argument";
+        case FFAI_ERR_UNSUPPORTED: return "unsupported";
+        case FFAI_ERR_CUDA: return "CUDA error";
+        case FFAI_ERR_NOT_READY: return "weights not set";
+        case FFAI_ERR_NCCL: return "NCCL error";
+        case FFAI_ERR_DEVICE_CHECK: return "device-side check failed";
+    }
+    return "unknown status";
+}
+
+// ───────────────────────────── lifecycle ─────────────────────────────
+
+extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_layer** out_layer) {
+    if (!config || !out_layer) return FFAI_ERR_INVALID_ARG;
+    *out_layer = nullptr;
+    ffai_moe_layer* L = new (std::nothrow) ffai_moe_layer();
+    if (!L) return FFAI_ERR_CUDA;
+    int rc = validate_config(config, L);
+    if (rc != FFAI_OK) {
+        // hand the object back so the caller can read the message, but mark it unusable
+        L->cfg = ffai_moe_config{};
+        *out_layer = L;
+        return rc;
+    }
+    L->cfg = *config;
+    const ffai_moe_config& c = L->cfg;
+    const int world = c.ep_world <= 1 ? 1 : c.ep_world;
+    L->e_local = c.n_experts / world;
+    *out_layer = L;
+    if (ffai_cuda_device_count() <= 0) return fail(L, FFAI_ERR_CUDA, "no CUDA device available (there is no CPU fallback)");
+    CUDA_TRY(L, cudaGetDevice(&L->device));
+
+    const size_t T = c.max_tokens, K = c.top_k, E = c.n_experts, H = c.hidden, I = c.intermediate;
+    const size_t M = T * K;
+    if ((rc = ws_alloc(L, &L->logits, T * E))) return rc;
+    if ((rc = ws_alloc(L, &L->indices, M))) return rc;
+    if ((rc = ws_alloc(L, &L->rweights, M))) return rc;
+    if ((rc = ws_alloc(L, &L->counts, E))) return rc;
+    if ((rc = ws_alloc(L, &L->offsets, E + 1))) return rc;
+    if ((rc = ws_alloc(L, &L->perm, M))) return rc;
+    if ((rc = ws_alloc(L, &L->inv_perm, M))) return rc;
+    if ((rc = ws_alloc(L, &L->block_hist, (size_t)plan_num_blocks((int)M) * E))) return rc;
+    if ((rc = ws_alloc(L, &L->inner, M * I))) return rc;
+    if ((rc = ws_alloc(L, &L->y, M * H))) return rc;
+    if (c.shared_intermediate > 0) {
+        if ((rc = ws_alloc(L, &L->sh_inner, T * c.shared_intermediate))) return rc;
+        if ((rc = ws_alloc(L, &L->sh_y, T * H))) return rc;
+        if ((rc = ws_alloc(L, &L->sh_gate, T))) return rc;
+    }
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_weights* w) {
+    if (!L || !w) return FFAI_ERR_INVALID_ARG;
+    if (L->cfg.struct_size == 0) return fail(L, FFAI_ERR_INVALID_ARG, "layer was not created successfully");
+    if (w->struct_size != sizeof(ffai_moe_weights))
+        return fail(L, FFAI_ERR_INVALID_ARG, "weights.struct_size %u != %zu", w->struct_size, sizeof(ffai_moe_weights));
+    if (w->location != FFAI_MEM_HOST && w->location != FFAI_MEM_DEVICE)
+        return fail(L, FFAI_ERR_INVALID_ARG, "unknown weights.location %d", w->location);
+    const ffai_moe_config& c = L->cfg;
+    CUDA_TRY(L, cudaSetDevice(L->device));
+    free_list(L->owned_weights);
+    L->weights_set = false;
+    L->w = ffai_moe_weights{};
+    int rc;
+    const int loc = w->location;
+    if ((rc = upload_linear(L, w->router, c.router_kind, c.n_experts, c.hidden, c.router_bits,
+                            c.router_group_size, loc, &L->w.router, "router")))
+        return rc;
+    if (c.router_has_bias && !w->router.bias) return fail(L, FFAI_ERR_INVALID_ARG, "router_has_bias set but router.bias is null");
+    if (!c.router_has_bias) L->w.router.bias = nullptr;
+    if (c.router_expert_bias) {
+        if (!w->router_expert_bias) return fail(L, FFAI_ERR_INVALID_ARG, "router_expert_bias set but pointer is null");
+        if ((rc = upload(L, w->router_expert_bias, (size_t)c.n_experts * 4, loc, (const void**)&L->w.router_expert_bias))) return rc;
+    }
+    const int El = L->e_local;
+    if ((rc = upload_qproj(L, w->gate_proj, El, c.intermediate, c.hidden, c.expert_bits, c.expert_group_size, loc, &L->w.gate_proj, "gate_proj"))) return rc;
+    if ((rc = upload_qproj(L, w->up_proj, El, c.intermediate, c.hidden, c.expert_bits, c.expert_group_size, loc, &L->w.up_proj, "up_proj"))) return rc;
+    if ((rc = upload_qproj(L, w->down_proj, El, c.hidden, c.intermediate, c.expert_bits, c.expert_group_size, loc, &L->w.down_proj, "down_proj"))) return rc;
+    if (c.expert_row_bias && (!w->gate_proj.row_bias || !w->up_proj.row_bias || !w->down_proj.row_bias))
+        return fail(L, FFAI_ERR_INVALID_ARG, "expert_row_bias set but a row_bias pointer is null");
+    if (!c.expert_row_bias) L->w.gate_proj.row_bias = L->w.up_proj.row_bias = L->w.down_proj.row_bias = nullptr;
+    if (c.shared_intermediate > 0) {
+        const int Is = c.shared_intermediate;
+        if ((rc = upload_qproj(L, w->shared_gate_proj, 1, Is, c.hidden, c.shared_bits, c.shared_group_size, loc, &L->w.shared_gate_proj, "shared_gate_proj"))) return rc;
+        if ((rc = upload_qproj(L, w->shared_up_proj, 1, Is, c.hidden, c.shared_bits, c.shared_group_size, loc, &L->w.shared_up_proj, "shared_up_proj"))) return rc;
+        if ((rc = upload_qproj(L, w->shared_down_proj, 1, c.hidden, Is, c.shared_bits, c.shared_group_size, loc, &L->w.shared_down_proj, "shared_down_proj"))) return rc;
+        L->w.shared_gate_proj.row_bias = L->w.shared_up_proj.row_bias = L->w.shared_down_proj.row_bias = nullptr;
+        if (c.shared_gate_kind != FFAI_LINEAR_NONE)
+            if ((rc = upload_linear(L, w->shared_gate, c.shared_gate_kind, 1, c.hidden, c.shared_gate_bits, c.shared_gate_group_size, loc, &L->w.shared_gate, "shared_gate"))) return rc;
+    }
+    L->weights_set = true;
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_moe_destroy(ffai_moe_layer* L) {
+    if (!L) return FFAI_OK;
+    if (L->device >= 0) cudaSetDevice(L->device);
+    free_list(L->owned_weights);
+    free_list(L->owned_ws);
+    for (void* p : L->owned_pinned) cudaFreeHost(p);
+    if (L->ev_made)
+        for (auto& a : L->ev) for (auto& b : a) for (auto& e : b) cudaEventDestroy(e);
+    if (L->own_stream) cudaStreamDestroy(L->own_stream);
+    delete L;
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API const char* ffai_moe_last_error(const ffai_moe_layer* L) { return L ? L->err.c_str() : ""; }
+
+extern "C" FFAI_API int ffai_moe_set_nccl_comm(ffai_moe_layer* L, void* comm) {
+    if (!L) return FFAI_ERR_INVALID_ARG;
+    L->nccl_comm = comm;
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_moe_set_stage_timing(ffai_moe_layer* L, int enabled) {
+    if (!L) return FFAI_ERR_INVALID_ARG;
+    if (enabled && !L->ev_made) {
+        for (auto& a : L->ev) for (auto& b : a) for (auto& e : b) CUDA_TRY(L, cudaEventCreate(&e));
+        L->ev_made = true;
+    }
+    L->timing = enabled != 0;
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_moe_get_stage_ms(ffai_moe_layer* L, float out_ms[FFAI_N_STAGES]) {
+    if (!L || !out_ms) return FFAI_ERR_INVALID_ARG;
+    for (int i = 0; i < FFAI_N_STAGES; ++i) out_ms[i] = 0.0f;
+    if (!L->ev_made) return FFAI_OK;
+    for (int i = 0; i < FFAI_N_STAGES; ++i)
+        for (int s = 0; s < L->ev_segments[i]; ++s) {
+            float ms = 0.0f;
+            CUDA_TRY(L, cudaEventSynchronize(L->ev[i][s][1]));
+            CUDA_TRY(L, cudaEventElapsedTime(&ms, L->ev[i][s][0], L->ev[i][s][1]));
+            out_ms[i] += ms;
+        }
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_moe_last_launch_count(const ffai_moe_layer* L) { return L ? L->launches : 0; }
+
+// ───────────────────────────── forward ─────────────────────────────
+
+namespace {
+
+RouterParams router_params(const ffai_moe_layer* L) {
+    const ffai_moe_config& c = L->cfg;
+    RouterParams p{};
+    p.weight = L->w.router.weight;
+    p.scales = L->w.router.scales;
+    p.biases = L->w.router.biases;
+    p.bias = L->w.router.bias;
+    p.expert_bias = c.router_expert_bias ? L->w.router_expert_bias : nullptr;
+    p.kind = c.router_kind;
+    p.bits = c.router_bits;
+    p.group_size = c.router_group_size;
+    p.hidden = c.hidden;
+    p.n_experts = c.n_experts;
+    p.top_k = c.top_k;
+    p.gating_mode = c.gating_mode;
+    p.norm_topk_prob = c.norm_topk_prob;
+    p.logits_bf16 = c.router_logits_bf16;
+    return p;
+}
+
+GemvParams gemv_params(const ffai_qproj& a, const ffai_qproj* b, int N, int K, int gs, int n_experts) {
+    GemvParams p{};
+    p.weight = a.weight; p.scales = a.scales; p.biases = a.biases; p.row_bias = a.row_bias;
+    if (b) { p.weight2 = b->weight; p.scales2 = b->scales; p.biases2 = b->biases; p.row_bias2 = b->row_bias; }
+    p.N = N; p.K = K; p.group_size = gs; p.n_experts = n_experts;
+    p.in_row_div = 1;
+    return p;
+}
+
+int copy_debug(ffai_moe_layer* L, const ffai_moe_debug* d, int T, cudaStream_t st, cudaMemcpyKind kind) {
+    if (!d) return FFAI_OK;
+    const ffai_moe_config& c = L->cfg;
+    const size_t M = (size_t)T * c.top_k, E = c.n_experts;
+    if (d->indices) CUDA_TRY(L, cudaMemcpyAsync(d->indices, L->indices, M * 4, kind, st));
+    if (d->weights) CUDA_TRY(L, cudaMemcpyAsync(d->weights, L->rweights, M * 4, kind, st));
+    if (d->logits) CUDA_TRY(L, cudaMemcpyAsync(d->logits, L->logits, (size_t)T * E * 4, kind, st));
+    if (d->counts) CUDA_TRY(L, cudaMemcpyAsync(d->counts, L->counts, E * 4, kind, st));
+    if (d->offsets) CUDA_TRY(L, cudaMemcpyAsync(d->offsets, L->offsets, (E + 1) * 4, kind, st));
+    if (d->perm) CUDA_TRY(L, cudaMemcpyAsync(d->perm, L->perm, M * 4, kind, st));
+    if (d->inv_perm) CUDA_TRY(L, cudaMemcpyAsync(d->inv_perm, L->inv_perm, M * 4, kind, st));
+    return FFAI_OK;
+}
+
+int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, const uint16_t* residual,
+                   cudaStream_t st) {
+    const ffai_moe_config& c = L->cfg;
+    const int H = c.hidden, I = c.intermediate, E = c.n_experts, K = c.top_k;
+    const int M = T * K;
+    int rc;
+    L->launches = 0;
+    for (auto& n : L->ev_segments) n = 0;
+
+    // stage 0: router (projection + bias + top-k + softmax)
+    stage_begin(L, ST_ROUTER, st);
+    RouterParams rp = router_params(L);
+    if ((rc = launch_router(rp, x, T, L->indices, L->rweights, L->logits, st)))
+        return fail(L, rc, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    L->launches += 1;
+    stage_end(L, ST_ROUTER, st);
+
+    // stage 1: dispatch plan
+    stage_begin(L, ST_PLAN, st);
+    int nl = launch_plan(L->indices, M, E, L->counts, L->offsets, L->perm, L->inv_perm, L->block_hist, st);
+    if (nl < 0) return fail(L, FFAI_ERR_CUDA, "plan launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    L->launches += nl;
+    stage_end(L, ST_PLAN, st);
+
+    // stage 2: gather — the CUDA-core path reads rows through the permutation; nothing to launch
+
+    // stage 3: gate/up products + activation -> inner[M, I]
+    stage_begin(L, ST_GATE_UP, st);
+    {
+        GemvParams p = gemv_params(L->w.gate_proj, &L->w.up_proj, I, H, c.expert_group_size, E);
+        p.offsets = L->offsets;
+        p.in_row_ids = L->perm;
+        p.in_row_div = K;
+        p.n_rows = M;
+        p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
+        if ((rc = launch_grouped_gemv<uint16_t, float, true>(p, c.expert_bits, x, L->inner, E, st)))
+            return fail(L, rc, "gate/up launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += 1;
+    }
+    stage_end(L, ST_GATE_UP, st);
+    // stage 4: down product -> y[M, H]
+    stage_begin(L, ST_DOWN, st);
+    {
+        GemvParams p = gemv_params(L->w.down_proj, nullptr, H, I, c.expert_group_size, E);
+        p.offsets = L->offsets;
+        p.n_rows = M;
+        if ((rc = launch_grouped_gemv<float, float, false>(p, c.expert_bits, L->inner, L->y, E, st)))
+            return fail(L, rc, "down launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += 1;
+    }
+    stage_end(L, ST_DOWN, st);
+    // shared expert
+    const float* sh_y = nullptr;
+    const float* sh_gate = nullptr;
+    stage_begin(L, ST_SHARED, st);
+    if (c.shared_intermediate > 0) {
+        const int Is = c.shared_intermediate;
+        GemvParams p = gemv_params(L->w.shared_gate_proj, &L->w.shared_up_proj, Is, H, c.shared_group_size, 1);
+        p.n_rows = T;
+        p.activation = FFAI_ACT_SWIGLU;
+        if ((rc = launch_grouped_gemv<uint16_t, float, true>(p, c.shared_bits, x, L->sh_inner, 1, st)))
+            return fail(L, rc, "shared gate/up launch failed");
+        GemvParams d = gemv_params(L->w.shared_down_proj, nullptr, H, Is, c.shared_group_size, 1);
+        d.n_rows = T;
+        if ((rc = launch_grouped_gemv<float, float, false>(d, c.shared_bits, L->sh_inner, L->sh_y, 1, st)))
+            return fail(L, rc, "shared down launch failed");
+        L->launches += 2;
+        sh_y = L->sh_y;
+        if (c.shared_gate_kind == FFAI_LINEAR_AFFINE) {
+            ffai_qproj g{(const uint32_t*)L->w.shared_gate.weight, L->w.shared_gate.scales, L->w.shared_gate.biases, nullptr};
+            GemvParams gp = gemv_params(g, nullptr, 1, H, c.shared_gate_group_size, 1);
+            gp.n_rows = T;
+            if ((rc = launch_grouped_gemv<uint16_t, float, false>(gp, c.shared_gate_bits, x, L->sh_gate, 1, st)))
+                return fail(L, rc, "shared gate launch failed");
+            L->launches += 1;
+            sh_gate = L->sh_gate;
+        } else if (c.shared_gate_kind == FFAI_LINEAR_F32) {
+            dense_rowdot_kernel<float><<<(T + 3) / 4, 128, 0, st>>>((const float*)L->w.shared_gate.weight, x, L->sh_gate, T, H);
+            L->launches += 1;
+            sh_gate = L->sh_gate;
+        } else if (c.shared_gate_kind == FFAI_LINEAR_BF16) {
+            dense_rowdot_kernel<uint16_t><<<(T + 3) / 4, 128, 0, st>>>((const uint16_t*)L->w.shared_gate.weight, x, L->sh_gate, T, H);
+            L->launches += 1;
+            sh_gate = L->sh_gate;
+        }
+    }
+    stage_end(L, ST_SHARED, st);
+    stage_begin(L, ST_COMBINE, st);
+    combine_kernel<float, float><<<T, 256, 0, st>>>(L->y, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
+    L->launches += 1;
+    stage_end(L, ST_COMBINE, st);
+    if (cudaGetLastError() != cudaSuccess) return fail(L, FFAI_ERR_CUDA, "combine launch failed");
+    return FFAI_OK;
+}
+
+int check_forward_args(ffai_moe_layer* L, const void* x, int T, const void* out) {
+    if (!L) return FFAI_ERR_INVALID_ARG;
+    if (L->cfg.struct_size == 0) return fail(L, FFAI_ERR_INVALID_ARG, "layer was not created successfully");
+    if (!L->weights_set) return fail(L, FFAI_ERR_NOT_READY, "forward called before set_weights");
+    if (T < 0) return fail(L, FFAI_ERR_INVALID_ARG, "n_tokens must be >= 0");
+    if (T > L->cfg.max_tokens) return fail(L, FFAI_ERR_INVALID_ARG, "n_tokens %d exceeds max_tokens %d", T, L->cfg.max_tokens);
+    if (T > 0 && (!x || !out)) return fail(L, FFAI_ERR_INVALID_ARG, "x and out must be non-null");
+    return FFAI_OK;
+}
+
+}  // namespace
+
+extern "C" FFAI_API int ffai_moe_forward(ffai_moe_layer* L, const uint16_t* x, int32_t T, uint16_t* out,
+                                const uint16_t* residual, const ffai_moe_debug* debug, void* stream) {
+    int rc = check_forward_args(L, x, T, out);
+    if (rc) return rc;
+    if (T == 0) return FFAI_OK;
+    if (!aligned16(x) || !aligned16(out) || (residual && !aligned16(residual)))
+        return fail(L, FFAI_ERR_INVALID_ARG, "x/out/residual must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((rc = forward_device(L, x, T, out, residual, st))) return rc;
+    return copy_debug(L, debug, T, st, cudaMemcpyDeviceToDevice);
+}
+
+extern "C" FFAI_API int ffai_moe_forward_host(ffai_moe_layer* L, const uint16_t* x, int32_t T, uint16_t* out,
+                                     const uint16_t* residual, const ffai_moe_debug* debug) {
+    int rc = check_forward_args(L, x, T, out);
+    if (rc) return rc;
+    if (T == 0) return FFAI_OK;
+    const ffai_moe_config& c = L->cfg;
+    CUDA_TRY(L, cudaSetDevice(L->device));
+    const size_t cap = (size_t)c.max_tokens * c.hidden * 2;
+    if (!L->own_stream) {
+        CUDA_TRY(L, cudaStreamCreateWithFlags(&L->own_stream, cudaStreamNonBlocking));
+        void* p;
+        CUDA_TRY(L, cudaMallocHost(&p, cap)); L->owned_pinned.push_back(p); L->pin_x = (uint16_t*)p;
+        CUDA_TRY(L, cudaMallocHost(&p, cap)); L->owned_pinned.push_back(p); L->pin_out = (uint16_t*)p;
+        CUDA_TRY(L, cudaMallocHost(&p, cap)); L->owned_pinned.push_back(p); L->pin_res = (uint16_t*)p;
+        if ((rc = ws_alloc(L, &L->dev_x, cap / 2))) return rc;
+        if ((rc = ws_alloc(L, &L->dev_out, cap / 2))) return rc;
+        if ((rc = ws_alloc(L, &L->dev_res, cap / 2))) return rc;
+    }
+    cudaStream_t st = L->own_stream;
+    const size_t bytes = (size_t)T * c.hidden * 2;
+    // Stage through pinned memory so the copies are asynchronous DMA whatever the caller's buffer is.
+    memcpy(L->pin_x, x, bytes);
+    CUDA_TRY(L, cudaMemcpyAsync(L->dev_x, L->pin_x, bytes, cudaMemcpyHostToDevice, st));
+    const uint16_t* dres = nullptr;
+    if (residual) {
+        memcpy(L->pin_res, residual, bytes);
+        CUDA_TRY(L, cudaMemcpyAsync(L->dev_res, L->pin_res, bytes, cudaMemcpyHostToDevice, st));
+        dres = L->dev_res;
+    }
+    if ((rc = forward_device(L, L->dev_x, T, L->dev_out, dres, st))) return rc;
+    CUDA_TRY(L, cudaMemcpyAsync(L->pin_out, L->dev_out, bytes, cudaMemcpyDeviceToHost, st));
+    if ((rc = copy_debug(L, debug, T, st, cudaMemcpyDeviceToHost))) return rc;
+    CUDA_TRY(L, cudaStreamSynchronize(st));
+    memcpy(out, L->pin_out, bytes);
+    return FFAI_OK;
+}
+
+// ───────────────────────────── operator-level entry points ─────────────────────────────
+
+namespace {
+int op_check_quant(int bits, int gs, int in_dim) {
+    if (!valid_bits(bits) || !valid_gs(gs)) return FFAI_ERR_INVALID_ARG;
+    if (in_dim <= 0 || in_dim % 32 || in_dim % gs) return FFAI_ERR_INVALID_ARG;  // Ops.swift:4610-4615
+    return FFAI_OK;
+}
+int need_device() { return ffai_cuda_device_count() > 0 ? FFAI_OK : FFAI_ERR_CUDA; }
+}  // namespace
+
+extern "C" FFAI_API int ffai_op_dequant_gemv(const uint16_t* x, const uint32_t* weight, const uint16_t* scales,
+                                    const uint16_t* biases, uint16_t* out, int32_t out_dim,
+                                    int32_t in_dim, int32_t bits, int32_t gs, void* stream) {
+    if (!x || !weight || !scales || !biases || !out || out_dim <= 0) return FFAI_ERR_INVALID_ARG;
+    int rc = op_check_quant(bits, gs, in_dim);
+    if (rc) return rc;
+    if ((rc = need_device())) return rc;
+    ffai_qproj q{weight, scales, biases, nullptr};
+    GemvParams p = gemv_params(q, nullptr, out_dim, in_dim, gs, 1);
+    p.n_rows = 1;
+    return launch_grouped_gemv<uint16_t, uint16_t, false>(p, bits, x, out, 1, (cudaStream_t)stream);
+}
+
+extern "C" FFAI_API int ffai_op_dequant_gemv_expert_indexed(const uint16_t* x, const uint32_t* weight,
+                                                   const uint16_t* scales, const uint16_t* biases,
+                                                   const uint32_t* expert_index, uint16_t* out,
+                                                   int32_t n_experts, int32_t out_dim, int32_t in_dim,
+                                                   int32_t bits, int32_t gs, void* stream) {
+    if (!x || !weight || !scales || !biases || !out || !expert_index || out_dim <= 0 || n_experts <= 0)
+        return FFAI_ERR_INVALID_ARG;
+    int rc = op_check_quant(bits, gs, in_dim);
+    if (rc) return rc;
+    if ((rc = need_device())) return rc;
+    ffai_qproj q{weight, scales, biases, nullptr};
+    GemvParams p = gemv_params(q, nullptr, out_dim, in_dim, gs, n_experts);
+    p.n_rows = 1;
+    p.expert_index = expert_index;
+    return launch_grouped_gemv<uint16_t, uint16_t, false>(p, bits, x, out, 1, (cudaStream_t)stream);
+}
+
+extern "C" FFAI_API int ffai_op_moe_router_topk(const float* logits, uint32_t* indices, float* weights,
+                                       int32_t T, int32_t E, int32_t k, int32_t gating_mode,
+                                       int32_t norm, const float* expert_bias, void* stream) {
+    if (!logits || !indices || !weights || T <= 0) return FFAI_ERR_INVALID_ARG;
+    if (E <= 0 || E > FFAI_MAX_EXPERTS || k <= 0 || k > E || k > FFAI_MAX_TOP_K) return FFAI_ERR_INVALID_ARG;
+    if (gating_mode != 0 && gating_mode != 1) return FFAI_ERR_INVALID_ARG;
+    int rc;
+    if ((rc = need_device())) return rc;
+    RouterParams p{};
+    p.n_experts = E; p.top_k = k; p.gating_mode = gating_mode; p.norm_topk_prob = norm;
+    p.expert_bias = expert_bias;
+    const int warps = 4;
+    route_only_kernel<<<(T + warps - 1) / warps, warps * 32, (size_t)warps * 2 * E * sizeof(float),
+                        (cudaStream_t)stream>>>(p, logits, T, indices, weights);
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}
+
+extern "C" FFAI_API size_t ffai_op_moe_plan_workspace_bytes(int32_t n_rows, int32_t n_experts) {
+    if (n_rows <= 0 || n_experts <= 0) return 0;
+    return (size_t)plan_num_blocks(n_rows) * n_experts * sizeof(uint32_t);
+}
+
+extern "C" FFAI_API int ffai_op_moe_plan(const uint32_t* indices, int32_t T, int32_t k, int32_t E,
+                                uint32_t* counts, uint32_t* offsets, uint32_t* perm,
+                                uint32_t* inv_perm, void* workspace, void* stream) {
+    if (!indices || !counts || !offsets || !perm || !inv_perm || T <= 0 || k <= 0) return FFAI_ERR_INVALID_ARG;
+    if (E <= 0 || E > FFAI_MAX_EXPERTS) return FFAI_ERR_INVALID_ARG;
+    if ((int64_t)T * k > PLAN_ENTRIES_PER_WARP && !workspace) return FFAI_ERR_INVALID_ARG;
+    int rc;
+    if ((rc = need_device())) return rc;
+    return launch_plan(indices, T * k, E, counts, offsets, perm, inv_perm, (uint32_t*)workspace,
+                       (cudaStream_t)stream) < 0 ? FFAI_ERR_CUDA : FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_op_gather_rows(const uint16_t* table, const uint32_t* ids, uint16_t* out,
+                                   int32_t n_rows, int32_t row_len, void* stream) {
+    if (!table || !ids || !out || n_rows <= 0 || row_len <= 0 || row_len % 8) return FFAI_ERR_INVALID_ARG;
+    int rc;
+    if ((rc = need_device())) return rc;
+    gather_rows_kernel<<<(n_rows + 3) / 4, 128, 0, (cudaStream_t)stream>>>(table, ids, 1, out, n_rows, row_len);
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}
+
+extern "C" FFAI_API int ffai_op_moe_gather_dequant_gemm(const uint16_t* x, const uint32_t* weight,
+                                               const uint16_t* scales, const uint16_t* biases,
+                                               const uint32_t* indices, uint16_t* out, int32_t m_total,
+                                               int32_t n_out, int32_t k_in, int32_t n_experts,
+                                               int32_t bits, int32_t gs, void* stream) {
+    if (!x || !weight || !scales || !biases || !indices || !out) return FFAI_ERR_INVALID_ARG;
+    if (m_total <= 0 || n_out <= 0 || n_experts <= 0 || n_experts > FFAI_MAX_EXPERTS) return FFAI_ERR_INVALID_ARG;
+    int rc = op_check_quant(bits, gs, k_in);
+    if (rc) return rc;
+    if ((rc = need_device())) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t* offsets = nullptr;
+    if (cudaMallocAsync((void**)&offsets, (size_t)(n_experts + 1) * 4, st) != cudaSuccess) return FFAI_ERR_CUDA;
+    offsets_from_sorted_ids_kernel<<<(n_experts + 1 + 127) / 128, 128, 0, st>>>(indices, m_total, n_experts, offsets);
+    ffai_qproj q{weight, scales, biases, nullptr};
+    GemvParams p = gemv_params(q, nullptr, n_out, k_in, gs, n_experts);
+    p.offsets = offsets;
+    p.n_rows = m_total;
+    rc = launch_grouped_gemv<uint16_t, uint16_t, false>(p, bits, x, out, n_experts, st);
+    cudaFreeAsync(offsets, st);
+    return rc;
+}
+
+extern "C" FFAI_API int ffai_op_glu_activation(const uint16_t* gate, const uint16_t* up, uint16_t* out,
+                                      int64_t n, int32_t activation, float limit, float alpha,
+                                      void* stream) {
+    if (!gate || !up || !out || n <= 0 || activation < 0 || activation > FFAI_ACT_GELU_GLU) return FFAI_ERR_INVALID_ARG;
+    int rc;
+    if ((rc = need_device())) return rc;
+    glu_activation_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gate, up, out, n, activation, limit, alpha);
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}
+
+extern "C" FFAI_API int ffai_op_moe_unpermute(const uint16_t* expert_out, const uint32_t* inv_perm,
+                                     const float* weights, uint16_t* out, int32_t T, int32_t hidden,
+                                     int32_t k, void* stream) {
+    if (!expert_out || !inv_perm || !weights || !out || T <= 0 || hidden <= 0 || hidden % 4) return FFAI_ERR_INVALID_ARG;
+    if (k <= 0 || k > FFAI_MAX_TOP_K) return FFAI_ERR_INVALID_ARG;
+    int rc;
+    if ((rc = need_device())) return rc;
+    combine_kernel<uint16_t, float><<<T, 256, 0, (cudaStream_t)stream>>>(expert_out, inv_perm, weights, k, nullptr, nullptr, nullptr, out, hidden);
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}
+
+extern "C" FFAI_API int ffai_op_sigmoid_scalar_fma(const uint16_t* gate, const uint16_t* value,
+                                          const uint16_t* base, const uint16_t* residual,
+                                          uint16_t* out, int32_t n_rows, int32_t hidden, void* stream) {
+    if (!gate || !value || !base || !out || n_rows <= 0 || hidden <= 0) return FFAI_ERR_INVALID_ARG;
+    int rc;
+    if ((rc = need_device())) return rc;
+    sigmoid_scalar_fma_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(gate, value, base, residual, out, hidden);
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}

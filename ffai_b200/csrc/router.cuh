@@ -1,0 +1,227 @@
+// Router: projection + bias + top-k + softmax/renormalise, fused in one kernel.
+//
+// Replaces, per token: the router GEMV (FFAI Layers.swift:78-84 / :201-210,
+// GPTOSSText.swift:341-362), the device->host sync and MoERouter.route
+// (MoELayer.swift:140-296) or GPTOSSMoELayer's sort (GPTOSSText.swift:1346-1361),
+// and Ops.moeRouterTopKMany (Ops.swift:2598-2661).
+//
+// Accumulation order of a logit is fixed so that top-k is reproducible to the
+// bit: the hidden axis is cut into 64-wide chunks; inside a chunk products are
+// folded in ascending k with fused multiply-add starting from 0; chunk sums are
+// then added in ascending chunk order.  Top-k orders by (value desc, index asc).
+#pragma once
+#include "common.cuh"
+
+namespace ffai {
+
+struct RouterParams {
+    const void* weight;        // f32 / bf16 [E,H] or u32 [E, H*bits/32]
+    const uint16_t* scales;    // affine only
+    const uint16_t* biases;    // affine only
+    const uint16_t* bias;      // nullable projection bias [E], bf16
+    const float* expert_bias;  // nullable post-softmax bias [E]
+    int kind;                  // ffai_linear_kind: 1 f32, 2 bf16, 3 affine
+    int bits, group_size;
+    int hidden, n_experts, top_k;
+    int gating_mode, norm_topk_prob;
+    int logits_bf16;
+};
+
+// One 64-wide chunk of dot(x[t], W[e]) in ascending k with fused multiply-add.
+template <int KIND, int BITS>
+FFAI_DEVINL float router_chunk_dot(const RouterParams& p, const uint16_t* __restrict__ xrow, int e,
+                                   int k0, int k1) {
+    float acc = 0.0f;
+    const int H = p.hidden;
+    if (KIND == 1) {
+        const float* w = (const float*)p.weight + (size_t)e * H;
+        if (k1 - k0 == 64) {
+#pragma unroll
+            for (int j = 0; j < 64; j += 8) {
+                uint4 xv = *(const uint4*)(xrow + k0 + j);
+                float4 w0 = *(const float4*)(w + k0 + j), w1 = *(const float4*)(w + k0 + j + 4);
+                acc = __fmaf_rn(bf16lo(xv.x), w0.x, acc); acc = __fmaf_rn(bf16hi(xv.x), w0.y, acc);
+                acc = __fmaf_rn(bf16lo(xv.y), w0.z, acc); acc = __fmaf_rn(bf16hi(xv.y), w0.w, acc);
+                acc = __fmaf_rn(bf16lo(xv.z), w1.x, acc); acc = __fmaf_rn(bf16hi(xv.z), w1.y, acc);
+                acc = __fmaf_rn(bf16lo(xv.w), w1.z, acc); acc = __fmaf_rn(bf16hi(xv.w), w1.w, acc);
+            }
+        } else {
+            for (int k = k0; k < k1; ++k) acc = __fmaf_rn(bf16_bits_to_f32(xrow[k]), w[k], acc);
+        }
+    } else if (KIND == 2) {
+        const uint16_t* w = (const uint16_t*)p.weight + (size_t)e * H;
+        if (k1 - k0 == 64) {
+#pragma unroll
+            for (int j = 0; j < 64; j += 8) {
+                uint4 xv = *(const uint4*)(xrow + k0 + j);
+                uint4 wv = *(const uint4*)(w + k0 + j);
+                acc = __fmaf_rn(bf16lo(xv.x), bf16lo(wv.x), acc); acc = __fmaf_rn(bf16hi(xv.x), bf16hi(wv.x), acc);
+                acc = __fmaf_rn(bf16lo(xv.y), bf16lo(wv.y), acc); acc = __fmaf_rn(bf16hi(xv.y), bf16hi(wv.y), acc);
+                acc = __fmaf_rn(bf16lo(xv.z), bf16lo(wv.z), acc); acc = __fmaf_rn(bf16hi(xv.z), bf16hi(wv.z), acc);
+                acc = __fmaf_rn(bf16lo(xv.w), bf16lo(wv.w), acc); acc = __fmaf_rn(bf16hi(xv.w), bf16hi(wv.w), acc);
+            }
+        } else {
+            for (int k = k0; k < k1; ++k)
+                acc = __fmaf_rn(bf16_bits_to_f32(xrow[k]), bf16_bits_to_f32(w[k]), acc);
+        }
+    } else {
+        // affine: w = fma(scale, q, bias), one scale/bias per group_size values
+        const uint32_t* w = (const uint32_t*)p.weight + (size_t)e * (H * BITS / 32);
+        const int gpr = H / p.group_size;
+        for (int k = k0; k < k1; k += 32) {  // H is a multiple of 32; a 32-run lies in one group
+            const int g = k / p.group_size;
+            const float s = bf16_bits_to_f32(p.scales[(size_t)e * gpr + g]);
+            const float b = bf16_bits_to_f32(p.biases[(size_t)e * gpr + g]);
+            uint32_t words[BITS + 1];
+            const uint32_t* src = w + (k / 32) * BITS;
+#pragma unroll
+            for (int i = 0; i < BITS; ++i) words[i] = src[i];
+            words[BITS] = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                float q = small_uint_to_float(unpack_at<BITS>(words, j));
+                float wv = __fmaf_rn(s, q, b);
+                acc = __fmaf_rn(bf16_bits_to_f32(xrow[k + j]), wv, acc);
+            }
+        }
+    }
+    return acc;
+}
+
+// Warp-wide arg-best by (value desc, index asc).
+FFAI_DEVINL void warp_argbest(float& v, int& i) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        float ov = __shfl_xor_sync(0xFFFFFFFFu, v, m);
+        int oi = __shfl_xor_sync(0xFFFFFFFFu, i, m);
+        bool take = (oi >= 0) && (i < 0 || ov > v || (ov == v && oi < i));
+        if (take) { v = ov; i = oi; }
+    }
+}
+
+// Top-k of vals[0..E) in shared memory by one warp; selected indices (in
+// selection order) returned lane-wise: lane j < k holds index j.  `taken` is a
+// per-lane bit mask over the lane's strided elements (e = lane + 32*j).
+FFAI_DEVINL void warp_topk(const float* vals, int E, int k, int lane, int& my_idx, float& my_val) {
+    uint32_t taken = 0;
+    my_idx = -1;
+    my_val = 0.0f;
+    for (int r = 0; r < k; ++r) {
+        float bv = 0.0f;
+        int bi = -1;
+        for (int j = 0, e = lane; e < E; ++j, e += 32) {
+            if (taken & (1u << j)) continue;
+            float v = vals[e];
+            if (bi < 0 || v > bv) { bv = v; bi = e; }
+        }
+        warp_argbest(bv, bi);
+        if (bi >= 0 && (bi & 31) == lane) taken |= 1u << (bi >> 5);
+        if (lane == r) { my_idx = bi; my_val = bv; }
+    }
+}
+
+// Routing of one token by one warp, given its logits in shared memory.
+// `scratch` is E floats of shared memory (used by the general softmax path).
+FFAI_DEVINL void route_token_warp(const RouterParams& p, float* logits_s, float* scratch, int lane,
+                                  uint32_t* idx_out, float* w_out) {
+    const int E = p.n_experts, K = p.top_k;
+    int my_idx;
+    float my_val;
+    const bool fast = (p.gating_mode == 1) ||
+                      (p.gating_mode == 0 && p.norm_topk_prob && p.expert_bias == nullptr);
+    if (fast) {
+        // top-k of the logits, softmax over the picked (MoELayer.swift:146-172, 197-203)
+        warp_topk(logits_s, E, K, lane, my_idx, my_val);
+        float vmax = __shfl_sync(0xFFFFFFFFu, my_val, 0);  // selection order is value-desc
+        float ex = (lane < K) ? det_expf(__fsub_rn(my_val, vmax)) : 0.0f;
+        float sum = 0.0f;
+        for (int j = 0; j < K; ++j) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, ex, j));
+        float w = (sum > 0.0f) ? __fdiv_rn(ex, sum) : __fdiv_rn(1.0f, (float)K);
+        if (lane < K) { idx_out[lane] = (uint32_t)my_idx; w_out[lane] = w; }
+        return;
+    }
+    // general softmax-then-top-k (MoELayer.swift:174-195)
+    float vmax = -INFINITY;
+    for (int e = lane; e < E; e += 32) vmax = fmaxf(vmax, logits_s[e]);
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xFFFFFFFFu, vmax, m));
+    for (int e = lane; e < E; e += 32) scratch[e] = det_expf(__fsub_rn(logits_s[e], vmax));
+    __syncwarp();
+    float sum = 0.0f;
+    for (int e = 0; e < E; ++e) sum = __fadd_rn(sum, scratch[e]);  // ascending order, every lane
+    const bool degenerate = !(sum > 0.0f);
+    for (int e = lane; e < E; e += 32) {
+        float g = degenerate ? __fdiv_rn(1.0f, (float)E) : __fdiv_rn(scratch[e], sum);
+        if (p.expert_bias) g = __fadd_rn(g, p.expert_bias[e]);
+        scratch[e] = g;
+    }
+    __syncwarp();
+    warp_topk(scratch, E, K, lane, my_idx, my_val);
+    float w = my_val;
+    if (p.norm_topk_prob) {
+        float s2 = 0.0f;
+        for (int j = 0; j < K; ++j) s2 = __fadd_rn(s2, __shfl_sync(0xFFFFFFFFu, my_val, j));
+        if (s2 > 0.0f) w = __fdiv_rn(my_val, s2);
+    }
+    if (lane < K) { idx_out[lane] = (uint32_t)my_idx; w_out[lane] = w; }
+}
+
+// One block per token.  Threads walk (expert, chunk) pairs; chunk sums land in
+// shared memory; one thread per expert adds them in ascending chunk order; warp 0
+// routes.  Dynamic shared memory: E*nchunks + 2*E floats.
+template <int KIND, int BITS>
+__global__ void __launch_bounds__(512)
+router_token_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
+                    uint32_t* __restrict__ indices, float* __restrict__ weights,
+                    float* __restrict__ logits_out) {
+    extern __shared__ float smem[];
+    const int H = p.hidden, E = p.n_experts;
+    const int nchunks = (H + 63) / 64;
+    float* partial = smem;                 // [E][nchunks]
+    float* logits_s = smem + E * nchunks;  // [E]
+    float* scratch = logits_s + E;         // [E]
+    const int t = blockIdx.x;
+    if (t >= n_tokens) return;
+    const uint16_t* xrow = x + (size_t)t * H;
+    const int total = E * nchunks;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int e = i / nchunks, c = i - e * nchunks;
+        const int k0 = c * 64, k1 = min(k0 + 64, H);
+        partial[i] = router_chunk_dot<KIND, BITS>(p, xrow, e, k0, k1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        float total_e = 0.0f;
+        for (int c = 0; c < nchunks; ++c) total_e = __fadd_rn(total_e, partial[e * nchunks + c]);
+        if (p.logits_bf16) total_e = bf16_round(total_e);
+        if (p.bias) {
+            total_e = __fadd_rn(total_e, bf16_bits_to_f32(p.bias[e]));
+            if (p.logits_bf16) total_e = bf16_round(total_e);
+        }
+        logits_s[e] = total_e;
+        if (logits_out) logits_out[(size_t)t * E + e] = total_e;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32)
+        route_token_warp(p, logits_s, scratch, threadIdx.x, indices + (size_t)t * p.top_k,
+                         weights + (size_t)t * p.top_k);
+}
+
+// Routing only (logits already computed): one warp per token.
+__global__ void route_only_kernel(RouterParams p, const float* __restrict__ logits, int n_tokens,
+                                  uint32_t* __restrict__ indices, float* __restrict__ weights) {
+    extern __shared__ float smem[];
+    const int E = p.n_experts;
+    const int warps = blockDim.x / 32;
+    const int warp = threadIdx.x / 32, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * warps + warp;
+    float* logits_s = smem + (size_t)warp * 2 * E;
+    float* scratch = logits_s + E;
+    if (t >= n_tokens) return;
+    for (int e = lane; e < E; e += 32) logits_s[e] = logits[(size_t)t * E + e];
+    __syncwarp();
+    route_token_warp(p, logits_s, scratch, lane, indices + (size_t)t * p.top_k,
+                     weights + (size_t)t * p.top_k);
+}
+
+}  // namespace ffai

@@ -1,0 +1,303 @@
+/*
+ * ffai_cuda.h — C ABI of libffai_cuda: the sparse mixture-of-experts feed-forward
+ * block of FFAI (router → dispatch → grouped expert products → combine) over MLX
+ * affine-quantized weights, implemented as hand-written CUDA for sm_100a.
+ *
+ * The reference (thewafflehaus/FFAI) has no FFI boundary for this path: the block
+ * is called in-process through Swift methods.  Every entry point below therefore
+ * cites the Swift method (path within the FFAI project, file:line) whose work it
+ * replaces.  All signatures are plain C: pointers, sizes, an opaque handle, and a
+ * `void*` that carries a `cudaStream_t`.
+ *
+ * Conventions
+ *   - Activations are bf16 (uint16_t bit patterns), row-major, contiguous.
+ *   - Packed weights are uint32 words in the MLX affine layout: a row of `in`
+ *     values at `bits` bits is `in*bits/32` little-endian words holding one
+ *     contiguous LSB-first bit stream (value i occupies stream bits
+ *     [i*bits, (i+1)*bits)); `w = scale*q + bias` with one bf16 scale and one
+ *     bf16 bias per `group_size` input values.
+ *     (FFAI: Sources/FFAI/Layers.swift:133-189, Ops/QuantizedOpsValidation.swift:52-57,
+ *      bit layout pinned by Tests/FFAITests/Ops/QuantizedOpsTests.swift:33-124.)
+ *   - Every function returns an `ffai_status`; nothing traps.  The reference
+ *     traps via `precondition` (e.g. Sources/FFAI/Ops/Ops.swift:4588-4615); each
+ *     such precondition maps to FFAI_ERR_INVALID_ARG here.
+ *   - One handle may be used by one stream at a time (the reference's threading
+ *     contract, Sources/FFAI/Models/MoELayer.swift:311-318).
+ *   - There is no CPU fallback: without a CUDA device every compute entry point
+ *     returns FFAI_ERR_CUDA.
+ */
+#ifndef FFAI_CUDA_H
+#define FFAI_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FFAI_API __attribute__((visibility("default")))
+#else
+#define FFAI_API
+#endif
+
+#define FFAI_CUDA_ABI_VERSION 1
+#define FFAI_MAX_TOP_K 32
+#define FFAI_MAX_EXPERTS 1024
+
+typedef enum ffai_status {
+    FFAI_OK = 0,
+    FFAI_ERR_INVALID_ARG = 1, /* a reference `precondition` would have failed   */
+    FFAI_ERR_UNSUPPORTED = 2, /* valid request, not implemented for this shape   */
+    FFAI_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed               */
+    FFAI_ERR_NOT_READY = 4,   /* forward before set_weights                      */
+    FFAI_ERR_NCCL = 5,        /* expert-parallel exchange failed                 */
+    FFAI_ERR_DEVICE_CHECK = 6 /* a bounded device-side wait or check gave up     */
+} ffai_status;
+
+/* MoEGatingMode — Sources/FFAI/Models/MoELayer.swift:71-78 */
+typedef enum ffai_gating_mode {
+    FFAI_GATING_SOFTMAX_THEN_TOPK = 0,
+    FFAI_GATING_TOPK_THEN_SOFTMAX = 1
+} ffai_gating_mode;
+
+/* Expert activation.
+ *   SWIGLU          silu(gate)*up                 Sources/FFAI/Ops/Ops.swift:6400-6452
+ *   CLAMPED_SWIGLU  g=min(gate,L); u=clamp(up,-L,L);
+ *                   (u+1) * g / (1+exp(-alpha*g))  Sources/FFAI/Models/Text/GPTOSSText.swift:1414-1431
+ *   GELU_GLU        gelu_tanh(gate)*up             Sources/FFAI/Ops/OpsFused.swift:55-87
+ */
+typedef enum ffai_activation {
+    FFAI_ACT_SWIGLU = 0,
+    FFAI_ACT_CLAMPED_SWIGLU = 1,
+    FFAI_ACT_GELU_GLU = 2
+} ffai_activation;
+
+/* Storage type of a dense-or-quantized projection (router, shared-expert gate). */
+typedef enum ffai_linear_kind {
+    FFAI_LINEAR_NONE = 0,
+    FFAI_LINEAR_F32 = 1,   /* Linear, fp32 weight  — Sources/FFAI/Layers.swift:24-130 */
+    FFAI_LINEAR_BF16 = 2,  /* Linear, bf16 weight                                      */
+    FFAI_LINEAR_AFFINE = 3 /* QuantizedLinear      — Sources/FFAI/Layers.swift:133-289 */
+} ffai_linear_kind;
+
+typedef enum ffai_mem_location {
+    FFAI_MEM_HOST = 0,  /* library allocates device memory and copies          */
+    FFAI_MEM_DEVICE = 1 /* library borrows the device pointers (no copy); the   */
+                        /* caller keeps them alive until destroy/set_weights   */
+} ffai_mem_location;
+
+/*
+ * Layer description.  One struct covers MoELayer (MoELayer.swift:319-498),
+ * GPTOSSMoELayer (GPTOSSText.swift:1302-1337) and Qwen35MoEFFN
+ * (Qwen3xText.swift:870-926).  Zero-initialise, set `struct_size`, fill in.
+ */
+typedef struct ffai_moe_config {
+    uint32_t struct_size;      /* = sizeof(ffai_moe_config) */
+    int32_t hidden;            /* H, multiple of 64                                   */
+    int32_t intermediate;      /* I, multiple of 64                                   */
+    int32_t n_experts;         /* E (global count, also under expert parallelism)     */
+    int32_t top_k;             /* 1..min(E, FFAI_MAX_TOP_K)                           */
+    int32_t gating_mode;       /* ffai_gating_mode                                    */
+    int32_t norm_topk_prob;    /* MoERouter.normTopKProb, MoELayer.swift:92-95        */
+    int32_t router_expert_bias;/* 1: post-softmax additive bias (LFM2), :97-103       */
+    int32_t activation;        /* ffai_activation                                     */
+    float swiglu_limit;        /* L  (GPT-OSS swiglu_limit, GPTOSSText.swift:120)      */
+    float swiglu_alpha;        /* alpha (1.702, GPTOSSText.swift:959)                  */
+    int32_t router_kind;       /* ffai_linear_kind                                    */
+    int32_t router_bits;       /* AFFINE only: 2,3,4,5,6,8                            */
+    int32_t router_group_size; /* AFFINE only: 32,64,128                              */
+    int32_t router_has_bias;   /* GPTOSSBiasedLinear, GPTOSSText.swift:341-362        */
+    int32_t router_logits_bf16;/* 1: logits are rounded to bf16 before top-k, as the  */
+                               /* reference's bf16 logits tensor is (MoELayer.swift:540,572) */
+    int32_t expert_bits;       /* 3,4,5,6,8 (2 accepted)                              */
+    int32_t expert_group_size; /* 32,64,128                                           */
+    int32_t expert_row_bias;   /* 1: per-row projection bias b_g,b_u,b_d (GPT-OSS)    */
+    int32_t shared_intermediate;/* 0: no shared expert                                */
+    int32_t shared_bits;
+    int32_t shared_group_size;
+    int32_t shared_gate_kind;  /* ffai_linear_kind; NONE: shared output added         */
+                               /* unconditionally (MoELayer.swift:621-624); otherwise  */
+                               /* scaled by sigmoid(gate·x) (Qwen3xText.swift:1013-1035) */
+    int32_t shared_gate_bits;
+    int32_t shared_gate_group_size;
+    int32_t max_tokens;        /* largest T a forward call may pass                   */
+    int32_t ep_rank;           /* expert parallelism: this rank, 0 when ep_world<=1   */
+    int32_t ep_world;          /* 0 or 1: single GPU                                  */
+    int32_t reserved[8];
+} ffai_moe_config;
+
+/* One stacked quantized projection: weight [n, out, in*bits/32] u32,
+ * scales/biases [n, out, in/group] bf16, optional row bias [n, out] bf16.
+ * (StackedInt4Experts, MoELayer.swift:347-391; n = 1 for the shared expert.) */
+typedef struct ffai_qproj {
+    const uint32_t* weight;
+    const uint16_t* scales;
+    const uint16_t* biases;
+    const uint16_t* row_bias; /* nullable */
+} ffai_qproj;
+
+/* A dense or quantized [out, in] projection (router; shared-expert gate). */
+typedef struct ffai_linear {
+    const void* weight;       /* f32 / bf16 [out,in], or u32 [out, in*bits/32]  */
+    const uint16_t* scales;   /* AFFINE only */
+    const uint16_t* biases;   /* AFFINE only */
+    const uint16_t* bias;     /* nullable projection bias [out], bf16           */
+} ffai_linear;
+
+typedef struct ffai_moe_weights {
+    uint32_t struct_size;     /* = sizeof(ffai_moe_weights) */
+    int32_t location;         /* ffai_mem_location, applies to every pointer    */
+    ffai_linear router;       /* [E, H]                                         */
+    const float* router_expert_bias; /* [E] fp32, nullable                      */
+    ffai_qproj gate_proj;     /* [E_local, I, H]                                 */
+    ffai_qproj up_proj;       /* [E_local, I, H]                                 */
+    ffai_qproj down_proj;     /* [E_local, H, I]                                 */
+    ffai_qproj shared_gate_proj; /* [1, I_s, H]                                  */
+    ffai_qproj shared_up_proj;   /* [1, I_s, H]                                  */
+    ffai_qproj shared_down_proj; /* [1, H, I_s]                                  */
+    ffai_linear shared_gate;  /* [1, H]                                         */
+} ffai_moe_weights;
+
+/* Optional per-call routing/dispatch outputs (device pointers for
+ * ffai_moe_forward, host pointers for ffai_moe_forward_host; any may be NULL). */
+typedef struct ffai_moe_debug {
+    uint32_t* indices;  /* [T, k]   selected experts, value-desc / index-asc     */
+    float* weights;     /* [T, k]   combine weights                              */
+    float* logits;      /* [T, E]   router logits as seen by top-k               */
+    uint32_t* counts;   /* [E]      rows per expert                              */
+    uint32_t* offsets;  /* [E+1]    exclusive scan of counts                     */
+    uint32_t* perm;     /* [T*k]    sorted position -> token*k+slot              */
+    uint32_t* inv_perm; /* [T*k]    token*k+slot -> sorted position              */
+} ffai_moe_debug;
+
+typedef struct ffai_moe_layer ffai_moe_layer; /* opaque */
+
+/* Library / device probes. */
+FFAI_API int ffai_cuda_abi_version(void);
+/* Number of visible CUDA devices; 0 without a GPU (never an error). */
+FFAI_API int ffai_cuda_device_count(void);
+FFAI_API const char* ffai_status_string(int status);
+
+/*
+ * Lifecycle.
+ * create   replaces MoELayer.init / MoERouter.init (MoELayer.swift:105-124, 440-498),
+ *          GPTOSSMoELayer.init (GPTOSSText.swift:1311-1325), Qwen35MoEFFN.init.
+ *          Allocates all workspace for `max_tokens` on the current CUDA device.
+ * set_weights  replaces the borrowed-tensor hand-off of Qwen35Hybrid.buildMoE /
+ *          tryLoadStackedInt4 (Qwen3xText.swift:598-739).
+ * destroy  frees everything the library allocated.
+ */
+FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_layer** out_layer);
+FFAI_API int ffai_moe_set_weights(ffai_moe_layer* layer, const ffai_moe_weights* weights);
+FFAI_API int ffai_moe_destroy(ffai_moe_layer* layer);
+FFAI_API const char* ffai_moe_last_error(const ffai_moe_layer* layer);
+
+/*
+ * forward — replaces MoELayer.decode (MoELayer.swift:530-634, T = 1),
+ * MoELayer.decodeMany (:677-969), GPTOSSMoELayer.decode (GPTOSSText.swift:1340-1392)
+ * and Qwen35MoEFFN.forward / forwardMany (Qwen3xText.swift:928-1103).
+ *   x, out, residual: device bf16 [T, H]; residual nullable; out complete when
+ *   `stream` reaches the end of the call.  No allocation, no host sync.
+ */
+FFAI_API int ffai_moe_forward(ffai_moe_layer* layer, const uint16_t* x, int32_t n_tokens,
+                     uint16_t* out, const uint16_t* residual,
+                     const ffai_moe_debug* debug, void* cuda_stream);
+
+/* Same call with HOST buffers: copies x (and residual) to the device, runs
+ * forward, copies out (and debug outputs) back, and waits.  This is what a
+ * caller holding host tensors uses, as the reference's callers do with
+ * shared-storage MTLBuffers (Sources/FFAI/Device.swift:23-64). */
+FFAI_API int ffai_moe_forward_host(ffai_moe_layer* layer, const uint16_t* x, int32_t n_tokens,
+                          uint16_t* out, const uint16_t* residual,
+                          const ffai_moe_debug* debug);
+
+/* Expert parallelism: attach an initialised ncclComm_t (one rank per GPU) before
+ * the first forward when config.ep_world > 1.  No reference counterpart (the
+ * reference is single-device). */
+FFAI_API int ffai_moe_set_nccl_comm(ffai_moe_layer* layer, void* nccl_comm);
+
+/* Device time of the stages of the most recent forward on this handle, in
+ * milliseconds (CUDA events recorded on the call's stream when timing is on).
+ * Names mirror the reference's stages: router, plan, gather, gate_up, down,
+ * combine, shared, exchange.  Replaces the signpost phases of
+ * Sources/FFAI/Telemetry/Profiling.swift:76-117. */
+#define FFAI_N_STAGES 8
+FFAI_API int ffai_moe_set_stage_timing(ffai_moe_layer* layer, int enabled);
+FFAI_API int ffai_moe_get_stage_ms(ffai_moe_layer* layer, float out_ms[FFAI_N_STAGES]);
+/* Number of kernels the most recent forward launched. */
+FFAI_API int ffai_moe_last_launch_count(const ffai_moe_layer* layer);
+
+/* ───────────────────────── operator-level entry points ─────────────────────────
+ * Thin wrappers over the same kernels the layer uses, shaped like the
+ * reference's `Ops.*` so its unit tests can be restated one-for-one.  All
+ * pointers are DEVICE pointers; `stream` is a cudaStream_t.                     */
+
+/* Ops.dequantGemv — Sources/FFAI/Ops/Ops.swift:1489-1693.
+ * out[o] = sum_i (scales[o,i/gs]*q[o,i] + biases[o,i/gs]) * x[i]; x, out bf16. */
+FFAI_API int ffai_op_dequant_gemv(const uint16_t* x, const uint32_t* weight,
+                         const uint16_t* scales, const uint16_t* biases,
+                         uint16_t* out, int32_t out_dim, int32_t in_dim,
+                         int32_t bits, int32_t group_size, void* stream);
+
+/* Ops.dequantGemvInt4ExpertIndexed — Ops.swift:2444-2519: the expert slab is
+ * chosen on the device from expert_index[0] in a stacked [E,out,in*bits/32]. */
+FFAI_API int ffai_op_dequant_gemv_expert_indexed(const uint16_t* x, const uint32_t* weight,
+                                        const uint16_t* scales, const uint16_t* biases,
+                                        const uint32_t* expert_index, uint16_t* out,
+                                        int32_t n_experts, int32_t out_dim, int32_t in_dim,
+                                        int32_t bits, int32_t group_size, void* stream);
+
+/* MoERouter.route (MoELayer.swift:140-205) and Ops.moeRouterTopKMany
+ * (Ops.swift:2598-2661): logits fp32 [T,E] -> indices u32 [T,k], weights fp32 [T,k].
+ * expert_bias nullable [E]. */
+FFAI_API int ffai_op_moe_router_topk(const float* logits, uint32_t* indices, float* weights,
+                            int32_t n_tokens, int32_t n_experts, int32_t k,
+                            int32_t gating_mode, int32_t norm_topk_prob,
+                            const float* expert_bias, void* stream);
+
+/* Plan build of MoELayer.decodeMany (MoELayer.swift:752-792), made a stable
+ * counting sort by (expert, token, slot).  workspace: device, at least
+ * ffai_op_moe_plan_workspace_bytes(n_tokens*k, E) bytes. */
+FFAI_API size_t ffai_op_moe_plan_workspace_bytes(int32_t n_rows, int32_t n_experts);
+FFAI_API int ffai_op_moe_plan(const uint32_t* indices, int32_t n_tokens, int32_t k,
+                     int32_t n_experts, uint32_t* counts, uint32_t* offsets,
+                     uint32_t* perm, uint32_t* inv_perm, void* workspace, void* stream);
+
+/* Ops.gather — Ops.swift:308-346: out[m,:] = table[ids[m],:], bf16 rows. */
+FFAI_API int ffai_op_gather_rows(const uint16_t* table, const uint32_t* ids, uint16_t* out,
+                        int32_t n_rows, int32_t row_len, void* stream);
+
+/* Ops.moeGatherDequantGemmInt4 (+Bm8/Bm64Mpp/M1) — Ops.swift:4553-4708, 4912-5201,
+ * 6499-6585: out[m,n] = sum_k dequant(W[indices[m]])[n,k] * x[m,k]; rows sorted by
+ * expert; x,out bf16; any supported bit width. */
+FFAI_API int ffai_op_moe_gather_dequant_gemm(const uint16_t* x, const uint32_t* weight,
+                                    const uint16_t* scales, const uint16_t* biases,
+                                    const uint32_t* indices, uint16_t* out,
+                                    int32_t m_total, int32_t n_out, int32_t k_in,
+                                    int32_t n_experts, int32_t bits, int32_t group_size,
+                                    void* stream);
+
+/* Ops.swiglu (Ops.swift:6400-6452), GPT-OSS clamped form, Ops.fusedGateGelu. */
+FFAI_API int ffai_op_glu_activation(const uint16_t* gate, const uint16_t* up, uint16_t* out,
+                           int64_t n, int32_t activation, float limit, float alpha,
+                           void* stream);
+
+/* Ops.moeUnpermute — Ops.swift:5030-5110:
+ * out[t,:] = sum_s weights[t,s] * expert_out[inv_perm[t*k+s],:], slot order. */
+FFAI_API int ffai_op_moe_unpermute(const uint16_t* expert_out, const uint32_t* inv_perm,
+                          const float* weights, uint16_t* out, int32_t n_tokens,
+                          int32_t hidden, int32_t k, void* stream);
+
+/* Ops.sigmoidScalarFMA / sigmoidScalarFMAResidual — Ops.swift:6255-6334,
+ * OpsFused.swift:699-753, batched over rows:
+ * out[t,:] = [residual[t,:] +] base[t,:] + sigmoid(gate[t]) * value[t,:]. */
+FFAI_API int ffai_op_sigmoid_scalar_fma(const uint16_t* gate, const uint16_t* value,
+                               const uint16_t* base, const uint16_t* residual,
+                               uint16_t* out, int32_t n_rows, int32_t hidden, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FFAI_CUDA_H */
