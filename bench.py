@@ -1,0 +1,319 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE block: tokens/s of one layer forward, with the kernel roofline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Workloads (seeded synthetic weights and activations, shapes of the benchmark configurations):
+    cfg2_b64 (default), cfg2_b1, cfg2_b8, cfg2_b32   GPT-OSS-20B-shaped decode batches
+    cfg3                                            Qwen3-30B-A3B-shaped 2048-token prefill
+    cfg1                                            tiny layer
+
+A step is one forward of the layer over one batch.  Each step is timed on the device with a
+CUDA-event pair on the launching stream; between steps a 256 MiB buffer is overwritten so the
+next step finds none of its weights in L2 (the flush is not timed).  With N > 1 every rank runs
+its own replica of the layer on its own batch (decode does not shard); time is the max over ranks.
+
+One JSON line is printed by rank 0.  `value` is device-resident throughput, `e2e` the same metric
+through the host-buffer entry point of the C ABI (pinned-memory copies inside the timed region),
+`roofline` describes the dominant kernel, `cpu_baseline` is the scalar CPU oracle on this host.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import numpy as np
+
+from ffai_b200 import capi, synth
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def workload(name: str):
+    """-> (spec, tokens per step, regime)"""
+    if name.startswith("cfg2"):
+        b = int(name.split("_b")[1]) if "_b" in name else 64
+        return synth.cfg2_gptoss(), b, "decode"
+    if name == "cfg3":
+        return synth.cfg3_qwen(), 2048, "prefill"
+    if name == "cfg1":
+        return synth.cfg1_tiny(), 16, "decode"
+    raise SystemExit(f"unknown workload {name}")
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline(spec, n_tokens: int, seed: int, min_seconds: float, impl_line: bool = False):
+    """The scalar CPU oracle on this host's cores, on a bounded sample of the workload."""
+    import oracle
+    oracle.build()
+    host = synth.make_layer(spec, seed)
+    sample_tokens = min(n_tokens, 64)
+    x = synth.make_tokens(sample_tokens, spec.hidden, seed)
+    threads = oracle.lib().orc_num_threads()
+    oracle.moe_forward(host, x[:1])  # touch the weights once
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        oracle.moe_forward(host, x)
+        reps += 1
+        if time.perf_counter() - t0 >= min_seconds or reps >= 50:
+            break
+    dt = time.perf_counter() - t0
+    return {"value": sample_tokens * reps / dt, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{reps} forward(s) of {sample_tokens} tokens of {spec.name} ({dt:.1f} s), "
+                      f"expert-parallel over {threads} host threads"}, dt / reps
+
+
+def run_reference(args, spec, n_tokens, rank, world):
+    """--impl reference: the reference's CPU arithmetic (the oracle port; the Swift/Metal
+    reference cannot be built on this box) on the host cores, same config and metric."""
+    if rank != 0:
+        return
+    per_step_s = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base, sec = cpu_baseline(spec, n_tokens, args.seed, min_seconds=0.0)
+        if i >= args.warmup:
+            per_step_s.append(sec)
+        if sum(per_step_s) > 120:
+            break
+    sample_tokens = min(n_tokens, 64)
+    ms = 1e3 * statistics.mean(per_step_s)
+    value = sample_tokens / (ms / 1e3)
+    base["value"] = value
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "impl": "reference", "n_gpus": world,
+            "steps": len(per_step_s), "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
+            "config": {"workload": args.workload, "layer": spec.name, "tokens_per_step": sample_tokens},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="cfg2_b64")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    spec, n_tokens, regime = workload(args.workload)
+
+    if args.impl == "reference":
+        run_reference(args, spec, n_tokens, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from ffai_b200.moe import MoELayer
+
+    lib = capi.load()
+    if lib.ffai_cuda_device_count() <= 0:
+        raise SystemExit("bench.py needs a CUDA device: libffai_cuda has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    host = synth.make_layer(spec, args.seed)
+    layer = MoELayer(host, n_tokens)
+    layer.set_stage_timing(True)
+    H = spec.hidden
+    n_batches = 8
+    xs_host = [synth.make_tokens(n_tokens, H, args.seed + 100 * rank + i) for i in range(n_batches)]
+    xs_dev = [torch.from_numpy(x.view(np.int16)).cuda() for x in xs_host]
+    out_dev = torch.zeros(n_tokens * H, dtype=torch.int16, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream()
+
+    # distinct experts selected per batch (for the algorithmic decode bytes)
+    distinct = []
+    for x in xs_host:
+        _, dbg = layer.forward_host(x, debug=True)
+        distinct.append(int((dbg.counts > 0).sum()))
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def step(i, timed):
+        flush.zero_()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        layer.forward_ptr(xs_dev[i % n_batches].data_ptr(), n_tokens, out_dev.data_ptr(), stream=stream.cuda_stream)
+        ev1.record(stream)
+        if timed:
+            ev1.synchronize()
+            return ev0.elapsed_time(ev1), layer.stage_ms(), layer.launch_count()
+        return None
+
+    for i in range(args.warmup):
+        step(i, False)
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    times, stages, launches = [], [], 0
+    for i in range(args.steps):
+        ms, st, nl = step(i, True)
+        times.append(ms); stages.append(st); launches += nl
+    sync_all()
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end to end through the host-buffer entry point (copies inside the timed region)
+    e2e_times = []
+    for i in range(3 + args.steps):
+        flush.zero_()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        layer.forward_host(xs_host[i % n_batches])
+        dt = time.perf_counter() - t0
+        if i >= 3:
+            e2e_times.append(dt * 1e3)
+            launches += layer.launch_count()
+
+    ms_step = statistics.mean(times)
+    e2e_ms = statistics.mean(e2e_times)
+    if world > 1:
+        t = torch.tensor([ms_step, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, e2e_ms = float(t[0]), float(t[1])
+        lt = torch.tensor([launches], device="cuda", dtype=torch.int64)
+        dist.all_reduce(lt)
+        launches = int(lt[0])
+
+    if rank == 0:
+        peaks = measured_peaks()
+        used = [distinct[i % n_batches] for i in range(args.steps)]
+        mean_distinct = statistics.mean(used)
+        stage_mean = {k: statistics.mean(s[k] for s in stages) for k in stages[0]}
+        bpw = spec.bytes_per_weight()
+        if regime == "decode":
+            # dominant kernel: the fused gate/up product (2 of the 3 projections' bytes)
+            kernel, kms = "gate_up", stage_mean["gate_up"]
+            alg_bytes = mean_distinct * 2.0 * spec.hidden * spec.intermediate * bpw + n_tokens * H * 2.0
+            achieved = alg_bytes / (kms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peaks["hbm_gbs"],
+                        "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                        "traffic": None, "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kms}
+            layer_bytes = spec.decode_bytes(n_tokens, mean_distinct)
+            layer_frac = layer_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"]
+        else:
+            fl = spec.prefill_flops(n_tokens)
+            kernel, kms = "gate_up", stage_mean["gate_up"]
+            alg = fl["routed"] * 2.0 / 3.0
+            achieved = alg / (kms * 1e-3) / 1e12
+            roofline = {"bound": "tensor", "kernel": kernel, "achieved": achieved, "peak": peaks["bf16_tflops"],
+                        "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "peak_source": peaks["source"],
+                        "traffic": None, "algorithmic_flops_per_launch": alg, "kernel_ms": kms}
+            layer_frac = (fl["routed"] + fl["shared"] + fl["router"]) / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"]
+        line = {
+            "metric": METRIC, "value": world * n_tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u4 weights, bf16 activations, f32 accumulate",
+            "data": "synthetic (seeded Philox; shapes and value distributions of the benchmark configuration)",
+            "config": {"workload": args.workload, "layer": spec.name, "tokens_per_step": n_tokens, "regime": regime,
+                       "hidden": spec.hidden, "intermediate": spec.intermediate, "experts": spec.n_experts,
+                       "top_k": spec.top_k, "bits": spec.expert_bits, "group_size": spec.expert_group_size,
+                       "distinct_experts_per_step": mean_distinct, "input_batches_rotated": n_batches,
+                       "l2": "256 MiB buffer overwritten between steps (not timed)",
+                       "parallelism": "replicas" if world > 1 else "single"},
+            "e2e": {"value": world * n_tokens / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": n_tokens * H * 2, "d2h_bytes_per_step": n_tokens * H * 2},
+            "gpu_launches": launches,
+            "roofline": roofline,
+            "layer_roofline_frac": layer_frac,
+            "stage_ms": stage_mean,
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"], _ = cpu_baseline(spec, n_tokens, args.seed, args.cpu_seconds)
+        print(json.dumps(line), flush=True)
+    layer.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

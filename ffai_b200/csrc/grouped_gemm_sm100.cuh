@@ -1,0 +1,507 @@
+// Grouped 4-bit dequant GEMM for sm_100a: TMA -> shared memory -> in-SMEM dequant ->
+// tcgen05.mma with TMEM accumulators -> fused activation epilogue.
+//
+// Replaces the reference's grouped int4 matmuls over expert-sorted rows
+// (Ops.moeGatherDequantGemmInt4 and its Bm8 / Bm64Mpp tiles, FFAI Ops.swift:4553-4708,
+// 4912-5201) together with Ops.swiglu between them (Ops.swift:6400-6452):
+//     out[row, n] = sum_k (scale[e,n,k/gs] * q[e,n,k] + bias[e,n,k/gs]) * x[row, k],   e = expert of row.
+//
+// Orientation: the packed weights are the M side of the MMA (128 weight rows per tile, one
+// TMEM lane each), the tokens routed to the expert are the N side (16..128 columns), so an
+// expert with few rows costs a narrow instruction instead of a padded 128-row tile and each
+// weight tile is unpacked once per token tile.
+//
+// Warp roles in a 448-thread CTA (persistent; tiles are (expert, token tile, 128-row tile)):
+//   warp 0      TMA producer: packed weight tile(s) [128 rows x 32 B] and the activation tile
+//               [NTOK rows x 128 B, 128-byte swizzle] per 64-wide k block, ring "R"
+//   warp 1      MMA issuer (one thread): 4 x tcgen05.mma (K=16) per k block and accumulator;
+//               owns TMEM allocation
+//   warps 2-9   dequant: 256 threads, thread = (weight row, half of the k block); unpack 4-bit
+//               to bf16 (w = fma(q, scale, bias) rounded once), store into the 128-byte-swizzled
+//               K-major operand tile, ring "A"
+//   warps 10-13 epilogue: tcgen05.ld the accumulators, bias + activation, store
+// Every mbarrier wait is bounded (about one second); on expiry the kernel raises an error
+// word, stops issuing work, waits (bounded) for its own copies in flight, frees TMEM and returns.
+//
+// K order: a 4-bit word holds 8 consecutive k.  The unpack yields the pairs (0,4),(1,5),(2,6),(3,7),
+// so operand tiles keep every 8-run in the order 0,4,1,5,2,6,3,7.  The activation side is written
+// in the same order by its producer (the row gather, or the previous GEMM's epilogue), which makes
+// the permutation invisible to the dot product.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace ffai {
+namespace g100 {
+
+constexpr int BM = 128;        // weight rows per tile (TMEM lanes)
+constexpr int BK = 64;         // k per pipeline stage (one 128-byte swizzle row of bf16)
+constexpr int NA = 3;          // stages of the dequantised-operand ring
+constexpr int THREADS = 448;   // 14 warps
+constexpr int N_DEQ_WARPS = 8;
+constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;
+
+enum : uint32_t { ERR_NONE = 0, ERR_WAIT_TIMEOUT = 1 };
+
+struct Params {
+    const uint16_t* scales;    // [E, n_out, K/gs]
+    const uint16_t* biases;
+    const uint16_t* row_bias;  // nullable [E, n_out]
+    const uint16_t* scales2;   // second projection (fused gate/up)
+    const uint16_t* biases2;
+    const uint16_t* row_bias2;
+    int n_out;                 // output rows per expert
+    int K;
+    int group_size;
+    int n_experts;
+    const uint32_t* offsets;       // [E+1] row ranges per expert in the sorted row space
+    const uint32_t* tile_offsets;  // [E+1] prefix sum of token tiles per expert
+    int m_tiles;                   // ceil(n_out / 128)
+    int activation;
+    float limit, alpha;
+    void* out;                 // [rows, out_ld]
+    int out_ld;
+    int out_permute8;          // 1: store column n at (n & ~7) | {0,2,4,6,1,3,5,7}[n & 7]
+    uint32_t* error_word;
+};
+
+// ───────────────────────── PTX wrappers ─────────────────────────
+
+FFAI_DEVINL uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+FFAI_DEVINL uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+FFAI_DEVINL void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+FFAI_DEVINL void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+FFAI_DEVINL void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+FFAI_DEVINL bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait.  Returns false when the limit expires or another thread of the CTA gave up.
+FFAI_DEVINL bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    for (int i = 0; i < 32; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+FFAI_DEVINL void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+FFAI_DEVINL void prefetch_tmap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+FFAI_DEVINL void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+FFAI_DEVINL void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+FFAI_DEVINL void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+FFAI_DEVINL void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+FFAI_DEVINL void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+FFAI_DEVINL void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+FFAI_DEVINL void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]^T, bf16 inputs, fp32 accumulate.
+FFAI_DEVINL void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// mbarrier arrives once all tcgen05 operations issued so far by this thread have completed.
+FFAI_DEVINL void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+FFAI_DEVINL void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+FFAI_DEVINL void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes (64 bf16),
+// 8-row groups 1024 bytes apart.  Descriptor fields (sm_100 shared-memory matrix descriptor):
+// start>>4 [0,14), leading byte offset>>4 [16,30) (unused for swizzled K-major), stride byte
+// offset>>4 [32,46) = 1024>>4, version 1 at [46,48), swizzle mode 2 (128 B) at [61,64).
+FFAI_DEVINL uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// kind::f16 instruction descriptor: D fp32 (bit 4), A bf16 (bit 7), B bf16 (bit 10), both
+// K-major (bits 15, 16 clear), N>>3 at [17,23), M>>4 at [24,29).
+FFAI_DEVINL uint32_t make_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// One packed word (8 x 4-bit) -> 8 bf16 weights in the order 0,4,1,5,2,6,3,7 as 4 packed pairs.
+// (q | 0x4300) is the bf16 value 128+q exactly; subtracting 128 is exact; the fused
+// multiply-add rounds scale*q+bias to bf16 once.
+FFAI_DEVINL uint4 dequant_word_bf16(uint32_t w, __nv_bfloat162 s2, __nv_bfloat162 b2) {
+    const __nv_bfloat162 k128 = __floats2bfloat162_rn(128.0f, 128.0f);
+    uint32_t t[4];
+    t[0] = (w & 0x000F000Fu) | 0x43004300u;
+    t[1] = ((w >> 4) & 0x000F000Fu) | 0x43004300u;
+    t[2] = ((w >> 8) & 0x000F000Fu) | 0x43004300u;
+    t[3] = ((w >> 12) & 0x000F000Fu) | 0x43004300u;
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 q = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&t[i]), k128);
+        __nv_bfloat162 v = __hfma2(q, s2, b2);
+        o[i] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+FFAI_DEVINL int permute8_store_col(int n) {
+    // k 0..7 live at positions 0,2,4,6,1,3,5,7 of their 8-run
+    const int k = n & 7;
+    return (n & ~7) | (((k & 3) << 1) | (k >> 2));
+}
+
+// Tile index -> (expert, token-tile, row-tile).  Consecutive tiles share the token tile so the
+// activation tile stays hot in L2 across the CTAs that work on one expert.
+struct TileCoord {
+    int expert, row_begin, n_cols_valid, m_tile;
+};
+FFAI_DEVINL TileCoord decode_tile(const Params& p, int tile, int ntok) {
+    const int g = tile / p.m_tiles;
+    int lo = 0, hi = p.n_experts;  // find e with tile_offsets[e] <= g < tile_offsets[e+1]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if ((int)p.tile_offsets[mid] <= g) lo = mid; else hi = mid;
+    }
+    TileCoord c;
+    c.expert = lo;
+    const int nt = g - (int)p.tile_offsets[lo];
+    c.row_begin = (int)p.offsets[lo] + nt * ntok;
+    c.n_cols_valid = min(ntok, (int)p.offsets[lo + 1] - c.row_begin);
+    c.m_tile = tile - g * p.m_tiles;
+    return c;
+}
+
+template <bool FUSED, int NTOK>
+struct SmemLayout {
+    static constexpr int NPROJ = FUSED ? 2 : 1;
+    static constexpr int A_TILE = BM * BK * 2;            // 16 KB bf16 operand tile
+    static constexpr int A_STAGE = NPROJ * A_TILE;
+    static constexpr int RAW_TILE = BM * (BK / 2);        // 4 KB packed
+    static constexpr int X_TILE = NTOK * BK * 2;          // NTOK rows x 128 B
+    static constexpr int R_STAGE = ((NPROJ * RAW_TILE + X_TILE + 1023) / 1024) * 1024;
+    // ring R depth: as deep as fits next to ring A in ~200 KB (more bytes in flight for the
+    // HBM-bound narrow-tile case)
+    static constexpr int NR = ((200 * 1024 - NA * A_STAGE) / R_STAGE) > 8 ? 8 : ((200 * 1024 - NA * A_STAGE) / R_STAGE);
+    static constexpr int OFF_A = 0;
+    static constexpr int OFF_R = NA * A_STAGE;            // X tile first (1024-aligned), raw after
+    static constexpr int OFF_BAR = OFF_R + NR * R_STAGE;
+    static constexpr int N_BARS = 2 * NR + 2 * NA + 4;
+    static constexpr int TOTAL = OFF_BAR + N_BARS * 8 + 16 + 1024;  // + alignment slack
+    static constexpr int TMEM_COLS_RAW = 2 * NPROJ * NTOK;
+    static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;
+    static_assert(NR >= 2, "ring R too shallow");
+    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns must be a power of two <= 512");
+};
+
+// FUSED:  out[row, n] = act(Wg[e][n]·x[row] + bg, Wu[e][n]·x[row] + bu), bf16, optionally 8-run permuted
+// !FUSED: out[row, n] = W[e][n]·x[row] + b, TOut
+template <bool FUSED, int NTOK, typename TOut>
+__global__ void __launch_bounds__(THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
+                    const __grid_constant__ CUtensorMap tm_x, const Params p) {
+    using L = SmemLayout<FUSED, NTOK>;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment for the swizzled operand tiles
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = sbase + L::OFF_BAR;
+    auto r_full = [&](int s) { return bar0 + 8u * s; };
+    auto r_empty = [&](int s) { return bar0 + 8u * (L::NR + s); };
+    auto a_full = [&](int s) { return bar0 + 8u * (2 * L::NR + s); };
+    auto a_empty = [&](int s) { return bar0 + 8u * (2 * L::NR + NA + s); };
+    auto acc_full = [&](int b) { return bar0 + 8u * (2 * L::NR + 2 * NA + b); };
+    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * L::NR + 2 * NA + 2 + b); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + L::N_BARS * 8);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KB = p.K / BK;
+    const int total_tiles = (int)p.tile_offsets[p.n_experts] * p.m_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < L::NR; ++s) { mbar_init(r_full(s), 1); mbar_init(r_empty(s), N_DEQ_WARPS + 1); }
+        for (int s = 0; s < NA; ++s) { mbar_init(a_full(s), N_DEQ_WARPS); mbar_init(a_empty(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tm_w);
+        if (FUSED) prefetch_tmap(&tm_w2);
+        prefetch_tmap(&tm_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), L::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ───────────── TMA producer ─────────────
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const TileCoord c = decode_tile(p, tile, NTOK);
+                const int wrow = c.expert * p.n_out + c.m_tile * BM;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % L::NR;
+                    const uint32_t ph = (it / L::NR) & 1;
+                    if (!mbar_wait(r_empty(s), ph ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t stage = sbase + L::OFF_R + s * L::R_STAGE;
+                    mbar_arrive_expect_tx(r_full(s), L::NPROJ * L::RAW_TILE + L::X_TILE);
+                    tma_load_2d(stage, &tm_x, kb * BK, c.row_begin, r_full(s));
+                    tma_load_2d(stage + L::X_TILE, &tm_w, kb * (BK / 8), wrow, r_full(s));
+                    if (FUSED) tma_load_2d(stage + L::X_TILE + L::RAW_TILE, &tm_w2, kb * (BK / 8), wrow, r_full(s));
+                }
+            }
+            if (!ok) {
+                // copies already issued still land in this CTA's shared memory: wait for them (bounded)
+                for (int s = 0; s < L::NR; ++s) {
+                    const uint64_t t0 = global_timer_ns();
+                    while (!mbar_try_wait(r_full(s), 0) && !mbar_try_wait(r_full(s), 1) &&
+                           global_timer_ns() - t0 < 2000000ull) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ───────────── MMA issuer ─────────────
+        if (lane == 0) {
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+                const TileCoord c = decode_tile(p, tile, NTOK);
+                const int ncols = (c.n_cols_valid + 15) & ~15;
+                const uint32_t idesc = make_idesc_bf16(BM, ncols);
+                const int buf = tcount & 1;
+                const uint32_t acc_ph = (tcount >> 1) & 1;
+                if (!mbar_wait(acc_empty(buf), acc_ph ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d0 = tmem_base + (uint32_t)(buf * L::NPROJ * NTOK);
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int sr = it % L::NR, sa = it % NA;
+                    const uint32_t phr = (it / L::NR) & 1, pha = (it / NA) & 1;
+                    if (!mbar_wait(r_full(sr), phr, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(a_full(sa), pha, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t xa = sbase + L::OFF_R + sr * L::R_STAGE;
+                    const uint32_t aa = sbase + L::OFF_A + sa * L::A_STAGE;
+#pragma unroll
+                    for (int k16 = 0; k16 < BK / 16; ++k16) {
+                        const uint64_t bd = make_kmajor_sw128_desc(xa + k16 * 32);
+                        const uint64_t ad = make_kmajor_sw128_desc(aa + k16 * 32);
+                        const uint32_t acc = (kb | k16) != 0 ? 1u : 0u;
+                        umma_bf16(d0, ad, bd, idesc, acc);
+                        if (FUSED) {
+                            const uint64_t ad2 = make_kmajor_sw128_desc(aa + L::A_TILE + k16 * 32);
+                            umma_bf16(d0 + NTOK, ad2, bd, idesc, acc);
+                        }
+                    }
+                    umma_commit(a_empty(sa));
+                    umma_commit(r_empty(sr));
+                }
+                if (ok) umma_commit(acc_full(buf));
+            }
+        }
+    } else if (warp < 2 + N_DEQ_WARPS) {
+        // ───────────── dequant ─────────────
+        const int d = warp - 2;
+        const int half = d >> 2;                 // which 32-k half of the 64-k block
+        const int r = ((d & 3) << 5) | lane;     // weight row within the tile
+        const int gpr = p.K / p.group_size;
+        const long total_rows = (long)p.n_experts * p.n_out;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const TileCoord c = decode_tile(p, tile, NTOK);
+            long grow = (long)c.expert * p.n_out + c.m_tile * BM + r;
+            if (grow >= total_rows) grow = total_rows - 1;  // rows past the tensor: zero-filled by TMA, masked at store
+            const uint16_t* sp = p.scales + grow * gpr;
+            const uint16_t* bp = p.biases + grow * gpr;
+            const uint16_t* sp2 = FUSED ? p.scales2 + grow * gpr : nullptr;
+            const uint16_t* bp2 = FUSED ? p.biases2 + grow * gpr : nullptr;
+            auto group_of = [&](int kb) { return (kb * BK + half * 32) / p.group_size; };
+            uint16_t s_n = sp[group_of(0)], b_n = bp[group_of(0)], s2_n = 0, b2_n = 0;
+            if (FUSED) { s2_n = sp2[group_of(0)]; b2_n = bp2[group_of(0)]; }
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+                const uint16_t s_c = s_n, b_c = b_n, s2_c = s2_n, b2_c = b2_n;
+                if (kb + 1 < KB) {  // prefetch the next block's scale and bias
+                    const int g = group_of(kb + 1);
+                    s_n = sp[g]; b_n = bp[g];
+                    if (FUSED) { s2_n = sp2[g]; b2_n = bp2[g]; }
+                }
+                const int sr = it % L::NR, sa = it % NA;
+                const uint32_t phr = (it / L::NR) & 1, pha = (it / NA) & 1;
+                if (!mbar_wait(r_full(sr), phr, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(a_empty(sa), pha ^ 1, abort_flag)) { ok = false; break; }
+                const uint8_t* raw = smem + L::OFF_R + sr * L::R_STAGE + L::X_TILE;
+                uint8_t* at = smem + L::OFF_A + sa * L::A_STAGE;
+#pragma unroll
+                for (int pj = 0; pj < L::NPROJ; ++pj) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(raw + pj * L::RAW_TILE + r * 32 + half * 16);
+                    const uint16_t sb = pj ? s2_c : s_c, bb = pj ? b2_c : b_c;
+                    __nv_bfloat162 s2, b2;
+                    *reinterpret_cast<uint32_t*>(&s2) = (uint32_t)sb | ((uint32_t)sb << 16);
+                    *reinterpret_cast<uint32_t*>(&b2) = (uint32_t)bb | ((uint32_t)bb << 16);
+                    const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+                    uint8_t* row = at + pj * L::A_TILE + r * 128;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int chunk = (half * 4 + j) ^ (r & 7);
+                        *reinterpret_cast<uint4*>(row + chunk * 16) = dequant_word_bf16(words[j], s2, b2);
+                    }
+                }
+                fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(a_full(sa));
+                    mbar_arrive(r_empty(sr));
+                }
+            }
+        }
+    } else {
+        // ───────────── epilogue ─────────────
+        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+            const TileCoord c = decode_tile(p, tile, NTOK);
+            const int buf = tcount & 1;
+            const uint32_t acc_ph = (tcount >> 1) & 1;
+            if (!mbar_wait(acc_full(buf), acc_ph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int n = c.m_tile * BM + q * 32 + lane;  // output row (weight row) of this thread
+            const bool n_ok = n < p.n_out;
+            float rb1 = 0.0f, rb2 = 0.0f;
+            if (n_ok && p.row_bias) rb1 = bf16_bits_to_f32(p.row_bias[(size_t)c.expert * p.n_out + n]);
+            if (FUSED && n_ok && p.row_bias2) rb2 = bf16_bits_to_f32(p.row_bias2[(size_t)c.expert * p.n_out + n]);
+            const int ncol = p.out_permute8 ? permute8_store_col(n) : n;
+            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * L::NPROJ * NTOK);
+            for (int c0 = 0; c0 < c.n_cols_valid; c0 += 16) {
+                uint32_t a[16], b[16];
+                tmem_ld16(t0 + c0, a);
+                if (FUSED) tmem_ld16(t0 + NTOK + c0, b);
+                tmem_ld_wait();
+                if (n_ok) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j < c.n_cols_valid) {
+                            float v = __uint_as_float(a[j]) + rb1;
+                            if (FUSED) v = glu_activation(v, __uint_as_float(b[j]) + rb2, p.activation, p.limit, p.alpha);
+                            TOut* o = reinterpret_cast<TOut*>(p.out) + (size_t)(c.row_begin + c0 + j) * p.out_ld + ncol;
+                            if (sizeof(TOut) == 2) *reinterpret_cast<uint16_t*>(o) = f32_to_bf16_bits(v);
+                            else *reinterpret_cast<float*>(o) = v;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(buf));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && p.error_word) atomicExch(p.error_word, (uint32_t)ERR_WAIT_TIMEOUT);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, L::TMEM_COLS);
+    }
+}
+
+// Token tiles per expert and their prefix sum (one block).
+__global__ void tile_schedule_kernel(const uint32_t* __restrict__ offsets, int n_experts, int ntok,
+                                     uint32_t* __restrict__ tile_offsets) {
+    if (threadIdx.x == 0) {
+        uint32_t run = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            tile_offsets[e] = run;
+            const uint32_t cnt = offsets[e + 1] - offsets[e];
+            run += (cnt + ntok - 1) / ntok;
+        }
+        tile_offsets[n_experts] = run;
+    }
+}
+
+// Row gather into the expert-contiguous buffer with every 8-run stored in the order
+// 0,4,1,5,2,6,3,7 (the order the 4-bit unpack produces).  One warp per row.
+__global__ void gather_rows_perm8_kernel(const uint16_t* __restrict__ table, const uint32_t* __restrict__ ids,
+                                         int id_div, uint16_t* __restrict__ out, int n_rows, int row_len) {
+    const int warps = blockDim.x / 32;
+    const int row = blockIdx.x * warps + threadIdx.x / 32;
+    if (row >= n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const uint32_t src = ids ? ids[row] / (uint32_t)id_div : (uint32_t)row;
+    const uint4* s = (const uint4*)(table + (size_t)src * row_len);
+    uint4* d = (uint4*)(out + (size_t)row * row_len);
+    for (int i = lane; i < row_len / 8; i += 32) {
+        const uint4 v = s[i];
+        uint4 o;
+        o.x = __byte_perm(v.x, v.z, 0x5410);
+        o.y = __byte_perm(v.x, v.z, 0x7632);
+        o.z = __byte_perm(v.y, v.w, 0x5410);
+        o.w = __byte_perm(v.y, v.w, 0x7632);
+        d[i] = o;
+    }
+}
+
+}  // namespace g100
+}  // namespace ffai

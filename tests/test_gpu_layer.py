@@ -1,0 +1,192 @@
+"""Whole-block parity on the GPU, through the C ABI, against the CPU oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import refcases as rc
+from ffai_b200 import capi, synth
+from ffai_b200.moe import MoELayer
+from helpers import assert_parity, from_dev, parity, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def run_and_check(oracle_mod, spec, T, seed=0, residual=False, max_tokens=None, layer=None, host=None,
+                  token_mask=None, rel_rms_tol=5e-3, max_abs_norm_tol=2e-2):
+    host = host or synth.make_layer(spec, seed)
+    x = synth.make_tokens(T, spec.hidden, seed)
+    res = synth.make_tokens(T, spec.hidden, seed + 17) if residual else None
+    own = layer is None
+    layer = layer or MoELayer(host, max_tokens or T)
+    try:
+        out, dbg = layer.forward_host(x, residual=res, debug=True)
+    finally:
+        if own:
+            layer.close()
+    ref = oracle_mod.moe_forward(host, x, residual=res, token_mask=token_mask)
+    # routing: bit-exact
+    assert np.array_equal(dbg.logits, ref.logits), "router logits differ"
+    assert np.array_equal(dbg.indices, ref.indices), "expert indices differ"
+    assert np.array_equal(dbg.weights, ref.weights), "combine weights differ"
+    assert np.array_equal(dbg.counts, ref.counts)
+    assert np.array_equal(dbg.offsets, ref.offsets)
+    assert np.array_equal(dbg.perm, ref.perm)
+    assert np.array_equal(dbg.inv_perm, ref.inv_perm)
+    if token_mask is not None:
+        sel = np.nonzero(token_mask)[0]
+        return assert_parity(out[sel], ref.out_f32[sel], rel_rms_tol, max_abs_norm_tol, what=spec.name)
+    return assert_parity(out, ref.out_f32, rel_rms_tol, max_abs_norm_tol, what=spec.name)
+
+
+def test_cfg1_tiny_layer(oracle_mod):
+    run_and_check(oracle_mod, synth.cfg1_tiny(), 16)
+
+
+@pytest.mark.parametrize("T", [1, 8, 32, 64])
+def test_cfg2_gptoss_decode_batches(oracle_mod, T):
+    run_and_check(oracle_mod, synth.cfg2_gptoss(), T)
+
+
+def test_cfg2_with_expert_row_biases_and_residual(oracle_mod):
+    run_and_check(oracle_mod, synth.cfg2_gptoss().with_(expert_row_bias=1), 5, residual=True)
+
+
+def test_cfg3_qwen_small_prefill(oracle_mod):
+    run_and_check(oracle_mod, synth.cfg3_qwen(), 96)
+
+
+def test_cfg3_single_token(oracle_mod):
+    run_and_check(oracle_mod, synth.cfg3_qwen(), 1)
+
+
+def test_cfg4_shared_expert_small(oracle_mod):
+    run_and_check(oracle_mod, synth.cfg4_shared(), 48)
+
+
+def test_shared_expert_without_gate(oracle_mod):
+    spec = synth.cfg1_tiny().with_(name="granite_style", shared_intermediate=256, shared_bits=4, shared_group_size=64)
+    run_and_check(oracle_mod, spec, 7)
+
+
+@pytest.mark.parametrize("bits", [3, 5, 6, 8])
+def test_odd_bit_widths(oracle_mod, bits):
+    spec = synth.LayerSpec(f"bits{bits}", 512, 256, 16, 4, expert_bits=bits)
+    run_and_check(oracle_mod, spec, 40)
+
+
+@pytest.mark.parametrize("gs", [32, 128])
+def test_group_sizes(oracle_mod, gs):
+    spec = synth.LayerSpec(f"gs{gs}", 512, 256, 8, 2, expert_group_size=gs)
+    run_and_check(oracle_mod, spec, 9)
+
+
+def test_softmax_without_renormalisation_and_expert_bias(oracle_mod):
+    spec = synth.LayerSpec("raw_softmax", 256, 128, 16, 4, norm_topk_prob=0)
+    run_and_check(oracle_mod, spec, 33)
+    spec = synth.LayerSpec("lfm2_bias", 256, 128, 16, 4, router_expert_bias=1)
+    run_and_check(oracle_mod, spec, 33)
+
+
+def test_gelu_glu_activation(oracle_mod):
+    spec = synth.LayerSpec("gelu", 256, 128, 8, 2, activation=capi.ACT_GELU_GLU, gating_mode=capi.GATING_TOPK_THEN_SOFTMAX)
+    run_and_check(oracle_mod, spec, 12)
+
+
+def test_skewed_routing_layer(oracle_mod):
+    spec = synth.LayerSpec("skew", 512, 256, 64, 8, router_has_bias=1, zipf_s=1.1, zipf_strength=1.5)
+    p = run_and_check(oracle_mod, spec, 200)
+    assert p["ref_rms"] > 0
+
+
+def test_ragged_token_counts_on_one_handle(oracle_mod):
+    """One handle, many batch sizes (empty, 1, odd, max): no state leaks between calls."""
+    spec = synth.LayerSpec("ragged", 256, 128, 8, 2)
+    host = synth.make_layer(spec, 3)
+    layer = MoELayer(host, 70)
+    try:
+        out, _ = layer.forward_host(np.zeros((0, spec.hidden), dtype=np.uint16))
+        assert out.shape == (0, spec.hidden)
+        for T in (70, 1, 13, 64, 2, 70):
+            run_and_check(oracle_mod, spec, T, seed=T, layer=layer, host=host)
+        with pytest.raises(capi.FFAICudaError) as ei:
+            layer.forward_host(np.zeros((71, spec.hidden), dtype=np.uint16))
+        assert ei.value.status == capi.FFAI_ERR_INVALID_ARG
+    finally:
+        layer.close()
+
+
+def test_all_tokens_to_the_same_experts(oracle_mod):
+    """Collision extreme: identical rows route every token to the same k experts."""
+    spec = synth.LayerSpec("collide", 256, 128, 8, 2)
+    host = synth.make_layer(spec, 4)
+    x = np.repeat(synth.make_tokens(1, spec.hidden, 4), 50, axis=0)
+    layer = MoELayer(host, 50)
+    try:
+        out, dbg = layer.forward_host(x, debug=True)
+    finally:
+        layer.close()
+    ref = oracle_mod.moe_forward(host, x)
+    assert np.array_equal(dbg.indices, ref.indices) and np.array_equal(dbg.perm, ref.perm)
+    assert (dbg.counts > 0).sum() == 2
+    assert_parity(out, ref.out_f32)
+    assert np.all(out == out[0])      # identical rows give identical outputs: the reduction order is fixed
+
+
+@pytest.mark.parametrize("with_shared", [False, True])
+def test_reference_four_expert_layer(oracle_mod, with_shared):
+    """MoELayerTests.swift:150-265 through the C ABI."""
+    arrays, x, expected = rc.four_expert_layer(with_shared)
+    spec = synth.LayerSpec("four_expert", 64, 64, 4, 2, router_kind=capi.LINEAR_F32, router_logits_bf16=0,
+                           shared_intermediate=64 if with_shared else 0, shared_bits=4, shared_group_size=64)
+    host = synth.HostLayer(spec, arrays)
+    layer = MoELayer(host, 1)
+    try:
+        out, dbg = layer.forward_host(synth.f32_to_bf16(x)[None, :], debug=True)
+    finally:
+        layer.close()
+    assert dbg.indices[0].tolist() == [1, 2]
+    assert np.allclose(dbg.weights[0], [0.73107, 0.26893], atol=1e-4)
+    got = float(synth.bf16_to_f32(out)[0, 0])
+    assert abs(got - expected) <= abs(expected) * 2.0 ** -8 + 1e-3
+
+
+def test_device_pointer_forward_matches_host_forward(oracle_mod):
+    import torch
+    spec = synth.cfg1_tiny()
+    host = synth.make_layer(spec, 0)
+    x = synth.make_tokens(16, spec.hidden, 0)
+    layer = MoELayer(host, 16)
+    try:
+        out_h, _ = layer.forward_host(x)
+        dx = to_dev(x)
+        dout = torch.zeros(16 * spec.hidden, dtype=torch.int16, device="cuda")
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            layer.forward_ptr(dx.data_ptr(), 16, dout.data_ptr(), stream=st.cuda_stream)
+        st.synchronize()
+        assert layer.launch_count() > 0
+        assert np.array_equal(from_dev(dout, np.uint16).reshape(16, -1), out_h)
+    finally:
+        layer.close()
+
+
+def test_forward_is_deterministic(oracle_mod):
+    spec = synth.cfg2_gptoss()
+    host = synth.make_layer(spec, 0)
+    x = synth.make_tokens(32, spec.hidden, 0)
+    layer = MoELayer(host, 32)
+    try:
+        a, _ = layer.forward_host(x)
+        b, _ = layer.forward_host(x)
+    finally:
+        layer.close()
+    assert np.array_equal(a, b)
+
+
+def test_cfg3_full_prefill_sampled_tokens(oracle_mod):
+    """Full 2048-token prefill: routing checked for every token, outputs for a token sample."""
+    spec = synth.cfg3_qwen()
+    mask = np.zeros(2048, dtype=np.uint8)
+    mask[np.random.default_rng(0).choice(2048, size=64, replace=False)] = 1
+    run_and_check(oracle_mod, spec, 2048, token_mask=mask)
