@@ -146,6 +146,8 @@ SIGNATURES = {
     "ffai_moe_forward": (C.c_int, [_P, _P, _I, _P, _P, C.POINTER(MoEDebug), _P]),
     "ffai_moe_forward_host": (C.c_int, [_P, _P, _I, _P, _P, C.POINTER(MoEDebug)]),
     "ffai_moe_set_nccl_comm": (C.c_int, [_P, _P]),
+    "ffai_moe_set_option": (C.c_int, [_P, C.c_char_p, _I]),
+    "ffai_moe_check_device_status": (C.c_int, [_P]),
     "ffai_moe_set_stage_timing": (C.c_int, [_P, C.c_int]),
     "ffai_moe_get_stage_ms": (C.c_int, [_P, C.POINTER(C.c_float * N_STAGES)]),
     "ffai_moe_last_launch_count": (C.c_int, [_P]),

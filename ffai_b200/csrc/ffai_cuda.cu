@@ -15,6 +15,7 @@
 #include "expert_gemv.cuh"
 #include "plan.cuh"
 #include "router.cuh"
+#include "tc_path.cuh"
 
 using namespace ffai;
 
@@ -44,6 +45,22 @@ struct ffai_moe_layer {
     float* sh_inner = nullptr;      // [T,Is]
     float* sh_y = nullptr;          // [T,H]
     float* sh_gate = nullptr;       // [T]
+
+    // tensor-core path (tcgen05 grouped GEMM): bf16 staging buffers, schedules, tensor maps
+    bool tc_ok = false;              // tensor maps encoded, buffers allocated
+    int n_sms = 0;
+    int opt_path = 0;                // 0 auto, 1 force CUDA-core GEMV, 2 force tensor-core
+    int opt_tc_min_rows = 0;         // auto: smallest T*k routed through the tensor-core path
+    uint16_t* xg = nullptr;          // [M,H]  expert-contiguous input rows (8-run permuted)
+    uint16_t* inner_bf = nullptr;    // [M,I]  activation output (8-run permuted)
+    uint16_t* y_bf = nullptr;        // [M,H]
+    uint32_t* tile_offsets = nullptr;    // [E+1]
+    uint16_t* sh_x = nullptr;        // [T,H]  shared expert input (8-run permuted)
+    uint16_t* sh_inner_bf = nullptr; // [T,Is]
+    uint32_t* sh_sched = nullptr;    // offsets[2] + tile_offsets[2]
+    uint32_t* error_word = nullptr;
+    CUtensorMap tm_gate{}, tm_up{}, tm_down{}, tm_sh_gate{}, tm_sh_up{}, tm_sh_down{};
+    CUtensorMap tm_xg[2]{}, tm_inner[2]{}, tm_sh_x[2]{}, tm_sh_inner[2]{};  // [0]: 16-row box, [1]: 128-row box
 
     // host-buffer entry point
     cudaStream_t own_stream = nullptr;
@@ -219,6 +236,24 @@ int launch_router_kind(const RouterParams& p, const uint16_t* x, int T, uint32_t
     return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
 }
 
+// Many tokens: tiled projection, then one warp per token routes.  Returns launches or -1.
+int launch_router_batched(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w,
+                          float* logits, cudaStream_t st) {
+    dim3 grid((T + 63) / 64, (p.n_experts + 63) / 64);
+    switch (p.kind) {
+        case FFAI_LINEAR_F32: router_logits_tiled_kernel<1, 4><<<grid, 256, 0, st>>>(p, x, T, logits); break;
+        case FFAI_LINEAR_BF16: router_logits_tiled_kernel<2, 4><<<grid, 256, 0, st>>>(p, x, T, logits); break;
+        case FFAI_LINEAR_AFFINE:
+            BITS_SWITCH(p.bits, (router_logits_tiled_kernel<3, B><<<grid, 256, 0, st>>>(p, x, T, logits)));
+            break;
+        default: return -1;
+    }
+    const int warps = 4;
+    route_only_kernel<<<(T + warps - 1) / warps, warps * 32, (size_t)warps * 2 * p.n_experts * sizeof(float), st>>>(
+        p, logits, T, idx, w);
+    return cudaGetLastError() == cudaSuccess ? 2 : -1;
+}
+
 int launch_router(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w,
                   float* logits, cudaStream_t st) {
     switch (p.kind) {
@@ -377,6 +412,23 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
         if ((rc = ws_alloc(L, &L->sh_y, T * H))) return rc;
         if ((rc = ws_alloc(L, &L->sh_gate, T))) return rc;
     }
+    if ((rc = ws_alloc(L, &L->error_word, 1))) return rc;
+    CUDA_TRY(L, cudaMemset(L->error_word, 0, 4));
+    CUDA_TRY(L, cudaDeviceGetAttribute(&L->n_sms, cudaDevAttrMultiProcessorCount, L->device));
+    int cc_major = 0;
+    CUDA_TRY(L, cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, L->device));
+    if (cc_major == 10 && (c.expert_bits == 4 || (c.shared_intermediate > 0 && c.shared_bits == 4))) {
+        const size_t Mp = M < 128 ? 128 : M, Tp = T < 128 ? 128 : T;  // at least one full TMA box of rows
+        if ((rc = ws_alloc(L, &L->xg, Mp * H))) return rc;
+        if ((rc = ws_alloc(L, &L->inner_bf, Mp * I))) return rc;
+        if ((rc = ws_alloc(L, &L->y_bf, M * H))) return rc;
+        if ((rc = ws_alloc(L, &L->tile_offsets, E + 1))) return rc;
+        if (c.shared_intermediate > 0 && c.shared_bits == 4) {
+            if ((rc = ws_alloc(L, &L->sh_x, Tp * H))) return rc;
+            if ((rc = ws_alloc(L, &L->sh_inner_bf, Tp * c.shared_intermediate))) return rc;
+            if ((rc = ws_alloc(L, &L->sh_sched, 4))) return rc;
+        }
+    }
     return FFAI_OK;
 }
 
@@ -419,6 +471,37 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
         if (c.shared_gate_kind != FFAI_LINEAR_NONE)
             if ((rc = upload_linear(L, w->shared_gate, c.shared_gate_kind, 1, c.hidden, c.shared_gate_bits, c.shared_gate_group_size, loc, &L->w.shared_gate, "shared_gate"))) return rc;
     }
+    // tensor maps for the tcgen05 path
+    L->tc_ok = false;
+    if (L->xg) {
+        using namespace g100;
+        const uint32_t boxes[2] = {16, 128};
+        uint64_t Mcap = (uint64_t)c.max_tokens * c.top_k, Tcap = (uint64_t)c.max_tokens;
+        if (Mcap < 128) Mcap = 128;
+        if (Tcap < 128) Tcap = 128;
+        bool ok = true;
+        if (c.expert_bits == 4) {
+            ok = ok && make_weight_map(&L->tm_gate, L->w.gate_proj.weight, (uint64_t)El * c.intermediate, c.hidden / 8);
+            ok = ok && make_weight_map(&L->tm_up, L->w.up_proj.weight, (uint64_t)El * c.intermediate, c.hidden / 8);
+            ok = ok && make_weight_map(&L->tm_down, L->w.down_proj.weight, (uint64_t)El * c.hidden, c.intermediate / 8);
+            for (int i = 0; i < 2; ++i) {
+                ok = ok && make_act_map(&L->tm_xg[i], L->xg, Mcap, c.hidden, boxes[i]);
+                ok = ok && make_act_map(&L->tm_inner[i], L->inner_bf, Mcap, c.intermediate, boxes[i]);
+            }
+        }
+        if (L->sh_x) {
+            const int Is = c.shared_intermediate;
+            ok = ok && make_weight_map(&L->tm_sh_gate, L->w.shared_gate_proj.weight, Is, c.hidden / 8);
+            ok = ok && make_weight_map(&L->tm_sh_up, L->w.shared_up_proj.weight, Is, c.hidden / 8);
+            ok = ok && make_weight_map(&L->tm_sh_down, L->w.shared_down_proj.weight, c.hidden, Is / 8);
+            for (int i = 0; i < 2; ++i) {
+                ok = ok && make_act_map(&L->tm_sh_x[i], L->sh_x, Tcap, c.hidden, boxes[i]);
+                ok = ok && make_act_map(&L->tm_sh_inner[i], L->sh_inner_bf, Tcap, Is, boxes[i]);
+            }
+        }
+        if (!ok) return fail(L, FFAI_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+        L->tc_ok = true;
+    }
     L->weights_set = true;
     return FFAI_OK;
 }
@@ -441,6 +524,35 @@ extern "C" FFAI_API const char* ffai_moe_last_error(const ffai_moe_layer* L) { r
 extern "C" FFAI_API int ffai_moe_set_nccl_comm(ffai_moe_layer* L, void* comm) {
     if (!L) return FFAI_ERR_INVALID_ARG;
     L->nccl_comm = comm;
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name, int32_t value) {
+    if (!L || !name) return FFAI_ERR_INVALID_ARG;
+    if (!strcmp(name, "path")) {
+        if (value < 0 || value > 2) return fail(L, FFAI_ERR_INVALID_ARG, "option path must be 0, 1 or 2");
+        L->opt_path = value;
+        return FFAI_OK;
+    }
+    if (!strcmp(name, "tc_min_rows")) {
+        if (value < 0) return fail(L, FFAI_ERR_INVALID_ARG, "option tc_min_rows must be >= 0");
+        L->opt_tc_min_rows = value;
+        return FFAI_OK;
+    }
+    return fail(L, FFAI_ERR_INVALID_ARG, "unknown option %s", name);
+}
+
+extern "C" FFAI_API int ffai_moe_check_device_status(ffai_moe_layer* L) {
+    if (!L) return FFAI_ERR_INVALID_ARG;
+    if (!L->error_word) return FFAI_OK;
+    CUDA_TRY(L, cudaSetDevice(L->device));
+    CUDA_TRY(L, cudaDeviceSynchronize());
+    uint32_t word = 0;
+    CUDA_TRY(L, cudaMemcpy(&word, L->error_word, 4, cudaMemcpyDeviceToHost));
+    if (word) {
+        CUDA_TRY(L, cudaMemset(L->error_word, 0, 4));
+        return fail(L, FFAI_ERR_DEVICE_CHECK, "a kernel gave up a bounded wait (code %u)", word);
+    }
     return FFAI_OK;
 }
 
@@ -529,9 +641,15 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     // stage 0: router (projection + bias + top-k + softmax)
     stage_begin(L, ST_ROUTER, st);
     RouterParams rp = router_params(L);
-    if ((rc = launch_router(rp, x, T, L->indices, L->rweights, L->logits, st)))
-        return fail(L, rc, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
-    L->launches += 1;
+    if (T >= 96) {
+        int nr = launch_router_batched(rp, x, T, L->indices, L->rweights, L->logits, st);
+        if (nr < 0) return fail(L, FFAI_ERR_CUDA, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += nr;
+    } else {
+        if ((rc = launch_router(rp, x, T, L->indices, L->rweights, L->logits, st)))
+            return fail(L, rc, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += 1;
+    }
     stage_end(L, ST_ROUTER, st);
 
     // stage 1: dispatch plan
@@ -541,49 +659,122 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     L->launches += nl;
     stage_end(L, ST_PLAN, st);
 
-    // stage 2: gather — the CUDA-core path reads rows through the permutation; nothing to launch
+    // Path choice: the tcgen05 grouped GEMM for 4-bit experts once there are enough routed rows,
+    // the CUDA-core grouped GEMV otherwise (any bit width, tiny batches).
+    const int tc_min_rows = L->opt_tc_min_rows > 0 ? L->opt_tc_min_rows : 64;
+    const bool tc_experts = L->tc_ok && c.expert_bits == 4 && L->opt_path != 1 && (L->opt_path == 2 || M >= tc_min_rows);
+    const bool tc_shared = L->tc_ok && L->sh_x && L->opt_path != 1 && (L->opt_path == 2 || T >= 16);
+    // token-tile width: narrow tiles when experts see few rows each
+    const int tix = ((double)M / E) * 1.5 <= 16.0 ? 0 : 1;
 
-    // stage 3: gate/up products + activation -> inner[M, I]
-    stage_begin(L, ST_GATE_UP, st);
-    {
-        GemvParams p = gemv_params(L->w.gate_proj, &L->w.up_proj, I, H, c.expert_group_size, E);
-        p.offsets = L->offsets;
-        p.in_row_ids = L->perm;
-        p.in_row_div = K;
-        p.n_rows = M;
+    if (tc_experts) {
+        using namespace g100;
+        const int ntok = tix ? 128 : 16;
+        stage_begin(L, ST_GATHER, st);
+        tile_schedule_kernel<<<1, 32, 0, st>>>(L->offsets, E, ntok, L->tile_offsets);
+        gather_rows_perm8_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, K, L->xg, M, H);
+        L->launches += 2;
+        stage_end(L, ST_GATHER, st);
+
+        Params p{};
+        p.n_experts = E; p.group_size = c.expert_group_size;
+        p.offsets = L->offsets; p.tile_offsets = L->tile_offsets;
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
-        if ((rc = launch_grouped_gemv<uint16_t, float, true>(p, c.expert_bits, x, L->inner, E, st)))
-            return fail(L, rc, "gate/up launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        p.error_word = L->error_word;
+
+        stage_begin(L, ST_GATE_UP, st);
+        p.scales = L->w.gate_proj.scales; p.biases = L->w.gate_proj.biases; p.row_bias = L->w.gate_proj.row_bias;
+        p.scales2 = L->w.up_proj.scales; p.biases2 = L->w.up_proj.biases; p.row_bias2 = L->w.up_proj.row_bias;
+        p.n_out = I; p.K = H; p.m_tiles = (I + BM - 1) / BM;
+        p.out = L->inner_bf; p.out_ld = I; p.out_permute8 = 1;
+        int lrc = tix ? launch_grouped_gemm<true, 128, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg[1], p, L->n_sms, st)
+                      : launch_grouped_gemm<true, 16, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg[0], p, L->n_sms, st);
+        if (lrc) return fail(L, FFAI_ERR_CUDA, "gate/up grouped GEMM launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += 1;
-    }
-    stage_end(L, ST_GATE_UP, st);
-    // stage 4: down product -> y[M, H]
-    stage_begin(L, ST_DOWN, st);
-    {
-        GemvParams p = gemv_params(L->w.down_proj, nullptr, H, I, c.expert_group_size, E);
-        p.offsets = L->offsets;
-        p.n_rows = M;
-        if ((rc = launch_grouped_gemv<float, float, false>(p, c.expert_bits, L->inner, L->y, E, st)))
-            return fail(L, rc, "down launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        stage_end(L, ST_GATE_UP, st);
+
+        stage_begin(L, ST_DOWN, st);
+        p.scales = L->w.down_proj.scales; p.biases = L->w.down_proj.biases; p.row_bias = L->w.down_proj.row_bias;
+        p.scales2 = nullptr; p.biases2 = nullptr; p.row_bias2 = nullptr;
+        p.n_out = H; p.K = I; p.m_tiles = (H + BM - 1) / BM;
+        p.out = L->y_bf; p.out_ld = H; p.out_permute8 = 0;
+        lrc = tix ? launch_grouped_gemm<false, 128, uint16_t>(L->tm_down, L->tm_down, L->tm_inner[1], p, L->n_sms, st)
+                  : launch_grouped_gemm<false, 16, uint16_t>(L->tm_down, L->tm_down, L->tm_inner[0], p, L->n_sms, st);
+        if (lrc) return fail(L, FFAI_ERR_CUDA, "down grouped GEMM launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += 1;
+        stage_end(L, ST_DOWN, st);
+    } else {
+        // gate/up products + activation -> inner[M, I]; rows are read through the permutation
+        stage_begin(L, ST_GATE_UP, st);
+        {
+            GemvParams p = gemv_params(L->w.gate_proj, &L->w.up_proj, I, H, c.expert_group_size, E);
+            p.offsets = L->offsets;
+            p.in_row_ids = L->perm;
+            p.in_row_div = K;
+            p.n_rows = M;
+            p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
+            if ((rc = launch_grouped_gemv<uint16_t, float, true>(p, c.expert_bits, x, L->inner, E, st)))
+                return fail(L, rc, "gate/up launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+            L->launches += 1;
+        }
+        stage_end(L, ST_GATE_UP, st);
+        // down product -> y[M, H]
+        stage_begin(L, ST_DOWN, st);
+        {
+            GemvParams p = gemv_params(L->w.down_proj, nullptr, H, I, c.expert_group_size, E);
+            p.offsets = L->offsets;
+            p.n_rows = M;
+            if ((rc = launch_grouped_gemv<float, float, false>(p, c.expert_bits, L->inner, L->y, E, st)))
+                return fail(L, rc, "down launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+            L->launches += 1;
+        }
+        stage_end(L, ST_DOWN, st);
     }
-    stage_end(L, ST_DOWN, st);
+
     // shared expert
     const float* sh_y = nullptr;
     const float* sh_gate = nullptr;
     stage_begin(L, ST_SHARED, st);
     if (c.shared_intermediate > 0) {
         const int Is = c.shared_intermediate;
-        GemvParams p = gemv_params(L->w.shared_gate_proj, &L->w.shared_up_proj, Is, H, c.shared_group_size, 1);
-        p.n_rows = T;
-        p.activation = FFAI_ACT_SWIGLU;
-        if ((rc = launch_grouped_gemv<uint16_t, float, true>(p, c.shared_bits, x, L->sh_inner, 1, st)))
-            return fail(L, rc, "shared gate/up launch failed");
-        GemvParams d = gemv_params(L->w.shared_down_proj, nullptr, H, Is, c.shared_group_size, 1);
-        d.n_rows = T;
-        if ((rc = launch_grouped_gemv<float, float, false>(d, c.shared_bits, L->sh_inner, L->sh_y, 1, st)))
-            return fail(L, rc, "shared down launch failed");
-        L->launches += 2;
+        if (tc_shared) {
+            using namespace g100;
+            const int six = T <= 16 ? 0 : 1;
+            const int ntok = six ? 128 : 16;
+            single_group_schedule_kernel<<<1, 32, 0, st>>>(T, ntok, L->sh_sched);
+            gather_rows_perm8_kernel<<<(T + 7) / 8, 256, 0, st>>>(x, nullptr, 1, L->sh_x, T, H);
+            Params p{};
+            p.n_experts = 1; p.group_size = c.shared_group_size;
+            p.offsets = L->sh_sched; p.tile_offsets = L->sh_sched + 2;
+            p.activation = FFAI_ACT_SWIGLU;
+            p.error_word = L->error_word;
+            p.scales = L->w.shared_gate_proj.scales; p.biases = L->w.shared_gate_proj.biases;
+            p.scales2 = L->w.shared_up_proj.scales; p.biases2 = L->w.shared_up_proj.biases;
+            p.n_out = Is; p.K = H; p.m_tiles = (Is + BM - 1) / BM;
+            p.out = L->sh_inner_bf; p.out_ld = Is; p.out_permute8 = 1;
+            int lrc = six ? launch_grouped_gemm<true, 128, uint16_t>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x[1], p, L->n_sms, st)
+                          : launch_grouped_gemm<true, 16, uint16_t>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x[0], p, L->n_sms, st);
+            if (lrc) return fail(L, FFAI_ERR_CUDA, "shared gate/up grouped GEMM launch failed");
+            p.scales = L->w.shared_down_proj.scales; p.biases = L->w.shared_down_proj.biases;
+            p.scales2 = nullptr; p.biases2 = nullptr;
+            p.n_out = H; p.K = Is; p.m_tiles = (H + BM - 1) / BM;
+            p.out = L->sh_y; p.out_ld = H; p.out_permute8 = 0;
+            lrc = six ? launch_grouped_gemm<false, 128, float>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner[1], p, L->n_sms, st)
+                      : launch_grouped_gemm<false, 16, float>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner[0], p, L->n_sms, st);
+            if (lrc) return fail(L, FFAI_ERR_CUDA, "shared down grouped GEMM launch failed");
+            L->launches += 4;
+        } else {
+            GemvParams p = gemv_params(L->w.shared_gate_proj, &L->w.shared_up_proj, Is, H, c.shared_group_size, 1);
+            p.n_rows = T;
+            p.activation = FFAI_ACT_SWIGLU;
+            if ((rc = launch_grouped_gemv<uint16_t, float, true>(p, c.shared_bits, x, L->sh_inner, 1, st)))
+                return fail(L, rc, "shared gate/up launch failed");
+            GemvParams d = gemv_params(L->w.shared_down_proj, nullptr, H, Is, c.shared_group_size, 1);
+            d.n_rows = T;
+            if ((rc = launch_grouped_gemv<float, float, false>(d, c.shared_bits, L->sh_inner, L->sh_y, 1, st)))
+                return fail(L, rc, "shared down launch failed");
+            L->launches += 2;
+        }
         sh_y = L->sh_y;
         if (c.shared_gate_kind == FFAI_LINEAR_AFFINE) {
             ffai_qproj g{(const uint32_t*)L->w.shared_gate.weight, L->w.shared_gate.scales, L->w.shared_gate.biases, nullptr};
@@ -605,7 +796,10 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     }
     stage_end(L, ST_SHARED, st);
     stage_begin(L, ST_COMBINE, st);
-    combine_kernel<float, float><<<T, 256, 0, st>>>(L->y, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
+    if (tc_experts)
+        combine_kernel<uint16_t, float><<<T, 256, 0, st>>>(L->y_bf, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
+    else
+        combine_kernel<float, float><<<T, 256, 0, st>>>(L->y, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
     L->launches += 1;
     stage_end(L, ST_COMBINE, st);
     if (cudaGetLastError() != cudaSuccess) return fail(L, FFAI_ERR_CUDA, "combine launch failed");
@@ -649,7 +843,7 @@ extern "C" FFAI_API int ffai_moe_forward_host(ffai_moe_layer* L, const uint16_t*
         void* p;
         CUDA_TRY(L, cudaMallocHost(&p, cap)); L->owned_pinned.push_back(p); L->pin_x = (uint16_t*)p;
         CUDA_TRY(L, cudaMallocHost(&p, cap)); L->owned_pinned.push_back(p); L->pin_out = (uint16_t*)p;
-        CUDA_TRY(L, cudaMallocHost(&p, cap)); L->owned_pinned.push_back(p); L->pin_res = (uint16_t*)p;
+        CUDA_TRY(L, cudaMallocHost(&p, cap + 16)); L->owned_pinned.push_back(p); L->pin_res = (uint16_t*)p;
         if ((rc = ws_alloc(L, &L->dev_x, cap / 2))) return rc;
         if ((rc = ws_alloc(L, &L->dev_out, cap / 2))) return rc;
         if ((rc = ws_alloc(L, &L->dev_res, cap / 2))) return rc;
@@ -668,7 +862,13 @@ extern "C" FFAI_API int ffai_moe_forward_host(ffai_moe_layer* L, const uint16_t*
     if ((rc = forward_device(L, L->dev_x, T, L->dev_out, dres, st))) return rc;
     CUDA_TRY(L, cudaMemcpyAsync(L->pin_out, L->dev_out, bytes, cudaMemcpyDeviceToHost, st));
     if ((rc = copy_debug(L, debug, T, st, cudaMemcpyDeviceToHost))) return rc;
+    uint32_t* pin_err = reinterpret_cast<uint32_t*>(L->pin_res + cap / 2);
+    CUDA_TRY(L, cudaMemcpyAsync(pin_err, L->error_word, 4, cudaMemcpyDeviceToHost, st));
     CUDA_TRY(L, cudaStreamSynchronize(st));
+    if (*pin_err) {
+        cudaMemsetAsync(L->error_word, 0, 4, st);
+        return fail(L, FFAI_ERR_DEVICE_CHECK, "a kernel gave up a bounded wait (code %u)", *pin_err);
+    }
     memcpy(out, L->pin_out, bytes);
     return FFAI_OK;
 }

@@ -313,10 +313,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                 }
             }
             if (!ok) {
-                // copies already issued still land in this CTA's shared memory: wait for them (bounded)
-                for (int s = 0; s < L::NR; ++s) {
+                // Copies already issued still land in this CTA's shared memory: wait (bounded, 2 ms
+                // each) for the last NR issued stages before the CTA may exit.
+                const uint32_t first = it > (uint32_t)L::NR ? it - L::NR : 0;
+                for (uint32_t j = first; j < it; ++j) {
                     const uint64_t t0 = global_timer_ns();
-                    while (!mbar_try_wait(r_full(s), 0) && !mbar_try_wait(r_full(s), 1) &&
+                    while (!mbar_try_wait(r_full(j % L::NR), (j / L::NR) & 1) &&
                            global_timer_ns() - t0 < 2000000ull) {}
                 }
             }
@@ -478,6 +480,16 @@ __global__ void tile_schedule_kernel(const uint32_t* __restrict__ offsets, int n
             run += (cnt + ntok - 1) / ntok;
         }
         tile_offsets[n_experts] = run;
+    }
+}
+
+// Schedule of a single group of n_rows rows (the shared expert): sched = {0, n_rows, 0, n_tiles}.
+__global__ void single_group_schedule_kernel(int n_rows, int ntok, uint32_t* __restrict__ sched) {
+    if (threadIdx.x == 0) {
+        sched[0] = 0;
+        sched[1] = (uint32_t)n_rows;
+        sched[2] = 0;
+        sched[3] = (uint32_t)((n_rows + ntok - 1) / ntok);
     }
 }
 

@@ -207,6 +207,133 @@ router_token_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens
                          weights + (size_t)t * p.top_k);
 }
 
+// Batched router projection for many tokens: a 64-token x 64-expert tile per block, 4x4 outputs
+// per thread, the hidden axis walked one 64-wide chunk at a time.  Inside a chunk every output
+// folds its products in ascending k with fused multiply-add from 0; the chunk sum is then added
+// to the running total — the same order as router_token_kernel, so both give identical bits.
+// Replaces the batched gate projection of MoELayer.decodeMany (FFAI MoELayer.swift:690,
+// Layers.swift:101-130, 217-287).
+template <int KIND, int BITS>
+__global__ void __launch_bounds__(256)
+router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
+                           float* __restrict__ logits_out) {
+    constexpr int TB = 64, EB = 64, LD = 68;  // LD: padded row length of the transposed tiles
+    __shared__ __align__(16) float xs[64 * LD];   // [k][token]
+    __shared__ __align__(16) float ws[64 * LD];   // [k][expert]
+    const int H = p.hidden, E = p.n_experts;
+    const int t0 = blockIdx.x * TB, e0 = blockIdx.y * EB;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float total[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) total[i][j] = 0.0f;
+
+    for (int k0 = 0; k0 < H; k0 += 64) {
+        // stage the chunk: 64x64 activations and 64x64 weights, both as fp32, transposed
+        for (int i = threadIdx.x; i < 64 * 8; i += 256) {
+            const int row = i >> 3, c8 = (i & 7) * 8;
+            const int t = t0 + row;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (t < n_tokens) v = *(const uint4*)(x + (size_t)t * H + k0 + c8);
+            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                xs[(c8 + 2 * j) * LD + row] = bf16lo(w4[j]);
+                xs[(c8 + 2 * j + 1) * LD + row] = bf16hi(w4[j]);
+            }
+        }
+        if (KIND == 1) {
+            const float* w = (const float*)p.weight;
+            for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+                const int row = i >> 4, c4 = (i & 15) * 4;
+                const int e = e0 + row;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (e < E) v = *(const float4*)(w + (size_t)e * H + k0 + c4);
+                ws[(c4 + 0) * LD + row] = v.x; ws[(c4 + 1) * LD + row] = v.y;
+                ws[(c4 + 2) * LD + row] = v.z; ws[(c4 + 3) * LD + row] = v.w;
+            }
+        } else if (KIND == 2) {
+            const uint16_t* w = (const uint16_t*)p.weight;
+            for (int i = threadIdx.x; i < 64 * 8; i += 256) {
+                const int row = i >> 3, c8 = (i & 7) * 8;
+                const int e = e0 + row;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (e < E) v = *(const uint4*)(w + (size_t)e * H + k0 + c8);
+                const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    ws[(c8 + 2 * j) * LD + row] = bf16lo(w4[j]);
+                    ws[(c8 + 2 * j + 1) * LD + row] = bf16hi(w4[j]);
+                }
+            }
+        } else {
+            // affine: one thread unpacks a 32-run of one expert row (w = fma(scale, q, bias))
+            const uint32_t* w = (const uint32_t*)p.weight;
+            const int gpr = H / p.group_size;
+            for (int i = threadIdx.x; i < 64 * 2; i += 256) {
+                const int row = i >> 1, h32 = (i & 1) * 32;
+                const int e = e0 + row;
+                if (e < E) {
+                    const int k = k0 + h32;
+                    const int g = k / p.group_size;
+                    const float sc = bf16_bits_to_f32(p.scales[(size_t)e * gpr + g]);
+                    const float bi = bf16_bits_to_f32(p.biases[(size_t)e * gpr + g]);
+                    uint32_t words[BITS + 1];
+                    const uint32_t* src = w + (size_t)e * (H * BITS / 32) + (k / 32) * BITS;
+#pragma unroll
+                    for (int j = 0; j < BITS; ++j) words[j] = src[j];
+                    words[BITS] = 0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        ws[(h32 + j) * LD + row] = __fmaf_rn(sc, small_uint_to_float(unpack_at<BITS>(words, j)), bi);
+                } else {
+                    for (int j = 0; j < 32; ++j) ws[(h32 + j) * LD + row] = 0.0f;
+                }
+            }
+        }
+        __syncthreads();
+        float part[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) part[i][j] = 0.0f;
+#pragma unroll 8
+        for (int k = 0; k < 64; ++k) {
+            const float4 xv = *(const float4*)(xs + k * LD + ty * 4);
+            const float4 wv = *(const float4*)(ws + k * LD + tx * 4);
+            const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
+            const float wa[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) part[i][j] = __fmaf_rn(xa[i], wa[j], part[i][j]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) total[i][j] = __fadd_rn(total[i][j], part[i][j]);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = t0 + ty * 4 + i;
+        if (t >= n_tokens) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = e0 + tx * 4 + j;
+            if (e >= E) continue;
+            float v = total[i][j];
+            if (p.logits_bf16) v = bf16_round(v);
+            if (p.bias) {
+                v = __fadd_rn(v, bf16_bits_to_f32(p.bias[e]));
+                if (p.logits_bf16) v = bf16_round(v);
+            }
+            logits_out[(size_t)t * E + e] = v;
+        }
+    }
+}
+
 // Routing only (logits already computed): one warp per token.
 __global__ void route_only_kernel(RouterParams p, const float* __restrict__ logits, int n_tokens,
                                   uint32_t* __restrict__ indices, float* __restrict__ weights) {

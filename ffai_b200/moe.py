@@ -87,6 +87,12 @@ class MoELayer:
                                        C.byref(debug) if debug is not None else None, stream or None)
         capi.check(rc, "ffai_moe_forward", self.handle)
 
+    def set_option(self, name: str, value: int) -> None:
+        capi.check(self.lib.ffai_moe_set_option(self.handle, name.encode(), int(value)), "ffai_moe_set_option", self.handle)
+
+    def check_device_status(self) -> None:
+        capi.check(self.lib.ffai_moe_check_device_status(self.handle), "ffai_moe_check_device_status", self.handle)
+
     def set_stage_timing(self, enabled: bool) -> None:
         capi.check(self.lib.ffai_moe_set_stage_timing(self.handle, 1 if enabled else 0), "set_stage_timing", self.handle)
 

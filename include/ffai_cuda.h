@@ -218,6 +218,17 @@ FFAI_API int ffai_moe_forward_host(ffai_moe_layer* layer, const uint16_t* x, int
  * reference is single-device). */
 FFAI_API int ffai_moe_set_nccl_comm(ffai_moe_layer* layer, void* nccl_comm);
 
+/* Execution options, replacing the reference's FFAI_MOE_* environment switches
+ * (Sources/FFAI/Models/MoELayer.swift:486-497).  Names:
+ *   "path"         0 automatic, 1 CUDA-core grouped GEMV only, 2 tcgen05 grouped GEMM whenever possible
+ *   "tc_min_rows"  smallest T*k that takes the tcgen05 path under "path" = 0 (0: default) */
+FFAI_API int ffai_moe_set_option(ffai_moe_layer* layer, const char* name, int32_t value);
+
+/* Waits for the device and reports whether any kernel of this handle raised its error word
+ * (a bounded device-side wait that expired): FFAI_OK or FFAI_ERR_DEVICE_CHECK.  The word is
+ * cleared by the call.  ffai_moe_forward_host performs this check itself. */
+FFAI_API int ffai_moe_check_device_status(ffai_moe_layer* layer);
+
 /* Device time of the stages of the most recent forward on this handle, in
  * milliseconds (CUDA events recorded on the call's stream when timing is on).
  * Names mirror the reference's stages: router, plan, gather, gate_up, down,
