@@ -170,6 +170,7 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--option", action="append", default=[], help="name=value execution option (experiments)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -197,6 +198,9 @@ def main():
     host = synth.make_layer(spec, args.seed)
     layer = MoELayer(host, n_tokens)
     layer.set_stage_timing(True)
+    for ov in args.option:
+        name, value = ov.split("=")
+        layer.set_option(name, int(value))
     H = spec.hidden
     n_batches = 8
     xs_host = [synth.make_tokens(n_tokens, H, args.seed + 100 * rank + i) for i in range(n_batches)]

@@ -148,6 +148,7 @@ SIGNATURES = {
     "ffai_moe_set_nccl_comm": (C.c_int, [_P, _P]),
     "ffai_moe_set_option": (C.c_int, [_P, C.c_char_p, _I]),
     "ffai_moe_check_device_status": (C.c_int, [_P]),
+    "ffai_moe_read_timeline": (C.c_int, [_P, C.POINTER(C.c_int64), _I]),
     "ffai_moe_set_stage_timing": (C.c_int, [_P, C.c_int]),
     "ffai_moe_get_stage_ms": (C.c_int, [_P, C.POINTER(C.c_float * N_STAGES)]),
     "ffai_moe_last_launch_count": (C.c_int, [_P]),

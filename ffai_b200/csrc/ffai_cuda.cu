@@ -51,6 +51,8 @@ struct ffai_moe_layer {
     int n_sms = 0;
     int opt_path = 0;                // 0 auto, 1 force CUDA-core GEMV, 2 force tensor-core
     int opt_tc_min_rows = 0;         // auto: smallest T*k routed through the tensor-core path
+    int opt_debug = 0;               // timing experiments (see g100::Params::debug_flags)
+    long long* timeline = nullptr;   // device buffer for the gate/up kernel's CTA-0 timeline (option "timeline")
     uint16_t* xg = nullptr;          // [M,H]  expert-contiguous input rows (8-run permuted)
     uint16_t* inner_bf = nullptr;    // [M,I]  activation output (8-run permuted)
     uint16_t* y_bf = nullptr;        // [M,H]
@@ -417,7 +419,9 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
     CUDA_TRY(L, cudaDeviceGetAttribute(&L->n_sms, cudaDevAttrMultiProcessorCount, L->device));
     int cc_major = 0;
     CUDA_TRY(L, cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, L->device));
-    if (cc_major == 10 && (c.expert_bits == 4 || (c.shared_intermediate > 0 && c.shared_bits == 4))) {
+    // the tcgen05 path needs every reduction length to hold at least one 256-k packed TMA box
+    const bool tc_shapes = H >= 256 && I >= 256 && (c.shared_intermediate == 0 || c.shared_intermediate >= 256);
+    if (cc_major == 10 && tc_shapes && (c.expert_bits == 4 || (c.shared_intermediate > 0 && c.shared_bits == 4))) {
         const size_t Mp = M < 128 ? 128 : M, Tp = T < 128 ? 128 : T;  // at least one full TMA box of rows
         if ((rc = ws_alloc(L, &L->xg, Mp * H))) return rc;
         if ((rc = ws_alloc(L, &L->inner_bf, Mp * I))) return rc;
@@ -539,7 +543,29 @@ extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name,
         L->opt_tc_min_rows = value;
         return FFAI_OK;
     }
+    if (!strcmp(name, "debug")) {
+        L->opt_debug = value;
+        return FFAI_OK;
+    }
+    if (!strcmp(name, "timeline")) {
+        if (value && !L->timeline) {
+            int rc = ws_alloc(L, &L->timeline, (size_t)g100::TL_ROLES * g100::TL_SLOTS * g100::TL_EVENTS);
+            if (rc) return rc;
+        }
+        if (!value) L->timeline = nullptr;
+        return FFAI_OK;
+    }
     return fail(L, FFAI_ERR_INVALID_ARG, "unknown option %s", name);
+}
+
+extern "C" FFAI_API int ffai_moe_read_timeline(ffai_moe_layer* L, int64_t* out, int32_t capacity) {
+    if (!L || !out) return FFAI_ERR_INVALID_ARG;
+    const int n = g100::TL_ROLES * g100::TL_SLOTS * g100::TL_EVENTS;
+    if (!L->timeline || capacity < n) return fail(L, FFAI_ERR_INVALID_ARG, "timeline not enabled or capacity < %d", n);
+    CUDA_TRY(L, cudaSetDevice(L->device));
+    CUDA_TRY(L, cudaDeviceSynchronize());
+    CUDA_TRY(L, cudaMemcpy(out, L->timeline, sizeof(long long) * n, cudaMemcpyDeviceToHost));
+    return FFAI_OK;
 }
 
 extern "C" FFAI_API int ffai_moe_check_device_status(ffai_moe_layer* L) {
@@ -681,6 +707,9 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         p.offsets = L->offsets; p.tile_offsets = L->tile_offsets;
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
         p.error_word = L->error_word;
+        p.debug_flags = L->opt_debug;
+        p.timeline = L->timeline;
+        if (L->timeline) cudaMemsetAsync(L->timeline, 0, sizeof(long long) * g100::TL_ROLES * g100::TL_SLOTS * g100::TL_EVENTS, st);
 
         stage_begin(L, ST_GATE_UP, st);
         p.scales = L->w.gate_proj.scales; p.biases = L->w.gate_proj.biases; p.row_bias = L->w.gate_proj.row_bias;
@@ -694,6 +723,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         stage_end(L, ST_GATE_UP, st);
 
         stage_begin(L, ST_DOWN, st);
+        p.timeline = nullptr;
         p.scales = L->w.down_proj.scales; p.biases = L->w.down_proj.biases; p.row_bias = L->w.down_proj.row_bias;
         p.scales2 = nullptr; p.biases2 = nullptr; p.row_bias2 = nullptr;
         p.n_out = H; p.K = I; p.m_tiles = (H + BM - 1) / BM;

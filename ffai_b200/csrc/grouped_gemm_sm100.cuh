@@ -11,12 +11,14 @@
 // expert with few rows costs a narrow instruction instead of a padded 128-row tile and each
 // weight tile is unpacked once per token tile.
 //
-// Warp roles in a 448-thread CTA (persistent; tiles are (expert, token tile, 128-row tile)):
-//   warp 0      TMA producer: packed weight tile(s) [128 rows x 32 B] and the activation tile
-//               [NTOK rows x 128 B, 128-byte swizzle] per 64-wide k block, ring "R"
-//   warp 1      MMA issuer (one thread): 4 x tcgen05.mma (K=16) per k block and accumulator;
+// Warp roles in a 480-thread CTA (persistent; tiles are (expert, token tile, 128-row tile)):
+//   warp 0      TMA producer of packed weights: [128 rows x 128 B] (256 k) per projection,
+//               128-byte swizzle, ring "W".  (A 32-byte-wide box per 64 k costs the TMA unit one
+//               request per row and ran at ~1 us per box; 128-byte rows are its natural unit.)
+//   warp 14     TMA producer of activations: [NTOK rows x 128 B] per 64 k, 128-byte swizzle, ring "X"
+//   warp 1      MMA issuer (one thread): 4 x tcgen05.mma (K=16) per 64 k and accumulator;
 //               owns TMEM allocation
-//   warps 2-9   dequant: 256 threads, thread = (weight row, half of the k block); unpack 4-bit
+//   warps 2-9   dequant: 256 threads, thread = (weight row, half of a 64-k block); unpack 4-bit
 //               to bf16 (w = fma(q, scale, bias) rounded once), store into the 128-byte-swizzled
 //               K-major operand tile, ring "A"
 //   warps 10-13 epilogue: tcgen05.ld the accumulators, bias + activation, store
@@ -36,10 +38,12 @@ namespace ffai {
 namespace g100 {
 
 constexpr int BM = 128;        // weight rows per tile (TMEM lanes)
-constexpr int BK = 64;         // k per pipeline stage (one 128-byte swizzle row of bf16)
-constexpr int NA = 3;          // stages of the dequantised-operand ring
-constexpr int THREADS = 448;   // 14 warps
+constexpr int BK = 64;         // k per MMA stage (one 128-byte swizzle row of bf16)
+constexpr int KS = 256;        // k per packed-weight TMA box (one 128-byte row of 4-bit values)
+constexpr int SUB = KS / BK;   // MMA stages per packed-weight stage
+constexpr int THREADS = 480;   // 15 warps
 constexpr int N_DEQ_WARPS = 8;
+constexpr int X_WARP = 14;     // warp that issues the activation TMA loads
 constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;
 
 enum : uint32_t { ERR_NONE = 0, ERR_WAIT_TIMEOUT = 1 };
@@ -64,7 +68,17 @@ struct Params {
     int out_ld;
     int out_permute8;          // 1: store column n at (n & ~7) | {0,2,4,6,1,3,5,7}[n & 7]
     uint32_t* error_word;
+    int debug_flags;           // timing experiments only (results invalid): 1 no proxy fence, 2 no unpack/store, 4 no MMA
+    long long* timeline;       // nullable: CTA 0 records clock64() per role / k block / event (TL_* layout)
 };
+
+// Timeline layout: [role][k-block index < TL_SLOTS][event < TL_EVENTS].
+constexpr int TL_ROLES = 5, TL_SLOTS = 96, TL_EVENTS = 4;
+enum { TL_WPROD = 0, TL_XPROD = 1, TL_MMA = 2, TL_DEQ = 3, TL_EPI = 4 };
+FFAI_DEVINL void tl_mark(const Params& p, int role, int idx, int ev) {
+    if (p.timeline && blockIdx.x == 0 && idx < TL_SLOTS)
+        p.timeline[(role * TL_SLOTS + idx) * TL_EVENTS + ev] = clock64();
+}
 
 // ───────────────────────── PTX wrappers ─────────────────────────
 
@@ -97,19 +111,34 @@ FFAI_DEVINL bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 // Bounded wait.  Returns false when the limit expires or another thread of the CTA gave up.
+// SLEEP_NS > 0: back off between polls (roles that wait long and must not steal issue slots).
+template <int SLEEP_NS>
 FFAI_DEVINL bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-    for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = 0;
+    for (uint32_t spin = 1;; ++spin) {
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    for (;;) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
-            *abort_flag = 1;
-            return false;
+        if ((spin & 63u) == 0) {  // the slow checks, once per 64 polls
+            if (*abort_flag) return false;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                return false;
+            }
         }
     }
 }
+
+// Ring position: stage index and phase bit, advanced without division.
+struct RingPos {
+    int stage;
+    uint32_t phase;
+    FFAI_DEVINL void advance(int depth) {
+        if (++stage == depth) { stage = 0; phase ^= 1u; }
+    }
+};
 
 FFAI_DEVINL void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile(
@@ -230,22 +259,25 @@ FFAI_DEVINL TileCoord decode_tile(const Params& p, int tile, int ntok) {
 template <bool FUSED, int NTOK>
 struct SmemLayout {
     static constexpr int NPROJ = FUSED ? 2 : 1;
-    static constexpr int A_TILE = BM * BK * 2;            // 16 KB bf16 operand tile
+    static constexpr int A_TILE = BM * BK * 2;             // 16 KB bf16 operand tile (128 rows x 64 k)
     static constexpr int A_STAGE = NPROJ * A_TILE;
-    static constexpr int RAW_TILE = BM * (BK / 2);        // 4 KB packed
-    static constexpr int X_TILE = NTOK * BK * 2;          // NTOK rows x 128 B
-    static constexpr int R_STAGE = ((NPROJ * RAW_TILE + X_TILE + 1023) / 1024) * 1024;
-    // ring R depth: as deep as fits next to ring A in ~200 KB (more bytes in flight for the
-    // HBM-bound narrow-tile case)
-    static constexpr int NR = ((200 * 1024 - NA * A_STAGE) / R_STAGE) > 8 ? 8 : ((200 * 1024 - NA * A_STAGE) / R_STAGE);
+    static constexpr int NA = (FUSED && NTOK > 64) ? 2 : 3;  // dequantised-operand ring
+    static constexpr int W_TILE = BM * (KS / 2);           // 16 KB packed (128 rows x 256 k x 4 bit)
+    static constexpr int W_STAGE = NPROJ * W_TILE;
+    static constexpr int X_TILE = ((NTOK * BK * 2 + 1023) / 1024) * 1024;  // NTOK rows x 128 B
+    static constexpr int NX = 4;                           // activation ring (64-k blocks)
+    static constexpr int BUDGET = 200 * 1024;
+    static constexpr int NW_FIT = (BUDGET - NA * A_STAGE - NX * X_TILE) / W_STAGE;
+    static constexpr int NW = NW_FIT > 6 ? 6 : NW_FIT;     // packed-weight ring (256-k super blocks)
     static constexpr int OFF_A = 0;
-    static constexpr int OFF_R = NA * A_STAGE;            // X tile first (1024-aligned), raw after
-    static constexpr int OFF_BAR = OFF_R + NR * R_STAGE;
-    static constexpr int N_BARS = 2 * NR + 2 * NA + 4;
+    static constexpr int OFF_W = OFF_A + NA * A_STAGE;
+    static constexpr int OFF_X = OFF_W + NW * W_STAGE;
+    static constexpr int OFF_BAR = OFF_X + NX * X_TILE;
+    static constexpr int N_BARS = 2 * NW + 2 * NX + 2 * NA + 4;
     static constexpr int TOTAL = OFF_BAR + N_BARS * 8 + 16 + 1024;  // + alignment slack
     static constexpr int TMEM_COLS_RAW = 2 * NPROJ * NTOK;
     static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;
-    static_assert(NR >= 2, "ring R too shallow");
+    static_assert(NW >= 2, "packed-weight ring too shallow");
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns must be a power of two <= 512");
 };
 
@@ -256,26 +288,31 @@ __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
                     const __grid_constant__ CUtensorMap tm_x, const Params p) {
     using L = SmemLayout<FUSED, NTOK>;
+    constexpr int NA = L::NA;
     extern __shared__ uint8_t smem_raw[];
-    // 1024-byte alignment for the swizzled operand tiles
+    // 1024-byte alignment for the swizzled tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar0 = sbase + L::OFF_BAR;
-    auto r_full = [&](int s) { return bar0 + 8u * s; };
-    auto r_empty = [&](int s) { return bar0 + 8u * (L::NR + s); };
-    auto a_full = [&](int s) { return bar0 + 8u * (2 * L::NR + s); };
-    auto a_empty = [&](int s) { return bar0 + 8u * (2 * L::NR + NA + s); };
-    auto acc_full = [&](int b) { return bar0 + 8u * (2 * L::NR + 2 * NA + b); };
-    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * L::NR + 2 * NA + 2 + b); };
+    auto w_full = [&](int s) { return bar0 + 8u * s; };
+    auto w_empty = [&](int s) { return bar0 + 8u * (L::NW + s); };
+    auto x_full = [&](int s) { return bar0 + 8u * (2 * L::NW + s); };
+    auto x_empty = [&](int s) { return bar0 + 8u * (2 * L::NW + L::NX + s); };
+    auto a_full = [&](int s) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + s); };
+    auto a_empty = [&](int s) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + NA + s); };
+    auto acc_full = [&](int b) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + 2 * NA + b); };
+    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + 2 * NA + 2 + b); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + L::N_BARS * 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int KB = p.K / BK;
+    const int KB = p.K / BK;                 // 64-k blocks
+    const int SB = (KB + SUB - 1) / SUB;     // 256-k super blocks
     const int total_tiles = (int)p.tile_offsets[p.n_experts] * p.m_tiles;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < L::NR; ++s) { mbar_init(r_full(s), 1); mbar_init(r_empty(s), N_DEQ_WARPS + 1); }
+        for (int s = 0; s < L::NW; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), N_DEQ_WARPS); }
+        for (int s = 0; s < L::NX; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 1); }
         for (int s = 0; s < NA; ++s) { mbar_init(a_full(s), N_DEQ_WARPS); mbar_init(a_empty(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
         *abort_flag = 0;
@@ -294,39 +331,67 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ───────────── TMA producer ─────────────
+        // ───────────── TMA producer, packed weights: one 128-row x 128-byte box per projection per 256 k ─────────────
         if (lane == 0) {
-            uint32_t it = 0;
+            RingPos wp{0, 0};
+            uint32_t issued = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const TileCoord c = decode_tile(p, tile, NTOK);
                 const int wrow = c.expert * p.n_out + c.m_tile * BM;
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int s = it % L::NR;
-                    const uint32_t ph = (it / L::NR) & 1;
-                    if (!mbar_wait(r_empty(s), ph ^ 1, abort_flag)) { ok = false; break; }
-                    const uint32_t stage = sbase + L::OFF_R + s * L::R_STAGE;
-                    mbar_arrive_expect_tx(r_full(s), L::NPROJ * L::RAW_TILE + L::X_TILE);
-                    tma_load_2d(stage, &tm_x, kb * BK, c.row_begin, r_full(s));
-                    tma_load_2d(stage + L::X_TILE, &tm_w, kb * (BK / 8), wrow, r_full(s));
-                    if (FUSED) tma_load_2d(stage + L::X_TILE + L::RAW_TILE, &tm_w2, kb * (BK / 8), wrow, r_full(s));
+                for (int sb = 0; sb < SB; ++sb) {
+                    tl_mark(p, TL_WPROD, (int)issued, 0);
+                    if (!mbar_wait<64>(w_empty(wp.stage), wp.phase ^ 1, abort_flag)) { ok = false; break; }
+                    tl_mark(p, TL_WPROD, (int)issued, 1);
+                    const uint32_t stage = sbase + L::OFF_W + wp.stage * L::W_STAGE;
+                    mbar_arrive_expect_tx(w_full(wp.stage), L::W_STAGE);
+                    tma_load_2d(stage, &tm_w, sb * (KS / 8), wrow, w_full(wp.stage));
+                    if (FUSED) tma_load_2d(stage + L::W_TILE, &tm_w2, sb * (KS / 8), wrow, w_full(wp.stage));
+                    wp.advance(L::NW);
+                    ++issued;
                 }
             }
             if (!ok) {
-                // Copies already issued still land in this CTA's shared memory: wait (bounded, 2 ms
-                // each) for the last NR issued stages before the CTA may exit.
-                const uint32_t first = it > (uint32_t)L::NR ? it - L::NR : 0;
-                for (uint32_t j = first; j < it; ++j) {
+                // copies already issued still land in this CTA's shared memory: wait for them (bounded, 2 ms each)
+                const uint32_t first = issued > (uint32_t)L::NW ? issued - L::NW : 0;
+                for (uint32_t j = first; j < issued; ++j) {
                     const uint64_t t0 = global_timer_ns();
-                    while (!mbar_try_wait(r_full(j % L::NR), (j / L::NR) & 1) &&
-                           global_timer_ns() - t0 < 2000000ull) {}
+                    while (!mbar_try_wait(w_full(j % L::NW), (j / L::NW) & 1) && global_timer_ns() - t0 < 2000000ull) {}
+                }
+            }
+        }
+    } else if (warp == X_WARP) {
+        // ───────────── TMA producer, activations: NTOK rows x 128 bytes per 64 k ─────────────
+        if (lane == 0) {
+            RingPos xp{0, 0};
+            uint32_t issued = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const TileCoord c = decode_tile(p, tile, NTOK);
+                for (int kb = 0; kb < KB; ++kb) {
+                    tl_mark(p, TL_XPROD, (int)issued, 0);
+                    if (!mbar_wait<32>(x_empty(xp.stage), xp.phase ^ 1, abort_flag)) { ok = false; break; }
+                    tl_mark(p, TL_XPROD, (int)issued, 1);
+                    mbar_arrive_expect_tx(x_full(xp.stage), NTOK * BK * 2);
+                    tma_load_2d(sbase + L::OFF_X + xp.stage * L::X_TILE, &tm_x, kb * BK, c.row_begin, x_full(xp.stage));
+                    xp.advance(L::NX);
+                    ++issued;
+                }
+            }
+            if (!ok) {
+                const uint32_t first = issued > (uint32_t)L::NX ? issued - L::NX : 0;
+                for (uint32_t j = first; j < issued; ++j) {
+                    const uint64_t t0 = global_timer_ns();
+                    while (!mbar_try_wait(x_full(j % L::NX), (j / L::NX) & 1) && global_timer_ns() - t0 < 2000000ull) {}
                 }
             }
         }
     } else if (warp == 1) {
         // ───────────── MMA issuer ─────────────
         if (lane == 0) {
-            uint32_t it = 0, tcount = 0;
+            RingPos xp{0, 0}, ap{0, 0};
+            uint32_t tcount = 0;
+            int gk = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
                 const TileCoord c = decode_tile(p, tile, NTOK);
@@ -334,43 +399,52 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                 const uint32_t idesc = make_idesc_bf16(BM, ncols);
                 const int buf = tcount & 1;
                 const uint32_t acc_ph = (tcount >> 1) & 1;
-                if (!mbar_wait(acc_empty(buf), acc_ph ^ 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait<32>(acc_empty(buf), acc_ph ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d0 = tmem_base + (uint32_t)(buf * L::NPROJ * NTOK);
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int sr = it % L::NR, sa = it % NA;
-                    const uint32_t phr = (it / L::NR) & 1, pha = (it / NA) & 1;
-                    if (!mbar_wait(r_full(sr), phr, abort_flag)) { ok = false; break; }
-                    if (!mbar_wait(a_full(sa), pha, abort_flag)) { ok = false; break; }
+                for (int kb = 0; kb < KB; ++kb, ++gk) {
+                    if (!mbar_wait<0>(x_full(xp.stage), xp.phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait<0>(a_full(ap.stage), ap.phase, abort_flag)) { ok = false; break; }
+                    tl_mark(p, TL_MMA, gk, 0);
                     tc_fence_after();
-                    const uint32_t xa = sbase + L::OFF_R + sr * L::R_STAGE;
-                    const uint32_t aa = sbase + L::OFF_A + sa * L::A_STAGE;
+                    const uint64_t bd0 = make_kmajor_sw128_desc(sbase + L::OFF_X + xp.stage * L::X_TILE);
+                    const uint32_t aa = sbase + L::OFF_A + ap.stage * L::A_STAGE;
+                    const uint64_t ad0 = make_kmajor_sw128_desc(aa);
+                    const uint64_t ad1 = make_kmajor_sw128_desc(aa + L::A_TILE);
 #pragma unroll
                     for (int k16 = 0; k16 < BK / 16; ++k16) {
-                        const uint64_t bd = make_kmajor_sw128_desc(xa + k16 * 32);
-                        const uint64_t ad = make_kmajor_sw128_desc(aa + k16 * 32);
+                        if (p.debug_flags & 4) break;
+                        // advancing 16 k inside the swizzled row = +32 bytes = +2 in the (addr >> 4) field
                         const uint32_t acc = (kb | k16) != 0 ? 1u : 0u;
-                        umma_bf16(d0, ad, bd, idesc, acc);
-                        if (FUSED) {
-                            const uint64_t ad2 = make_kmajor_sw128_desc(aa + L::A_TILE + k16 * 32);
-                            umma_bf16(d0 + NTOK, ad2, bd, idesc, acc);
-                        }
+                        umma_bf16(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, acc);
+                        if (FUSED) umma_bf16(d0 + NTOK, ad1 + 2 * k16, bd0 + 2 * k16, idesc, acc);
                     }
-                    umma_commit(a_empty(sa));
-                    umma_commit(r_empty(sr));
+                    tl_mark(p, TL_MMA, gk, 1);
+                    umma_commit(a_empty(ap.stage));
+                    tl_mark(p, TL_MMA, gk, 2);
+                    umma_commit(x_empty(xp.stage));
+                    tl_mark(p, TL_MMA, gk, 3);
+                    xp.advance(L::NX);
+                    ap.advance(NA);
                 }
                 if (ok) umma_commit(acc_full(buf));
             }
         }
     } else if (warp < 2 + N_DEQ_WARPS) {
         // ───────────── dequant ─────────────
-        const int d = warp - 2;
-        const int half = d >> 2;                 // which 32-k half of the 64-k block
-        const int r = ((d & 3) << 5) | lane;     // weight row within the tile
+        // 256 threads: thread = (weight row r, 32-k half of a 64-k block).  A warp covers 16 rows x 2
+        // halves, eight consecutive rows per quarter-warp, so both the 16-byte reads of the
+        // 128-byte-swizzled packed tile and the 16-byte stores into the 128-byte-swizzled operand
+        // tile touch eight distinct chunk columns: no bank conflicts either way.
+        const int dw = warp - 2;
+        const int half = (lane >> 3) & 1;
+        const int r = dw * 16 + (lane & 7) + ((lane >> 4) << 3);
         const int gpr = p.K / p.group_size;
         const long total_rows = (long)p.n_experts * p.n_out;
-        uint32_t it = 0;
+        RingPos wp{0, 0}, ap{0, 0};
         bool ok = true;
+        int gk = 0;
+        const bool tl_on = (warp == 2 && lane == 0);
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const TileCoord c = decode_tile(p, tile, NTOK);
             long grow = (long)c.expert * p.n_out + c.m_tile * BM + r;
@@ -379,43 +453,61 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             const uint16_t* bp = p.biases + grow * gpr;
             const uint16_t* sp2 = FUSED ? p.scales2 + grow * gpr : nullptr;
             const uint16_t* bp2 = FUSED ? p.biases2 + grow * gpr : nullptr;
-            auto group_of = [&](int kb) { return (kb * BK + half * 32) / p.group_size; };
-            uint16_t s_n = sp[group_of(0)], b_n = bp[group_of(0)], s2_n = 0, b2_n = 0;
-            if (FUSED) { s2_n = sp2[group_of(0)]; b2_n = bp2[group_of(0)]; }
-            for (int kb = 0; kb < KB; ++kb, ++it) {
-                const uint16_t s_c = s_n, b_c = b_n, s2_c = s2_n, b2_c = b2_n;
-                if (kb + 1 < KB) {  // prefetch the next block's scale and bias
-                    const int g = group_of(kb + 1);
-                    s_n = sp[g]; b_n = bp[g];
-                    if (FUSED) { s2_n = sp2[g]; b2_n = bp2[g]; }
-                }
-                const int sr = it % L::NR, sa = it % NA;
-                const uint32_t phr = (it / L::NR) & 1, pha = (it / NA) & 1;
-                if (!mbar_wait(r_full(sr), phr, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(a_empty(sa), pha ^ 1, abort_flag)) { ok = false; break; }
-                const uint8_t* raw = smem + L::OFF_R + sr * L::R_STAGE + L::X_TILE;
-                uint8_t* at = smem + L::OFF_A + sa * L::A_STAGE;
+            // (scale | bias << 16) per 64-k block, fetched one super block ahead so the loads are off the critical path
+            uint32_t sb_nxt[SUB], sb2_nxt[SUB];
+            auto fetch_scales = [&](int kb0) {
 #pragma unroll
-                for (int pj = 0; pj < L::NPROJ; ++pj) {
-                    const uint4 wv = *reinterpret_cast<const uint4*>(raw + pj * L::RAW_TILE + r * 32 + half * 16);
-                    const uint16_t sb = pj ? s2_c : s_c, bb = pj ? b2_c : b_c;
-                    __nv_bfloat162 s2, b2;
-                    *reinterpret_cast<uint32_t*>(&s2) = (uint32_t)sb | ((uint32_t)sb << 16);
-                    *reinterpret_cast<uint32_t*>(&b2) = (uint32_t)bb | ((uint32_t)bb << 16);
-                    const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
-                    uint8_t* row = at + pj * L::A_TILE + r * 128;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int chunk = (half * 4 + j) ^ (r & 7);
-                        *reinterpret_cast<uint4*>(row + chunk * 16) = dequant_word_bf16(words[j], s2, b2);
+                for (int j = 0; j < SUB; ++j) {
+                    const int kb = kb0 + j;
+                    if (kb < KB) {
+                        const int g = (kb * BK + half * 32) / p.group_size;
+                        sb_nxt[j] = (uint32_t)sp[g] | ((uint32_t)bp[g] << 16);
+                        if (FUSED) sb2_nxt[j] = (uint32_t)sp2[g] | ((uint32_t)bp2[g] << 16);
                     }
                 }
-                fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(a_full(sa));
-                    mbar_arrive(r_empty(sr));
+            };
+            fetch_scales(0);
+            for (int sb = 0; sb < SB && ok; ++sb) {
+                uint32_t sb_cur[SUB], sb2_cur[SUB];
+#pragma unroll
+                for (int j = 0; j < SUB; ++j) { sb_cur[j] = sb_nxt[j]; sb2_cur[j] = FUSED ? sb2_nxt[j] : 0u; }
+                fetch_scales((sb + 1) * SUB);
+                if (tl_on) tl_mark(p, TL_DEQ, gk, 0);
+                if (!mbar_wait<0>(w_full(wp.stage), wp.phase, abort_flag)) { ok = false; break; }
+                const uint8_t* wrow_s = smem + L::OFF_W + wp.stage * L::W_STAGE + r * 128;
+#pragma unroll
+                for (int j = 0; j < SUB; ++j) {
+                    if (sb * SUB + j >= KB) break;
+                    if (tl_on) tl_mark(p, TL_DEQ, gk, 1);
+                    if (!mbar_wait<0>(a_empty(ap.stage), ap.phase ^ 1, abort_flag)) { ok = false; break; }
+                    if (tl_on) tl_mark(p, TL_DEQ, gk, 2);
+                    uint8_t* row = smem + L::OFF_A + ap.stage * L::A_STAGE + r * 128;
+#pragma unroll
+                    for (int pj = 0; pj < L::NPROJ; ++pj) {
+                        if (p.debug_flags & 2) break;
+                        // logical 16-byte chunk 2j+half of the packed row, at its swizzled position
+                        const uint4 wv = *reinterpret_cast<const uint4*>(wrow_s + pj * L::W_TILE + (((2 * j + half) ^ (r & 7)) << 4));
+                        const uint32_t sbv = pj ? sb2_cur[j] : sb_cur[j];
+                        __nv_bfloat162 s2, b2;
+                        *reinterpret_cast<uint32_t*>(&s2) = __byte_perm(sbv, sbv, 0x1010);
+                        *reinterpret_cast<uint32_t*>(&b2) = __byte_perm(sbv, sbv, 0x3232);
+                        const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj) {
+                            const int chunk = (half * 4 + jj) ^ (r & 7);
+                            *reinterpret_cast<uint4*>(row + pj * L::A_TILE + chunk * 16) = dequant_word_bf16(words[jj], s2, b2);
+                        }
+                    }
+                    if (!(p.debug_flags & 1)) fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(a_full(ap.stage));
+                    if (tl_on) tl_mark(p, TL_DEQ, gk, 3);
+                    ++gk;
+                    ap.advance(NA);
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(w_empty(wp.stage));  // this warp is done reading the packed stage
+                wp.advance(L::NW);
             }
         }
     } else {
@@ -427,7 +519,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             const TileCoord c = decode_tile(p, tile, NTOK);
             const int buf = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1;
-            if (!mbar_wait(acc_full(buf), acc_ph, abort_flag)) { ok = false; break; }
+            if (warp == 10 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 0);
+            if (!mbar_wait<256>(acc_full(buf), acc_ph, abort_flag)) { ok = false; break; }
+            if (warp == 10 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 1);
             tc_fence_after();
             const int n = c.m_tile * BM + q * 32 + lane;  // output row (weight row) of this thread
             const bool n_ok = n < p.n_out;
@@ -457,6 +551,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty(buf));
+            if (warp == 10 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 2);
         }
     }
 

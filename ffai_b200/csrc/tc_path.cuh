@@ -29,16 +29,16 @@ inline EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// Packed weights [rows, words_per_row] u32; box = 8 words (64 x 4-bit) x 128 rows, no swizzle.
+// Packed weights [rows, words_per_row] u32; box = 32 words (256 x 4-bit = 128 B) x 128 rows, 128-byte swizzle.
 inline bool make_weight_map(CUtensorMap* m, const uint32_t* w, uint64_t rows, uint64_t words_per_row) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {words_per_row, rows};
     cuuint64_t strides[1] = {words_per_row * 4};
-    cuuint32_t box[2] = {(cuuint32_t)(BK / 8), (cuuint32_t)BM};
+    cuuint32_t box[2] = {(cuuint32_t)(KS / 8), (cuuint32_t)BM};
     cuuint32_t estr[2] = {1, 1};
     return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t*>(w), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

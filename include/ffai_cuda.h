@@ -224,6 +224,13 @@ FFAI_API int ffai_moe_set_nccl_comm(ffai_moe_layer* layer, void* nccl_comm);
  *   "tc_min_rows"  smallest T*k that takes the tcgen05 path under "path" = 0 (0: default) */
 FFAI_API int ffai_moe_set_option(ffai_moe_layer* layer, const char* name, int32_t value);
 
+/* Profiling aid for the tcgen05 grouped GEMM (the device-side counterpart of the reference's
+ * signpost intervals, Sources/FFAI/Telemetry/Profiling.swift:76-117).  After
+ * ffai_moe_set_option(layer, "timeline", 1), CTA 0 of the gate/up kernel records its SM clock at
+ * fixed points of each warp role for its first 96 k-blocks; this call waits for the device and
+ * copies the 5 x 96 x 4 table ([role][k block][event], 0 = not reached) into `out`. */
+FFAI_API int ffai_moe_read_timeline(ffai_moe_layer* layer, int64_t* out, int32_t capacity);
+
 /* Waits for the device and reports whether any kernel of this handle raised its error word
  * (a bounded device-side wait that expired): FFAI_OK or FFAI_ERR_DEVICE_CHECK.  The word is
  * cleared by the call.  ffai_moe_forward_host performs this check itself. */
