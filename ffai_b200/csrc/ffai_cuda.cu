@@ -13,6 +13,7 @@
 #include "combine.cuh"
 #include "common.cuh"
 #include "expert_gemv.cuh"
+#include "expert_mma_decode.cuh"
 #include "plan.cuh"
 #include "router.cuh"
 #include "tc_path.cuh"
@@ -49,13 +50,16 @@ struct ffai_moe_layer {
     // tensor-core path (tcgen05 grouped GEMM): bf16 staging buffers, schedules, tensor maps
     bool tc_ok = false;              // tensor maps encoded, buffers allocated
     int n_sms = 0;
-    int opt_path = 0;                // 0 auto, 1 force CUDA-core GEMV, 2 force tensor-core
+    int opt_path = 0;                // 0 auto, 1 CUDA-core GEMV, 2 tcgen05 grouped GEMM, 3 register-streaming decode
     int opt_tc_min_rows = 0;         // auto: smallest T*k routed through the tensor-core path
     int opt_debug = 0;               // timing experiments (see g100::Params::debug_flags)
     long long* timeline = nullptr;   // device buffer for the gate/up kernel's CTA-0 timeline (option "timeline")
     uint16_t* xg = nullptr;          // [M,H]  expert-contiguous input rows (8-run permuted)
     uint16_t* inner_bf = nullptr;    // [M,I]  activation output (8-run permuted)
     uint16_t* y_bf = nullptr;        // [M,H]
+    float* xsum = nullptr;           // [M, H/64]  64-run sums of xg rows
+    float* inner_sum = nullptr;      // [M, I/64]  64-run sums of inner rows
+    bool mma_ok = false;             // register-streaming decode kernels usable (4-bit, group 64/128)
     uint32_t* tile_offsets = nullptr;    // [E+1]
     uint16_t* sh_x = nullptr;        // [T,H]  shared expert input (8-run permuted)
     uint16_t* sh_inner_bf = nullptr; // [T,Is]
@@ -419,18 +423,26 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
     CUDA_TRY(L, cudaDeviceGetAttribute(&L->n_sms, cudaDevAttrMultiProcessorCount, L->device));
     int cc_major = 0;
     CUDA_TRY(L, cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, L->device));
-    // the tcgen05 path needs every reduction length to hold at least one 256-k packed TMA box
+    // 4-bit experts: bf16 staging buffers shared by the register-streaming decode kernels and the
+    // tcgen05 grouped GEMM.  The tcgen05 path also needs every reduction length to hold at least one
+    // 256-k packed TMA box.
     const bool tc_shapes = H >= 256 && I >= 256 && (c.shared_intermediate == 0 || c.shared_intermediate >= 256);
-    if (cc_major == 10 && tc_shapes && (c.expert_bits == 4 || (c.shared_intermediate > 0 && c.shared_bits == 4))) {
+    const bool want_tc = cc_major == 10 && tc_shapes;
+    if (c.expert_bits == 4 || (want_tc && c.shared_intermediate > 0 && c.shared_bits == 4)) {
         const size_t Mp = M < 128 ? 128 : M, Tp = T < 128 ? 128 : T;  // at least one full TMA box of rows
         if ((rc = ws_alloc(L, &L->xg, Mp * H))) return rc;
         if ((rc = ws_alloc(L, &L->inner_bf, Mp * I))) return rc;
-        if ((rc = ws_alloc(L, &L->y_bf, M * H))) return rc;
-        if ((rc = ws_alloc(L, &L->tile_offsets, E + 1))) return rc;
-        if (c.shared_intermediate > 0 && c.shared_bits == 4) {
-            if ((rc = ws_alloc(L, &L->sh_x, Tp * H))) return rc;
-            if ((rc = ws_alloc(L, &L->sh_inner_bf, Tp * c.shared_intermediate))) return rc;
-            if ((rc = ws_alloc(L, &L->sh_sched, 4))) return rc;
+        if ((rc = ws_alloc(L, &L->xsum, M * (H / 64)))) return rc;
+        if ((rc = ws_alloc(L, &L->inner_sum, M * (I / 64)))) return rc;
+        L->mma_ok = c.expert_bits == 4 && (c.expert_group_size == 64 || c.expert_group_size == 128);
+        if (want_tc) {
+            if ((rc = ws_alloc(L, &L->y_bf, M * H))) return rc;
+            if ((rc = ws_alloc(L, &L->tile_offsets, E + 1))) return rc;
+            if (c.shared_intermediate > 0 && c.shared_bits == 4) {
+                if ((rc = ws_alloc(L, &L->sh_x, Tp * H))) return rc;
+                if ((rc = ws_alloc(L, &L->sh_inner_bf, Tp * c.shared_intermediate))) return rc;
+                if ((rc = ws_alloc(L, &L->sh_sched, 4))) return rc;
+            }
         }
     }
     return FFAI_OK;
@@ -477,7 +489,7 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
     }
     // tensor maps for the tcgen05 path
     L->tc_ok = false;
-    if (L->xg) {
+    if (L->tile_offsets) {
         using namespace g100;
         const uint32_t boxes[2] = {16, 128};
         uint64_t Mcap = (uint64_t)c.max_tokens * c.top_k, Tcap = (uint64_t)c.max_tokens;
@@ -534,7 +546,7 @@ extern "C" FFAI_API int ffai_moe_set_nccl_comm(ffai_moe_layer* L, void* comm) {
 extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name, int32_t value) {
     if (!L || !name) return FFAI_ERR_INVALID_ARG;
     if (!strcmp(name, "path")) {
-        if (value < 0 || value > 2) return fail(L, FFAI_ERR_INVALID_ARG, "option path must be 0, 1 or 2");
+        if (value < 0 || value > 3) return fail(L, FFAI_ERR_INVALID_ARG, "option path must be 0..3");
         L->opt_path = value;
         return FFAI_OK;
     }
@@ -685,14 +697,63 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     L->launches += nl;
     stage_end(L, ST_PLAN, st);
 
-    // Path choice: the tcgen05 grouped GEMM for 4-bit experts once there are enough routed rows,
-    // the CUDA-core grouped GEMV otherwise (any bit width, tiny batches).
-    const int tc_min_rows = L->opt_tc_min_rows > 0 ? L->opt_tc_min_rows : 64;
-    const bool tc_experts = L->tc_ok && c.expert_bits == 4 && L->opt_path != 1 && (L->opt_path == 2 || M >= tc_min_rows);
-    const bool tc_shared = L->tc_ok && L->sh_x && L->opt_path != 1 && (L->opt_path == 2 || T >= 16);
-    // token-tile width: narrow tiles when experts see few rows each
-    const int tix = ((double)M / E) * 1.5 <= 16.0 ? 0 : 1;
+    // Path choice for the routed experts:
+    //   register-streaming mma kernels  4-bit, few rows per expert (decode): bound by HBM
+    //   tcgen05 grouped GEMM            4-bit, many rows per expert (prefill): bound by the tensor cores
+    //   CUDA-core grouped GEMV          any bit width / group size, and shapes the others do not take
+    const double rows_per_expert = (double)M / E;
+    const bool can_tc = L->tc_ok && c.expert_bits == 4;
+    bool mma_experts = false, tc_experts = false;
+    if (L->opt_path == 3) mma_experts = L->mma_ok;
+    else if (L->opt_path == 2) tc_experts = can_tc;
+    else if (L->opt_path == 0) {
+        if (L->mma_ok && (rows_per_expert <= 12.0 || !can_tc)) mma_experts = rows_per_expert <= 48.0;
+        if (!mma_experts && can_tc) tc_experts = M >= (L->opt_tc_min_rows > 0 ? L->opt_tc_min_rows : 64);
+        if (!mma_experts && !tc_experts && L->mma_ok && rows_per_expert <= 48.0) mma_experts = true;
+    }
+    const bool tc_shared = L->tc_ok && L->sh_x && L->opt_path != 1 && L->opt_path != 3 && (L->opt_path == 2 || T >= 16);
+    // token-tile width of the tcgen05 path: narrow tiles when experts see few rows each
+    const int tix = rows_per_expert * 1.5 <= 16.0 ? 0 : 1;
 
+    if (mma_experts) {
+        using namespace dmma;
+        stage_begin(L, ST_GATHER, st);
+        gather_perm8_sum64_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, K, L->xg, L->xsum, M, H);
+        L->launches += 1;
+        stage_end(L, ST_GATHER, st);
+
+        Params p{};
+        p.group_size = c.expert_group_size;
+        p.offsets = L->offsets;
+        p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
+        const bool wide = rows_per_expert > 4.0;  // 16 activation rows per pass instead of 8
+
+        stage_begin(L, ST_GATE_UP, st);
+        p.w1 = L->w.gate_proj.weight; p.s1 = L->w.gate_proj.scales; p.b1 = L->w.gate_proj.biases; p.rb1 = L->w.gate_proj.row_bias;
+        p.w2 = L->w.up_proj.weight; p.s2 = L->w.up_proj.scales; p.b2 = L->w.up_proj.biases; p.rb2 = L->w.up_proj.row_bias;
+        p.N = I; p.K = H; p.x = L->xg; p.xsum = L->xsum; p.out = L->inner_bf;
+        {
+            dim3 grid((I / 16 + 3) / 4, E);
+            if (wide) grouped_mma_decode_kernel<true, 2><<<grid, 128, 0, st>>>(p);
+            else grouped_mma_decode_kernel<true, 1><<<grid, 128, 0, st>>>(p);
+        }
+        sum64_rows_kernel<<<(M + 7) / 8, 256, 0, st>>>(L->inner_bf, L->inner_sum, M, I);
+        L->launches += 2;
+        stage_end(L, ST_GATE_UP, st);
+
+        stage_begin(L, ST_DOWN, st);
+        p.w1 = L->w.down_proj.weight; p.s1 = L->w.down_proj.scales; p.b1 = L->w.down_proj.biases; p.rb1 = L->w.down_proj.row_bias;
+        p.w2 = nullptr; p.s2 = nullptr; p.b2 = nullptr; p.rb2 = nullptr;
+        p.N = H; p.K = I; p.x = L->inner_bf; p.xsum = L->inner_sum; p.out = L->y;
+        {
+            dim3 grid((H / 16 + 3) / 4, E);
+            if (wide) grouped_mma_decode_kernel<false, 2><<<grid, 128, 0, st>>>(p);
+            else grouped_mma_decode_kernel<false, 1><<<grid, 128, 0, st>>>(p);
+        }
+        L->launches += 1;
+        stage_end(L, ST_DOWN, st);
+        if (cudaGetLastError() != cudaSuccess) return fail(L, FFAI_ERR_CUDA, "decode kernels launch failed");
+    } else
     if (tc_experts) {
         using namespace g100;
         const int ntok = tix ? 128 : 16;

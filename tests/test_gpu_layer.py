@@ -263,3 +263,44 @@ def test_tc_and_gemv_paths_agree_on_routing_and_nearly_on_values(oracle_mod):
     assert np.array_equal(b, c)                       # the tensor-core path is deterministic too
     fa, fb = synth.bf16_to_f32(a).astype(np.float64), synth.bf16_to_f32(b).astype(np.float64)
     assert np.sqrt(((fa - fb) ** 2).mean()) / np.sqrt((fa ** 2).mean()) < 5e-3
+
+
+# ── the register-streaming decode kernels (forced), same oracle, same tolerances ──
+
+MMA = 3  # option "path": per-warp streaming mma.sync kernels
+
+
+@pytest.mark.parametrize("T", [1, 2, 8, 9, 32, 64])
+def test_mma_cfg2_decode(oracle_mod, T):
+    run_and_check(oracle_mod, synth.cfg2_gptoss(), T, path=MMA)
+
+
+def test_mma_cfg2_row_bias_residual(oracle_mod):
+    run_and_check(oracle_mod, synth.cfg2_gptoss().with_(expert_row_bias=1), 21, residual=True, path=MMA)
+
+
+@pytest.mark.parametrize("T", [1, 16, 40])
+def test_mma_cfg1_and_cfg3_shapes(oracle_mod, T):
+    run_and_check(oracle_mod, synth.cfg1_tiny(), T, path=MMA)
+    run_and_check(oracle_mod, synth.cfg3_qwen(), T, path=MMA)
+
+
+def test_mma_group_size_128_and_many_rows_per_expert(oracle_mod):
+    # 70 tokens over 8 experts: several passes of 8/16 activation rows per expert
+    run_and_check(oracle_mod, synth.LayerSpec("mma_gs128", 512, 256, 8, 2, expert_group_size=128), 70, path=MMA)
+    run_and_check(oracle_mod, synth.LayerSpec("mma_small", 64, 64, 4, 2), 5, path=MMA)
+
+
+def test_auto_path_is_deterministic_and_matches_forced_paths(oracle_mod):
+    spec = synth.cfg2_gptoss()
+    host = synth.make_layer(spec, 0)
+    x = synth.make_tokens(8, spec.hidden, 0)
+    layer = MoELayer(host, 8)
+    try:
+        a, _ = layer.forward_host(x)
+        b, _ = layer.forward_host(x)
+        layer.set_option("path", MMA)
+        c, _ = layer.forward_host(x)
+    finally:
+        layer.close()
+    assert np.array_equal(a, b) and np.array_equal(a, c)   # small batches take the streaming kernels
