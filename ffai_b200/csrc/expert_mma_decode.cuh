@@ -1,5 +1,7 @@
-// Decode-regime grouped 4-bit dequant products: weights stream straight from HBM into
-// registers, one warp per 16 weight rows, no shared memory and no cross-warp handshakes.
+// Decode-regime grouped 4-bit dequant products: packed weights stream from HBM through a
+// cp.async-staged shared-memory ring (16-byte asynchronous copies, three 256-k stages in
+// flight) into registers, one warp per 16 weight rows; the only synchronisation is one
+// __syncthreads per stage.
 //
 // Replaces, for small batches, the reference's per-expert GEMV chain
 // (Ops.dequantGemvInt4ExpertIndexedMany, FFAI Ops.swift:2529-2587; the fused
@@ -9,11 +11,11 @@
 //
 // A warp owns 16 consecutive output rows of one expert (for gate/up: the 16 gate rows and
 // the 16 up rows, so the activation is applied in registers) and walks the reduction axis
-// one 64-value group at a time.  Per group a lane loads two packed words per row it
-// touches (8-byte loads; a warp covers 8 rows x 32 contiguous bytes), turns each word into
+// one 64-value group at a time.  Per group a lane reads two packed words per row it
+// touches from the staged tile, turns each word into
 // four bf16 pairs holding 128+q exactly ((q | 0x4300) is the bf16 128+q), and feeds them to
 // mma.sync.m16n8k16 as the A operand; the B operand is the 8 (or 16) activation rows routed
-// to this expert, read through L1.  The tensor core is only the dot-product engine here:
+// to this expert, staged alongside.  The tensor core is only the dot-product engine here:
 // the kernel is bound by HBM.  After each group the fp32 partial is folded in with the
 // group's scale and bias:
 //     sum_k (s*q_k + b) x_k = s * sum_k (128+q_k) x_k + (b - 128 s) * sum_k x_k,
@@ -41,7 +43,8 @@ struct Params {
     int N, K, group_size;  // group_size 64 or 128
     const uint32_t* offsets;  // [E+1] rows per expert in the sorted row space
     const uint16_t* x;        // [rows, K] bf16, 8-run permuted
-    const float* xsum;        // [rows, K/64] sum of each 64-run of x
+    const float* xsum;        // [rows, xsum_pitch] sum of each 64-run of x; pitch = K/64 rounded up to 4
+    int xsum_pitch;
     void* out;                // FUSED: bf16 [rows, N] 8-run permuted;  else fp32 [rows, N]
     int activation;
     float limit, alpha;
@@ -73,48 +76,102 @@ FFAI_DEVINL int permute8_col(int n) {
     return (n & ~7) | (((k & 3) << 1) | (k >> 2));
 }
 
-// grid: (ceil(N/16 / 4), E); block: 128 threads = 4 warps, each warp one 16-row block.
+FFAI_DEVINL void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+FFAI_DEVINL void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+FFAI_DEVINL void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Shared-memory staging geometry.  A stage is 256 k: per weight row 128 bytes (pitch 160 so the
+// 8-byte fragment reads of eight rows fall in distinct banks), per activation row 512 bytes
+// (pitch 528 for the 16-byte fragment reads).
+constexpr int STG_K = 256;                 // k per stage
+constexpr int STG_GROUPS = STG_K / 64;     // 64-runs per stage
+constexpr int W_PITCH = 160;
+constexpr int X_PITCH = 528;
+constexpr int WARPS = 4;                   // warps per CTA, 16 weight rows each
+constexpr int DEPTH = 3;                   // stages in flight
+
+template <bool FUSED, int NT>
+struct StageLayout {
+    static constexpr int NP = FUSED ? 2 : 1;
+    static constexpr int W_BYTES = WARPS * NP * 16 * W_PITCH;   // packed weight rows of the whole CTA
+    static constexpr int X_BYTES = NT * 8 * X_PITCH;            // activation rows shared by the CTA
+    static constexpr int S_BYTES = NT * 8 * 16;                 // their 64-run sums: 4 floats per row
+    static constexpr int STAGE = W_BYTES + X_BYTES + S_BYTES;
+    static constexpr int TOTAL = DEPTH * STAGE;
+};
+
+// grid: (ceil(N / 64), E); block: 128 threads = 4 warps; warp w owns rows [64*bx + 16*w, +16) of expert by.
+// The four warps share the expert, hence the activation rows: weights and activations are staged by the
+// whole CTA with cp.async (16-byte asynchronous copies, DEPTH stages in flight, one __syncthreads per stage).
 // NT: activation rows handled per pass over the weights, in units of 8.
 template <bool FUSED, int NT>
 __global__ void __launch_bounds__(128)
 grouped_mma_decode_kernel(const Params p) {
-    constexpr int NP = FUSED ? 2 : 1;
+    using SL = StageLayout<FUSED, NT>;
+    constexpr int NP = SL::NP;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int e = blockIdx.y;
-    const int rb = blockIdx.x * 4 + warp;
-    if (rb * 16 >= p.N) return;
     const int row0 = (int)p.offsets[e], cnt = (int)p.offsets[e + 1] - row0;
     if (cnt <= 0) return;
-
+    const int cta_row = blockIdx.x * 64;           // first weight row (within the expert) of this CTA
     const int K = p.K, wpr = K / 8, gpr = K / p.group_size, n64 = K / 64;
+    const int n_stages = (K + STG_K - 1) / STG_K;
     const int gshift = p.group_size == 128 ? 1 : 0;  // 64-run index -> scale group index
-    const size_t rlo = (size_t)e * p.N + rb * 16 + g, rhi = rlo + 8;
-    const uint32_t* wp[NP][2];
+    const int rb_row = cta_row + warp * 16;        // this warp's first row
+    const bool warp_active = rb_row < p.N;         // N is a multiple of 16
+    const size_t rlo = (size_t)e * p.N + (warp_active ? rb_row : 0) + g, rhi = rlo + 8;
     const uint16_t* sp[NP][2];
     const uint16_t* bp[NP][2];
-    wp[0][0] = p.w1 + rlo * wpr + 2 * t; wp[0][1] = p.w1 + rhi * wpr + 2 * t;
     sp[0][0] = p.s1 + rlo * gpr; sp[0][1] = p.s1 + rhi * gpr;
     bp[0][0] = p.b1 + rlo * gpr; bp[0][1] = p.b1 + rhi * gpr;
     if (FUSED) {
-        wp[NP - 1][0] = p.w2 + rlo * wpr + 2 * t; wp[NP - 1][1] = p.w2 + rhi * wpr + 2 * t;
         sp[NP - 1][0] = p.s2 + rlo * gpr; sp[NP - 1][1] = p.s2 + rhi * gpr;
         bp[NP - 1][0] = p.b2 + rlo * gpr; bp[NP - 1][1] = p.b2 + rhi * gpr;
     }
+    const int rows_in_cta = min(64, p.N - cta_row);  // multiple of 16
 
     for (int tok0 = 0; tok0 < cnt; tok0 += 8 * NT) {
-        // activation row read by this lane as B operand (column g of each 8-wide tile), and the
-        // two rows whose results this lane holds (columns 2t, 2t+1); clamped, masked at the store
-        const uint16_t* xrow[NT];
-        const float* sxa[NT];
-        const float* sxb[NT];
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            const int last = cnt - 1;
-            xrow[j] = p.x + (size_t)(row0 + min(tok0 + 8 * j + g, last)) * K + 16 * t;
-            sxa[j] = p.xsum + (size_t)(row0 + min(tok0 + 8 * j + 2 * t, last)) * n64;
-            sxb[j] = p.xsum + (size_t)(row0 + min(tok0 + 8 * j + 2 * t + 1, last)) * n64;
-        }
+        const int ntok = min(8 * NT, cnt - tok0);
+        // issue the asynchronous copies of one stage: CTA-wide, 16 bytes per copy
+        auto issue_stage = [&](int st) {
+            if (st < n_stages) {
+                const uint32_t dst = sbase + (st % DEPTH) * SL::STAGE;
+                const int kbytes_w = min(STG_K, K - st * STG_K) / 2;   // valid packed bytes per row in this stage
+                const int kbytes_x = kbytes_w * 4;                     // valid activation bytes per row
+                // weights: NP * 64 rows x 8 chunks
+                for (int c = threadIdx.x; c < NP * 64 * 8; c += 128) {
+                    const int col = c & 7, r = (c >> 3) & 63, q = c >> 9;
+                    if (r < rows_in_cta) {
+                        const uint32_t* base = q ? p.w2 : p.w1;
+                        const uint8_t* src = reinterpret_cast<const uint8_t*>(base + ((size_t)e * p.N + cta_row + r) * wpr) +
+                                             st * (STG_K / 2) + col * 16;
+                        const uint32_t d = dst + (((r >> 4) * NP + q) * 16 + (r & 15)) * W_PITCH + col * 16;
+                        const int valid = kbytes_w - col * 16;
+                        if (valid > 0) cp_async16(d, src, 16);
+                    }
+                }
+                // activations: ntok rows x 32 chunks
+                for (int c = threadIdx.x; c < ntok * 32; c += 128) {
+                    const int col = c & 31, r = c >> 5;
+                    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.x + (size_t)(row0 + tok0 + r) * K) +
+                                         st * (STG_K * 2) + col * 16;
+                    const uint32_t d = dst + SL::W_BYTES + r * X_PITCH + col * 16;
+                    if (col * 16 < kbytes_x) cp_async16(d, src, 16);
+                }
+                // 64-run sums of those rows: 4 floats per row
+                if (threadIdx.x < ntok)
+                    cp_async16(dst + SL::W_BYTES + SL::X_BYTES + threadIdx.x * 16,
+                               p.xsum + (size_t)(row0 + tok0 + threadIdx.x) * p.xsum_pitch + st * STG_GROUPS, 16);
+            }
+            cp_async_commit();
+        };
+
         float tot[NT][NP][4];
 #pragma unroll
         for (int j = 0; j < NT; ++j)
@@ -123,89 +180,126 @@ grouped_mma_decode_kernel(const Params p) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) tot[j][q][i] = 0.0f;
 
-        // software pipeline: packed words of the next group are in flight while this one is consumed
-        uint2 wnext[NP][2];
+        __syncthreads();  // every warp is done with the previous pass's stages
 #pragma unroll
-        for (int q = 0; q < NP; ++q) { wnext[q][0] = ld_stream_u2(wp[q][0]); wnext[q][1] = ld_stream_u2(wp[q][1]); }
+        for (int st = 0; st < DEPTH - 1; ++st) issue_stage(st);
+        // (scale | bias << 16) of stages st and st+1, alternating slots
+        uint32_t sb_cur[NP][2], sb_nxt[NP][2];
+        auto fetch_sb = [&](int st, uint32_t (*dst)[2]) {
+            const int Gm = min(st * STG_GROUPS + t, n64 - 1) >> gshift;
+#pragma unroll
+            for (int q = 0; q < NP; ++q)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    dst[q][h] = (uint32_t)__ldg(sp[q][h] + Gm) | ((uint32_t)__ldg(bp[q][h] + Gm) << 16);
+        };
+        fetch_sb(0, sb_cur);
+        fetch_sb(1, sb_nxt);
 
-        for (int G = 0; G < n64; ++G) {
-            uint2 wcur[NP][2];
+        for (int st = 0; st < n_stages; ++st) {
+            cp_async_wait<DEPTH - 2>();   // stage st has landed (this thread's copies)
+            __syncthreads();              // ... and everyone else's; stage st-1 is free again
+            issue_stage(st + DEPTH - 1);
+            if (warp_active) {
+                const uint8_t* stage = smem + (st % DEPTH) * SL::STAGE;
+                const uint8_t* wst = stage + warp * NP * 16 * W_PITCH;
+                const uint8_t* xst = stage + SL::W_BYTES;
+                const float* sst = reinterpret_cast<const float*>(xst + SL::X_BYTES);
+                const int groups = min(STG_GROUPS, n64 - st * STG_GROUPS);
+                // scale / bias: lane (g, t) holds 64-run st*4+t of its two rows (shared by shuffle below);
+                // the values of the stage after next are fetched now, so the loads never stall the warp
+                uint32_t sbv[NP][2], sbn[NP][2];
+                fetch_sb(st + 2, sbn);
 #pragma unroll
-            for (int q = 0; q < NP; ++q) { wcur[q][0] = wnext[q][0]; wcur[q][1] = wnext[q][1]; }
-            if (G + 1 < n64) {
+                for (int q = 0; q < NP; ++q)
 #pragma unroll
-                for (int q = 0; q < NP; ++q) {
-                    wnext[q][0] = ld_stream_u2(wp[q][0] + (G + 1) * 8);
-                    wnext[q][1] = ld_stream_u2(wp[q][1] + (G + 1) * 8);
-                }
-            }
-            // scale and (bias - 128*scale) of the two rows this lane's results belong to
-            float sc[NP][2], bm[NP][2];
-            const int gi = G >> gshift;
+                    for (int h = 0; h < 2; ++h) {
+                        sbv[q][h] = sb_cur[q][h];
+                        sb_cur[q][h] = sb_nxt[q][h];
+                        sb_nxt[q][h] = sbn[q][h];
+                    }
+                float s_l[NP][2], b_l[NP][2];
 #pragma unroll
-            for (int q = 0; q < NP; ++q)
+                for (int q = 0; q < NP; ++q)
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const float s = bf16_bits_to_f32(__ldg(sp[q][h] + gi));
-                    const float b = bf16_bits_to_f32(__ldg(bp[q][h] + gi));
-                    sc[q][h] = s;
-                    bm[q][h] = fmaf(-128.0f, s, b);
-                }
-            // A fragments: [projection][word 0/1][row lo/hi][pair 0..3]
-            uint32_t af[NP][2][2][4];
+                    for (int h = 0; h < 2; ++h) {
+                        s_l[q][h] = __uint_as_float(sbv[q][h] << 16);
+                        b_l[q][h] = __uint_as_float(sbv[q][h] & 0xFFFF0000u);
+                    }
+                for (int Gi = 0; Gi < groups; ++Gi) {
+                    const int src_lane = (lane & ~3) | Gi;
+                    float sc[NP][2], bm[NP][2];
 #pragma unroll
-            for (int q = 0; q < NP; ++q)
+                    for (int q = 0; q < NP; ++q)
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    unpack_word_128(wcur[q][h].x, af[q][0][h]);
-                    unpack_word_128(wcur[q][h].y, af[q][1][h]);
-                }
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                const uint4 x0 = __ldg(reinterpret_cast<const uint4*>(xrow[j] + G * 64));
-                const uint4 x1 = __ldg(reinterpret_cast<const uint4*>(xrow[j] + G * 64 + 8));
-                const uint32_t xb[2][4] = {{x0.x, x0.y, x0.z, x0.w}, {x1.x, x1.y, x1.z, x1.w}};
-                const float sx0 = __ldg(sxa[j] + G), sx1 = __ldg(sxb[j] + G);
-#pragma unroll
-                for (int q = 0; q < NP; ++q) {
-                    float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int w = 0; w < 2; ++w)
-#pragma unroll
-                        for (int hp = 0; hp < 2; ++hp) {
-                            // k-slots (2t,2t+1) <- pair 2hp, (2t+8,2t+9) <- pair 2hp+1 of word w
-                            const uint32_t a[4] = {af[q][w][0][2 * hp], af[q][w][1][2 * hp],
-                                                   af[q][w][0][2 * hp + 1], af[q][w][1][2 * hp + 1]};
-                            mma_bf16_16816(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
+                        for (int h = 0; h < 2; ++h) {
+                            const float s = __shfl_sync(0xFFFFFFFFu, s_l[q][h], src_lane);
+                            const float b = __shfl_sync(0xFFFFFFFFu, b_l[q][h], src_lane);
+                            sc[q][h] = s;
+                            bm[q][h] = fmaf(-128.0f, s, b);
                         }
-                    tot[j][q][0] = fmaf(sc[q][0], c[0], fmaf(bm[q][0], sx0, tot[j][q][0]));
-                    tot[j][q][1] = fmaf(sc[q][0], c[1], fmaf(bm[q][0], sx1, tot[j][q][1]));
-                    tot[j][q][2] = fmaf(sc[q][1], c[2], fmaf(bm[q][1], sx0, tot[j][q][2]));
-                    tot[j][q][3] = fmaf(sc[q][1], c[3], fmaf(bm[q][1], sx1, tot[j][q][3]));
+                    // A fragments: [projection][word 0/1][row lo/hi][pair 0..3]
+                    uint32_t af[NP][2][2][4];
+#pragma unroll
+                    for (int q = 0; q < NP; ++q)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint2 wv = *reinterpret_cast<const uint2*>(wst + (q * 16 + g + 8 * h) * W_PITCH + Gi * 32 + t * 8);
+                            unpack_word_128(wv.x, af[q][0][h]);
+                            unpack_word_128(wv.y, af[q][1][h]);
+                        }
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        const uint8_t* xr = xst + (8 * j + g) * X_PITCH + Gi * 128 + t * 32;
+                        const uint4 x0 = *reinterpret_cast<const uint4*>(xr);
+                        const uint4 x1 = *reinterpret_cast<const uint4*>(xr + 16);
+                        const uint32_t xb[2][4] = {{x0.x, x0.y, x0.z, x0.w}, {x1.x, x1.y, x1.z, x1.w}};
+                        const float sx0 = sst[(8 * j + 2 * t) * 4 + Gi], sx1 = sst[(8 * j + 2 * t + 1) * 4 + Gi];
+#pragma unroll
+                        for (int q = 0; q < NP; ++q) {
+                            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                            for (int w = 0; w < 2; ++w)
+#pragma unroll
+                                for (int hp = 0; hp < 2; ++hp) {
+                                    // k-slots (2t,2t+1) <- pair 2hp, (2t+8,2t+9) <- pair 2hp+1 of word w
+                                    const uint32_t a[4] = {af[q][w][0][2 * hp], af[q][w][1][2 * hp],
+                                                           af[q][w][0][2 * hp + 1], af[q][w][1][2 * hp + 1]};
+                                    mma_bf16_16816(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
+                                }
+                            tot[j][q][0] = fmaf(sc[q][0], c[0], fmaf(bm[q][0], sx0, tot[j][q][0]));
+                            tot[j][q][1] = fmaf(sc[q][0], c[1], fmaf(bm[q][0], sx1, tot[j][q][1]));
+                            tot[j][q][2] = fmaf(sc[q][1], c[2], fmaf(bm[q][1], sx0, tot[j][q][2]));
+                            tot[j][q][3] = fmaf(sc[q][1], c[3], fmaf(bm[q][1], sx1, tot[j][q][3]));
+                        }
+                    }
                 }
             }
         }
+        cp_async_wait<0>();
 
         // results: value i -> (row g + 8*(i>>1), activation row tok0 + 8j + 2t + (i&1))
+        if (warp_active) {
 #pragma unroll
-        for (int j = 0; j < NT; ++j)
+            for (int j = 0; j < NT; ++j)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int tok = tok0 + 8 * j + 2 * t + (i & 1);
-                if (tok >= cnt) continue;
-                const int n = rb * 16 + g + 8 * (i >> 1);
-                const size_t rr = (size_t)e * p.N + n;
-                float v = tot[j][0][i];
-                if (p.rb1) v += bf16_bits_to_f32(p.rb1[rr]);
-                if (FUSED) {
-                    float u = tot[j][NP - 1][i];
-                    if (p.rb2) u += bf16_bits_to_f32(p.rb2[rr]);
-                    v = glu_activation(v, u, p.activation, p.limit, p.alpha);
-                    reinterpret_cast<uint16_t*>(p.out)[(size_t)(row0 + tok) * p.N + permute8_col(n)] = f32_to_bf16_bits(v);
-                } else {
-                    reinterpret_cast<float*>(p.out)[(size_t)(row0 + tok) * p.N + n] = v;
+                for (int i = 0; i < 4; ++i) {
+                    const int tok = tok0 + 8 * j + 2 * t + (i & 1);
+                    if (tok >= cnt) continue;
+                    const int n = rb_row + g + 8 * (i >> 1);
+                    const size_t rr = (size_t)e * p.N + n;
+                    float v = tot[j][0][i];
+                    if (p.rb1) v += bf16_bits_to_f32(p.rb1[rr]);
+                    if (FUSED) {
+                        float u = tot[j][NP - 1][i];
+                        if (p.rb2) u += bf16_bits_to_f32(p.rb2[rr]);
+                        v = glu_activation(v, u, p.activation, p.limit, p.alpha);
+                        reinterpret_cast<uint16_t*>(p.out)[(size_t)(row0 + tok) * p.N + permute8_col(n)] = f32_to_bf16_bits(v);
+                    } else {
+                        reinterpret_cast<float*>(p.out)[(size_t)(row0 + tok) * p.N + n] = v;
+                    }
                 }
-            }
+        }
     }
 }
 
@@ -213,7 +307,7 @@ grouped_mma_decode_kernel(const Params p) {
 // 64-run (fp32).  One warp per output row.  ids nullable (identity), id_div as in Ops.gather use.
 __global__ void gather_perm8_sum64_kernel(const uint16_t* __restrict__ table, const uint32_t* __restrict__ ids,
                                           int id_div, uint16_t* __restrict__ out, float* __restrict__ sums,
-                                          int n_rows, int row_len) {
+                                          int n_rows, int row_len, int sum_pitch) {
     const int warps = blockDim.x / 32;
     const int row = blockIdx.x * warps + threadIdx.x / 32;
     if (row >= n_rows) return;
@@ -240,14 +334,14 @@ __global__ void gather_perm8_sum64_kernel(const uint16_t* __restrict__ table, co
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 4);
-        if ((lane & 7) == 0 && i < chunks) sums[(size_t)row * (row_len / 64) + (i >> 3)] = part;
+        if ((lane & 7) == 0 && i < chunks) sums[(size_t)row * sum_pitch + (i >> 3)] = part;
     }
 }
 
 // Sum of every 64-run of rows that are already stored 8-run permuted (the sum does not depend
 // on the order inside a run).  One warp per row.
 __global__ void sum64_rows_kernel(const uint16_t* __restrict__ rows, float* __restrict__ sums, int n_rows,
-                                  int row_len) {
+                                  int row_len, int sum_pitch) {
     const int warps = blockDim.x / 32;
     const int row = blockIdx.x * warps + threadIdx.x / 32;
     if (row >= n_rows) return;
@@ -265,7 +359,7 @@ __global__ void sum64_rows_kernel(const uint16_t* __restrict__ rows, float* __re
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 4);
-        if ((lane & 7) == 0 && i < chunks) sums[(size_t)row * (row_len / 64) + (i >> 3)] = part;
+        if ((lane & 7) == 0 && i < chunks) sums[(size_t)row * sum_pitch + (i >> 3)] = part;
     }
 }
 

@@ -285,6 +285,18 @@ int launch_plan(const uint32_t* indices, int n_rows, int E, uint32_t* counts, ui
     return cudaGetLastError() == cudaSuccess ? 3 : -1;
 }
 
+template <bool FUSED, int NT>
+void launch_mma_decode(const dmma::Params& p, dim3 grid, cudaStream_t st) {
+    using SL = dmma::StageLayout<FUSED, NT>;
+    auto k = dmma::grouped_mma_decode_kernel<FUSED, NT>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::TOTAL);
+        attr_set = true;
+    }
+    k<<<grid, 128, SL::TOTAL, st>>>(p);
+}
+
 // dense [1,H] projection per token (shared-expert gate stored as f32 / bf16)
 template <typename TW>
 __global__ void dense_rowdot_kernel(const TW* __restrict__ w, const uint16_t* __restrict__ x,
@@ -432,8 +444,9 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
         const size_t Mp = M < 128 ? 128 : M, Tp = T < 128 ? 128 : T;  // at least one full TMA box of rows
         if ((rc = ws_alloc(L, &L->xg, Mp * H))) return rc;
         if ((rc = ws_alloc(L, &L->inner_bf, Mp * I))) return rc;
-        if ((rc = ws_alloc(L, &L->xsum, M * (H / 64)))) return rc;
-        if ((rc = ws_alloc(L, &L->inner_sum, M * (I / 64)))) return rc;
+        // 64-run sums, row pitch rounded up to 4 floats (16-byte rows for cp.async), + one spare row
+        if ((rc = ws_alloc(L, &L->xsum, (M + 1) * (size_t)((H / 64 + 3) & ~3)))) return rc;
+        if ((rc = ws_alloc(L, &L->inner_sum, (M + 1) * (size_t)((I / 64 + 3) & ~3)))) return rc;
         L->mma_ok = c.expert_bits == 4 && (c.expert_group_size == 64 || c.expert_group_size == 128);
         if (want_tc) {
             if ((rc = ws_alloc(L, &L->y_bf, M * H))) return rc;
@@ -718,7 +731,8 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     if (mma_experts) {
         using namespace dmma;
         stage_begin(L, ST_GATHER, st);
-        gather_perm8_sum64_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, K, L->xg, L->xsum, M, H);
+        const int xp_h = (H / 64 + 3) & ~3, xp_i = (I / 64 + 3) & ~3;
+        gather_perm8_sum64_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, K, L->xg, L->xsum, M, H, xp_h);
         L->launches += 1;
         stage_end(L, ST_GATHER, st);
 
@@ -731,24 +745,24 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         stage_begin(L, ST_GATE_UP, st);
         p.w1 = L->w.gate_proj.weight; p.s1 = L->w.gate_proj.scales; p.b1 = L->w.gate_proj.biases; p.rb1 = L->w.gate_proj.row_bias;
         p.w2 = L->w.up_proj.weight; p.s2 = L->w.up_proj.scales; p.b2 = L->w.up_proj.biases; p.rb2 = L->w.up_proj.row_bias;
-        p.N = I; p.K = H; p.x = L->xg; p.xsum = L->xsum; p.out = L->inner_bf;
+        p.N = I; p.K = H; p.x = L->xg; p.xsum = L->xsum; p.xsum_pitch = xp_h; p.out = L->inner_bf;
         {
-            dim3 grid((I / 16 + 3) / 4, E);
-            if (wide) grouped_mma_decode_kernel<true, 2><<<grid, 128, 0, st>>>(p);
-            else grouped_mma_decode_kernel<true, 1><<<grid, 128, 0, st>>>(p);
+            dim3 grid((I + 63) / 64, E);
+            if (wide) launch_mma_decode<true, 2>(p, grid, st);
+            else launch_mma_decode<true, 1>(p, grid, st);
         }
-        sum64_rows_kernel<<<(M + 7) / 8, 256, 0, st>>>(L->inner_bf, L->inner_sum, M, I);
+        sum64_rows_kernel<<<(M + 7) / 8, 256, 0, st>>>(L->inner_bf, L->inner_sum, M, I, xp_i);
         L->launches += 2;
         stage_end(L, ST_GATE_UP, st);
 
         stage_begin(L, ST_DOWN, st);
         p.w1 = L->w.down_proj.weight; p.s1 = L->w.down_proj.scales; p.b1 = L->w.down_proj.biases; p.rb1 = L->w.down_proj.row_bias;
         p.w2 = nullptr; p.s2 = nullptr; p.b2 = nullptr; p.rb2 = nullptr;
-        p.N = H; p.K = I; p.x = L->inner_bf; p.xsum = L->inner_sum; p.out = L->y;
+        p.N = H; p.K = I; p.x = L->inner_bf; p.xsum = L->inner_sum; p.xsum_pitch = xp_i; p.out = L->y;
         {
-            dim3 grid((H / 16 + 3) / 4, E);
-            if (wide) grouped_mma_decode_kernel<false, 2><<<grid, 128, 0, st>>>(p);
-            else grouped_mma_decode_kernel<false, 1><<<grid, 128, 0, st>>>(p);
+            dim3 grid((H + 63) / 64, E);
+            if (wide) launch_mma_decode<false, 2>(p, grid, st);
+            else launch_mma_decode<false, 1>(p, grid, st);
         }
         L->launches += 1;
         stage_end(L, ST_DOWN, st);
