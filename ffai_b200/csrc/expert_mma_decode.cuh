@@ -1,7 +1,7 @@
-// Decode-regime grouped 4-bit dequant products: packed weights stream from HBM through a
-// cp.async-staged shared-memory ring (16-byte asynchronous copies, three 256-k stages in
-// flight) into registers, one warp per 16 weight rows; the only synchronisation is one
-// __syncthreads per stage.
+// Decode-regime grouped 4-bit dequant products: packed weights stream from HBM through
+// per-warp cp.async-staged shared-memory rings (16-byte asynchronous copies, three 128-k
+// stages in flight per warp) into registers, one warp per 16 weight rows; warps do not
+// synchronise with each other inside the stream.
 //
 // Replaces, for small batches, the reference's per-expert GEMV chain
 // (Ops.dequantGemvInt4ExpertIndexedMany, FFAI Ops.swift:2529-2587; the fused
@@ -40,6 +40,8 @@ struct Params {
     const uint16_t* s2;
     const uint16_t* b2;
     const uint16_t* rb2;
+    const uint32_t* sb1;   // repacked (scale | bias << 16): [E, N/16, K/64, 16]  (see repack_scale_bias_kernel)
+    const uint32_t* sb2;
     int N, K, group_size;  // group_size 64 or 128
     const uint32_t* offsets;  // [E+1] rows per expert in the sorted row space
     const uint16_t* x;        // [rows, K] bf16, 8-run permuted
@@ -76,102 +78,115 @@ FFAI_DEVINL int permute8_col(int n) {
     return (n & ~7) | (((k & 3) << 1) | (k >> 2));
 }
 
-FFAI_DEVINL void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+FFAI_DEVINL void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 FFAI_DEVINL void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 FFAI_DEVINL void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Shared-memory staging geometry.  A stage is 256 k: per weight row 128 bytes (pitch 160 so the
-// 8-byte fragment reads of eight rows fall in distinct banks), per activation row 512 bytes
-// (pitch 528 for the 16-byte fragment reads).
-constexpr int STG_K = 256;                 // k per stage
-constexpr int STG_GROUPS = STG_K / 64;     // 64-runs per stage
-constexpr int W_PITCH = 160;
-constexpr int X_PITCH = 528;
-constexpr int WARPS = 4;                   // warps per CTA, 16 weight rows each
-constexpr int DEPTH = 3;                   // stages in flight
+// First MMA of a group: accumulator starts from zero (lets the compiler use the zero register).
+FFAI_DEVINL void mma_bf16_16816_zero(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+}
 
-template <bool FUSED, int NT>
-struct StageLayout {
+// Per-warp staging geometry.  A stage is 128 k (two 64-runs): per weight row 64 packed bytes at a
+// 96-byte pitch (so the 8-byte fragment reads of eight rows fall in distinct banks), followed by the
+// packed (scale | bias << 16) words of the stage, 16 rows x 2 runs per projection.
+constexpr int STG_RUNS = 2;
+constexpr int W_PITCH = 96;
+constexpr int DEPTH = 3;                   // stages in flight per warp
+
+template <bool FUSED>
+struct WarpStage {
     static constexpr int NP = FUSED ? 2 : 1;
-    static constexpr int W_BYTES = WARPS * NP * 16 * W_PITCH;   // packed weight rows of the whole CTA
-    static constexpr int X_BYTES = NT * 8 * X_PITCH;            // activation rows shared by the CTA
-    static constexpr int S_BYTES = NT * 8 * 16;                 // their 64-run sums: 4 floats per row
-    static constexpr int STAGE = W_BYTES + X_BYTES + S_BYTES;
-    static constexpr int TOTAL = DEPTH * STAGE;
+    static constexpr int W_BYTES = NP * 16 * W_PITCH;
+    static constexpr int SB_BYTES = NP * STG_RUNS * 64;
+    static constexpr int STAGE = W_BYTES + SB_BYTES;
+    static constexpr int PER_WARP = DEPTH * STAGE;
+    static constexpr int TOTAL = 4 * PER_WARP;
 };
 
-// grid: (ceil(N / 64), E); block: 128 threads = 4 warps; warp w owns rows [64*bx + 16*w, +16) of expert by.
-// The four warps share the expert, hence the activation rows: weights and activations are staged by the
-// whole CTA with cp.async (16-byte asynchronous copies, DEPTH stages in flight, one __syncthreads per stage).
+// grid: (ceil(N / 16 / (4 / KSPLIT)), E); block: 128 threads = 4 warps.
+// Warp w works on 16-row block (w / KSPLIT) of the CTA and on the (w % KSPLIT)-th slice of the
+// reduction axis; with KSPLIT > 1 the slices are summed in a fixed order through shared memory at
+// the end (tiny batches: more warps in flight per active expert).  Every warp streams its own packed
+// rows and scale words through its own cp.async ring (16-byte asynchronous copies, DEPTH stages of
+// 128 k in flight) and synchronises with nobody until the final reduction.
 // NT: activation rows handled per pass over the weights, in units of 8.
-template <bool FUSED, int NT>
+template <bool FUSED, int NT, int KSPLIT>
 __global__ void __launch_bounds__(128)
 grouped_mma_decode_kernel(const Params p) {
-    using SL = StageLayout<FUSED, NT>;
-    constexpr int NP = SL::NP;
+    using WS = WarpStage<FUSED>;
+    constexpr int NP = WS::NP;
+    constexpr int RBW = 4 / KSPLIT;  // 16-row blocks per CTA
     extern __shared__ __align__(16) uint8_t smem[];
-    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int e = blockIdx.y;
     const int row0 = (int)p.offsets[e], cnt = (int)p.offsets[e + 1] - row0;
     if (cnt <= 0) return;
-    const int cta_row = blockIdx.x * 64;           // first weight row (within the expert) of this CTA
-    const int K = p.K, wpr = K / 8, gpr = K / p.group_size, n64 = K / 64;
-    const int n_stages = (K + STG_K - 1) / STG_K;
-    const int gshift = p.group_size == 128 ? 1 : 0;  // 64-run index -> scale group index
-    const int rb_row = cta_row + warp * 16;        // this warp's first row
-    const bool warp_active = rb_row < p.N;         // N is a multiple of 16
-    const size_t rlo = (size_t)e * p.N + (warp_active ? rb_row : 0) + g, rhi = rlo + 8;
-    const uint16_t* sp[NP][2];
-    const uint16_t* bp[NP][2];
-    sp[0][0] = p.s1 + rlo * gpr; sp[0][1] = p.s1 + rhi * gpr;
-    bp[0][0] = p.b1 + rlo * gpr; bp[0][1] = p.b1 + rhi * gpr;
-    if (FUSED) {
-        sp[NP - 1][0] = p.s2 + rlo * gpr; sp[NP - 1][1] = p.s2 + rhi * gpr;
-        bp[NP - 1][0] = p.b2 + rlo * gpr; bp[NP - 1][1] = p.b2 + rhi * gpr;
+    const int K = p.K, wpr = K / 8, n64 = K / 64;
+    const int rb = blockIdx.x * RBW + warp / KSPLIT;   // 16-row block within the expert
+    const int ks = warp % KSPLIT;
+    const int rb_row = rb * 16;
+    const bool warp_active = rb_row < p.N;             // N is a multiple of 16
+    const int per = (n64 + KSPLIT - 1) / KSPLIT;
+    const int G0 = min(ks * per, n64), G1 = min(G0 + per, n64);
+    const int n_runs = warp_active ? G1 - G0 : 0;
+    const int n_stages = (n_runs + STG_RUNS - 1) / STG_RUNS;
+
+    uint8_t* wsm = smem + warp * WS::PER_WARP;
+    const uint32_t wsm_u32 = (uint32_t)__cvta_generic_to_shared(wsm);
+
+    // what this lane copies per stage: NP*2 packed-weight chunks (row (lane>>2) + 8i, 16-byte column lane&3)
+    // and, lanes 0..NP*8-1, one chunk of scale words
+    const uint8_t* wsrc[NP * 2];
+    {
+        const int col = lane & 3;
+#pragma unroll
+        for (int i = 0; i < NP * 2; ++i) {
+            const int ridx = (lane >> 2) + 8 * i;  // 0 .. NP*16-1
+            const uint32_t* base = (ridx >= 16) ? p.w2 : p.w1;
+            const size_t row = (size_t)e * p.N + (warp_active ? rb_row : 0) + (ridx & 15);
+            wsrc[i] = reinterpret_cast<const uint8_t*>(base + row * wpr) + G0 * 32 + col * 16;
+        }
     }
-    const int rows_in_cta = min(64, p.N - cta_row);  // multiple of 16
+    const int sb_q = lane >> 3;  // projection whose scale words this lane copies (valid when < NP)
+    const uint8_t* sbsrc = reinterpret_cast<const uint8_t*>(
+        ((sb_q == 1 && FUSED) ? p.sb2 : p.sb1) + (((size_t)e * (p.N / 16) + (warp_active ? rb : 0)) * n64 + G0) * 16) + (lane & 7) * 16;
+
+    auto issue_stage = [&](int st) {
+        if (st < n_stages) {
+            const uint32_t dst = wsm_u32 + (st % DEPTH) * WS::STAGE;
+            const int runs_left = n_runs - st * STG_RUNS;           // >= 1
+            if ((lane & 3) < 2 * runs_left) {                        // 16-byte columns 0,1: first run; 2,3: second
+#pragma unroll
+                for (int i = 0; i < NP * 2; ++i)
+                    cp_async16(dst + ((lane >> 2) + 8 * i) * W_PITCH + (lane & 3) * 16, wsrc[i] + st * 64);
+            }
+            if (sb_q < NP && (lane & 7) < 4 * runs_left)             // 4 chunks of scale words per run
+                cp_async16(dst + WS::W_BYTES + sb_q * (STG_RUNS * 64) + (lane & 7) * 16, sbsrc + st * (STG_RUNS * 64));
+        }
+        cp_async_commit();
+    };
 
     for (int tok0 = 0; tok0 < cnt; tok0 += 8 * NT) {
-        const int ntok = min(8 * NT, cnt - tok0);
-        // issue the asynchronous copies of one stage: CTA-wide, 16 bytes per copy
-        auto issue_stage = [&](int st) {
-            if (st < n_stages) {
-                const uint32_t dst = sbase + (st % DEPTH) * SL::STAGE;
-                const int kbytes_w = min(STG_K, K - st * STG_K) / 2;   // valid packed bytes per row in this stage
-                const int kbytes_x = kbytes_w * 4;                     // valid activation bytes per row
-                // weights: NP * 64 rows x 8 chunks
-                for (int c = threadIdx.x; c < NP * 64 * 8; c += 128) {
-                    const int col = c & 7, r = (c >> 3) & 63, q = c >> 9;
-                    if (r < rows_in_cta) {
-                        const uint32_t* base = q ? p.w2 : p.w1;
-                        const uint8_t* src = reinterpret_cast<const uint8_t*>(base + ((size_t)e * p.N + cta_row + r) * wpr) +
-                                             st * (STG_K / 2) + col * 16;
-                        const uint32_t d = dst + (((r >> 4) * NP + q) * 16 + (r & 15)) * W_PITCH + col * 16;
-                        const int valid = kbytes_w - col * 16;
-                        if (valid > 0) cp_async16(d, src, 16);
-                    }
-                }
-                // activations: ntok rows x 32 chunks
-                for (int c = threadIdx.x; c < ntok * 32; c += 128) {
-                    const int col = c & 31, r = c >> 5;
-                    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.x + (size_t)(row0 + tok0 + r) * K) +
-                                         st * (STG_K * 2) + col * 16;
-                    const uint32_t d = dst + SL::W_BYTES + r * X_PITCH + col * 16;
-                    if (col * 16 < kbytes_x) cp_async16(d, src, 16);
-                }
-                // 64-run sums of those rows: 4 floats per row
-                if (threadIdx.x < ntok)
-                    cp_async16(dst + SL::W_BYTES + SL::X_BYTES + threadIdx.x * 16,
-                               p.xsum + (size_t)(row0 + tok0 + threadIdx.x) * p.xsum_pitch + st * STG_GROUPS, 16);
-            }
-            cp_async_commit();
-        };
-
+        // activation row read by this lane as B operand (column g of each 8-wide tile) and the two rows
+        // whose results it holds (columns 2t, 2t+1); clamped to the last valid row, masked at the store
+        const uint16_t* xrow[NT];
+        const float* sxa[NT];
+        const float* sxb[NT];
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const int last = cnt - 1;
+            xrow[j] = p.x + (size_t)(row0 + min(tok0 + 8 * j + g, last)) * K + 16 * t;
+            sxa[j] = p.xsum + (size_t)(row0 + min(tok0 + 8 * j + 2 * t, last)) * p.xsum_pitch;
+            sxb[j] = p.xsum + (size_t)(row0 + min(tok0 + 8 * j + 2 * t + 1, last)) * p.xsum_pitch;
+        }
         float tot[NT][NP][4];
 #pragma unroll
         for (int j = 0; j < NT; ++j)
@@ -180,61 +195,58 @@ grouped_mma_decode_kernel(const Params p) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) tot[j][q][i] = 0.0f;
 
-        __syncthreads();  // every warp is done with the previous pass's stages
+        __syncwarp();
 #pragma unroll
         for (int st = 0; st < DEPTH - 1; ++st) issue_stage(st);
-        // (scale | bias << 16) of stages st and st+1, alternating slots
-        uint32_t sb_cur[NP][2], sb_nxt[NP][2];
-        auto fetch_sb = [&](int st, uint32_t (*dst)[2]) {
-            const int Gm = min(st * STG_GROUPS + t, n64 - 1) >> gshift;
+
+        // activations of the first run (prefetched one run ahead from here on)
+        uint4 xn[NT][2];
+        float sxn[NT][2];
+        if (n_runs > 0) {
 #pragma unroll
-            for (int q = 0; q < NP; ++q)
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-                    dst[q][h] = (uint32_t)__ldg(sp[q][h] + Gm) | ((uint32_t)__ldg(bp[q][h] + Gm) << 16);
-        };
-        fetch_sb(0, sb_cur);
-        fetch_sb(1, sb_nxt);
+            for (int j = 0; j < NT; ++j) {
+                xn[j][0] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + G0 * 64));
+                xn[j][1] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + G0 * 64 + 8));
+                sxn[j][0] = __ldg(sxa[j] + G0);
+                sxn[j][1] = __ldg(sxb[j] + G0);
+            }
+        }
 
         for (int st = 0; st < n_stages; ++st) {
-            cp_async_wait<DEPTH - 2>();   // stage st has landed (this thread's copies)
-            __syncthreads();              // ... and everyone else's; stage st-1 is free again
+            cp_async_wait<DEPTH - 2>();   // this lane's copies of stage st have landed
+            __syncwarp();                 // ... and the other lanes'; the slot of stage st-1 is free again
             issue_stage(st + DEPTH - 1);
-            if (warp_active) {
-                const uint8_t* stage = smem + (st % DEPTH) * SL::STAGE;
-                const uint8_t* wst = stage + warp * NP * 16 * W_PITCH;
-                const uint8_t* xst = stage + SL::W_BYTES;
-                const float* sst = reinterpret_cast<const float*>(xst + SL::X_BYTES);
-                const int groups = min(STG_GROUPS, n64 - st * STG_GROUPS);
-                // scale / bias: lane (g, t) holds 64-run st*4+t of its two rows (shared by shuffle below);
-                // the values of the stage after next are fetched now, so the loads never stall the warp
-                uint32_t sbv[NP][2], sbn[NP][2];
-                fetch_sb(st + 2, sbn);
+            const uint8_t* stage = wsm + (st % DEPTH) * WS::STAGE;
 #pragma unroll
-                for (int q = 0; q < NP; ++q)
+            for (int Gi = 0; Gi < STG_RUNS; ++Gi) {
+                const int G = G0 + st * STG_RUNS + Gi;
+                if (G < G1) {
+                    // this run's activations; start fetching the next run's
+                    uint4 xc[NT][2];
+                    float sxc[NT][2];
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        sbv[q][h] = sb_cur[q][h];
-                        sb_cur[q][h] = sb_nxt[q][h];
-                        sb_nxt[q][h] = sbn[q][h];
+                    for (int j = 0; j < NT; ++j) {
+                        xc[j][0] = xn[j][0]; xc[j][1] = xn[j][1];
+                        sxc[j][0] = sxn[j][0]; sxc[j][1] = sxn[j][1];
                     }
-                float s_l[NP][2], b_l[NP][2];
+                    if (G + 1 < G1) {
 #pragma unroll
-                for (int q = 0; q < NP; ++q)
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        s_l[q][h] = __uint_as_float(sbv[q][h] << 16);
-                        b_l[q][h] = __uint_as_float(sbv[q][h] & 0xFFFF0000u);
+                        for (int j = 0; j < NT; ++j) {
+                            xn[j][0] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + (G + 1) * 64));
+                            xn[j][1] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + (G + 1) * 64 + 8));
+                            sxn[j][0] = __ldg(sxa[j] + G + 1);
+                            sxn[j][1] = __ldg(sxb[j] + G + 1);
+                        }
                     }
-                for (int Gi = 0; Gi < groups; ++Gi) {
-                    const int src_lane = (lane & ~3) | Gi;
+                    // scale and (bias - 128*scale) of the two rows this lane's results belong to
                     float sc[NP][2], bm[NP][2];
 #pragma unroll
                     for (int q = 0; q < NP; ++q)
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            const float s = __shfl_sync(0xFFFFFFFFu, s_l[q][h], src_lane);
-                            const float b = __shfl_sync(0xFFFFFFFFu, b_l[q][h], src_lane);
+                            const uint32_t v = *reinterpret_cast<const uint32_t*>(
+                                stage + WS::W_BYTES + q * (STG_RUNS * 64) + Gi * 64 + (g + 8 * h) * 4);
+                            const float s = __uint_as_float(v << 16), b = __uint_as_float(v & 0xFFFF0000u);
                             sc[q][h] = s;
                             bm[q][h] = fmaf(-128.0f, s, b);
                         }
@@ -244,20 +256,17 @@ grouped_mma_decode_kernel(const Params p) {
                     for (int q = 0; q < NP; ++q)
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            const uint2 wv = *reinterpret_cast<const uint2*>(wst + (q * 16 + g + 8 * h) * W_PITCH + Gi * 32 + t * 8);
+                            const uint2 wv = *reinterpret_cast<const uint2*>(stage + (q * 16 + g + 8 * h) * W_PITCH + Gi * 32 + t * 8);
                             unpack_word_128(wv.x, af[q][0][h]);
                             unpack_word_128(wv.y, af[q][1][h]);
                         }
 #pragma unroll
                     for (int j = 0; j < NT; ++j) {
-                        const uint8_t* xr = xst + (8 * j + g) * X_PITCH + Gi * 128 + t * 32;
-                        const uint4 x0 = *reinterpret_cast<const uint4*>(xr);
-                        const uint4 x1 = *reinterpret_cast<const uint4*>(xr + 16);
-                        const uint32_t xb[2][4] = {{x0.x, x0.y, x0.z, x0.w}, {x1.x, x1.y, x1.z, x1.w}};
-                        const float sx0 = sst[(8 * j + 2 * t) * 4 + Gi], sx1 = sst[(8 * j + 2 * t + 1) * 4 + Gi];
+                        const uint32_t xb[2][4] = {{xc[j][0].x, xc[j][0].y, xc[j][0].z, xc[j][0].w},
+                                                   {xc[j][1].x, xc[j][1].y, xc[j][1].z, xc[j][1].w}};
 #pragma unroll
                         for (int q = 0; q < NP; ++q) {
-                            float c[4] = {0.f, 0.f, 0.f, 0.f};
+                            float c[4];
 #pragma unroll
                             for (int w = 0; w < 2; ++w)
 #pragma unroll
@@ -265,12 +274,13 @@ grouped_mma_decode_kernel(const Params p) {
                                     // k-slots (2t,2t+1) <- pair 2hp, (2t+8,2t+9) <- pair 2hp+1 of word w
                                     const uint32_t a[4] = {af[q][w][0][2 * hp], af[q][w][1][2 * hp],
                                                            af[q][w][0][2 * hp + 1], af[q][w][1][2 * hp + 1]};
-                                    mma_bf16_16816(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
+                                    if (w == 0 && hp == 0) mma_bf16_16816_zero(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
+                                    else mma_bf16_16816(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
                                 }
-                            tot[j][q][0] = fmaf(sc[q][0], c[0], fmaf(bm[q][0], sx0, tot[j][q][0]));
-                            tot[j][q][1] = fmaf(sc[q][0], c[1], fmaf(bm[q][0], sx1, tot[j][q][1]));
-                            tot[j][q][2] = fmaf(sc[q][1], c[2], fmaf(bm[q][1], sx0, tot[j][q][2]));
-                            tot[j][q][3] = fmaf(sc[q][1], c[3], fmaf(bm[q][1], sx1, tot[j][q][3]));
+                            tot[j][q][0] = fmaf(sc[q][0], c[0], fmaf(bm[q][0], sxc[j][0], tot[j][q][0]));
+                            tot[j][q][1] = fmaf(sc[q][0], c[1], fmaf(bm[q][0], sxc[j][1], tot[j][q][1]));
+                            tot[j][q][2] = fmaf(sc[q][1], c[2], fmaf(bm[q][1], sxc[j][0], tot[j][q][2]));
+                            tot[j][q][3] = fmaf(sc[q][1], c[3], fmaf(bm[q][1], sxc[j][1], tot[j][q][3]));
                         }
                     }
                 }
@@ -278,8 +288,34 @@ grouped_mma_decode_kernel(const Params p) {
         }
         cp_async_wait<0>();
 
+        if (KSPLIT > 1) {
+            // fixed-order sum of the reduction slices: slices 1.. park their partials, slice 0 adds them in order
+            __syncthreads();  // every warp is out of its ring: reuse the start of shared memory
+            float* red = reinterpret_cast<float*>(smem);
+            constexpr int PER_WARP_VALS = NT * NP * 4 * 32;
+            if (ks > 0) {
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int q = 0; q < NP; ++q)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) red[warp * PER_WARP_VALS + ((j * NP + q) * 4 + i) * 32 + lane] = tot[j][q][i];
+            }
+            __syncthreads();
+            if (ks == 0) {
+                for (int o = 1; o < KSPLIT; ++o)
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+#pragma unroll
+                        for (int q = 0; q < NP; ++q)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) tot[j][q][i] += red[(warp + o) * PER_WARP_VALS + ((j * NP + q) * 4 + i) * 32 + lane];
+            }
+            __syncthreads();  // the next pass's copies may overwrite the parked partials
+        }
+
         // results: value i -> (row g + 8*(i>>1), activation row tok0 + 8j + 2t + (i&1))
-        if (warp_active) {
+        if (warp_active && ks == 0) {
 #pragma unroll
             for (int j = 0; j < NT; ++j)
 #pragma unroll
@@ -301,6 +337,25 @@ grouped_mma_decode_kernel(const Params p) {
                 }
         }
     }
+}
+
+// Scale and bias of a stacked projection repacked for the streaming kernels:
+//   out[((e * N/16 + rb) * K/64 + G) * 16 + r] = scale | bias << 16   of row rb*16 + r, 64-run G
+// so that the 16 rows of a block are contiguous per run and a warp's stage is one 128-byte copy.
+__global__ void repack_scale_bias_kernel(const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
+                                         uint32_t* __restrict__ out, int n_experts, int N, int K, int group_size) {
+    const size_t total = (size_t)n_experts * N * (K / 64);
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int r = (int)(i & 15);
+    const size_t rest = i >> 4;
+    const int n64 = K / 64;
+    const int G = (int)(rest % n64);
+    const size_t blk = rest / n64;  // e * N/16 + rb
+    const size_t row = blk * 16 + r;  // e * N + rb*16 + r
+    const int gpr = K / group_size;
+    const size_t src = row * gpr + (size_t)(G * 64 / group_size);
+    out[i] = (uint32_t)scales[src] | ((uint32_t)biases[src] << 16);
 }
 
 // Gather rows into expert-sorted order with the 8-run permutation, and write the sum of every

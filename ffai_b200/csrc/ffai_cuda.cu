@@ -53,6 +53,7 @@ struct ffai_moe_layer {
     int opt_path = 0;                // 0 auto, 1 CUDA-core GEMV, 2 tcgen05 grouped GEMM, 3 register-streaming decode
     int opt_tc_min_rows = 0;         // auto: smallest T*k routed through the tensor-core path
     int opt_debug = 0;               // timing experiments (see g100::Params::debug_flags)
+    int opt_ksplit = 0;              // streaming kernels: 0 automatic, else 1, 2 or 4 reduction slices
     long long* timeline = nullptr;   // device buffer for the gate/up kernel's CTA-0 timeline (option "timeline")
     uint16_t* xg = nullptr;          // [M,H]  expert-contiguous input rows (8-run permuted)
     uint16_t* inner_bf = nullptr;    // [M,I]  activation output (8-run permuted)
@@ -60,6 +61,9 @@ struct ffai_moe_layer {
     float* xsum = nullptr;           // [M, H/64]  64-run sums of xg rows
     float* inner_sum = nullptr;      // [M, I/64]  64-run sums of inner rows
     bool mma_ok = false;             // register-streaming decode kernels usable (4-bit, group 64/128)
+    uint32_t* sb_gate = nullptr;     // repacked (scale | bias << 16) words of the expert projections
+    uint32_t* sb_up = nullptr;
+    uint32_t* sb_down = nullptr;
     uint32_t* tile_offsets = nullptr;    // [E+1]
     uint16_t* sh_x = nullptr;        // [T,H]  shared expert input (8-run permuted)
     uint16_t* sh_inner_bf = nullptr; // [T,Is]
@@ -285,16 +289,32 @@ int launch_plan(const uint32_t* indices, int n_rows, int E, uint32_t* counts, ui
     return cudaGetLastError() == cudaSuccess ? 3 : -1;
 }
 
-template <bool FUSED, int NT>
-void launch_mma_decode(const dmma::Params& p, dim3 grid, cudaStream_t st) {
-    using SL = dmma::StageLayout<FUSED, NT>;
-    auto k = dmma::grouped_mma_decode_kernel<FUSED, NT>;
+template <bool FUSED, int NT, int KSPLIT>
+void launch_mma_decode_k(const dmma::Params& p, int n_experts, cudaStream_t st) {
+    using WS = dmma::WarpStage<FUSED>;
+    auto k = dmma::grouped_mma_decode_kernel<FUSED, NT, KSPLIT>;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::TOTAL);
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, WS::TOTAL);
         attr_set = true;
     }
-    k<<<grid, 128, SL::TOTAL, st>>>(p);
+    const int rbw = 4 / KSPLIT;
+    dim3 grid((p.N / 16 + rbw - 1) / rbw, n_experts);
+    k<<<grid, 128, WS::TOTAL, st>>>(p);
+}
+
+// nt: 8-row activation tiles per pass (1 or 2); ksplit: slices of the reduction axis per 16-row block (1, 2, 4)
+template <bool FUSED>
+void launch_mma_decode(const dmma::Params& p, int n_experts, int nt, int ksplit, cudaStream_t st) {
+    if (nt == 2) {
+        if (ksplit == 4) launch_mma_decode_k<FUSED, 2, 4>(p, n_experts, st);
+        else if (ksplit == 2) launch_mma_decode_k<FUSED, 2, 2>(p, n_experts, st);
+        else launch_mma_decode_k<FUSED, 2, 1>(p, n_experts, st);
+    } else {
+        if (ksplit == 4) launch_mma_decode_k<FUSED, 1, 4>(p, n_experts, st);
+        else if (ksplit == 2) launch_mma_decode_k<FUSED, 1, 2>(p, n_experts, st);
+        else launch_mma_decode_k<FUSED, 1, 1>(p, n_experts, st);
+    }
 }
 
 // dense [1,H] projection per token (shared-expert gate stored as f32 / bf16)
@@ -531,6 +551,24 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
         if (!ok) return fail(L, FFAI_ERR_CUDA, "cuTensorMapEncodeTiled failed");
         L->tc_ok = true;
     }
+    // scale/bias words repacked for the streaming decode kernels (owned copies, freed with the weights)
+    L->sb_gate = L->sb_up = L->sb_down = nullptr;
+    if (L->mma_ok) {
+        auto repack = [&](const ffai_qproj& q, int N, int K, uint32_t** out) -> int {
+            const size_t total = (size_t)El * N * (K / 64);
+            void* p = nullptr;
+            CUDA_TRY(L, cudaMalloc(&p, total * 4));
+            L->owned_weights.push_back(p);
+            *out = static_cast<uint32_t*>(p);
+            dmma::repack_scale_bias_kernel<<<(unsigned)((total + 255) / 256), 256>>>(q.scales, q.biases, *out, El, N, K, c.expert_group_size);
+            CUDA_TRY(L, cudaGetLastError());
+            return FFAI_OK;
+        };
+        if ((rc = repack(L->w.gate_proj, c.intermediate, c.hidden, &L->sb_gate))) return rc;
+        if ((rc = repack(L->w.up_proj, c.intermediate, c.hidden, &L->sb_up))) return rc;
+        if ((rc = repack(L->w.down_proj, c.hidden, c.intermediate, &L->sb_down))) return rc;
+        CUDA_TRY(L, cudaDeviceSynchronize());
+    }
     L->weights_set = true;
     return FFAI_OK;
 }
@@ -566,6 +604,11 @@ extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name,
     if (!strcmp(name, "tc_min_rows")) {
         if (value < 0) return fail(L, FFAI_ERR_INVALID_ARG, "option tc_min_rows must be >= 0");
         L->opt_tc_min_rows = value;
+        return FFAI_OK;
+    }
+    if (!strcmp(name, "ksplit")) {
+        if (value != 0 && value != 1 && value != 2 && value != 4) return fail(L, FFAI_ERR_INVALID_ARG, "option ksplit must be 0, 1, 2 or 4");
+        L->opt_ksplit = value;
         return FFAI_OK;
     }
     if (!strcmp(name, "debug")) {
@@ -740,17 +783,16 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         p.group_size = c.expert_group_size;
         p.offsets = L->offsets;
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
-        const bool wide = rows_per_expert > 4.0;  // 16 activation rows per pass instead of 8
+        const int nt = rows_per_expert > 4.0 ? 2 : 1;  // 16 activation rows per pass instead of 8
+        // few routed rows -> few active experts -> slice the reduction axis to keep every SM busy
+        const int ksplit = L->opt_ksplit > 0 ? L->opt_ksplit : (M <= 8 ? 4 : (M <= 24 ? 2 : 1));
 
         stage_begin(L, ST_GATE_UP, st);
         p.w1 = L->w.gate_proj.weight; p.s1 = L->w.gate_proj.scales; p.b1 = L->w.gate_proj.biases; p.rb1 = L->w.gate_proj.row_bias;
         p.w2 = L->w.up_proj.weight; p.s2 = L->w.up_proj.scales; p.b2 = L->w.up_proj.biases; p.rb2 = L->w.up_proj.row_bias;
+        p.sb1 = L->sb_gate; p.sb2 = L->sb_up;
         p.N = I; p.K = H; p.x = L->xg; p.xsum = L->xsum; p.xsum_pitch = xp_h; p.out = L->inner_bf;
-        {
-            dim3 grid((I + 63) / 64, E);
-            if (wide) launch_mma_decode<true, 2>(p, grid, st);
-            else launch_mma_decode<true, 1>(p, grid, st);
-        }
+        launch_mma_decode<true>(p, E, nt, ksplit, st);
         sum64_rows_kernel<<<(M + 7) / 8, 256, 0, st>>>(L->inner_bf, L->inner_sum, M, I, xp_i);
         L->launches += 2;
         stage_end(L, ST_GATE_UP, st);
@@ -758,12 +800,9 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         stage_begin(L, ST_DOWN, st);
         p.w1 = L->w.down_proj.weight; p.s1 = L->w.down_proj.scales; p.b1 = L->w.down_proj.biases; p.rb1 = L->w.down_proj.row_bias;
         p.w2 = nullptr; p.s2 = nullptr; p.b2 = nullptr; p.rb2 = nullptr;
+        p.sb1 = L->sb_down; p.sb2 = nullptr;
         p.N = H; p.K = I; p.x = L->inner_bf; p.xsum = L->inner_sum; p.xsum_pitch = xp_i; p.out = L->y;
-        {
-            dim3 grid((H + 63) / 64, E);
-            if (wide) launch_mma_decode<false, 2>(p, grid, st);
-            else launch_mma_decode<false, 1>(p, grid, st);
-        }
+        launch_mma_decode<false>(p, E, nt, ksplit, st);
         L->launches += 1;
         stage_end(L, ST_DOWN, st);
         if (cudaGetLastError() != cudaSuccess) return fail(L, FFAI_ERR_CUDA, "decode kernels launch failed");
