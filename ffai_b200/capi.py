@@ -157,6 +157,7 @@ SIGNATURES = {
     "ffai_op_moe_router_topk": (C.c_int, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
     "ffai_op_moe_plan_workspace_bytes": (C.c_size_t, [_I, _I]),
     "ffai_op_moe_plan": (C.c_int, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "ffai_op_moe_plan_static": (C.c_int, [_P, _I, _I, _I, _P, _P, _P, _P, _P]),
     "ffai_op_gather_rows": (C.c_int, [_P, _P, _P, _I, _I, _P]),
     "ffai_op_moe_gather_dequant_gemm": (C.c_int, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "ffai_op_glu_activation": (C.c_int, [_P, _P, _P, C.c_int64, _I, C.c_float, C.c_float, _P]),

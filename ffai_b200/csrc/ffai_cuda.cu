@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -1090,6 +1091,48 @@ extern "C" FFAI_API int ffai_op_moe_plan(const uint32_t* indices, int32_t T, int
     if ((rc = need_device())) return rc;
     return launch_plan(indices, T * k, E, counts, offsets, perm, inv_perm, (uint32_t*)workspace,
                        (cudaStream_t)stream) < 0 ? FFAI_ERR_CUDA : FFAI_OK;
+}
+
+// ── plan without allocation ──
+// Per-block histograms of the three-pass plan, resident in the library's device image.  In host
+// code this name is only a handle for cudaGetSymbolAddress; kernels get the looked-up address.
+static __device__ __align__(256) uint32_t g_plan_static_hist[(FFAI_PLAN_STATIC_MAX_ROWS / PLAN_ENTRIES_PER_WARP) * FFAI_MAX_EXPERTS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+uint32_t* g_plan_static_ptr[kMaxDevices] = {};
+std::mutex g_plan_static_mutex;
+
+// Address of the array on the current device, looked up once per device.
+int plan_static_scratch(uint32_t** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FFAI_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_plan_static_mutex);
+    if (!g_plan_static_ptr[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_plan_static_hist) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return FFAI_ERR_CUDA;
+        }
+        g_plan_static_ptr[dev] = static_cast<uint32_t*>(p);
+    }
+    *out = g_plan_static_ptr[dev];
+    return FFAI_OK;
+}
+}  // namespace
+
+extern "C" FFAI_API int ffai_op_moe_plan_static(const uint32_t* indices, int32_t T, int32_t k, int32_t E,
+                                                uint32_t* counts, uint32_t* offsets, uint32_t* perm,
+                                                uint32_t* inv_perm, void* stream) {
+    if (!indices || !counts || !offsets || !perm || !inv_perm || T <= 0 || k <= 0) return FFAI_ERR_INVALID_ARG;
+    if (E <= 0 || E > FFAI_MAX_EXPERTS) return FFAI_ERR_INVALID_ARG;
+    if ((int64_t)T * k > FFAI_PLAN_STATIC_MAX_ROWS) return FFAI_ERR_INVALID_ARG;
+    int rc;
+    if ((rc = need_device())) return rc;
+    uint32_t* scratch = nullptr;
+    if ((rc = plan_static_scratch(&scratch))) return rc;
+    return launch_plan(indices, T * k, E, counts, offsets, perm, inv_perm, scratch, (cudaStream_t)stream) < 0
+               ? FFAI_ERR_CUDA : FFAI_OK;
 }
 
 extern "C" FFAI_API int ffai_op_gather_rows(const uint16_t* table, const uint32_t* ids, uint16_t* out,

@@ -283,6 +283,27 @@ FFAI_API int ffai_op_moe_plan(const uint32_t* indices, int32_t n_tokens, int32_t
                      int32_t n_experts, uint32_t* counts, uint32_t* offsets,
                      uint32_t* perm, uint32_t* inv_perm, void* workspace, void* stream);
 
+/* Dispatch plan for callers that must not allocate.  No counterpart in the reference.
+ *
+ * Same inputs, outputs and results as ffai_op_moe_plan, but the caller passes no workspace and the
+ * call never touches the CUDA allocator (no cudaMalloc / cudaFree, no allocating library routine):
+ * the per-block histograms live in a fixed array inside the library's device image
+ * (FFAI_PLAN_STATIC_MAX_ROWS / 1024 blocks x FFAI_MAX_EXPERTS counters = 512 KiB, held by every GPU
+ * that loads the library until the process exits).  It is meant for hosts that own all device
+ * memory themselves and forbid a plug-in to allocate once serving has started - an inference
+ * server with a pre-sized arena, or code running where an allocator call would block or fail.
+ *
+ * Limits: n_tokens * k <= FFAI_PLAN_STATIC_MAX_ROWS and n_experts <= FFAI_MAX_EXPERTS, otherwise
+ * FFAI_ERR_INVALID_ARG.  The first call on each device looks up the address of the array (with that
+ * device current); make that first call before starting any stream capture.  All calls on a
+ * device share the one array, which keeps the previous call's contents: every counter a call reads
+ * is rewritten by that call first, so nothing needs clearing, but two calls that overlap on the
+ * GPU (different streams) race on it - serialise them. */
+#define FFAI_PLAN_STATIC_MAX_ROWS 131072
+FFAI_API int ffai_op_moe_plan_static(const uint32_t* indices, int32_t n_tokens, int32_t k,
+                                     int32_t n_experts, uint32_t* counts, uint32_t* offsets,
+                                     uint32_t* perm, uint32_t* inv_perm, void* stream);
+
 /* Ops.gather — Ops.swift:308-346: out[m,:] = table[ids[m],:], bf16 rows. */
 FFAI_API int ffai_op_gather_rows(const uint16_t* table, const uint32_t* ids, uint16_t* out,
                         int32_t n_rows, int32_t row_len, void* stream);
