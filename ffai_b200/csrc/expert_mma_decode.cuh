@@ -60,11 +60,19 @@ FFAI_DEVINL void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32
 }
 
 // One packed word -> 4 bf16 pairs (128+n0,128+n4), (128+n1,128+n5), (128+n2,128+n6), (128+n3,128+n7).
+// The three right shifts are written as high halves of 32x32 multiplies (w >> s == mulhi(w, 2^(32-s))):
+// integer multiplies issue on the FMA pipe, which is nearly idle here, while shifts and logic ops
+// share the half-rate ALU pipe that bounds this kernel.
+FFAI_DEVINL uint32_t shr_mul(uint32_t w, uint32_t pow2) {
+    uint32_t r;
+    asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(w), "r"(pow2));
+    return r;
+}
 FFAI_DEVINL void unpack_word_128(uint32_t w, uint32_t* o) {
     o[0] = (w & 0x000F000Fu) | 0x43004300u;
-    o[1] = ((w >> 4) & 0x000F000Fu) | 0x43004300u;
-    o[2] = ((w >> 8) & 0x000F000Fu) | 0x43004300u;
-    o[3] = ((w >> 12) & 0x000F000Fu) | 0x43004300u;
+    o[1] = (shr_mul(w, 1u << 28) & 0x000F000Fu) | 0x43004300u;
+    o[2] = (shr_mul(w, 1u << 24) & 0x000F000Fu) | 0x43004300u;
+    o[3] = (shr_mul(w, 1u << 20) & 0x000F000Fu) | 0x43004300u;
 }
 
 FFAI_DEVINL uint2 ld_stream_u2(const uint32_t* p) {
@@ -118,7 +126,7 @@ struct WarpStage {
 // 128 k in flight) and synchronises with nobody until the final reduction.
 // NT: activation rows handled per pass over the weights, in units of 8.
 template <bool FUSED, int NT, int KSPLIT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 grouped_mma_decode_kernel(const Params p) {
     using WS = WarpStage<FUSED>;
     constexpr int NP = WS::NP;
@@ -199,18 +207,20 @@ grouped_mma_decode_kernel(const Params p) {
 #pragma unroll
         for (int st = 0; st < DEPTH - 1; ++st) issue_stage(st);
 
-        // activations of the first run (prefetched one run ahead from here on)
-        uint4 xn[NT][2];
-        float sxn[NT][2];
-        if (n_runs > 0) {
+        // activations, fetched one run ahead into two alternating register sets (run parity within a
+        // stage is a compile-time index, so nothing is copied between them)
+        uint4 xbuf[STG_RUNS][NT][2];
+        float sxbuf[STG_RUNS][NT][2];
+        auto fetch_x = [&](int G, uint4 (*xd)[2], float (*sd)[2]) {
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                xn[j][0] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + G0 * 64));
-                xn[j][1] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + G0 * 64 + 8));
-                sxn[j][0] = __ldg(sxa[j] + G0);
-                sxn[j][1] = __ldg(sxb[j] + G0);
+                xd[j][0] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + G * 64));
+                xd[j][1] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + G * 64 + 8));
+                sd[j][0] = __ldg(sxa[j] + G);
+                sd[j][1] = __ldg(sxb[j] + G);
             }
-        }
+        };
+        if (n_runs > 0) fetch_x(G0, xbuf[0], sxbuf[0]);
 
         for (int st = 0; st < n_stages; ++st) {
             cp_async_wait<DEPTH - 2>();   // this lane's copies of stage st have landed
@@ -221,23 +231,10 @@ grouped_mma_decode_kernel(const Params p) {
             for (int Gi = 0; Gi < STG_RUNS; ++Gi) {
                 const int G = G0 + st * STG_RUNS + Gi;
                 if (G < G1) {
-                    // this run's activations; start fetching the next run's
-                    uint4 xc[NT][2];
-                    float sxc[NT][2];
-#pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        xc[j][0] = xn[j][0]; xc[j][1] = xn[j][1];
-                        sxc[j][0] = sxn[j][0]; sxc[j][1] = sxn[j][1];
-                    }
-                    if (G + 1 < G1) {
-#pragma unroll
-                        for (int j = 0; j < NT; ++j) {
-                            xn[j][0] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + (G + 1) * 64));
-                            xn[j][1] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + (G + 1) * 64 + 8));
-                            sxn[j][0] = __ldg(sxa[j] + G + 1);
-                            sxn[j][1] = __ldg(sxb[j] + G + 1);
-                        }
-                    }
+                    // this run's activations are in set Gi; start fetching the next run's into the other set
+                    uint4 (*xc)[2] = xbuf[Gi];
+                    float (*sxc)[2] = sxbuf[Gi];
+                    if (G + 1 < G1) fetch_x(G + 1, xbuf[(Gi + 1) % STG_RUNS], sxbuf[(Gi + 1) % STG_RUNS]);
                     // scale and (bias - 128*scale) of the two rows this lane's results belong to
                     float sc[NP][2], bm[NP][2];
 #pragma unroll

@@ -36,14 +36,22 @@ FFAI_DEVINL float router_chunk_dot(const RouterParams& p, const uint16_t* __rest
     if (KIND == 1) {
         const float* w = (const float*)p.weight + (size_t)e * H;
         if (k1 - k0 == 64) {
+            // all loads of the chunk first, then the dependent chain: one memory latency per chunk, not eight
+            uint4 xv[8];
+            float4 wv[16];
 #pragma unroll
-            for (int j = 0; j < 64; j += 8) {
-                uint4 xv = *(const uint4*)(xrow + k0 + j);
-                float4 w0 = *(const float4*)(w + k0 + j), w1 = *(const float4*)(w + k0 + j + 4);
-                acc = __fmaf_rn(bf16lo(xv.x), w0.x, acc); acc = __fmaf_rn(bf16hi(xv.x), w0.y, acc);
-                acc = __fmaf_rn(bf16lo(xv.y), w0.z, acc); acc = __fmaf_rn(bf16hi(xv.y), w0.w, acc);
-                acc = __fmaf_rn(bf16lo(xv.z), w1.x, acc); acc = __fmaf_rn(bf16hi(xv.z), w1.y, acc);
-                acc = __fmaf_rn(bf16lo(xv.w), w1.z, acc); acc = __fmaf_rn(bf16hi(xv.w), w1.w, acc);
+            for (int j = 0; j < 8; ++j) {
+                xv[j] = *(const uint4*)(xrow + k0 + 8 * j);
+                wv[2 * j] = *(const float4*)(w + k0 + 8 * j);
+                wv[2 * j + 1] = *(const float4*)(w + k0 + 8 * j + 4);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 w0 = wv[2 * j], w1 = wv[2 * j + 1];
+                acc = __fmaf_rn(bf16lo(xv[j].x), w0.x, acc); acc = __fmaf_rn(bf16hi(xv[j].x), w0.y, acc);
+                acc = __fmaf_rn(bf16lo(xv[j].y), w0.z, acc); acc = __fmaf_rn(bf16hi(xv[j].y), w0.w, acc);
+                acc = __fmaf_rn(bf16lo(xv[j].z), w1.x, acc); acc = __fmaf_rn(bf16hi(xv[j].z), w1.y, acc);
+                acc = __fmaf_rn(bf16lo(xv[j].w), w1.z, acc); acc = __fmaf_rn(bf16hi(xv[j].w), w1.w, acc);
             }
         } else {
             for (int k = k0; k < k1; ++k) acc = __fmaf_rn(bf16_bits_to_f32(xrow[k]), w[k], acc);
@@ -51,14 +59,18 @@ FFAI_DEVINL float router_chunk_dot(const RouterParams& p, const uint16_t* __rest
     } else if (KIND == 2) {
         const uint16_t* w = (const uint16_t*)p.weight + (size_t)e * H;
         if (k1 - k0 == 64) {
+            uint4 xv[8], wv[8];
 #pragma unroll
-            for (int j = 0; j < 64; j += 8) {
-                uint4 xv = *(const uint4*)(xrow + k0 + j);
-                uint4 wv = *(const uint4*)(w + k0 + j);
-                acc = __fmaf_rn(bf16lo(xv.x), bf16lo(wv.x), acc); acc = __fmaf_rn(bf16hi(xv.x), bf16hi(wv.x), acc);
-                acc = __fmaf_rn(bf16lo(xv.y), bf16lo(wv.y), acc); acc = __fmaf_rn(bf16hi(xv.y), bf16hi(wv.y), acc);
-                acc = __fmaf_rn(bf16lo(xv.z), bf16lo(wv.z), acc); acc = __fmaf_rn(bf16hi(xv.z), bf16hi(wv.z), acc);
-                acc = __fmaf_rn(bf16lo(xv.w), bf16lo(wv.w), acc); acc = __fmaf_rn(bf16hi(xv.w), bf16hi(wv.w), acc);
+            for (int j = 0; j < 8; ++j) {
+                xv[j] = *(const uint4*)(xrow + k0 + 8 * j);
+                wv[j] = *(const uint4*)(w + k0 + 8 * j);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                acc = __fmaf_rn(bf16lo(xv[j].x), bf16lo(wv[j].x), acc); acc = __fmaf_rn(bf16hi(xv[j].x), bf16hi(wv[j].x), acc);
+                acc = __fmaf_rn(bf16lo(xv[j].y), bf16lo(wv[j].y), acc); acc = __fmaf_rn(bf16hi(xv[j].y), bf16hi(wv[j].y), acc);
+                acc = __fmaf_rn(bf16lo(xv[j].z), bf16lo(wv[j].z), acc); acc = __fmaf_rn(bf16hi(xv[j].z), bf16hi(wv[j].z), acc);
+                acc = __fmaf_rn(bf16lo(xv[j].w), bf16lo(wv[j].w), acc); acc = __fmaf_rn(bf16hi(xv[j].w), bf16hi(wv[j].w), acc);
             }
         } else {
             for (int k = k0; k < k1; ++k)
