@@ -73,7 +73,8 @@ FFAI_DEVINL float warp_sum(float v) {
     return v;
 }
 
-// Expert activation on one (gate, up) pair; fp32 math.
+// Expert activation on one (gate, up) pair; fp32 math with the fast exponential and reciprocal
+// (a few ulp; the epilogue that calls this shares issue slots with the dequant warps).
 //   0 SwiGLU          silu(g)*u                      (FFAI Ops.swift:6400-6452)
 //   1 clamped SwiGLU  GPT-OSS host loop              (FFAI GPTOSSText.swift:1421-1431)
 //   2 GELU-GLU        tanh-approximate gelu(g)*u     (FFAI OpsFused.swift:55-87)
@@ -81,14 +82,14 @@ FFAI_DEVINL float glu_activation(float g, float u, int activation, float limit, 
     if (activation == 1) {
         g = fminf(g, limit);
         u = fminf(fmaxf(u, -limit), limit);
-        float glu = g / (1.0f + __expf(-alpha * g));
+        float glu = __fdividef(g, 1.0f + __expf(-alpha * g));
         return glu * (u + 1.0f);
     }
     if (activation == 2) {
         float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
         return 0.5f * g * (1.0f + tanhf(inner)) * u;
     }
-    float silu = g / (1.0f + __expf(-g));
+    float silu = __fdividef(g, 1.0f + __expf(-g));
     return silu * u;
 }
 

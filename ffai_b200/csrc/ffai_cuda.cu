@@ -42,6 +42,9 @@ struct ffai_moe_layer {
     uint32_t* perm = nullptr;       // [M]
     uint32_t* inv_perm = nullptr;   // [M]
     uint32_t* block_hist = nullptr; // [nblocks,E]
+    float* router_partials = nullptr;  // [H/64][T][E] chunk sums of the split batched router (when it fits 64 MiB)
+    size_t router_partials_cap = 0;    // in floats
+    uint32_t* tickets = nullptr;    // [min(T,96)] per-token arrival counters of the small-batch router (self-resetting)
     float* inner = nullptr;         // [M,I]
     float* y = nullptr;             // [M,H]
     float* sh_inner = nullptr;      // [T,Is]
@@ -71,7 +74,7 @@ struct ffai_moe_layer {
     uint32_t* sh_sched = nullptr;    // offsets[2] + tile_offsets[2]
     uint32_t* error_word = nullptr;
     CUtensorMap tm_gate{}, tm_up{}, tm_down{}, tm_sh_gate{}, tm_sh_up{}, tm_sh_down{};
-    CUtensorMap tm_xg[2]{}, tm_inner[2]{}, tm_sh_x[2]{}, tm_sh_inner[2]{};  // [0]: 16-row box, [1]: 128-row box
+    CUtensorMap tm_xg{}, tm_inner{}, tm_sh_x{}, tm_sh_inner{};  // activation maps: 64 k x 128-row boxes
 
     // host-buffer entry point
     cudaStream_t own_stream = nullptr;
@@ -247,22 +250,64 @@ int launch_router_kind(const RouterParams& p, const uint16_t* x, int T, uint32_t
     return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
 }
 
-// Many tokens: tiled projection, then one warp per token routes.  Returns launches or -1.
+template <int KIND, int BITS>
+void launch_router_tiled(const RouterParams& p, const uint16_t* x, int T, float* logits, float* partials, int n_sms,
+                         cudaStream_t st) {
+    const int eb = (p.n_experts + 63) / 64;
+    const unsigned z = partials ? p.hidden / 64 : 1;
+    // smallest token tile whose grid still gives every SM a block
+    if (((T + 63) / 64) * eb * (int)z >= n_sms) {
+        router_logits_tiled_kernel<KIND, BITS, 64><<<dim3((T + 63) / 64, eb, z), 256, 0, st>>>(p, x, T, logits, partials);
+    } else if (((T + 31) / 32) * eb * (int)z >= n_sms) {
+        router_logits_tiled_kernel<KIND, BITS, 32><<<dim3((T + 31) / 32, eb, z), 128, 0, st>>>(p, x, T, logits, partials);
+    } else {
+        router_logits_tiled_kernel<KIND, BITS, 16><<<dim3((T + 15) / 16, eb, z), 64, 0, st>>>(p, x, T, logits, partials);
+    }
+}
+
+// Many tokens: tiled projection, then one warp per token routes.  When the un-split grid would leave SMs
+// idle and the chunk-sum buffer is available, the hidden axis is split over blockIdx.z (one 64-wide chunk
+// per block) and the chunk sums are added in order by the routing kernel.  Returns launches or -1.
 int launch_router_batched(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w,
-                          float* logits, cudaStream_t st) {
-    dim3 grid((T + 63) / 64, (p.n_experts + 63) / 64);
+                          float* logits, float* partials, size_t partials_capacity, int n_sms, cudaStream_t st) {
+    const int n_chunks = p.hidden / 64;
+    const bool few_blocks = ((T + 63) / 64) * ((p.n_experts + 63) / 64) < 4 * n_sms;
+    if (!(partials && few_blocks && (size_t)T * p.n_experts * n_chunks <= partials_capacity)) partials = nullptr;
     switch (p.kind) {
-        case FFAI_LINEAR_F32: router_logits_tiled_kernel<1, 4><<<grid, 256, 0, st>>>(p, x, T, logits); break;
-        case FFAI_LINEAR_BF16: router_logits_tiled_kernel<2, 4><<<grid, 256, 0, st>>>(p, x, T, logits); break;
+        case FFAI_LINEAR_F32: launch_router_tiled<1, 4>(p, x, T, logits, partials, n_sms, st); break;
+        case FFAI_LINEAR_BF16: launch_router_tiled<2, 4>(p, x, T, logits, partials, n_sms, st); break;
         case FFAI_LINEAR_AFFINE:
-            BITS_SWITCH(p.bits, (router_logits_tiled_kernel<3, B><<<grid, 256, 0, st>>>(p, x, T, logits)));
+            BITS_SWITCH(p.bits, (launch_router_tiled<3, B>(p, x, T, logits, partials, n_sms, st)));
             break;
         default: return -1;
     }
     const int warps = 4;
-    route_only_kernel<<<(T + warps - 1) / warps, warps * 32, (size_t)warps * 2 * p.n_experts * sizeof(float), st>>>(
-        p, logits, T, idx, w);
+    const size_t smem = (size_t)warps * 2 * p.n_experts * sizeof(float);
+    if (partials)
+        route_from_partials_kernel<<<(T + warps - 1) / warps, warps * 32, smem, st>>>(p, partials, n_chunks, T, idx, w, logits);
+    else
+        route_only_kernel<<<(T + warps - 1) / warps, warps * 32, smem, st>>>(p, logits, T, idx, w);
     return cudaGetLastError() == cudaSuccess ? 2 : -1;
+}
+
+// Few tokens, dense router weights: staged rows + last-block routing.  Returns 0, or -1 when the
+// shape does not fit (the caller then uses router_token_kernel).
+template <int KIND>
+int launch_router_rows(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w, float* logits,
+                       uint32_t* tickets, cudaStream_t st) {
+    const int wbytes = KIND == 1 ? 4 : 2;
+    const size_t smem = (size_t)ROUTER_ROWS * p.hidden * wbytes + (size_t)p.hidden * 2 +
+                        (size_t)ROUTER_ROWS * (p.hidden / 64) * 4 + 2 * (size_t)p.n_experts * 4;
+    if (smem > 200 * 1024 || p.hidden % 64) return -1;
+    auto k = router_rows_kernel<KIND>;
+    static size_t attr = 0;
+    if (smem > 48 * 1024 && smem > attr) {
+        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
+        attr = smem;
+    }
+    dim3 grid((p.n_experts + ROUTER_ROWS - 1) / ROUTER_ROWS, T);
+    k<<<grid, 256, smem, st>>>(p, x, T, idx, w, logits, tickets);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 int launch_router(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w,
@@ -444,6 +489,12 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
     if ((rc = ws_alloc(L, &L->perm, M))) return rc;
     if ((rc = ws_alloc(L, &L->inv_perm, M))) return rc;
     if ((rc = ws_alloc(L, &L->block_hist, (size_t)plan_num_blocks((int)M) * E))) return rc;
+    if (T >= 96 && T * E * (H / 64) * sizeof(float) <= (size_t)64 << 20) {
+        L->router_partials_cap = T * E * (H / 64);
+        if ((rc = ws_alloc(L, &L->router_partials, L->router_partials_cap))) return rc;
+    }
+    if ((rc = ws_alloc(L, &L->tickets, 96))) return rc;
+    CUDA_TRY(L, cudaMemset(L->tickets, 0, 96 * sizeof(uint32_t)));
     if ((rc = ws_alloc(L, &L->inner, M * I))) return rc;
     if ((rc = ws_alloc(L, &L->y, M * H))) return rc;
     if (c.shared_intermediate > 0) {
@@ -525,7 +576,6 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
     L->tc_ok = false;
     if (L->tile_offsets) {
         using namespace g100;
-        const uint32_t boxes[2] = {16, 128};
         uint64_t Mcap = (uint64_t)c.max_tokens * c.top_k, Tcap = (uint64_t)c.max_tokens;
         if (Mcap < 128) Mcap = 128;
         if (Tcap < 128) Tcap = 128;
@@ -534,20 +584,16 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
             ok = ok && make_weight_map(&L->tm_gate, L->w.gate_proj.weight, (uint64_t)El * c.intermediate, c.hidden / 8);
             ok = ok && make_weight_map(&L->tm_up, L->w.up_proj.weight, (uint64_t)El * c.intermediate, c.hidden / 8);
             ok = ok && make_weight_map(&L->tm_down, L->w.down_proj.weight, (uint64_t)El * c.hidden, c.intermediate / 8);
-            for (int i = 0; i < 2; ++i) {
-                ok = ok && make_act_map(&L->tm_xg[i], L->xg, Mcap, c.hidden, boxes[i]);
-                ok = ok && make_act_map(&L->tm_inner[i], L->inner_bf, Mcap, c.intermediate, boxes[i]);
-            }
+            ok = ok && make_act_map(&L->tm_xg, L->xg, Mcap, c.hidden, BM);
+            ok = ok && make_act_map(&L->tm_inner, L->inner_bf, Mcap, c.intermediate, BM);
         }
         if (L->sh_x) {
             const int Is = c.shared_intermediate;
             ok = ok && make_weight_map(&L->tm_sh_gate, L->w.shared_gate_proj.weight, Is, c.hidden / 8);
             ok = ok && make_weight_map(&L->tm_sh_up, L->w.shared_up_proj.weight, Is, c.hidden / 8);
             ok = ok && make_weight_map(&L->tm_sh_down, L->w.shared_down_proj.weight, c.hidden, Is / 8);
-            for (int i = 0; i < 2; ++i) {
-                ok = ok && make_act_map(&L->tm_sh_x[i], L->sh_x, Tcap, c.hidden, boxes[i]);
-                ok = ok && make_act_map(&L->tm_sh_inner[i], L->sh_inner_bf, Tcap, Is, boxes[i]);
-            }
+            ok = ok && make_act_map(&L->tm_sh_x, L->sh_x, Tcap, c.hidden, BM);
+            ok = ok && make_act_map(&L->tm_sh_inner, L->sh_inner_bf, Tcap, Is, BM);
         }
         if (!ok) return fail(L, FFAI_ERR_CUDA, "cuTensorMapEncodeTiled failed");
         L->tc_ok = true;
@@ -737,9 +783,13 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     stage_begin(L, ST_ROUTER, st);
     RouterParams rp = router_params(L);
     if (T >= 96) {
-        int nr = launch_router_batched(rp, x, T, L->indices, L->rweights, L->logits, st);
+        int nr = launch_router_batched(rp, x, T, L->indices, L->rweights, L->logits, L->router_partials,
+                                       L->router_partials_cap, L->n_sms, st);
         if (nr < 0) return fail(L, FFAI_ERR_CUDA, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += nr;
+    } else if ((rp.kind == FFAI_LINEAR_F32 && launch_router_rows<1>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, st) == 0) ||
+               (rp.kind == FFAI_LINEAR_BF16 && launch_router_rows<2>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, st) == 0)) {
+        L->launches += 1;
     } else {
         if ((rc = launch_router(rp, x, T, L->indices, L->rweights, L->logits, st)))
             return fail(L, rc, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -769,8 +819,6 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         if (!mma_experts && !tc_experts && L->mma_ok && rows_per_expert <= 48.0) mma_experts = true;
     }
     const bool tc_shared = L->tc_ok && L->sh_x && L->opt_path != 1 && L->opt_path != 3 && (L->opt_path == 2 || T >= 16);
-    // token-tile width of the tcgen05 path: narrow tiles when experts see few rows each
-    const int tix = rows_per_expert * 1.5 <= 16.0 ? 0 : 1;
 
     if (mma_experts) {
         using namespace dmma;
@@ -810,9 +858,8 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     } else
     if (tc_experts) {
         using namespace g100;
-        const int ntok = tix ? 128 : 16;
         stage_begin(L, ST_GATHER, st);
-        tile_schedule_kernel<<<1, 32, 0, st>>>(L->offsets, E, ntok, L->tile_offsets);
+        tile_schedule_kernel<<<1, 32, 0, st>>>(L->offsets, E, BM, L->tile_offsets);
         gather_rows_perm8_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, K, L->xg, M, H);
         L->launches += 2;
         stage_end(L, ST_GATHER, st);
@@ -829,11 +876,10 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         stage_begin(L, ST_GATE_UP, st);
         p.scales = L->w.gate_proj.scales; p.biases = L->w.gate_proj.biases; p.row_bias = L->w.gate_proj.row_bias;
         p.scales2 = L->w.up_proj.scales; p.biases2 = L->w.up_proj.biases; p.row_bias2 = L->w.up_proj.row_bias;
-        p.n_out = I; p.K = H; p.m_tiles = (I + BM - 1) / BM;
+        p.n_out = I; p.K = H; p.m_tiles = (I + BN / 2 - 1) / (BN / 2);
         p.out = L->inner_bf; p.out_ld = I; p.out_permute8 = 1;
-        int lrc = tix ? launch_grouped_gemm<true, 128, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg[1], p, L->n_sms, st)
-                      : launch_grouped_gemm<true, 16, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg[0], p, L->n_sms, st);
-        if (lrc) return fail(L, FFAI_ERR_CUDA, "gate/up grouped GEMM launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        if (launch_grouped_gemm<true, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg, p, L->n_sms, st))
+            return fail(L, FFAI_ERR_CUDA, "gate/up grouped GEMM launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += 1;
         stage_end(L, ST_GATE_UP, st);
 
@@ -841,11 +887,10 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         p.timeline = nullptr;
         p.scales = L->w.down_proj.scales; p.biases = L->w.down_proj.biases; p.row_bias = L->w.down_proj.row_bias;
         p.scales2 = nullptr; p.biases2 = nullptr; p.row_bias2 = nullptr;
-        p.n_out = H; p.K = I; p.m_tiles = (H + BM - 1) / BM;
+        p.n_out = H; p.K = I; p.m_tiles = (H + BN - 1) / BN;
         p.out = L->y_bf; p.out_ld = H; p.out_permute8 = 0;
-        lrc = tix ? launch_grouped_gemm<false, 128, uint16_t>(L->tm_down, L->tm_down, L->tm_inner[1], p, L->n_sms, st)
-                  : launch_grouped_gemm<false, 16, uint16_t>(L->tm_down, L->tm_down, L->tm_inner[0], p, L->n_sms, st);
-        if (lrc) return fail(L, FFAI_ERR_CUDA, "down grouped GEMM launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        if (launch_grouped_gemm<false, uint16_t>(L->tm_down, L->tm_down, L->tm_inner, p, L->n_sms, st))
+            return fail(L, FFAI_ERR_CUDA, "down grouped GEMM launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += 1;
         stage_end(L, ST_DOWN, st);
     } else {
@@ -884,9 +929,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         const int Is = c.shared_intermediate;
         if (tc_shared) {
             using namespace g100;
-            const int six = T <= 16 ? 0 : 1;
-            const int ntok = six ? 128 : 16;
-            single_group_schedule_kernel<<<1, 32, 0, st>>>(T, ntok, L->sh_sched);
+            single_group_schedule_kernel<<<1, 32, 0, st>>>(T, BM, L->sh_sched);
             gather_rows_perm8_kernel<<<(T + 7) / 8, 256, 0, st>>>(x, nullptr, 1, L->sh_x, T, H);
             Params p{};
             p.n_experts = 1; p.group_size = c.shared_group_size;
@@ -895,18 +938,16 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
             p.error_word = L->error_word;
             p.scales = L->w.shared_gate_proj.scales; p.biases = L->w.shared_gate_proj.biases;
             p.scales2 = L->w.shared_up_proj.scales; p.biases2 = L->w.shared_up_proj.biases;
-            p.n_out = Is; p.K = H; p.m_tiles = (Is + BM - 1) / BM;
+            p.n_out = Is; p.K = H; p.m_tiles = (Is + BN / 2 - 1) / (BN / 2);
             p.out = L->sh_inner_bf; p.out_ld = Is; p.out_permute8 = 1;
-            int lrc = six ? launch_grouped_gemm<true, 128, uint16_t>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x[1], p, L->n_sms, st)
-                          : launch_grouped_gemm<true, 16, uint16_t>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x[0], p, L->n_sms, st);
-            if (lrc) return fail(L, FFAI_ERR_CUDA, "shared gate/up grouped GEMM launch failed");
+            if (launch_grouped_gemm<true, uint16_t>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x, p, L->n_sms, st))
+                return fail(L, FFAI_ERR_CUDA, "shared gate/up grouped GEMM launch failed");
             p.scales = L->w.shared_down_proj.scales; p.biases = L->w.shared_down_proj.biases;
             p.scales2 = nullptr; p.biases2 = nullptr;
-            p.n_out = H; p.K = Is; p.m_tiles = (H + BM - 1) / BM;
+            p.n_out = H; p.K = Is; p.m_tiles = (H + BN - 1) / BN;
             p.out = L->sh_y; p.out_ld = H; p.out_permute8 = 0;
-            lrc = six ? launch_grouped_gemm<false, 128, float>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner[1], p, L->n_sms, st)
-                      : launch_grouped_gemm<false, 16, float>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner[0], p, L->n_sms, st);
-            if (lrc) return fail(L, FFAI_ERR_CUDA, "shared down grouped GEMM launch failed");
+            if (launch_grouped_gemm<false, float>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner, p, L->n_sms, st))
+                return fail(L, FFAI_ERR_CUDA, "shared down grouped GEMM launch failed");
             L->launches += 4;
         } else {
             GemvParams p = gemv_params(L->w.shared_gate_proj, &L->w.shared_up_proj, Is, H, c.shared_group_size, 1);

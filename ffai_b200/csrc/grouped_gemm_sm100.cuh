@@ -6,22 +6,23 @@
 // 4912-5201) together with Ops.swiglu between them (Ops.swift:6400-6452):
 //     out[row, n] = sum_k (scale[e,n,k/gs] * q[e,n,k] + bias[e,n,k/gs]) * x[row, k],   e = expert of row.
 //
-// Orientation: the packed weights are the M side of the MMA (128 weight rows per tile, one
-// TMEM lane each), the tokens routed to the expert are the N side (16..128 columns), so an
-// expert with few rows costs a narrow instruction instead of a padded 128-row tile and each
-// weight tile is unpacked once per token tile.
+// Orientation: the activation rows routed to an expert are the M side of the MMA (128 rows per
+// tile, one TMEM lane each); the weight rows are the N side, 256 per instruction - for gate/up the
+// 128 gate rows and the 128 matching up rows of the expert, so one tcgen05.mma (128 x 256 x 16)
+// feeds both halves of the activation and a thread of the epilogue finds gate and up of one output
+// element in its own TMEM lane.  (Measured with the device timeline: one tcgen05.mma costs its
+// issuing thread 80-100 clk whatever its N; only N = 256 keeps the tensor pipe busy that long.)
 //
-// Warp roles in a 480-thread CTA (persistent; tiles are (expert, token tile, 128-row tile)):
-//   warp 0      TMA producer of packed weights: [128 rows x 128 B] (256 k) per projection,
-//               128-byte swizzle, ring "W".  (A 32-byte-wide box per 64 k costs the TMA unit one
-//               request per row and ran at ~1 us per box; 128-byte rows are its natural unit.)
-//   warp 14     TMA producer of activations: [NTOK rows x 128 B] per 64 k, 128-byte swizzle, ring "X"
-//   warp 1      MMA issuer (one thread): 4 x tcgen05.mma (K=16) per 64 k and accumulator;
-//               owns TMEM allocation
-//   warps 2-9   dequant: 256 threads, thread = (weight row, half of a 64-k block); unpack 4-bit
-//               to bf16 (w = fma(q, scale, bias) rounded once), store into the 128-byte-swizzled
-//               K-major operand tile, ring "A"
-//   warps 10-13 epilogue: tcgen05.ld the accumulators, bias + activation, store
+// Warp roles in a 768-thread CTA (persistent; tiles are (expert, 128-row token tile, weight-row tile)):
+//   warp 0       TMA producer of packed weights: two boxes of [128 rows x 128 B] (256 k) per stage,
+//                128-byte swizzle, ring "W"
+//   warp 2       TMA producer of activations: [128 rows x 128 B] per 64 k, 128-byte swizzle, ring "X"
+//   warp 1       MMA issuer (one thread): 4 x tcgen05.mma (M128 N256 K16) per 64 k; owns TMEM
+//                (two accumulators of 256 columns, so the epilogue of a tile overlaps the next tile)
+//   warps 4-19   dequant: 512 threads, thread = (weight row, half of a 64-k block); unpack 4-bit to
+//                bf16 (w = fma(q, scale, bias) rounded once), store into the 128-byte-swizzled K-major
+//                operand tile, ring "B"
+//   warps 20-23  epilogue: tcgen05.ld 16 columns at a time, bias + activation, 16-byte stores
 // Every mbarrier wait is bounded (about one second); on expiry the kernel raises an error
 // word, stops issuing work, waits (bounded) for its own copies in flight, frees TMEM and returns.
 //
@@ -37,13 +38,18 @@
 namespace ffai {
 namespace g100 {
 
-constexpr int BM = 128;        // weight rows per tile (TMEM lanes)
+constexpr int BM = 128;        // activation rows per tile (the MMA's M: one TMEM lane each)
+constexpr int BN = 256;        // weight rows per tile (the MMA's N: one fp32 TMEM column each)
 constexpr int BK = 64;         // k per MMA stage (one 128-byte swizzle row of bf16)
 constexpr int KS = 256;        // k per packed-weight TMA box (one 128-byte row of 4-bit values)
 constexpr int SUB = KS / BK;   // MMA stages per packed-weight stage
-constexpr int THREADS = 480;   // 15 warps
-constexpr int N_DEQ_WARPS = 8;
-constexpr int X_WARP = 14;     // warp that issues the activation TMA loads
+constexpr int THREADS = 768;   // 24 warps
+constexpr int W_WARP = 0;      // packed-weight TMA producer
+constexpr int MMA_WARP = 1;    // MMA issuer, owns TMEM
+constexpr int X_WARP = 2;      // activation TMA producer (warp 3 idles: keeps the epilogue warps quadrant-aligned)
+constexpr int DEQ_WARP0 = 4;   // first of the dequant warps
+constexpr int N_DEQ_WARPS = 16;
+constexpr int EPI_WARP0 = 20;  // four epilogue warps, warp % 4 = TMEM lane quadrant
 constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;
 
 enum : uint32_t { ERR_NONE = 0, ERR_WAIT_TIMEOUT = 1 };
@@ -75,9 +81,16 @@ struct Params {
 // Timeline layout: [role][k-block index < TL_SLOTS][event < TL_EVENTS].
 constexpr int TL_ROLES = 5, TL_SLOTS = 96, TL_EVENTS = 4;
 enum { TL_WPROD = 0, TL_XPROD = 1, TL_MMA = 2, TL_DEQ = 3, TL_EPI = 4 };
+#ifndef FFAI_G100_TIMELINE
+#define FFAI_G100_TIMELINE 0   // 1: compile the timeline marks in (profiling builds); 0: they vanish
+#endif
 FFAI_DEVINL void tl_mark(const Params& p, int role, int idx, int ev) {
+#if FFAI_G100_TIMELINE
     if (p.timeline && blockIdx.x == 0 && idx < TL_SLOTS)
         p.timeline[(role * TL_SLOTS + idx) * TL_EVENTS + ev] = clock64();
+#else
+    (void)p; (void)role; (void)idx; (void)ev;
+#endif
 }
 
 // ───────────────────────── PTX wrappers ─────────────────────────
@@ -103,23 +116,22 @@ FFAI_DEVINL bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(20000u)   // the thread may stay suspended up to 20 us per try; it wakes when the phase completes
         : "memory");
     return done != 0;
 }
 // Bounded wait.  Returns false when the limit expires or another thread of the CTA gave up.
-// SLEEP_NS > 0: back off between polls (roles that wait long and must not steal issue slots).
+// Waiting threads are suspended by the hardware inside try_wait (time hint), so they take no issue slots.
 template <int SLEEP_NS>
 FFAI_DEVINL bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     for (uint32_t spin = 1;; ++spin) {
-        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 63u) == 0) {  // the slow checks, once per 64 polls
+        if ((spin & 7u) == 0) {  // the slow checks, once per 8 tries (each try may sleep up to 20 us)
             if (*abort_flag) return false;
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
@@ -216,9 +228,10 @@ FFAI_DEVINL uint4 dequant_word_bf16(uint32_t w, __nv_bfloat162 s2, __nv_bfloat16
     const __nv_bfloat162 k128 = __floats2bfloat162_rn(128.0f, 128.0f);
     uint32_t t[4];
     t[0] = (w & 0x000F000Fu) | 0x43004300u;
-    t[1] = ((w >> 4) & 0x000F000Fu) | 0x43004300u;
-    t[2] = ((w >> 8) & 0x000F000Fu) | 0x43004300u;
-    t[3] = ((w >> 12) & 0x000F000Fu) | 0x43004300u;
+    // right shifts as high halves of multiplies: they issue on the FMA pipe instead of the half-rate ALU pipe
+    t[1] = (__umulhi(w, 1u << 28) & 0x000F000Fu) | 0x43004300u;
+    t[2] = (__umulhi(w, 1u << 24) & 0x000F000Fu) | 0x43004300u;
+    t[3] = (__umulhi(w, 1u << 20) & 0x000F000Fu) | 0x43004300u;
     uint32_t o[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -227,6 +240,13 @@ FFAI_DEVINL uint4 dequant_word_bf16(uint32_t w, __nv_bfloat162 s2, __nv_bfloat16
         o[i] = *reinterpret_cast<uint32_t*>(&v);
     }
     return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Two floats -> packed bf16 pair (lo, hi), round to nearest even, one convert instruction.
+FFAI_DEVINL uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
 }
 
 FFAI_DEVINL int permute8_store_col(int n) {
@@ -256,39 +276,34 @@ FFAI_DEVINL TileCoord decode_tile(const Params& p, int tile, int ntok) {
     return c;
 }
 
-template <bool FUSED, int NTOK>
+template <bool FUSED>
 struct SmemLayout {
-    static constexpr int NPROJ = FUSED ? 2 : 1;
-    static constexpr int A_TILE = BM * BK * 2;             // 16 KB bf16 operand tile (128 rows x 64 k)
-    static constexpr int A_STAGE = NPROJ * A_TILE;
-    static constexpr int NA = (FUSED && NTOK > 64) ? 2 : 3;  // dequantised-operand ring
-    static constexpr int W_TILE = BM * (KS / 2);           // 16 KB packed (128 rows x 256 k x 4 bit)
-    static constexpr int W_STAGE = NPROJ * W_TILE;
-    static constexpr int X_TILE = ((NTOK * BK * 2 + 1023) / 1024) * 1024;  // NTOK rows x 128 B
-    static constexpr int NX = 4;                           // activation ring (64-k blocks)
-    static constexpr int BUDGET = 200 * 1024;
-    static constexpr int NW_FIT = (BUDGET - NA * A_STAGE - NX * X_TILE) / W_STAGE;
-    static constexpr int NW = NW_FIT > 6 ? 6 : NW_FIT;     // packed-weight ring (256-k super blocks)
-    static constexpr int OFF_A = 0;
-    static constexpr int OFF_W = OFF_A + NA * A_STAGE;
+    static constexpr int B_STAGE = BN * BK * 2;            // 32 KB: 256 weight rows x 64 k, bf16, dequantised
+    static constexpr int NB = 3;                           // dequantised-operand ring
+    static constexpr int W_STAGE = BN * (KS / 2);          // 32 KB: 256 weight rows x 256 k, packed 4-bit
+    static constexpr int NW = 2;                           // packed-weight ring (256-k super blocks)
+    static constexpr int X_TILE = BM * BK * 2;             // 16 KB: 128 activation rows x 64 k
+    static constexpr int NX = 3;                           // activation ring
+    static constexpr int OFF_B = 0;
+    static constexpr int OFF_W = OFF_B + NB * B_STAGE;
     static constexpr int OFF_X = OFF_W + NW * W_STAGE;
     static constexpr int OFF_BAR = OFF_X + NX * X_TILE;
-    static constexpr int N_BARS = 2 * NW + 2 * NX + 2 * NA + 4;
+    static constexpr int N_BARS = 2 * NW + 2 * NX + 2 * NB + 4;
     static constexpr int TOTAL = OFF_BAR + N_BARS * 8 + 16 + 1024;  // + alignment slack
-    static constexpr int TMEM_COLS_RAW = 2 * NPROJ * NTOK;
-    static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;
-    static_assert(NW >= 2, "packed-weight ring too shallow");
-    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns must be a power of two <= 512");
+    static constexpr int TMEM_COLS = 2 * BN;               // two accumulators of 256 fp32 columns
+    static_assert(TOTAL <= 227 * 1024, "shared memory budget");
 };
 
-// FUSED:  out[row, n] = act(Wg[e][n]·x[row] + bg, Wu[e][n]·x[row] + bu), bf16, optionally 8-run permuted
-// !FUSED: out[row, n] = W[e][n]·x[row] + b, TOut
-template <bool FUSED, int NTOK, typename TOut>
+// One CTA tile: 128 activation rows (the MMA's M, one TMEM lane each) x 256 weight rows (the MMA's N).
+// FUSED:  the 256 weight rows are 128 gate rows and the 128 matching up rows of one expert;
+//         out[row, n] = act(Wg[e][n]·x[row] + bg, Wu[e][n]·x[row] + bu), bf16, optionally 8-run permuted
+// !FUSED: 256 consecutive rows of one projection;  out[row, n] = W[e][n]·x[row] + b, TOut
+template <bool FUSED, typename TOut>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
                     const __grid_constant__ CUtensorMap tm_x, const Params p) {
-    using L = SmemLayout<FUSED, NTOK>;
-    constexpr int NA = L::NA;
+    using L = SmemLayout<FUSED>;
+    constexpr int NB = L::NB;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -298,10 +313,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     auto w_empty = [&](int s) { return bar0 + 8u * (L::NW + s); };
     auto x_full = [&](int s) { return bar0 + 8u * (2 * L::NW + s); };
     auto x_empty = [&](int s) { return bar0 + 8u * (2 * L::NW + L::NX + s); };
-    auto a_full = [&](int s) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + s); };
-    auto a_empty = [&](int s) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + NA + s); };
-    auto acc_full = [&](int b) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + 2 * NA + b); };
-    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + 2 * NA + 2 + b); };
+    auto b_full = [&](int s) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + s); };
+    auto b_empty = [&](int s) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + NB + s); };
+    auto acc_full = [&](int b) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + 2 * NB + b); };
+    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + 2 * NB + 2 + b); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + L::N_BARS * 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -309,11 +324,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const int KB = p.K / BK;                 // 64-k blocks
     const int SB = (KB + SUB - 1) / SUB;     // 256-k super blocks
     const int total_tiles = (int)p.tile_offsets[p.n_experts] * p.m_tiles;
+    constexpr int ROWS_PER_TILE = FUSED ? BN / 2 : BN;   // output rows of one projection covered by a tile
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < L::NW; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), N_DEQ_WARPS); }
         for (int s = 0; s < L::NX; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 1); }
-        for (int s = 0; s < NA; ++s) { mbar_init(a_full(s), N_DEQ_WARPS); mbar_init(a_empty(s), 1); }
+        for (int s = 0; s < NB; ++s) { mbar_init(b_full(s), N_DEQ_WARPS); mbar_init(b_empty(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
         *abort_flag = 0;
         fence_barrier_init();
@@ -321,7 +337,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (FUSED) prefetch_tmap(&tm_w2);
         prefetch_tmap(&tm_x);
     }
-    if (warp == 1) {
+    if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), L::TMEM_COLS);
         tmem_relinquish();
     }
@@ -330,15 +346,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
-        // ───────────── TMA producer, packed weights: one 128-row x 128-byte box per projection per 256 k ─────────────
+    if (warp == W_WARP) {
+        // ───────────── TMA producer, packed weights: two 128-row x 128-byte boxes per 256 k ─────────────
         if (lane == 0) {
             RingPos wp{0, 0};
             uint32_t issued = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileCoord c = decode_tile(p, tile, NTOK);
-                const int wrow = c.expert * p.n_out + c.m_tile * BM;
+                const TileCoord c = decode_tile(p, tile, BM);
+                const int wrow = c.expert * p.n_out + c.m_tile * ROWS_PER_TILE;
                 for (int sb = 0; sb < SB; ++sb) {
                     tl_mark(p, TL_WPROD, (int)issued, 0);
                     if (!mbar_wait<64>(w_empty(wp.stage), wp.phase ^ 1, abort_flag)) { ok = false; break; }
@@ -346,7 +362,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                     const uint32_t stage = sbase + L::OFF_W + wp.stage * L::W_STAGE;
                     mbar_arrive_expect_tx(w_full(wp.stage), L::W_STAGE);
                     tma_load_2d(stage, &tm_w, sb * (KS / 8), wrow, w_full(wp.stage));
-                    if (FUSED) tma_load_2d(stage + L::W_TILE, &tm_w2, sb * (KS / 8), wrow, w_full(wp.stage));
+                    if (FUSED) tma_load_2d(stage + L::W_STAGE / 2, &tm_w2, sb * (KS / 8), wrow, w_full(wp.stage));
+                    else tma_load_2d(stage + L::W_STAGE / 2, &tm_w, sb * (KS / 8), wrow + BN / 2, w_full(wp.stage));
                     wp.advance(L::NW);
                     ++issued;
                 }
@@ -361,18 +378,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             }
         }
     } else if (warp == X_WARP) {
-        // ───────────── TMA producer, activations: NTOK rows x 128 bytes per 64 k ─────────────
+        // ───────────── TMA producer, activations: 128 rows x 128 bytes per 64 k ─────────────
         if (lane == 0) {
             RingPos xp{0, 0};
             uint32_t issued = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileCoord c = decode_tile(p, tile, NTOK);
+                const TileCoord c = decode_tile(p, tile, BM);
                 for (int kb = 0; kb < KB; ++kb) {
-                    tl_mark(p, TL_XPROD, (int)issued, 0);
                     if (!mbar_wait<32>(x_empty(xp.stage), xp.phase ^ 1, abort_flag)) { ok = false; break; }
-                    tl_mark(p, TL_XPROD, (int)issued, 1);
-                    mbar_arrive_expect_tx(x_full(xp.stage), NTOK * BK * 2);
+                    mbar_arrive_expect_tx(x_full(xp.stage), L::X_TILE);
                     tma_load_2d(sbase + L::OFF_X + xp.stage * L::X_TILE, &tm_x, kb * BK, c.row_begin, x_full(xp.stage));
                     xp.advance(L::NX);
                     ++issued;
@@ -386,179 +401,193 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                 }
             }
         }
-    } else if (warp == 1) {
-        // ───────────── MMA issuer ─────────────
+    } else if (warp == MMA_WARP) {
+        // ───────────── MMA issuer: 4 x (128 x 256 x 16) per 64 k ─────────────
         if (lane == 0) {
-            RingPos xp{0, 0}, ap{0, 0};
+            RingPos xp{0, 0}, bp{0, 0};
             uint32_t tcount = 0;
             int gk = 0;
             bool ok = true;
+            const uint32_t idesc = make_idesc_bf16(BM, BN);
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-                const TileCoord c = decode_tile(p, tile, NTOK);
-                const int ncols = (c.n_cols_valid + 15) & ~15;
-                const uint32_t idesc = make_idesc_bf16(BM, ncols);
                 const int buf = tcount & 1;
                 const uint32_t acc_ph = (tcount >> 1) & 1;
                 if (!mbar_wait<32>(acc_empty(buf), acc_ph ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d0 = tmem_base + (uint32_t)(buf * L::NPROJ * NTOK);
+                const uint32_t d0 = tmem_base + (uint32_t)(buf * BN);
                 for (int kb = 0; kb < KB; ++kb, ++gk) {
                     if (!mbar_wait<0>(x_full(xp.stage), xp.phase, abort_flag)) { ok = false; break; }
-                    if (!mbar_wait<0>(a_full(ap.stage), ap.phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait<0>(b_full(bp.stage), bp.phase, abort_flag)) { ok = false; break; }
                     tl_mark(p, TL_MMA, gk, 0);
                     tc_fence_after();
-                    const uint64_t bd0 = make_kmajor_sw128_desc(sbase + L::OFF_X + xp.stage * L::X_TILE);
-                    const uint32_t aa = sbase + L::OFF_A + ap.stage * L::A_STAGE;
-                    const uint64_t ad0 = make_kmajor_sw128_desc(aa);
-                    const uint64_t ad1 = make_kmajor_sw128_desc(aa + L::A_TILE);
+                    const uint64_t ad0 = make_kmajor_sw128_desc(sbase + L::OFF_X + xp.stage * L::X_TILE);
+                    const uint64_t bd0 = make_kmajor_sw128_desc(sbase + L::OFF_B + bp.stage * L::B_STAGE);
 #pragma unroll
                     for (int k16 = 0; k16 < BK / 16; ++k16) {
-                        if (p.debug_flags & 4) break;
                         // advancing 16 k inside the swizzled row = +32 bytes = +2 in the (addr >> 4) field
-                        const uint32_t acc = (kb | k16) != 0 ? 1u : 0u;
-                        umma_bf16(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, acc);
-                        if (FUSED) umma_bf16(d0 + NTOK, ad1 + 2 * k16, bd0 + 2 * k16, idesc, acc);
+                        umma_bf16(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, (kb | k16) != 0 ? 1u : 0u);
                     }
                     tl_mark(p, TL_MMA, gk, 1);
-                    umma_commit(a_empty(ap.stage));
-                    tl_mark(p, TL_MMA, gk, 2);
+                    umma_commit(b_empty(bp.stage));
                     umma_commit(x_empty(xp.stage));
                     tl_mark(p, TL_MMA, gk, 3);
                     xp.advance(L::NX);
-                    ap.advance(NA);
+                    bp.advance(NB);
                 }
                 if (ok) umma_commit(acc_full(buf));
             }
         }
-    } else if (warp < 2 + N_DEQ_WARPS) {
-        // ───────────── dequant ─────────────
-        // 256 threads: thread = (weight row r, 32-k half of a 64-k block).  A warp covers 16 rows x 2
-        // halves, eight consecutive rows per quarter-warp, so both the 16-byte reads of the
-        // 128-byte-swizzled packed tile and the 16-byte stores into the 128-byte-swizzled operand
-        // tile touch eight distinct chunk columns: no bank conflicts either way.
-        const int dw = warp - 2;
+    } else if (warp >= DEQ_WARP0 && warp < DEQ_WARP0 + N_DEQ_WARPS) {
+        // ───────────── dequant: 512 threads, thread = (weight row r of 256, 32-k half of a 64-k block) ─────────────
+        // A warp covers 16 rows x 2 halves, eight consecutive rows per quarter-warp, so both the 16-byte
+        // reads of the 128-byte-swizzled packed tile and the 16-byte stores into the 128-byte-swizzled
+        // operand tile touch eight distinct chunk columns: no bank conflicts either way.
+        const int dw = warp - DEQ_WARP0;
         const int half = (lane >> 3) & 1;
-        const int r = dw * 16 + (lane & 7) + ((lane >> 4) << 3);
+        const int r = dw * 16 + (lane & 7) + ((lane >> 4) << 3);   // 0..255
         const int gpr = p.K / p.group_size;
+        const int gshift = p.group_size == 32 ? 5 : (p.group_size == 64 ? 6 : 7);
         const long total_rows = (long)p.n_experts * p.n_out;
-        RingPos wp{0, 0}, ap{0, 0};
+        const bool second = FUSED && r >= BN / 2;                   // the up projection's half of the tile
+        const uint16_t* sbase_ptr = second ? p.scales2 : p.scales;
+        const uint16_t* bbase_ptr = second ? p.biases2 : p.biases;
+        const int r_in_proj = FUSED ? (r & (BN / 2 - 1)) : r;
+        RingPos wp{0, 0}, bp{0, 0};
         bool ok = true;
         int gk = 0;
-        const bool tl_on = (warp == 2 && lane == 0);
+        const bool tl_on = (warp == DEQ_WARP0 && lane == 0);
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const TileCoord c = decode_tile(p, tile, NTOK);
-            long grow = (long)c.expert * p.n_out + c.m_tile * BM + r;
+            const TileCoord c = decode_tile(p, tile, BM);
+            long grow = (long)c.expert * p.n_out + c.m_tile * ROWS_PER_TILE + r_in_proj;
             if (grow >= total_rows) grow = total_rows - 1;  // rows past the tensor: zero-filled by TMA, masked at store
-            const uint16_t* sp = p.scales + grow * gpr;
-            const uint16_t* bp = p.biases + grow * gpr;
-            const uint16_t* sp2 = FUSED ? p.scales2 + grow * gpr : nullptr;
-            const uint16_t* bp2 = FUSED ? p.biases2 + grow * gpr : nullptr;
-            // (scale | bias << 16) per 64-k block, fetched one super block ahead so the loads are off the critical path
-            uint32_t sb_nxt[SUB], sb2_nxt[SUB];
+            const uint16_t* sp = sbase_ptr + grow * gpr;
+            const uint16_t* bq = bbase_ptr + grow * gpr;
+            // scale and bias per 64-k block, fetched one super block ahead.  The loaded values are left
+            // untouched until the next super block: an instruction that consumes a load stalls the warp
+            // until the data arrives, which would put the memory latency back on the critical path.
+            uint16_t s_nxt[SUB], b_nxt[SUB];
             auto fetch_scales = [&](int kb0) {
 #pragma unroll
                 for (int j = 0; j < SUB; ++j) {
-                    const int kb = kb0 + j;
-                    if (kb < KB) {
-                        const int g = (kb * BK + half * 32) / p.group_size;
-                        sb_nxt[j] = (uint32_t)sp[g] | ((uint32_t)bp[g] << 16);
-                        if (FUSED) sb2_nxt[j] = (uint32_t)sp2[g] | ((uint32_t)bp2[g] << 16);
-                    }
+                    const int kb = min(kb0 + j, KB - 1);
+                    const int g = (kb * BK + half * 32) >> gshift;
+                    s_nxt[j] = sp[g];
+                    b_nxt[j] = bq[g];
                 }
             };
             fetch_scales(0);
             for (int sb = 0; sb < SB && ok; ++sb) {
-                uint32_t sb_cur[SUB], sb2_cur[SUB];
+                uint32_t sb_cur[SUB];
 #pragma unroll
-                for (int j = 0; j < SUB; ++j) { sb_cur[j] = sb_nxt[j]; sb2_cur[j] = FUSED ? sb2_nxt[j] : 0u; }
+                for (int j = 0; j < SUB; ++j) sb_cur[j] = (uint32_t)s_nxt[j] | ((uint32_t)b_nxt[j] << 16);
                 fetch_scales((sb + 1) * SUB);
                 if (tl_on) tl_mark(p, TL_DEQ, gk, 0);
                 if (!mbar_wait<0>(w_full(wp.stage), wp.phase, abort_flag)) { ok = false; break; }
+                if (tl_on) tl_mark(p, TL_DEQ, gk, 1);
                 const uint8_t* wrow_s = smem + L::OFF_W + wp.stage * L::W_STAGE + r * 128;
 #pragma unroll
                 for (int j = 0; j < SUB; ++j) {
                     if (sb * SUB + j >= KB) break;
-                    if (tl_on) tl_mark(p, TL_DEQ, gk, 1);
-                    if (!mbar_wait<0>(a_empty(ap.stage), ap.phase ^ 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait<0>(b_empty(bp.stage), bp.phase ^ 1, abort_flag)) { ok = false; break; }
                     if (tl_on) tl_mark(p, TL_DEQ, gk, 2);
-                    uint8_t* row = smem + L::OFF_A + ap.stage * L::A_STAGE + r * 128;
+                    uint8_t* row = smem + L::OFF_B + bp.stage * L::B_STAGE + r * 128;
+                    // logical 16-byte chunk 2j+half of the packed row, at its swizzled position
+                    const uint4 wv = *reinterpret_cast<const uint4*>(wrow_s + (((2 * j + half) ^ (r & 7)) << 4));
+                    const uint32_t sbv = sb_cur[j];
+                    __nv_bfloat162 s2, b2;
+                    *reinterpret_cast<uint32_t*>(&s2) = __byte_perm(sbv, sbv, 0x1010);
+                    *reinterpret_cast<uint32_t*>(&b2) = __byte_perm(sbv, sbv, 0x3232);
+                    const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-                    for (int pj = 0; pj < L::NPROJ; ++pj) {
-                        if (p.debug_flags & 2) break;
-                        // logical 16-byte chunk 2j+half of the packed row, at its swizzled position
-                        const uint4 wv = *reinterpret_cast<const uint4*>(wrow_s + pj * L::W_TILE + (((2 * j + half) ^ (r & 7)) << 4));
-                        const uint32_t sbv = pj ? sb2_cur[j] : sb_cur[j];
-                        __nv_bfloat162 s2, b2;
-                        *reinterpret_cast<uint32_t*>(&s2) = __byte_perm(sbv, sbv, 0x1010);
-                        *reinterpret_cast<uint32_t*>(&b2) = __byte_perm(sbv, sbv, 0x3232);
-                        const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj) {
-                            const int chunk = (half * 4 + jj) ^ (r & 7);
-                            *reinterpret_cast<uint4*>(row + pj * L::A_TILE + chunk * 16) = dequant_word_bf16(words[jj], s2, b2);
-                        }
+                    for (int jj = 0; jj < 4; ++jj) {
+                        const int chunk = (half * 4 + jj) ^ (r & 7);
+                        *reinterpret_cast<uint4*>(row + chunk * 16) = dequant_word_bf16(words[jj], s2, b2);
                     }
-                    if (!(p.debug_flags & 1)) fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+                    fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(a_full(ap.stage));
+                    if (lane == 0) mbar_arrive(b_full(bp.stage));
                     if (tl_on) tl_mark(p, TL_DEQ, gk, 3);
                     ++gk;
-                    ap.advance(NA);
+                    bp.advance(NB);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(w_empty(wp.stage));  // this warp is done reading the packed stage
                 wp.advance(L::NW);
             }
         }
-    } else {
-        // ───────────── epilogue ─────────────
+    } else if (warp >= EPI_WARP0) {
+        // ───────────── epilogue: thread = activation row (TMEM lane), walks the 256 accumulator columns ─────────────
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
         uint32_t tcount = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-            const TileCoord c = decode_tile(p, tile, NTOK);
+            const TileCoord c = decode_tile(p, tile, BM);
             const int buf = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1;
-            if (warp == 10 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 0);
+            if (warp == EPI_WARP0 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 0);
             if (!mbar_wait<256>(acc_full(buf), acc_ph, abort_flag)) { ok = false; break; }
-            if (warp == 10 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 1);
+            if (warp == EPI_WARP0 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 1);
             tc_fence_after();
-            const int n = c.m_tile * BM + q * 32 + lane;  // output row (weight row) of this thread
-            const bool n_ok = n < p.n_out;
-            float rb1 = 0.0f, rb2 = 0.0f;
-            if (n_ok && p.row_bias) rb1 = bf16_bits_to_f32(p.row_bias[(size_t)c.expert * p.n_out + n]);
-            if (FUSED && n_ok && p.row_bias2) rb2 = bf16_bits_to_f32(p.row_bias2[(size_t)c.expert * p.n_out + n]);
-            const int ncol = p.out_permute8 ? permute8_store_col(n) : n;
-            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * L::NPROJ * NTOK);
-            for (int c0 = 0; c0 < c.n_cols_valid; c0 += 16) {
+            const int tok = q * 32 + lane;                      // activation row within the tile
+            const bool tok_ok = tok < c.n_cols_valid;
+            const int n0 = c.m_tile * ROWS_PER_TILE;            // first output row of the tile
+            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+            const size_t ebase = (size_t)c.expert * p.n_out;
+            uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + (size_t)(c.row_begin + tok) * p.out_ld * sizeof(TOut);
+            for (int c0 = 0; c0 < ROWS_PER_TILE; c0 += 16) {
+                if (n0 + c0 >= p.n_out) break;                  // n_out is a multiple of 16: a chunk is all in or all out
                 uint32_t a[16], b[16];
                 tmem_ld16(t0 + c0, a);
-                if (FUSED) tmem_ld16(t0 + NTOK + c0, b);
+                if (FUSED) tmem_ld16(t0 + BN / 2 + c0, b);
                 tmem_ld_wait();
-                if (n_ok) {
+                if (tok_ok) {
+                    float v[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        if (c0 + j < c.n_cols_valid) {
-                            float v = __uint_as_float(a[j]) + rb1;
-                            if (FUSED) v = glu_activation(v, __uint_as_float(b[j]) + rb2, p.activation, p.limit, p.alpha);
-                            TOut* o = reinterpret_cast<TOut*>(p.out) + (size_t)(c.row_begin + c0 + j) * p.out_ld + ncol;
-                            if (sizeof(TOut) == 2) *reinterpret_cast<uint16_t*>(o) = f32_to_bf16_bits(v);
-                            else *reinterpret_cast<float*>(o) = v;
+                        float x = __uint_as_float(a[j]);
+                        if (p.row_bias) x += bf16_bits_to_f32(p.row_bias[ebase + n0 + c0 + j]);
+                        if (FUSED) {
+                            float u = __uint_as_float(b[j]);
+                            if (p.row_bias2) u += bf16_bits_to_f32(p.row_bias2[ebase + n0 + c0 + j]);
+                            x = glu_activation(x, u, p.activation, p.limit, p.alpha);
                         }
+                        v[j] = x;
+                    }
+                    if (sizeof(TOut) == 2) {
+                        // 16 bf16 = two 16-byte stores; with the 8-run permutation, run positions hold k = 0,4,1,5,2,6,3,7
+                        uint32_t w8[8];
+                        if (p.out_permute8) {
+#pragma unroll
+                            for (int h8 = 0; h8 < 2; ++h8)
+#pragma unroll
+                                for (int pp = 0; pp < 4; ++pp)
+                                    w8[h8 * 4 + pp] = pack_bf16x2(v[h8 * 8 + pp], v[h8 * 8 + pp + 4]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                w8[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(orow + (size_t)(n0 + c0) * 2);
+                        dst[0] = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+                        dst[1] = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+                    } else {
+                        float4* dst = reinterpret_cast<float4*>(orow + (size_t)(n0 + c0) * 4);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty(buf));
-            if (warp == 10 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 2);
+            if (warp == EPI_WARP0 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 2);
         }
     }
 
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag && p.error_word) atomicExch(p.error_word, (uint32_t)ERR_WAIT_TIMEOUT);
-    if (warp == 1) {
+    if (warp == MMA_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem_base, L::TMEM_COLS);
     }

@@ -219,17 +219,119 @@ router_token_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens
                          weights + (size_t)t * p.top_k);
 }
 
-// Batched router projection for many tokens: a 64-token x 64-expert tile per block, 4x4 outputs
+// Small-batch router for dense (fp32 / bf16) weights: grid (ceil(E / ROWS), T), 256 threads.
+// A block stages ROWS weight rows and the token's activation row in shared memory with coalesced
+// 16-byte asynchronous copies (the per-(expert, chunk) work items of router_token_kernel made every
+// lane touch its own 128-byte line: tag-lookup bound on one SM), then each thread folds one
+// (expert, chunk) pair from shared memory in the fixed order, one thread per expert adds the chunk
+// sums, and the last block to finish a token (a ticket counter that resets itself) routes it.
+// Shared-memory rows are stored with the 16-byte pieces of each 64-value line XOR-swizzled by the
+// line index, so threads that read consecutive lines hit distinct banks.
+constexpr int ROUTER_ROWS = 8;
+
+template <int KIND>  // 1: fp32 weights, 2: bf16 weights
+__global__ void __launch_bounds__(256)
+router_rows_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
+                   uint32_t* __restrict__ indices, float* __restrict__ weights,
+                   float* __restrict__ logits_out, uint32_t* __restrict__ tickets) {
+    constexpr int WBYTES = KIND == 1 ? 4 : 2;
+    constexpr int LINE16 = 64 * WBYTES / 16;   // 16-byte pieces per 64-value line of a weight row
+    extern __shared__ __align__(16) uint8_t rsm[];
+    const int H = p.hidden, E = p.n_experts;
+    const int nchunks = H / 64;
+    const int t = blockIdx.y;
+    const int e0 = blockIdx.x * ROUTER_ROWS;
+    const int rows = min(ROUTER_ROWS, E - e0);
+    uint8_t* wsm = rsm;                                          // [ROWS][H * WBYTES]
+    uint8_t* xsm = wsm + (size_t)ROUTER_ROWS * H * WBYTES;       // [H * 2]
+    float* partial = reinterpret_cast<float*>(xsm + (size_t)H * 2);  // [ROWS][nchunks]
+    float* lsm = partial + ROUTER_ROWS * nchunks;                // [2 * E] (routing, last block only)
+    __shared__ uint32_t ticket_s;
+    const uint32_t wsm_u = (uint32_t)__cvta_generic_to_shared(wsm), xsm_u = (uint32_t)__cvta_generic_to_shared(xsm);
+
+    // stage: weight rows (rows * nchunks * LINE16 pieces) and the activation row (nchunks * 8 pieces)
+    const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(p.weight) + (size_t)e0 * H * WBYTES;
+    const int wpieces = rows * nchunks * LINE16;
+    for (int i = threadIdx.x; i < wpieces; i += blockDim.x) {
+        const int line = i / LINE16, j = i - line * LINE16;      // line = row * nchunks + chunk
+        const uint32_t dst = wsm_u + (uint32_t)(line * LINE16 + (j ^ (line & 7))) * 16;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(wsrc + (size_t)i * 16) : "memory");
+    }
+    const uint8_t* xsrc = reinterpret_cast<const uint8_t*>(x + (size_t)t * H);
+    for (int i = threadIdx.x; i < nchunks * 8; i += blockDim.x) {
+        const int line = i >> 3, j = i & 7;
+        const uint32_t dst = xsm_u + (uint32_t)(line * 8 + (j ^ (line & 7))) * 16;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(xsrc + (size_t)i * 16) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    // one (row, chunk) pair per thread: 64 fused multiply-adds in ascending k
+    for (int i = threadIdx.x; i < rows * nchunks; i += blockDim.x) {
+        const int c = i % nchunks;
+        const int line = i;                                      // row * nchunks + chunk
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xsm + (size_t)(c * 8 + (j ^ (c & 7))) * 16);
+            const float xf[8] = {bf16lo(xv.x), bf16hi(xv.x), bf16lo(xv.y), bf16hi(xv.y),
+                                 bf16lo(xv.z), bf16hi(xv.z), bf16lo(xv.w), bf16hi(xv.w)};
+            if (KIND == 1) {
+                const float4 w0 = *reinterpret_cast<const float4*>(wsm + (size_t)(line * LINE16 + ((2 * j) ^ (line & 7))) * 16);
+                const float4 w1 = *reinterpret_cast<const float4*>(wsm + (size_t)(line * LINE16 + ((2 * j + 1) ^ (line & 7))) * 16);
+                acc = __fmaf_rn(xf[0], w0.x, acc); acc = __fmaf_rn(xf[1], w0.y, acc);
+                acc = __fmaf_rn(xf[2], w0.z, acc); acc = __fmaf_rn(xf[3], w0.w, acc);
+                acc = __fmaf_rn(xf[4], w1.x, acc); acc = __fmaf_rn(xf[5], w1.y, acc);
+                acc = __fmaf_rn(xf[6], w1.z, acc); acc = __fmaf_rn(xf[7], w1.w, acc);
+            } else {
+                const uint4 wv = *reinterpret_cast<const uint4*>(wsm + (size_t)(line * LINE16 + (j ^ (line & 7))) * 16);
+                acc = __fmaf_rn(xf[0], bf16lo(wv.x), acc); acc = __fmaf_rn(xf[1], bf16hi(wv.x), acc);
+                acc = __fmaf_rn(xf[2], bf16lo(wv.y), acc); acc = __fmaf_rn(xf[3], bf16hi(wv.y), acc);
+                acc = __fmaf_rn(xf[4], bf16lo(wv.z), acc); acc = __fmaf_rn(xf[5], bf16hi(wv.z), acc);
+                acc = __fmaf_rn(xf[6], bf16lo(wv.w), acc); acc = __fmaf_rn(xf[7], bf16hi(wv.w), acc);
+            }
+        }
+        partial[i] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x < rows) {
+        const int e = e0 + threadIdx.x;
+        float total = 0.0f;
+        for (int c = 0; c < nchunks; ++c) total = __fadd_rn(total, partial[threadIdx.x * nchunks + c]);
+        if (p.logits_bf16) total = bf16_round(total);
+        if (p.bias) {
+            total = __fadd_rn(total, bf16_bits_to_f32(p.bias[e]));
+            if (p.logits_bf16) total = bf16_round(total);
+        }
+        logits_out[(size_t)t * E + e] = total;
+    }
+    // last block of this token routes it
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ticket_s = atomicAdd(&tickets[t], 1u);
+    __syncthreads();
+    if (ticket_s != gridDim.x - 1) return;
+    __threadfence();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) lsm[e] = __ldcg(logits_out + (size_t)t * E + e);
+    if (threadIdx.x == 0) tickets[t] = 0;  // ready for the next call
+    __syncthreads();
+    if (threadIdx.x < 32)
+        route_token_warp(p, lsm, lsm + E, threadIdx.x, indices + (size_t)t * p.top_k, weights + (size_t)t * p.top_k);
+}
+
+// Batched router projection for many tokens: a TB-token x 64-expert tile per block (TB = 64, 32 or
+// 16, chosen so the grid covers the SMs), 4x4 outputs
 // per thread, the hidden axis walked one 64-wide chunk at a time.  Inside a chunk every output
 // folds its products in ascending k with fused multiply-add from 0; the chunk sum is then added
 // to the running total — the same order as router_token_kernel, so both give identical bits.
 // Replaces the batched gate projection of MoELayer.decodeMany (FFAI MoELayer.swift:690,
 // Layers.swift:101-130, 217-287).
-template <int KIND, int BITS>
-__global__ void __launch_bounds__(256)
+template <int KIND, int BITS, int TB>
+__global__ void __launch_bounds__(TB * 4)
 router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
-                           float* __restrict__ logits_out) {
-    constexpr int TB = 64, EB = 64, LD = 68;  // LD: padded row length of the transposed tiles
+                           float* __restrict__ logits_out, float* __restrict__ partials) {
+    constexpr int EB = 64, LD = 68, NTHR = TB * 4;  // LD: padded row length of the transposed tiles
     __shared__ __align__(16) float xs[64 * LD];   // [k][token]
     __shared__ __align__(16) float ws[64 * LD];   // [k][expert]
     const int H = p.hidden, E = p.n_experts;
@@ -241,9 +343,13 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
 #pragma unroll
         for (int j = 0; j < 4; ++j) total[i][j] = 0.0f;
 
-    for (int k0 = 0; k0 < H; k0 += 64) {
+    // partials != nullptr: blockIdx.z selects one chunk; its sums go to partials[chunk][token][expert]
+    // and route_from_partials_kernel adds the chunks in ascending order (same bits, more blocks).
+    const int kbeg = partials ? (int)blockIdx.z * 64 : 0;
+    const int kend = partials ? kbeg + 64 : H;
+    for (int k0 = kbeg; k0 < kend; k0 += 64) {
         // stage the chunk: 64x64 activations and 64x64 weights, both as fp32, transposed
-        for (int i = threadIdx.x; i < 64 * 8; i += 256) {
+        for (int i = threadIdx.x; i < TB * 8; i += NTHR) {
             const int row = i >> 3, c8 = (i & 7) * 8;
             const int t = t0 + row;
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -257,7 +363,7 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
         }
         if (KIND == 1) {
             const float* w = (const float*)p.weight;
-            for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+            for (int i = threadIdx.x; i < 64 * 16; i += NTHR) {
                 const int row = i >> 4, c4 = (i & 15) * 4;
                 const int e = e0 + row;
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -267,7 +373,7 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
             }
         } else if (KIND == 2) {
             const uint16_t* w = (const uint16_t*)p.weight;
-            for (int i = threadIdx.x; i < 64 * 8; i += 256) {
+            for (int i = threadIdx.x; i < 64 * 8; i += NTHR) {
                 const int row = i >> 3, c8 = (i & 7) * 8;
                 const int e = e0 + row;
                 uint4 v = make_uint4(0, 0, 0, 0);
@@ -283,7 +389,7 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
             // affine: one thread unpacks a 32-run of one expert row (w = fma(scale, q, bias))
             const uint32_t* w = (const uint32_t*)p.weight;
             const int gpr = H / p.group_size;
-            for (int i = threadIdx.x; i < 64 * 2; i += 256) {
+            for (int i = threadIdx.x; i < 64 * 2; i += NTHR) {
                 const int row = i >> 1, h32 = (i & 1) * 32;
                 const int e = e0 + row;
                 if (e < E) {
@@ -336,6 +442,10 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
             const int e = e0 + tx * 4 + j;
             if (e >= E) continue;
             float v = total[i][j];
+            if (partials) {  // 0 + chunk sum is the chunk sum: exact
+                partials[((size_t)blockIdx.z * n_tokens + t) * E + e] = v;
+                continue;
+            }
             if (p.logits_bf16) v = bf16_round(v);
             if (p.bias) {
                 v = __fadd_rn(v, bf16_bits_to_f32(p.bias[e]));
@@ -344,6 +454,34 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
             logits_out[(size_t)t * E + e] = v;
         }
     }
+}
+
+// Second half of the chunk-split projection: one warp per token adds the chunk sums of every expert in
+// ascending chunk order (the fixed order), applies rounding and bias, and routes.
+__global__ void route_from_partials_kernel(RouterParams p, const float* __restrict__ partials, int n_chunks,
+                                           int n_tokens, uint32_t* __restrict__ indices,
+                                           float* __restrict__ weights, float* __restrict__ logits_out) {
+    extern __shared__ float smem[];
+    const int E = p.n_experts;
+    const int warps = blockDim.x / 32;
+    const int warp = threadIdx.x / 32, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * warps + warp;
+    float* logits_s = smem + (size_t)warp * 2 * E;
+    float* scratch = logits_s + E;
+    if (t >= n_tokens) return;
+    for (int e = lane; e < E; e += 32) {
+        float total = 0.0f;
+        for (int c = 0; c < n_chunks; ++c) total = __fadd_rn(total, partials[((size_t)c * n_tokens + t) * E + e]);
+        if (p.logits_bf16) total = bf16_round(total);
+        if (p.bias) {
+            total = __fadd_rn(total, bf16_bits_to_f32(p.bias[e]));
+            if (p.logits_bf16) total = bf16_round(total);
+        }
+        logits_s[e] = total;
+        if (logits_out) logits_out[(size_t)t * E + e] = total;
+    }
+    __syncwarp();
+    route_token_warp(p, logits_s, scratch, lane, indices + (size_t)t * p.top_k, weights + (size_t)t * p.top_k);
 }
 
 // Routing only (logits already computed): one warp per token.
