@@ -146,6 +146,10 @@ SIGNATURES = {
     "ffai_moe_forward": (C.c_int, [_P, _P, _I, _P, _P, C.POINTER(MoEDebug), _P]),
     "ffai_moe_forward_host": (C.c_int, [_P, _P, _I, _P, _P, C.POINTER(MoEDebug)]),
     "ffai_moe_set_nccl_comm": (C.c_int, [_P, _P]),
+    "ffai_ep_get_unique_id": (C.c_int, [_P]),
+    "ffai_ep_comm_create": (C.c_int, [_P, _I, _I, C.POINTER(_P)]),
+    "ffai_ep_comm_destroy": (C.c_int, [_P]),
+    "ffai_ep_plan_exchange": (C.c_uint32, [_P, _I, _I, _P, _P, _P, _P]),
     "ffai_moe_set_option": (C.c_int, [_P, C.c_char_p, _I]),
     "ffai_moe_check_device_status": (C.c_int, [_P]),
     "ffai_moe_read_timeline": (C.c_int, [_P, C.POINTER(C.c_int64), _I]),

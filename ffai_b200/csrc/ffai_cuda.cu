@@ -14,6 +14,7 @@
 #include "combine.cuh"
 #include "common.cuh"
 #include "expert_gemv.cuh"
+#include "ep.cuh"
 #include "expert_mma_decode.cuh"
 #include "plan.cuh"
 #include "router.cuh"
@@ -75,6 +76,16 @@ struct ffai_moe_layer {
     uint32_t* error_word = nullptr;
     CUtensorMap tm_gate{}, tm_up{}, tm_down{}, tm_sh_gate{}, tm_sh_up{}, tm_sh_down{};
     CUtensorMap tm_xg{}, tm_inner{}, tm_sh_x{}, tm_sh_inner{};  // activation maps: 64 k x 128-row boxes
+
+    // expert parallelism (ep_world > 1): Mx = rows that may arrive here = world * max_tokens * top_k
+    size_t mx_rows = 0;              // capacity of xg / inner / y in rows (== M when single GPU)
+    uint16_t* ep_send_x = nullptr;   // [M,H]   my rows sorted by (global) expert, ready to leave
+    uint16_t* ep_recv_x = nullptr;   // [Mx,H]  rows as they arrive, source-rank order
+    float* ep_ret_y = nullptr;       // [Mx,H]  expert outputs back in arrival order
+    float* ep_home_y = nullptr;      // [M,H]   my rows' outputs, in my sorted order
+    uint32_t* ep_recv_counts = nullptr;  // [world][E_local] rows per (source, local expert)
+    uint32_t* ep_plan_dev = nullptr;     // local_offsets[E_local+1] | seg_src | seg_dst  (each world*E_local)
+    uint32_t* ep_pin = nullptr;          // pinned: recv_counts | offsets[E+1] | plan upload staging
 
     // host-buffer entry point
     cudaStream_t own_stream = nullptr;
@@ -481,6 +492,8 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
 
     const size_t T = c.max_tokens, K = c.top_k, E = c.n_experts, H = c.hidden, I = c.intermediate;
     const size_t M = T * K;
+    const size_t Mx = M * (size_t)world;   // rows that can arrive at this rank under expert parallelism
+    L->mx_rows = Mx;
     if ((rc = ws_alloc(L, &L->logits, T * E))) return rc;
     if ((rc = ws_alloc(L, &L->indices, M))) return rc;
     if ((rc = ws_alloc(L, &L->rweights, M))) return rc;
@@ -495,8 +508,21 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
     }
     if ((rc = ws_alloc(L, &L->tickets, 96))) return rc;
     CUDA_TRY(L, cudaMemset(L->tickets, 0, 96 * sizeof(uint32_t)));
-    if ((rc = ws_alloc(L, &L->inner, M * I))) return rc;
-    if ((rc = ws_alloc(L, &L->y, M * H))) return rc;
+    if ((rc = ws_alloc(L, &L->inner, Mx * I))) return rc;
+    if ((rc = ws_alloc(L, &L->y, Mx * H))) return rc;
+    if (world > 1) {
+        const size_t El = L->e_local, W = world;
+        if ((rc = ws_alloc(L, &L->ep_send_x, M * H))) return rc;
+        if ((rc = ws_alloc(L, &L->ep_recv_x, Mx * H))) return rc;
+        if ((rc = ws_alloc(L, &L->ep_ret_y, Mx * H))) return rc;
+        if ((rc = ws_alloc(L, &L->ep_home_y, M * H))) return rc;
+        if ((rc = ws_alloc(L, &L->ep_recv_counts, W * El))) return rc;
+        if ((rc = ws_alloc(L, &L->ep_plan_dev, (El + 1) + 2 * W * El))) return rc;
+        void* pin = nullptr;
+        CUDA_TRY(L, cudaMallocHost(&pin, sizeof(uint32_t) * (W * El + (E + 1) + (El + 1) + 2 * W * El)));
+        L->owned_pinned.push_back(pin);
+        L->ep_pin = static_cast<uint32_t*>(pin);
+    }
     if (c.shared_intermediate > 0) {
         if ((rc = ws_alloc(L, &L->sh_inner, T * c.shared_intermediate))) return rc;
         if ((rc = ws_alloc(L, &L->sh_y, T * H))) return rc;
@@ -513,15 +539,15 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
     const bool tc_shapes = H >= 256 && I >= 256 && (c.shared_intermediate == 0 || c.shared_intermediate >= 256);
     const bool want_tc = cc_major == 10 && tc_shapes;
     if (c.expert_bits == 4 || (want_tc && c.shared_intermediate > 0 && c.shared_bits == 4)) {
-        const size_t Mp = M < 128 ? 128 : M, Tp = T < 128 ? 128 : T;  // at least one full TMA box of rows
+        const size_t Mp = Mx < 128 ? 128 : Mx, Tp = T < 128 ? 128 : T;  // at least one full TMA box of rows
         if ((rc = ws_alloc(L, &L->xg, Mp * H))) return rc;
         if ((rc = ws_alloc(L, &L->inner_bf, Mp * I))) return rc;
         // 64-run sums, row pitch rounded up to 4 floats (16-byte rows for cp.async), + one spare row
-        if ((rc = ws_alloc(L, &L->xsum, (M + 1) * (size_t)((H / 64 + 3) & ~3)))) return rc;
-        if ((rc = ws_alloc(L, &L->inner_sum, (M + 1) * (size_t)((I / 64 + 3) & ~3)))) return rc;
+        if ((rc = ws_alloc(L, &L->xsum, (Mx + 1) * (size_t)((H / 64 + 3) & ~3)))) return rc;
+        if ((rc = ws_alloc(L, &L->inner_sum, (Mx + 1) * (size_t)((I / 64 + 3) & ~3)))) return rc;
         L->mma_ok = c.expert_bits == 4 && (c.expert_group_size == 64 || c.expert_group_size == 128);
         if (want_tc) {
-            if ((rc = ws_alloc(L, &L->y_bf, M * H))) return rc;
+            if (world == 1 && (rc = ws_alloc(L, &L->y_bf, M * H))) return rc;
             if ((rc = ws_alloc(L, &L->tile_offsets, E + 1))) return rc;
             if (c.shared_intermediate > 0 && c.shared_bits == 4) {
                 if ((rc = ws_alloc(L, &L->sh_x, Tp * H))) return rc;
@@ -530,6 +556,7 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
             }
         }
     }
+    if (world > 1 && !L->xg && (rc = ws_alloc(L, &L->xg, Mx * H))) return rc;  // regrouped rows for the GEMV path
     return FFAI_OK;
 }
 
@@ -576,7 +603,7 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
     L->tc_ok = false;
     if (L->tile_offsets) {
         using namespace g100;
-        uint64_t Mcap = (uint64_t)c.max_tokens * c.top_k, Tcap = (uint64_t)c.max_tokens;
+        uint64_t Mcap = L->mx_rows, Tcap = (uint64_t)c.max_tokens;
         if (Mcap < 128) Mcap = 128;
         if (Tcap < 128) Tcap = 128;
         bool ok = true;
@@ -639,6 +666,40 @@ extern "C" FFAI_API int ffai_moe_set_nccl_comm(ffai_moe_layer* L, void* comm) {
     if (!L) return FFAI_ERR_INVALID_ARG;
     L->nccl_comm = comm;
     return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_ep_get_unique_id(uint8_t out_id[128]) {
+    if (!out_id) return FFAI_ERR_INVALID_ARG;
+    static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId size");
+    if (!ep::nccl().ok) return FFAI_ERR_NCCL;
+    ncclUniqueId id;
+    if (ep::nccl().GetUniqueId(&id) != ncclSuccess) return FFAI_ERR_NCCL;
+    memcpy(out_id, &id, 128);
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_ep_comm_create(const uint8_t id_bytes[128], int32_t rank, int32_t world, void** out_comm) {
+    if (!id_bytes || !out_comm || world < 1 || rank < 0 || rank >= world) return FFAI_ERR_INVALID_ARG;
+    if (!ep::nccl().ok) return FFAI_ERR_NCCL;
+    ncclUniqueId id;
+    memcpy(&id, id_bytes, 128);
+    ncclComm_t comm = nullptr;
+    if (ep::nccl().CommInitRank(&comm, world, id, rank) != ncclSuccess) return FFAI_ERR_NCCL;
+    *out_comm = comm;
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_ep_comm_destroy(void* comm) {
+    if (!comm) return FFAI_OK;
+    if (!ep::nccl().ok) return FFAI_ERR_NCCL;
+    return ep::nccl().CommDestroy(static_cast<ncclComm_t>(comm)) == ncclSuccess ? FFAI_OK : FFAI_ERR_NCCL;
+}
+
+extern "C" FFAI_API uint32_t ffai_ep_plan_exchange(const uint32_t* recv_counts, int32_t world, int32_t e_local,
+                                                   uint32_t* rank_offsets, uint32_t* local_offsets,
+                                                   uint32_t* seg_src, uint32_t* seg_dst) {
+    if (!recv_counts || !rank_offsets || !local_offsets || !seg_src || !seg_dst || world < 1 || e_local < 1) return 0;
+    return ep::plan_exchange(recv_counts, world, e_local, rank_offsets, local_offsets, seg_src, seg_dst);
 }
 
 extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name, int32_t value) {
@@ -770,6 +831,187 @@ int copy_debug(ffai_moe_layer* L, const ffai_moe_debug* d, int T, cudaStream_t s
     return FFAI_OK;
 }
 
+
+// ───────────────────────────── expert parallelism ─────────────────────────────
+
+#define NCCL_TRY(L, expr)                                                                        \
+    do {                                                                                         \
+        ncclResult_t _r = (expr);                                                                \
+        if (_r != ncclSuccess)                                                                   \
+            return fail((L), FFAI_ERR_NCCL, "%s failed: %s", #expr,                              \
+                        ep::nccl().GetErrorString ? ep::nccl().GetErrorString(_r) : "nccl error"); \
+    } while (0)
+
+// All-to-all of byte ranges: rank d gets send[off_s[d], +len_s[d]); rank s's range lands at recv[off_r[s], +len_r[s]).
+int ep_all_to_all(ffai_moe_layer* L, const uint8_t* send, const size_t* off_s, const size_t* len_s, uint8_t* recv,
+                  const size_t* off_r, const size_t* len_r, cudaStream_t st) {
+    ep::NcclApi& n = ep::nccl();
+    ncclComm_t comm = static_cast<ncclComm_t>(L->nccl_comm);
+    const int W = L->cfg.ep_world, me = L->cfg.ep_rank;
+    NCCL_TRY(L, n.GroupStart());
+    for (int d = 0; d < W; ++d) {
+        if (d == me) continue;
+        if (len_s[d]) NCCL_TRY(L, n.Send(send + off_s[d], len_s[d], ncclUint8, d, comm, st));
+        if (len_r[d]) NCCL_TRY(L, n.Recv(recv + off_r[d], len_r[d], ncclUint8, d, comm, st));
+    }
+    NCCL_TRY(L, n.GroupEnd());
+    if (len_s[me]) CUDA_TRY(L, cudaMemcpyAsync(recv + off_r[me], send + off_s[me], len_s[me], cudaMemcpyDeviceToDevice, st));
+    return FFAI_OK;
+}
+
+// Whether rows travel 8-run permuted (the layout both 4-bit kernels read).  Every rank must agree, so
+// the rule looks only at the layer's configuration and options.
+bool ep_rows_perm8(const ffai_moe_layer* L) { return L->mma_ok && L->opt_path != 1; }
+
+// Routed experts over rows that are already expert-contiguous in L->xg (bf16; 8-run permuted when the layer's
+// experts are 4-bit with group 64/128, plain otherwise).  Output: fp32 rows in L->y.
+int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t* offsets_dev, cudaStream_t st) {
+    const ffai_moe_config& c = L->cfg;
+    const int H = c.hidden, I = c.intermediate;
+    if (n_rows <= 0) return FFAI_OK;
+    const double rpe = (double)n_rows / n_exp;
+    const bool can_tc = L->tc_ok && c.expert_bits == 4;
+    bool use_mma = false, use_tc = false;
+    if (ep_rows_perm8(L)) {   // the rows arrived 8-run permuted: one of the two 4-bit kernels must take them
+        if (L->opt_path == 3) use_mma = true;
+        else if (L->opt_path == 2) use_tc = can_tc;
+        else use_tc = can_tc && rpe > 12.0;
+        use_mma = !use_tc;
+    }
+    if (use_mma) {
+        using namespace dmma;
+        const int xp_h = (H / 64 + 3) & ~3, xp_i = (I / 64 + 3) & ~3;
+        sum64_rows_kernel<<<(n_rows + 7) / 8, 256, 0, st>>>(L->xg, L->xsum, n_rows, H, xp_h);
+        Params p{};
+        p.group_size = c.expert_group_size;
+        p.offsets = offsets_dev;
+        p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
+        const int nt = rpe > 4.0 ? 2 : 1;
+        const int ksplit = L->opt_ksplit > 0 ? L->opt_ksplit : (n_rows <= 8 ? 4 : (n_rows <= 24 ? 2 : 1));
+        p.w1 = L->w.gate_proj.weight; p.s1 = L->w.gate_proj.scales; p.b1 = L->w.gate_proj.biases; p.rb1 = L->w.gate_proj.row_bias;
+        p.w2 = L->w.up_proj.weight; p.s2 = L->w.up_proj.scales; p.b2 = L->w.up_proj.biases; p.rb2 = L->w.up_proj.row_bias;
+        p.sb1 = L->sb_gate; p.sb2 = L->sb_up;
+        p.N = I; p.K = H; p.x = L->xg; p.xsum = L->xsum; p.xsum_pitch = xp_h; p.out = L->inner_bf;
+        launch_mma_decode<true>(p, n_exp, nt, ksplit, st);
+        sum64_rows_kernel<<<(n_rows + 7) / 8, 256, 0, st>>>(L->inner_bf, L->inner_sum, n_rows, I, xp_i);
+        p.w1 = L->w.down_proj.weight; p.s1 = L->w.down_proj.scales; p.b1 = L->w.down_proj.biases; p.rb1 = L->w.down_proj.row_bias;
+        p.w2 = nullptr; p.s2 = nullptr; p.b2 = nullptr; p.rb2 = nullptr;
+        p.sb1 = L->sb_down; p.sb2 = nullptr;
+        p.N = H; p.K = I; p.x = L->inner_bf; p.xsum = L->inner_sum; p.xsum_pitch = xp_i; p.out = L->y;
+        launch_mma_decode<false>(p, n_exp, nt, ksplit, st);
+        L->launches += 4;
+    } else if (use_tc) {
+        using namespace g100;
+        tile_schedule_kernel<<<1, 32, 0, st>>>(offsets_dev, n_exp, BM, L->tile_offsets);
+        Params p{};
+        p.n_experts = n_exp; p.group_size = c.expert_group_size;
+        p.offsets = offsets_dev; p.tile_offsets = L->tile_offsets;
+        p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
+        p.error_word = L->error_word;
+        p.scales = L->w.gate_proj.scales; p.biases = L->w.gate_proj.biases; p.row_bias = L->w.gate_proj.row_bias;
+        p.scales2 = L->w.up_proj.scales; p.biases2 = L->w.up_proj.biases; p.row_bias2 = L->w.up_proj.row_bias;
+        p.n_out = I; p.K = H; p.m_tiles = (I + BN / 2 - 1) / (BN / 2);
+        p.out = L->inner_bf; p.out_ld = I; p.out_permute8 = 1;
+        if (launch_grouped_gemm<true, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg, p, L->n_sms, st))
+            return fail(L, FFAI_ERR_CUDA, "gate/up grouped GEMM launch failed");
+        p.scales = L->w.down_proj.scales; p.biases = L->w.down_proj.biases; p.row_bias = L->w.down_proj.row_bias;
+        p.scales2 = nullptr; p.biases2 = nullptr; p.row_bias2 = nullptr;
+        p.n_out = H; p.K = I; p.m_tiles = (H + BN - 1) / BN;
+        p.out = L->y; p.out_ld = H; p.out_permute8 = 0;
+        if (launch_grouped_gemm<false, float>(L->tm_down, L->tm_down, L->tm_inner, p, L->n_sms, st))
+            return fail(L, FFAI_ERR_CUDA, "down grouped GEMM launch failed");
+        L->launches += 3;
+    } else {
+        int rc;
+        GemvParams p = gemv_params(L->w.gate_proj, &L->w.up_proj, I, H, c.expert_group_size, n_exp);
+        p.offsets = offsets_dev;
+        p.n_rows = n_rows;
+        p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
+        if ((rc = launch_grouped_gemv<uint16_t, float, true>(p, c.expert_bits, L->xg, L->inner, n_exp, st))) return fail(L, rc, "gate/up launch failed");
+        GemvParams d = gemv_params(L->w.down_proj, nullptr, H, I, c.expert_group_size, n_exp);
+        d.offsets = offsets_dev;
+        d.n_rows = n_rows;
+        if ((rc = launch_grouped_gemv<float, float, false>(d, c.expert_bits, L->inner, L->y, n_exp, st))) return fail(L, rc, "down launch failed");
+        L->launches += 2;
+    }
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : fail(L, FFAI_ERR_CUDA, "expert kernels launch failed");
+}
+
+// The routed experts under expert parallelism: exchange counts, dispatch rows, compute, return rows.
+// On return L->ep_home_y holds, in this rank's sorted-row order, the fp32 expert outputs of its own rows.
+int forward_experts_ep(ffai_moe_layer* L, const uint16_t* x, int T, cudaStream_t st) {
+    const ffai_moe_config& c = L->cfg;
+    const int H = c.hidden, E = c.n_experts, K = c.top_k, W = c.ep_world, me = c.ep_rank, El = L->e_local;
+    const int M = T * K;
+    if (!L->nccl_comm || !ep::nccl().ok) return fail(L, FFAI_ERR_NCCL, "expert parallelism needs ffai_moe_set_nccl_comm first");
+    int rc;
+    // rows leave sorted by (expert, token, slot); 8-run permuted when the 4-bit kernels will consume them
+    stage_begin(L, ST_GATHER, st);
+    if (M == 0) { /* nothing leaves this rank */ }
+    else if (ep_rows_perm8(L)) g100::gather_rows_perm8_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, K, L->ep_send_x, M, H);
+    else gather_rows_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, K, L->ep_send_x, M, H);
+    L->launches += 1;
+    stage_end(L, ST_GATHER, st);
+
+    stage_begin(L, ST_EXCHANGE, st);
+    // 1. counts: rank d learns how many of my rows go to each of its experts
+    std::vector<size_t> so(W), sl(W), ro(W), rl(W);
+    for (int d = 0; d < W; ++d) { so[d] = (size_t)d * El * 4; sl[d] = (size_t)El * 4; ro[d] = (size_t)d * El * 4; rl[d] = (size_t)El * 4; }
+    if ((rc = ep_all_to_all(L, (const uint8_t*)L->counts, so.data(), sl.data(), (uint8_t*)L->ep_recv_counts, ro.data(), rl.data(), st))) return rc;
+    uint32_t* h_rc = L->ep_pin;                 // [W*El]
+    uint32_t* h_off = h_rc + (size_t)W * El;     // [E+1]
+    uint32_t* h_plan = h_off + (E + 1);          // local_offsets[El+1] | seg_src[W*El] | seg_dst[W*El]
+    CUDA_TRY(L, cudaMemcpyAsync(h_rc, L->ep_recv_counts, sizeof(uint32_t) * W * El, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(L, cudaMemcpyAsync(h_off, L->offsets, sizeof(uint32_t) * (E + 1), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(L, cudaStreamSynchronize(st));      // the one host round trip of the exchange: NCCL needs sizes on the host
+    // 2. plan
+    std::vector<uint32_t> rank_off(W + 1);
+    uint32_t* local_off = h_plan;
+    uint32_t* seg_src = h_plan + (El + 1);
+    uint32_t* seg_dst = seg_src + (size_t)W * El;
+    const uint32_t n_recv = ep::plan_exchange(h_rc, W, El, rank_off.data(), local_off, seg_src, seg_dst);
+    if (n_recv > L->mx_rows) return fail(L, FFAI_ERR_INVALID_ARG, "expert-parallel receive of %u rows exceeds capacity %zu", n_recv, L->mx_rows);
+    CUDA_TRY(L, cudaMemcpyAsync(L->ep_plan_dev, h_plan, sizeof(uint32_t) * ((El + 1) + 2 * (size_t)W * El), cudaMemcpyHostToDevice, st));
+    const uint32_t* d_local_off = L->ep_plan_dev;
+    const uint32_t* d_seg_src = L->ep_plan_dev + (El + 1);
+    const uint32_t* d_seg_dst = d_seg_src + (size_t)W * El;
+    // 3. dispatch rows
+    const size_t xrow = (size_t)H * 2, yrow = (size_t)H * 4;
+    for (int d = 0; d < W; ++d) {
+        so[d] = (size_t)h_off[d * El] * xrow;
+        sl[d] = (size_t)(h_off[(d + 1) * El] - h_off[d * El]) * xrow;
+        ro[d] = (size_t)rank_off[d] * xrow;
+        rl[d] = (size_t)(rank_off[d + 1] - rank_off[d]) * xrow;
+    }
+    if ((rc = ep_all_to_all(L, (const uint8_t*)L->ep_send_x, so.data(), sl.data(), (uint8_t*)L->ep_recv_x, ro.data(), rl.data(), st))) return rc;
+    // 4. regroup the per-source segments of each local expert (ascending source rank)
+    if (n_recv) {
+        ep::copy_segments_kernel<<<dim3(W * El, 8), 256, 0, st>>>((const uint8_t*)L->ep_recv_x, (uint8_t*)L->xg, d_seg_src, d_seg_dst, L->ep_recv_counts, (int)xrow);
+        L->launches += 1;
+    }
+    stage_end(L, ST_EXCHANGE, st);
+
+    stage_begin(L, ST_GATE_UP, st);
+    if ((rc = run_experts_on_rows(L, (int)n_recv, El, d_local_off, st))) return rc;
+    stage_end(L, ST_GATE_UP, st);
+
+    stage_begin(L, ST_EXCHANGE, st);
+    if (n_recv) {
+        ep::copy_segments_kernel<<<dim3(W * El, 8), 256, 0, st>>>((const uint8_t*)L->y, (uint8_t*)L->ep_ret_y, d_seg_dst, d_seg_src, L->ep_recv_counts, (int)yrow);
+        L->launches += 1;
+    }
+    // 5. results travel back along the same segments
+    for (int d = 0; d < W; ++d) {
+        const size_t s_off = so[d] / xrow, s_rows = sl[d] / xrow, r_off = ro[d] / xrow, r_rows = rl[d] / xrow;
+        so[d] = r_off * yrow; sl[d] = r_rows * yrow;   // what I received from d goes back to d
+        ro[d] = s_off * yrow; rl[d] = s_rows * yrow;   // what I sent to d comes back into my sorted order
+    }
+    if ((rc = ep_all_to_all(L, (const uint8_t*)L->ep_ret_y, so.data(), sl.data(), (uint8_t*)L->ep_home_y, ro.data(), rl.data(), st))) return rc;
+    stage_end(L, ST_EXCHANGE, st);
+    (void)me;
+    return FFAI_OK;
+}
+
 int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, const uint16_t* residual,
                    cudaStream_t st) {
     const ffai_moe_config& c = L->cfg;
@@ -778,6 +1020,11 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     int rc;
     L->launches = 0;
     for (auto& n : L->ev_segments) n = 0;
+    if (T == 0) {   // expert parallelism only: no rows of its own, but its experts serve the other ranks
+        CUDA_TRY(L, cudaMemsetAsync(L->counts, 0, sizeof(uint32_t) * E, st));
+        CUDA_TRY(L, cudaMemsetAsync(L->offsets, 0, sizeof(uint32_t) * (E + 1), st));
+        return forward_experts_ep(L, x, 0, st);
+    }
 
     // stage 0: router (projection + bias + top-k + softmax)
     stage_begin(L, ST_ROUTER, st);
@@ -804,6 +1051,10 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     L->launches += nl;
     stage_end(L, ST_PLAN, st);
 
+    const bool ep_on = c.ep_world > 1;
+    if (ep_on) {
+        if ((rc = forward_experts_ep(L, x, T, st))) return rc;
+    }
     // Path choice for the routed experts:
     //   register-streaming mma kernels  4-bit, few rows per expert (decode): bound by HBM
     //   tcgen05 grouped GEMM            4-bit, many rows per expert (prefill): bound by the tensor cores
@@ -811,7 +1062,8 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     const double rows_per_expert = (double)M / E;
     const bool can_tc = L->tc_ok && c.expert_bits == 4;
     bool mma_experts = false, tc_experts = false;
-    if (L->opt_path == 3) mma_experts = L->mma_ok;
+    if (ep_on) { /* done above */ }
+    else if (L->opt_path == 3) mma_experts = L->mma_ok;
     else if (L->opt_path == 2) tc_experts = can_tc;
     else if (L->opt_path == 0) {
         if (L->mma_ok && (rows_per_expert <= 12.0 || !can_tc)) mma_experts = rows_per_expert <= 48.0;
@@ -893,7 +1145,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
             return fail(L, FFAI_ERR_CUDA, "down grouped GEMM launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += 1;
         stage_end(L, ST_DOWN, st);
-    } else {
+    } else if (!ep_on) {
         // gate/up products + activation -> inner[M, I]; rows are read through the permutation
         stage_begin(L, ST_GATE_UP, st);
         {
@@ -982,7 +1234,9 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     }
     stage_end(L, ST_SHARED, st);
     stage_begin(L, ST_COMBINE, st);
-    if (tc_experts)
+    if (ep_on)
+        combine_kernel<float, float><<<T, 256, 0, st>>>(L->ep_home_y, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
+    else if (tc_experts)
         combine_kernel<uint16_t, float><<<T, 256, 0, st>>>(L->y_bf, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
     else
         combine_kernel<float, float><<<T, 256, 0, st>>>(L->y, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
@@ -1008,7 +1262,7 @@ extern "C" FFAI_API int ffai_moe_forward(ffai_moe_layer* L, const uint16_t* x, i
                                 const uint16_t* residual, const ffai_moe_debug* debug, void* stream) {
     int rc = check_forward_args(L, x, T, out);
     if (rc) return rc;
-    if (T == 0) return FFAI_OK;
+    if (T == 0 && L->cfg.ep_world <= 1) return FFAI_OK;   // an expert-parallel rank without tokens still serves its experts
     if (!aligned16(x) || !aligned16(out) || (residual && !aligned16(residual)))
         return fail(L, FFAI_ERR_INVALID_ARG, "x/out/residual must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -1020,7 +1274,7 @@ extern "C" FFAI_API int ffai_moe_forward_host(ffai_moe_layer* L, const uint16_t*
                                      const uint16_t* residual, const ffai_moe_debug* debug) {
     int rc = check_forward_args(L, x, T, out);
     if (rc) return rc;
-    if (T == 0) return FFAI_OK;
+    if (T == 0 && L->cfg.ep_world <= 1) return FFAI_OK;
     const ffai_moe_config& c = L->cfg;
     CUDA_TRY(L, cudaSetDevice(L->device));
     const size_t cap = (size_t)c.max_tokens * c.hidden * 2;
@@ -1036,17 +1290,34 @@ extern "C" FFAI_API int ffai_moe_forward_host(ffai_moe_layer* L, const uint16_t*
     }
     cudaStream_t st = L->own_stream;
     const size_t bytes = (size_t)T * c.hidden * 2;
-    // Stage through pinned memory so the copies are asynchronous DMA whatever the caller's buffer is.
-    memcpy(L->pin_x, x, bytes);
-    CUDA_TRY(L, cudaMemcpyAsync(L->dev_x, L->pin_x, bytes, cudaMemcpyHostToDevice, st));
+    // Page-locked caller buffers are copied from directly; pageable ones are staged through the handle's
+    // pinned buffers so the transfers are asynchronous DMA either way.
+    auto is_pinned = [](const void* p) {
+        cudaPointerAttributes a;
+        if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+        return a.type == cudaMemoryTypeHost;
+    };
+    const bool x_pinned = is_pinned(x), out_pinned = is_pinned(out);
+    if (bytes == 0) {
+        // nothing to stage
+    } else if (x_pinned) {
+        CUDA_TRY(L, cudaMemcpyAsync(L->dev_x, x, bytes, cudaMemcpyHostToDevice, st));
+    } else {
+        memcpy(L->pin_x, x, bytes);
+        CUDA_TRY(L, cudaMemcpyAsync(L->dev_x, L->pin_x, bytes, cudaMemcpyHostToDevice, st));
+    }
     const uint16_t* dres = nullptr;
-    if (residual) {
-        memcpy(L->pin_res, residual, bytes);
-        CUDA_TRY(L, cudaMemcpyAsync(L->dev_res, L->pin_res, bytes, cudaMemcpyHostToDevice, st));
+    if (residual && bytes) {
+        if (is_pinned(residual)) {
+            CUDA_TRY(L, cudaMemcpyAsync(L->dev_res, residual, bytes, cudaMemcpyHostToDevice, st));
+        } else {
+            memcpy(L->pin_res, residual, bytes);
+            CUDA_TRY(L, cudaMemcpyAsync(L->dev_res, L->pin_res, bytes, cudaMemcpyHostToDevice, st));
+        }
         dres = L->dev_res;
     }
     if ((rc = forward_device(L, L->dev_x, T, L->dev_out, dres, st))) return rc;
-    CUDA_TRY(L, cudaMemcpyAsync(L->pin_out, L->dev_out, bytes, cudaMemcpyDeviceToHost, st));
+    if (bytes) CUDA_TRY(L, cudaMemcpyAsync(out_pinned ? out : L->pin_out, L->dev_out, bytes, cudaMemcpyDeviceToHost, st));
     if ((rc = copy_debug(L, debug, T, st, cudaMemcpyDeviceToHost))) return rc;
     uint32_t* pin_err = reinterpret_cast<uint32_t*>(L->pin_res + cap / 2);
     CUDA_TRY(L, cudaMemcpyAsync(pin_err, L->error_word, 4, cudaMemcpyDeviceToHost, st));
@@ -1055,7 +1326,7 @@ extern "C" FFAI_API int ffai_moe_forward_host(ffai_moe_layer* L, const uint16_t*
         cudaMemsetAsync(L->error_word, 0, 4, st);
         return fail(L, FFAI_ERR_DEVICE_CHECK, "a kernel gave up a bounded wait (code %u)", *pin_err);
     }
-    memcpy(out, L->pin_out, bytes);
+    if (!out_pinned && bytes) memcpy(out, L->pin_out, bytes);
     return FFAI_OK;
 }
 

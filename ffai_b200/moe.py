@@ -42,7 +42,10 @@ class MoELayer:
     then call forward with ``[T, hidden]`` bf16 rows.
     """
 
-    def __init__(self, host_layer: HostLayer, max_tokens: int, ep_rank: int = 0, ep_world: int = 1):
+    def __init__(self, host_layer: HostLayer, max_tokens: int, ep_rank: int = 0, ep_world: int = 1,
+                 ep_comm: Optional[C.c_void_p] = None):
+        """``ep_world > 1`` shards the experts: this rank keeps block ``ep_rank`` of ``E/ep_world``
+        experts and ``ep_comm`` (see ``ffai_b200.ep``) carries the two row exchanges."""
         self.lib = capi.load()
         self.spec = host_layer.spec
         self.max_tokens = max_tokens
@@ -59,6 +62,8 @@ class MoELayer:
                     self.lib.ffai_moe_destroy(h)
         w = host_layer.weights_struct(ep_rank, ep_world)
         capi.check(self.lib.ffai_moe_set_weights(self.handle, C.byref(w)), "ffai_moe_set_weights", self.handle)
+        if ep_comm is not None:
+            capi.check(self.lib.ffai_moe_set_nccl_comm(self.handle, ep_comm), "ffai_moe_set_nccl_comm", self.handle)
 
     # host buffers in, host buffers out (copies inside the call)
     def forward_host(self, x: np.ndarray, residual: Optional[np.ndarray] = None,

@@ -218,6 +218,21 @@ FFAI_API int ffai_moe_forward_host(ffai_moe_layer* layer, const uint16_t* x, int
  * reference is single-device). */
 FFAI_API int ffai_moe_set_nccl_comm(ffai_moe_layer* layer, void* nccl_comm);
 
+/* Expert-parallel plumbing (no reference counterpart).  Rank 0 makes an id, the host code hands the 128
+ * bytes to every rank (any transport), each rank creates its communicator with its GPU current and
+ * attaches it with ffai_moe_set_nccl_comm.  NCCL is looked up at run time; single-GPU use needs none. */
+FFAI_API int ffai_ep_get_unique_id(uint8_t out_id[128]);
+FFAI_API int ffai_ep_comm_create(const uint8_t id[128], int32_t rank, int32_t world, void** out_comm);
+FFAI_API int ffai_ep_comm_destroy(void* comm);
+/* Host-side plan of one exchange from the per-(source rank, local expert) row counts
+ * recv_counts[world][e_local]: where each source's rows start in the receive buffer
+ * (rank_offsets[world+1]), the expert-contiguous layout after regrouping (local_offsets[e_local+1]),
+ * and the start of every (source, expert) segment in both (seg_src, seg_dst, [world*e_local]).
+ * Returns the number of rows received.  Integer arithmetic only; needs no GPU. */
+FFAI_API uint32_t ffai_ep_plan_exchange(const uint32_t* recv_counts, int32_t world, int32_t e_local,
+                                        uint32_t* rank_offsets, uint32_t* local_offsets,
+                                        uint32_t* seg_src, uint32_t* seg_dst);
+
 /* Execution options, replacing the reference's FFAI_MOE_* environment switches
  * (Sources/FFAI/Models/MoELayer.swift:486-497).  Names:
  *   "path"         0 automatic, 1 CUDA-core grouped GEMV only, 2 tcgen05 grouped GEMM whenever possible

@@ -1,0 +1,92 @@
+"""One rank of the expert-parallel GPU test, as run by test_gpu_ep.py (one process per GPU).
+
+Every rank holds the same layer (seeded) and its own tokens.  It runs the block with the experts
+sharded over the ranks and checks, per case: routing and dispatch plan bit-exact against the oracle,
+output within the parity gate against the oracle, and against the same block run with all experts
+on this GPU alone.
+usage: ep_gpu_worker.py <rank> <world> <port> <out.json>
+"""
+import json
+import os
+import sys
+import traceback
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+sys.path.insert(0, HERE)
+
+import torch
+import torch.distributed as dist
+
+import oracle
+from ffai_b200 import capi, ep, synth
+from ffai_b200.moe import MoELayer
+from helpers import parity
+
+CASES = [
+    # name, spec, tokens on rank r, forced path (None = automatic)
+    ("tiny_fp32_router", synth.cfg1_tiny(), lambda r: 16 + 4 * r, None),
+    ("tiny_gemv_forced", synth.cfg1_tiny(), lambda r: 9, 1),
+    ("gptoss_decode", synth.cfg2_gptoss(), lambda r: 8, None),
+    ("gptoss_decode_one_token", synth.cfg2_gptoss(), lambda r: 1, None),
+    ("qwen_prefill_tcgen05", synth.cfg3_qwen().with_(n_experts=32, name="qwen_32e"), lambda r: 192 + 64 * r, None),
+    ("six_bit_gemv", synth.LayerSpec("bits6", 512, 256, 16, 4, expert_bits=6), lambda r: 40, None),
+    ("shared_expert", synth.cfg4_shared().with_(n_experts=32, name="shared_32e"), lambda r: 24, None),
+    ("rank_without_tokens", synth.cfg1_tiny(), lambda r: 0 if r == 1 else 12, None),
+]
+
+
+def main():
+    rank, world, port, out_path = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), sys.argv[4]
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    torch.zeros(1, device="cuda")
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=120))
+    comm = ep.comm_from_store(store, rank, world)
+    results = []
+    try:
+        for name, spec, tokens_of, path in CASES:
+            T = tokens_of(rank)
+            max_t = max(tokens_of(r) for r in range(world))
+            host = synth.make_layer(spec, seed=5)
+            x = synth.make_tokens(T, spec.hidden, seed=1000 + rank) if T else np.zeros((0, spec.hidden), np.uint16)
+            lay = MoELayer(host, max_t, ep_rank=rank, ep_world=world, ep_comm=comm)
+            one = MoELayer(host, max(max_t, 1))
+            rec = {"case": name, "tokens": T}
+            try:
+                if path is not None:
+                    lay.set_option("path", path)
+                    one.set_option("path", path)
+                out, dbg = lay.forward_host(x, debug=True)
+                out2, _ = lay.forward_host(x)                      # a second call reuses every buffer
+                lay.check_device_status()
+                if T:
+                    solo, _ = one.forward_host(x)
+                    ref = oracle.moe_forward(host, x)
+                    rec["routing_exact"] = bool(np.array_equal(dbg.indices, ref.indices) and np.array_equal(dbg.weights, ref.weights)
+                                                and np.array_equal(dbg.perm, ref.perm) and np.array_equal(dbg.offsets, ref.offsets))
+                    pr = parity(out, ref.out_f32)
+                    rec["rel_rms"], rec["max_abs_norm"] = pr["rel_rms"], pr["max_abs_norm"]
+                    rec["rel_rms_vs_single_gpu"] = parity(out, synth.bf16_to_f32(solo))["rel_rms"]
+                    rec["repeatable"] = bool(np.array_equal(out, out2))
+                rec["launches"] = lay.launch_count()
+            finally:
+                lay.close()
+                one.close()
+            results.append(rec)
+        status = "ok"
+    except Exception:
+        status = traceback.format_exc()
+    torch.cuda.synchronize()
+    store.set(f"done{rank}", b"1")
+    for r in range(world):
+        store.wait([f"done{r}"])
+    ep.comm_destroy(comm)
+    with open(out_path, "w") as f:
+        json.dump({"rank": rank, "status": status, "cases": results}, f)
+
+
+if __name__ == "__main__":
+    main()

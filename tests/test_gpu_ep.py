@@ -1,0 +1,49 @@
+"""Expert parallelism on two GPUs: experts sharded across ranks, rows exchanged over NCCL inside
+the library.  Skipped on a single-GPU machine (the host-side protocol is covered on the CPU by
+test_ep_host.py)."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+from ffai_b200 import capi
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_two_gpu_expert_parallel_matches_oracle_and_single_gpu(tmp_path, ffai_lib, oracle_mod):
+    if capi.load().ffai_cuda_device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = []
+    for r in range(2):
+        out = tmp_path / f"r{r}.json"
+        procs.append((out, subprocess.Popen([sys.executable, os.path.join(HERE, "ep_gpu_worker.py"), str(r), "2", str(port), str(out)],
+                                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env)))
+    logs = []
+    for out, p in procs:
+        try:
+            log, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            raise
+        logs.append(log.decode()[-3000:])
+        assert p.returncode == 0, logs[-1]
+    for out, _ in procs:
+        res = json.loads(out.read_text())
+        assert res["status"] == "ok", res["status"]
+        assert len(res["cases"]) >= 8
+        for c in res["cases"]:
+            if not c["tokens"]:
+                continue
+            assert c["routing_exact"], c
+            assert c["repeatable"], c
+            assert c["rel_rms"] <= 5e-3 and c["max_abs_norm"] <= 2e-2, c
+            assert c["rel_rms_vs_single_gpu"] <= 5e-3, c
