@@ -7,11 +7,16 @@ Workloads (seeded synthetic weights and activations, shapes of the benchmark con
     cfg2_b64 (default), cfg2_b1, cfg2_b8, cfg2_b32   GPT-OSS-20B-shaped decode batches
     cfg3                                            Qwen3-30B-A3B-shaped 2048-token prefill
     cfg1                                            tiny layer
+    cfg4_ep, cfg3_ep                                256- / 128-expert layers, 2048 tokens per rank, experts
+                                                    sharded over the N ranks (expert parallelism: two NCCL
+                                                    all-to-all exchanges inside the timed step); N = 1 runs
+                                                    the same layer with all experts on one GPU
 
 A step is one forward of the layer over one batch.  Each step is timed on the device with a
 CUDA-event pair on the launching stream; between steps a 256 MiB buffer is overwritten so the
 next step finds none of its weights in L2 (the flush is not timed).  With N > 1 every rank runs
 its own replica of the layer on its own batch (decode does not shard); time is the max over ranks.
+The *_ep workloads instead shard the experts over the ranks and keep the tokens per rank fixed.
 
 One JSON line is printed by rank 0.  `value` is device-resident throughput, `e2e` the same metric
 through the host-buffer entry point of the C ABI (pinned-memory copies inside the timed region),
@@ -42,7 +47,11 @@ UNIT = "tokens/s"
 
 
 def workload(name: str):
-    """-> (spec, tokens per step, regime)"""
+    """-> (spec, tokens per step and rank, regime)"""
+    if name == "cfg4_ep":
+        return synth.cfg4_shared(), 2048, "prefill"
+    if name == "cfg3_ep":
+        return synth.cfg3_qwen(), 2048, "prefill"
     if name.startswith("cfg2"):
         b = int(name.split("_b")[1]) if "_b" in name else 64
         return synth.cfg2_gptoss(), b, "decode"
@@ -196,7 +205,17 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     host = synth.make_layer(spec, args.seed)
-    layer = MoELayer(host, n_tokens)
+    ep_mode = args.workload.endswith("_ep") and world > 1
+    ep_comm = None
+    if ep_mode:
+        from ffai_b200 import ep
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        uid = [ep.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        ep_comm = ep.comm_create(uid[0], rank, world)
+        layer = MoELayer(host, n_tokens, ep_rank=rank, ep_world=world, ep_comm=ep_comm)
+    else:
+        layer = MoELayer(host, n_tokens)
     layer.set_stage_timing(False)
     for ov in args.option:
         name, value = ov.split("=")
@@ -239,6 +258,8 @@ def main():
 
     for i in range(args.warmup):
         step(i, False)
+        if ep_mode:
+            sync_all()      # ranks enter every exchange together
     sync_all()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -247,6 +268,8 @@ def main():
     for i in range(args.steps):
         ms, _, nl = step(i, True)
         times.append(ms); launches += nl
+        if ep_mode:
+            sync_all()
     sync_all()
     clocks = sampler.stop() if rank == 0 else None
 
@@ -315,7 +338,8 @@ def main():
                        "top_k": spec.top_k, "bits": spec.expert_bits, "group_size": spec.expert_group_size,
                        "distinct_experts_per_step": mean_distinct, "input_batches_rotated": n_batches,
                        "l2": "256 MiB buffer overwritten between steps (not timed)",
-                       "parallelism": "replicas" if world > 1 else "single"},
+                       "parallelism": (f"ep{world}: experts sharded, tokens per rank fixed" if ep_mode else
+                                       "replicas" if world > 1 else "single")},
             "e2e": {"value": world * n_tokens / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": n_tokens * H * 2, "d2h_bytes_per_step": n_tokens * H * 2},
             "gpu_launches": launches,
@@ -324,10 +348,19 @@ def main():
             "stage_ms": stage_mean,
             "clocks": clocks,
         }
+        if ep_mode:
+            rows = n_tokens * spec.top_k
+            off_rank = (world - 1) / world      # share of a rank's rows whose expert lives on another rank (uniform routing)
+            line["ep"] = {"exchange_ms": stage_mean["exchange"], "rows_per_rank": rows,
+                          "dispatch_bytes_per_rank": rows * H * 2 * off_rank, "return_bytes_per_rank": rows * H * 4 * off_rank,
+                          "transport": "NCCL send/recv groups over NVLink, one host sync per step for the sizes"}
         if not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_baseline(spec, n_tokens, args.seed, args.cpu_seconds)
         print(json.dumps(line), flush=True)
     layer.close()
+    if ep_comm is not None:
+        sync_all()
+        ep.comm_destroy(ep_comm)
     if world > 1:
         dist.destroy_process_group()
 

@@ -108,6 +108,9 @@ constexpr int STG_RUNS = 2;
 constexpr int W_PITCH = 96;
 constexpr int DEPTH = 3;                   // stages in flight per warp
 
+// Runs of 64-run sums kept in shared memory per pass: whole stages, plus one stage that the look-ahead may touch.
+__host__ __device__ inline int xs_sm_runs(int n64) { return ((n64 + STG_RUNS - 1) / STG_RUNS + 1) * STG_RUNS; }
+
 template <bool FUSED>
 struct WarpStage {
     static constexpr int NP = FUSED ? 2 : 1;
@@ -118,13 +121,174 @@ struct WarpStage {
     static constexpr int TOTAL = 4 * PER_WARP;
 };
 
+// (w & mask) | expo with both constants held in registers: with immediates the compiler has to emit two
+// logic instructions per pair (one immediate operand per instruction), which doubles the load on the
+// half-rate pipe that bounds the kernel.
+FFAI_DEVINL uint32_t and_or(uint32_t w, uint32_t mask, uint32_t expo) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "r"(mask), "r"(expo));
+    return r;
+}
+FFAI_DEVINL void unpack_word_128r(uint32_t w, uint32_t* o, uint32_t mask, uint32_t expo) {
+    o[0] = and_or(w, mask, expo);
+    o[1] = and_or(shr_mul(w, 1u << 28), mask, expo);
+    o[2] = and_or(shr_mul(w, 1u << 24), mask, expo);
+    o[3] = and_or(shr_mul(w, 1u << 20), mask, expo);
+}
+// 16-byte asynchronous copy that reads `bytes` (16 or 0) from the source and zero-fills the rest.
+FFAI_DEVINL void cp_async16_zfill(uint32_t dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+
+// What a warp knows about its slice of the weights; does not change between passes over the activations.
+template <bool FUSED>
+struct WarpJob {
+    const uint8_t* wsrc[WarpStage<FUSED>::NP * 2];  // this lane's 16-byte column of the rows it copies, at the slice start
+    const uint8_t* sbsrc;                           // this lane's chunk of scale words, at the slice start
+    bool sb_lane;                                   // lane copies scale words
+    uint32_t wdst;                                  // shared-memory address of this lane's first weight chunk in slot 0
+    uint32_t sbdst;                                 // ... of its scale chunk in slot 0
+    int n_runs;                                     // 64-runs in the slice
+    int G0;                                         // first run of the slice
+};
+
+// One pass over the weights of a warp's 16-row block for up to 8*NT activation rows.
+// All stages have the same shape: the second run of an odd tail (and every stage issued past the
+// end) is copied with zero source bytes, so its weights and scale words read as zero and add nothing;
+// its activations are read from the last real run (finite values).
+template <bool FUSED, int NT>
+FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t* wsm, const float* xs_sm,
+                             int row0, int cnt, int tok0, int lane, float (*tot)[WarpStage<FUSED>::NP][4]) {
+    using WS = WarpStage<FUSED>;
+    constexpr int NP = WS::NP;
+    const int g = lane >> 2, t = lane & 3;
+    const int K = p.K;
+    const int n_runs = job.n_runs;
+    const int n_stages = (n_runs + STG_RUNS - 1) / STG_RUNS;
+    uint32_t mask, expo;
+    asm volatile("mov.u32 %0, 0x000F000F;" : "=r"(mask));
+    asm volatile("mov.u32 %0, 0x43004300;" : "=r"(expo));
+
+    // B-operand rows of this lane (column g of each 8-wide tile), clamped to the last valid row
+    const uint8_t* xrow[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+        xrow[j] = reinterpret_cast<const uint8_t*>(p.x + (size_t)(row0 + min(tok0 + 8 * j + g, cnt - 1)) * K + 16 * t) + (size_t)job.G0 * 128;
+    const uint32_t x_last = (uint32_t)(n_runs > 0 ? n_runs - 1 : 0) * 128u;
+
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int q = 0; q < NP; ++q)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tot[j][q][i] = 0.0f;
+
+    const uint32_t col_run = (uint32_t)(lane & 3) >> 1;          // which run of a stage this lane's weight column belongs to
+    const uint32_t sb_run = (uint32_t)(lane & 7) >> 2;           // ... and its scale chunk
+    uint32_t issue_off = 0;                                      // byte offset of the next stage in the source rows
+    uint32_t issue_slot = 0;                                     // byte offset of the ring slot it goes to
+    int issue_rem = n_runs;                                      // runs not yet issued (may go negative)
+    auto issue_stage = [&]() {
+        const uint32_t szw = (int)col_run < issue_rem ? 16u : 0u;
+#pragma unroll
+        for (int i = 0; i < NP * 2; ++i)
+            cp_async16_zfill(job.wdst + issue_slot + i * 8 * W_PITCH, job.wsrc[i] + issue_off, szw);
+        if (job.sb_lane) cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * 2, (int)sb_run < issue_rem ? 16u : 0u);
+        cp_async_commit();
+        issue_off += 64;
+        issue_rem -= STG_RUNS;
+        issue_slot = issue_slot == (DEPTH - 1) * WS::STAGE ? 0u : issue_slot + WS::STAGE;
+    };
+
+    __syncwarp();
+#pragma unroll
+    for (int st = 0; st < DEPTH - 1; ++st) issue_stage();
+
+    uint4 xbuf[STG_RUNS][NT][2];
+    auto fetch_x = [&](uint32_t off, uint4 (*xd)[2]) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const uint4* src = reinterpret_cast<const uint4*>(xrow[j] + off);
+            xd[j][0] = __ldg(src);
+            xd[j][1] = __ldg(src + 1);
+        }
+    };
+    uint32_t x_off = 0;
+    if (n_runs > 0) fetch_x(0, xbuf[0]);   // a warp without a slice must not touch the row at all
+
+    uint32_t use_slot = 0;
+    const float* xs_run = xs_sm + job.G0 * 16 + 2 * t;           // 16 floats (one per activation row of the pass) per run
+    for (int st = 0; st < n_stages; ++st) {
+        cp_async_wait<DEPTH - 2>();   // this lane's copies of the stage have landed
+        __syncwarp();                 // ... and the other lanes'; the slot of the previous stage is free again
+        issue_stage();
+        const uint8_t* stage = wsm + use_slot;
+        use_slot = use_slot == (DEPTH - 1) * WS::STAGE ? 0u : use_slot + WS::STAGE;
+#pragma unroll
+        for (int Gi = 0; Gi < STG_RUNS; ++Gi) {
+            // this run's activations are in set Gi; start fetching the next run's into the other set
+            uint4 (*xc)[2] = xbuf[Gi];
+            x_off = min(x_off + 128u, x_last);
+            fetch_x(x_off, xbuf[(Gi + 1) % STG_RUNS]);
+            float2 sx[NT];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) sx[j] = *reinterpret_cast<const float2*>(xs_run + Gi * 16 + 8 * j);
+#pragma unroll
+            for (int q = 0; q < NP; ++q) {
+                // scale and (bias - 128*scale) of the two rows this lane's results belong to
+                float sc[2], bm[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t v = *reinterpret_cast<const uint32_t*>(
+                        stage + WS::W_BYTES + q * (STG_RUNS * 64) + Gi * 64 + (g + 8 * h) * 4);
+                    const float s = __uint_as_float(v << 16), b = __uint_as_float(v & 0xFFFF0000u);
+                    sc[h] = s;
+                    bm[h] = fmaf(-128.0f, s, b);
+                }
+                // A fragments: [word 0/1][row lo/hi][pair 0..3]
+                uint32_t af[2][2][4];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint2 wv = *reinterpret_cast<const uint2*>(stage + (q * 16 + g + 8 * h) * W_PITCH + Gi * 32 + t * 8);
+                    unpack_word_128r(wv.x, af[0][h], mask, expo);
+                    unpack_word_128r(wv.y, af[1][h], mask, expo);
+                }
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const uint32_t xb[2][4] = {{xc[j][0].x, xc[j][0].y, xc[j][0].z, xc[j][0].w},
+                                               {xc[j][1].x, xc[j][1].y, xc[j][1].z, xc[j][1].w}};
+                    float c[4];
+#pragma unroll
+                    for (int w = 0; w < 2; ++w)
+#pragma unroll
+                        for (int hp = 0; hp < 2; ++hp) {
+                            // k-slots (2t,2t+1) <- pair 2hp, (2t+8,2t+9) <- pair 2hp+1 of word w
+                            const uint32_t a[4] = {af[w][0][2 * hp], af[w][1][2 * hp], af[w][0][2 * hp + 1], af[w][1][2 * hp + 1]};
+                            if (w == 0 && hp == 0) mma_bf16_16816_zero(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
+                            else mma_bf16_16816(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
+                        }
+                    tot[j][q][0] = fmaf(sc[0], c[0], fmaf(bm[0], sx[j].x, tot[j][q][0]));
+                    tot[j][q][1] = fmaf(sc[0], c[1], fmaf(bm[0], sx[j].y, tot[j][q][1]));
+                    tot[j][q][2] = fmaf(sc[1], c[2], fmaf(bm[1], sx[j].x, tot[j][q][2]));
+                    tot[j][q][3] = fmaf(sc[1], c[3], fmaf(bm[1], sx[j].y, tot[j][q][3]));
+                }
+            }
+        }
+        xs_run += STG_RUNS * 16;
+    }
+    cp_async_wait<0>();
+}
+
 // grid: (ceil(N / 16 / (4 / KSPLIT)), E); block: 128 threads = 4 warps.
 // Warp w works on 16-row block (w / KSPLIT) of the CTA and on the (w % KSPLIT)-th slice of the
 // reduction axis; with KSPLIT > 1 the slices are summed in a fixed order through shared memory at
 // the end (tiny batches: more warps in flight per active expert).  Every warp streams its own packed
 // rows and scale words through its own cp.async ring (16-byte asynchronous copies, DEPTH stages of
-// 128 k in flight) and synchronises with nobody until the final reduction.
-// NT: activation rows handled per pass over the weights, in units of 8.
+// 128 k in flight) and synchronises with nobody inside the stream.
+// NT: most activation rows handled per pass over the weights, in units of 8; a pass with 8 rows or
+// fewer left runs the one-tile body whatever NT is.
+// Shared memory: the rings, then 16 floats per 64-run (rounded up to whole stages, plus one stage)
+// holding the 64-run sums of the pass's activation rows, transposed so a lane reads its two rows at once.
 template <bool FUSED, int NT, int KSPLIT>
 __global__ void __launch_bounds__(128, 4)
 grouped_mma_decode_kernel(const Params p) {
@@ -144,15 +308,14 @@ grouped_mma_decode_kernel(const Params p) {
     const bool warp_active = rb_row < p.N;             // N is a multiple of 16
     const int per = (n64 + KSPLIT - 1) / KSPLIT;
     const int G0 = min(ks * per, n64), G1 = min(G0 + per, n64);
-    const int n_runs = warp_active ? G1 - G0 : 0;
-    const int n_stages = (n_runs + STG_RUNS - 1) / STG_RUNS;
 
     uint8_t* wsm = smem + warp * WS::PER_WARP;
-    const uint32_t wsm_u32 = (uint32_t)__cvta_generic_to_shared(wsm);
+    float* xs_sm = reinterpret_cast<float*>(smem + WS::TOTAL);
+    const int xs_runs = xs_sm_runs(n64);
 
-    // what this lane copies per stage: NP*2 packed-weight chunks (row (lane>>2) + 8i, 16-byte column lane&3)
-    // and, lanes 0..NP*8-1, one chunk of scale words
-    const uint8_t* wsrc[NP * 2];
+    WarpJob<FUSED> job;
+    job.n_runs = warp_active ? G1 - G0 : 0;
+    job.G0 = G0;
     {
         const int col = lane & 3;
 #pragma unroll
@@ -160,130 +323,41 @@ grouped_mma_decode_kernel(const Params p) {
             const int ridx = (lane >> 2) + 8 * i;  // 0 .. NP*16-1
             const uint32_t* base = (ridx >= 16) ? p.w2 : p.w1;
             const size_t row = (size_t)e * p.N + (warp_active ? rb_row : 0) + (ridx & 15);
-            wsrc[i] = reinterpret_cast<const uint8_t*>(base + row * wpr) + G0 * 32 + col * 16;
+            job.wsrc[i] = reinterpret_cast<const uint8_t*>(base + row * wpr) + G0 * 32 + col * 16;
         }
+        const int sb_q = lane >> 3;  // projection whose scale words this lane copies (valid when < NP)
+        job.sb_lane = sb_q < NP;
+        job.sbsrc = reinterpret_cast<const uint8_t*>(
+            ((sb_q == 1 && FUSED) ? p.sb2 : p.sb1) + (((size_t)e * (p.N / 16) + (warp_active ? rb : 0)) * n64 + G0) * 16) + (lane & 7) * 16;
+        const uint32_t wsm_u32 = (uint32_t)__cvta_generic_to_shared(wsm);
+        job.wdst = wsm_u32 + (lane >> 2) * W_PITCH + col * 16;
+        job.sbdst = wsm_u32 + WS::W_BYTES + (sb_q & (NP - 1)) * (STG_RUNS * 64) + (lane & 7) * 16;
     }
-    const int sb_q = lane >> 3;  // projection whose scale words this lane copies (valid when < NP)
-    const uint8_t* sbsrc = reinterpret_cast<const uint8_t*>(
-        ((sb_q == 1 && FUSED) ? p.sb2 : p.sb1) + (((size_t)e * (p.N / 16) + (warp_active ? rb : 0)) * n64 + G0) * 16) + (lane & 7) * 16;
-
-    auto issue_stage = [&](int st) {
-        if (st < n_stages) {
-            const uint32_t dst = wsm_u32 + (st % DEPTH) * WS::STAGE;
-            const int runs_left = n_runs - st * STG_RUNS;           // >= 1
-            if ((lane & 3) < 2 * runs_left) {                        // 16-byte columns 0,1: first run; 2,3: second
-#pragma unroll
-                for (int i = 0; i < NP * 2; ++i)
-                    cp_async16(dst + ((lane >> 2) + 8 * i) * W_PITCH + (lane & 3) * 16, wsrc[i] + st * 64);
-            }
-            if (sb_q < NP && (lane & 7) < 4 * runs_left)             // 4 chunks of scale words per run
-                cp_async16(dst + WS::W_BYTES + sb_q * (STG_RUNS * 64) + (lane & 7) * 16, sbsrc + st * (STG_RUNS * 64));
-        }
-        cp_async_commit();
-    };
 
     for (int tok0 = 0; tok0 < cnt; tok0 += 8 * NT) {
-        // activation row read by this lane as B operand (column g of each 8-wide tile) and the two rows
-        // whose results it holds (columns 2t, 2t+1); clamped to the last valid row, masked at the store
-        const uint16_t* xrow[NT];
-        const float* sxa[NT];
-        const float* sxb[NT];
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            const int last = cnt - 1;
-            xrow[j] = p.x + (size_t)(row0 + min(tok0 + 8 * j + g, last)) * K + 16 * t;
-            sxa[j] = p.xsum + (size_t)(row0 + min(tok0 + 8 * j + 2 * t, last)) * p.xsum_pitch;
-            sxb[j] = p.xsum + (size_t)(row0 + min(tok0 + 8 * j + 2 * t + 1, last)) * p.xsum_pitch;
+        // 64-run sums of the pass's activation rows -> shared memory, [run][row]; rows past the end and
+        // the padding runs read as zero
+        __syncthreads();   // the previous pass (or the reduction below) is done with shared memory
+        for (int i = threadIdx.x; i < xs_runs * 16; i += 128) {
+            const int r = i / xs_runs, G = i - r * xs_runs;
+            float v = 0.0f;
+            if (tok0 + r < cnt && G < n64) v = __ldg(p.xsum + (size_t)(row0 + tok0 + r) * p.xsum_pitch + G);
+            xs_sm[G * 16 + r] = v;
         }
+        __syncthreads();
+
         float tot[NT][NP][4];
+        if (NT == 1 || cnt - tok0 <= 8) {
+            decode_pass<FUSED, 1>(p, job, wsm, xs_sm, row0, cnt, tok0, lane, tot);
 #pragma unroll
-        for (int j = 0; j < NT; ++j)
+            for (int j = 1; j < NT; ++j)
 #pragma unroll
-            for (int q = 0; q < NP; ++q)
+                for (int q = 0; q < NP; ++q)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) tot[j][q][i] = 0.0f;
-
-        __syncwarp();
-#pragma unroll
-        for (int st = 0; st < DEPTH - 1; ++st) issue_stage(st);
-
-        // activations, fetched one run ahead into two alternating register sets (run parity within a
-        // stage is a compile-time index, so nothing is copied between them)
-        uint4 xbuf[STG_RUNS][NT][2];
-        float sxbuf[STG_RUNS][NT][2];
-        auto fetch_x = [&](int G, uint4 (*xd)[2], float (*sd)[2]) {
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                xd[j][0] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + G * 64));
-                xd[j][1] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + G * 64 + 8));
-                sd[j][0] = __ldg(sxa[j] + G);
-                sd[j][1] = __ldg(sxb[j] + G);
-            }
-        };
-        if (n_runs > 0) fetch_x(G0, xbuf[0], sxbuf[0]);
-
-        for (int st = 0; st < n_stages; ++st) {
-            cp_async_wait<DEPTH - 2>();   // this lane's copies of stage st have landed
-            __syncwarp();                 // ... and the other lanes'; the slot of stage st-1 is free again
-            issue_stage(st + DEPTH - 1);
-            const uint8_t* stage = wsm + (st % DEPTH) * WS::STAGE;
-#pragma unroll
-            for (int Gi = 0; Gi < STG_RUNS; ++Gi) {
-                const int G = G0 + st * STG_RUNS + Gi;
-                if (G < G1) {
-                    // this run's activations are in set Gi; start fetching the next run's into the other set
-                    uint4 (*xc)[2] = xbuf[Gi];
-                    float (*sxc)[2] = sxbuf[Gi];
-                    if (G + 1 < G1) fetch_x(G + 1, xbuf[(Gi + 1) % STG_RUNS], sxbuf[(Gi + 1) % STG_RUNS]);
-                    // scale and (bias - 128*scale) of the two rows this lane's results belong to
-                    float sc[NP][2], bm[NP][2];
-#pragma unroll
-                    for (int q = 0; q < NP; ++q)
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const uint32_t v = *reinterpret_cast<const uint32_t*>(
-                                stage + WS::W_BYTES + q * (STG_RUNS * 64) + Gi * 64 + (g + 8 * h) * 4);
-                            const float s = __uint_as_float(v << 16), b = __uint_as_float(v & 0xFFFF0000u);
-                            sc[q][h] = s;
-                            bm[q][h] = fmaf(-128.0f, s, b);
-                        }
-                    // A fragments: [projection][word 0/1][row lo/hi][pair 0..3]
-                    uint32_t af[NP][2][2][4];
-#pragma unroll
-                    for (int q = 0; q < NP; ++q)
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const uint2 wv = *reinterpret_cast<const uint2*>(stage + (q * 16 + g + 8 * h) * W_PITCH + Gi * 32 + t * 8);
-                            unpack_word_128(wv.x, af[q][0][h]);
-                            unpack_word_128(wv.y, af[q][1][h]);
-                        }
-#pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        const uint32_t xb[2][4] = {{xc[j][0].x, xc[j][0].y, xc[j][0].z, xc[j][0].w},
-                                                   {xc[j][1].x, xc[j][1].y, xc[j][1].z, xc[j][1].w}};
-#pragma unroll
-                        for (int q = 0; q < NP; ++q) {
-                            float c[4];
-#pragma unroll
-                            for (int w = 0; w < 2; ++w)
-#pragma unroll
-                                for (int hp = 0; hp < 2; ++hp) {
-                                    // k-slots (2t,2t+1) <- pair 2hp, (2t+8,2t+9) <- pair 2hp+1 of word w
-                                    const uint32_t a[4] = {af[q][w][0][2 * hp], af[q][w][1][2 * hp],
-                                                           af[q][w][0][2 * hp + 1], af[q][w][1][2 * hp + 1]};
-                                    if (w == 0 && hp == 0) mma_bf16_16816_zero(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
-                                    else mma_bf16_16816(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
-                                }
-                            tot[j][q][0] = fmaf(sc[q][0], c[0], fmaf(bm[q][0], sxc[j][0], tot[j][q][0]));
-                            tot[j][q][1] = fmaf(sc[q][0], c[1], fmaf(bm[q][0], sxc[j][1], tot[j][q][1]));
-                            tot[j][q][2] = fmaf(sc[q][1], c[2], fmaf(bm[q][1], sxc[j][0], tot[j][q][2]));
-                            tot[j][q][3] = fmaf(sc[q][1], c[3], fmaf(bm[q][1], sxc[j][1], tot[j][q][3]));
-                        }
-                    }
-                }
-            }
+                    for (int i = 0; i < 4; ++i) tot[j][q][i] = 0.0f;
+        } else {
+            decode_pass<FUSED, NT>(p, job, wsm, xs_sm, row0, cnt, tok0, lane, tot);
         }
-        cp_async_wait<0>();
 
         if (KSPLIT > 1) {
             // fixed-order sum of the reduction slices: slices 1.. park their partials, slice 0 adds them in order
@@ -308,7 +382,6 @@ grouped_mma_decode_kernel(const Params p) {
 #pragma unroll
                             for (int i = 0; i < 4; ++i) tot[j][q][i] += red[(warp + o) * PER_WARP_VALS + ((j * NP + q) * 4 + i) * 32 + lane];
             }
-            __syncthreads();  // the next pass's copies may overwrite the parked partials
         }
 
         // results: value i -> (row g + 8*(i>>1), activation row tok0 + 8j + 2t + (i&1))

@@ -350,14 +350,15 @@ template <bool FUSED, int NT, int KSPLIT>
 void launch_mma_decode_k(const dmma::Params& p, int n_experts, cudaStream_t st) {
     using WS = dmma::WarpStage<FUSED>;
     auto k = dmma::grouped_mma_decode_kernel<FUSED, NT, KSPLIT>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, WS::TOTAL);
-        attr_set = true;
+    const int smem = WS::TOTAL + dmma::xs_sm_runs(p.K / 64) * 64;
+    static int attr_smem = 0;
+    if (smem > attr_smem) {
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        attr_smem = smem;
     }
     const int rbw = 4 / KSPLIT;
     dim3 grid((p.N / 16 + rbw - 1) / rbw, n_experts);
-    k<<<grid, 128, WS::TOTAL, st>>>(p);
+    k<<<grid, 128, smem, st>>>(p);
 }
 
 // nt: 8-row activation tiles per pass (1 or 2); ksplit: slices of the reduction axis per 16-row block (1, 2, 4)
@@ -888,17 +889,21 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
         const int nt = rpe > 4.0 ? 2 : 1;
         const int ksplit = L->opt_ksplit > 0 ? L->opt_ksplit : (n_rows <= 8 ? 4 : (n_rows <= 24 ? 2 : 1));
+        stage_begin(L, ST_GATE_UP, st);
         p.w1 = L->w.gate_proj.weight; p.s1 = L->w.gate_proj.scales; p.b1 = L->w.gate_proj.biases; p.rb1 = L->w.gate_proj.row_bias;
         p.w2 = L->w.up_proj.weight; p.s2 = L->w.up_proj.scales; p.b2 = L->w.up_proj.biases; p.rb2 = L->w.up_proj.row_bias;
         p.sb1 = L->sb_gate; p.sb2 = L->sb_up;
         p.N = I; p.K = H; p.x = L->xg; p.xsum = L->xsum; p.xsum_pitch = xp_h; p.out = L->inner_bf;
         launch_mma_decode<true>(p, n_exp, nt, ksplit, st);
         sum64_rows_kernel<<<(n_rows + 7) / 8, 256, 0, st>>>(L->inner_bf, L->inner_sum, n_rows, I, xp_i);
+        stage_end(L, ST_GATE_UP, st);
+        stage_begin(L, ST_DOWN, st);
         p.w1 = L->w.down_proj.weight; p.s1 = L->w.down_proj.scales; p.b1 = L->w.down_proj.biases; p.rb1 = L->w.down_proj.row_bias;
         p.w2 = nullptr; p.s2 = nullptr; p.b2 = nullptr; p.rb2 = nullptr;
         p.sb1 = L->sb_down; p.sb2 = nullptr;
         p.N = H; p.K = I; p.x = L->inner_bf; p.xsum = L->inner_sum; p.xsum_pitch = xp_i; p.out = L->y;
         launch_mma_decode<false>(p, n_exp, nt, ksplit, st);
+        stage_end(L, ST_DOWN, st);
         L->launches += 4;
     } else if (use_tc) {
         using namespace g100;
@@ -908,18 +913,22 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         p.offsets = offsets_dev; p.tile_offsets = L->tile_offsets;
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
         p.error_word = L->error_word;
+        stage_begin(L, ST_GATE_UP, st);
         p.scales = L->w.gate_proj.scales; p.biases = L->w.gate_proj.biases; p.row_bias = L->w.gate_proj.row_bias;
         p.scales2 = L->w.up_proj.scales; p.biases2 = L->w.up_proj.biases; p.row_bias2 = L->w.up_proj.row_bias;
         p.n_out = I; p.K = H; p.m_tiles = (I + BN / 2 - 1) / (BN / 2);
         p.out = L->inner_bf; p.out_ld = I; p.out_permute8 = 1;
         if (launch_grouped_gemm<true, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg, p, L->n_sms, st))
             return fail(L, FFAI_ERR_CUDA, "gate/up grouped GEMM launch failed");
+        stage_end(L, ST_GATE_UP, st);
+        stage_begin(L, ST_DOWN, st);
         p.scales = L->w.down_proj.scales; p.biases = L->w.down_proj.biases; p.row_bias = L->w.down_proj.row_bias;
         p.scales2 = nullptr; p.biases2 = nullptr; p.row_bias2 = nullptr;
         p.n_out = H; p.K = I; p.m_tiles = (H + BN - 1) / BN;
         p.out = L->y; p.out_ld = H; p.out_permute8 = 0;
         if (launch_grouped_gemm<false, float>(L->tm_down, L->tm_down, L->tm_inner, p, L->n_sms, st))
             return fail(L, FFAI_ERR_CUDA, "down grouped GEMM launch failed");
+        stage_end(L, ST_DOWN, st);
         L->launches += 3;
     } else {
         int rc;
@@ -927,11 +936,15 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         p.offsets = offsets_dev;
         p.n_rows = n_rows;
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
+        stage_begin(L, ST_GATE_UP, st);
         if ((rc = launch_grouped_gemv<uint16_t, float, true>(p, c.expert_bits, L->xg, L->inner, n_exp, st))) return fail(L, rc, "gate/up launch failed");
+        stage_end(L, ST_GATE_UP, st);
+        stage_begin(L, ST_DOWN, st);
         GemvParams d = gemv_params(L->w.down_proj, nullptr, H, I, c.expert_group_size, n_exp);
         d.offsets = offsets_dev;
         d.n_rows = n_rows;
         if ((rc = launch_grouped_gemv<float, float, false>(d, c.expert_bits, L->inner, L->y, n_exp, st))) return fail(L, rc, "down launch failed");
+        stage_end(L, ST_DOWN, st);
         L->launches += 2;
     }
     return cudaGetLastError() == cudaSuccess ? FFAI_OK : fail(L, FFAI_ERR_CUDA, "expert kernels launch failed");
@@ -991,9 +1004,7 @@ int forward_experts_ep(ffai_moe_layer* L, const uint16_t* x, int T, cudaStream_t
     }
     stage_end(L, ST_EXCHANGE, st);
 
-    stage_begin(L, ST_GATE_UP, st);
     if ((rc = run_experts_on_rows(L, (int)n_recv, El, d_local_off, st))) return rc;
-    stage_end(L, ST_GATE_UP, st);
 
     stage_begin(L, ST_EXCHANGE, st);
     if (n_recv) {
