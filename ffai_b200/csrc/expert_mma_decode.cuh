@@ -101,24 +101,42 @@ FFAI_DEVINL void mma_bf16_16816_zero(float* c, const uint32_t* a, uint32_t b0, u
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
-// Per-warp staging geometry.  A stage is 128 k (two 64-runs): per weight row 64 packed bytes at a
-// 96-byte pitch (so the 8-byte fragment reads of eight rows fall in distinct banks), followed by the
-// packed (scale | bias << 16) words of the stage, 16 rows x 2 runs per projection.
+// Per-warp staging geometry.  A stage is 128 k (two 64-runs): per weight row 64 packed bytes, the four
+// 16-byte columns of a row XOR-swizzled with bit 1 of the row index (so the 8-byte fragment reads of a
+// half warp fall in 32 distinct banks), followed by the packed (scale | bias << 16) words of the
+// stage, 16 rows x 2 runs per projection.
 constexpr int STG_RUNS = 2;
-constexpr int W_PITCH = 96;
-constexpr int DEPTH = 3;                   // stages in flight per warp
+constexpr int W_PITCH = 64;
+#ifndef FFAI_DM_DEPTH_FUSED
+#define FFAI_DM_DEPTH_FUSED 3
+#endif
+#ifndef FFAI_DM_DEPTH_PLAIN
+#define FFAI_DM_DEPTH_PLAIN 4
+#endif
+#ifndef FFAI_DM_MIN_BLOCKS
+#define FFAI_DM_MIN_BLOCKS 4
+#endif
 
 // Runs of 64-run sums kept in shared memory per pass: whole stages, plus one stage that the look-ahead may touch.
 __host__ __device__ inline int xs_sm_runs(int n64) { return ((n64 + STG_RUNS - 1) / STG_RUNS + 1) * STG_RUNS; }
 
+// Block-shared activation ring (kernels without a split reduction axis): per stage 16 rows x 256 bytes
+// (128 k), rows padded to 272 bytes so the 16-byte fragment reads of a quarter warp hit distinct banks.
+constexpr int X_PITCH = 272;
+constexpr int X_STAGE = 16 * X_PITCH;
+
 template <bool FUSED>
 struct WarpStage {
     static constexpr int NP = FUSED ? 2 : 1;
+    static constexpr int DEPTH = FUSED ? FFAI_DM_DEPTH_FUSED : FFAI_DM_DEPTH_PLAIN;   // ring slots per warp; DEPTH-1 stages in flight
     static constexpr int W_BYTES = NP * 16 * W_PITCH;
     static constexpr int SB_BYTES = NP * STG_RUNS * 64;
     static constexpr int STAGE = W_BYTES + SB_BYTES;
     static constexpr int PER_WARP = DEPTH * STAGE;
     static constexpr int TOTAL = 4 * PER_WARP;
+    static constexpr int X_RING = DEPTH * X_STAGE;
+    // dynamic shared memory of a launch: weight rings, [activation ring], 64-run sums
+    static int smem_bytes(int n64, int ksplit) { return TOTAL + (ksplit == 1 ? X_RING : 0) + xs_sm_runs(n64) * 64; }
 };
 
 // (w & mask) | expo with both constants held in registers: with immediates the compiler has to emit two
@@ -129,11 +147,17 @@ FFAI_DEVINL uint32_t and_or(uint32_t w, uint32_t mask, uint32_t expo) {
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "r"(mask), "r"(expo));
     return r;
 }
+#ifndef FFAI_DM_ALU_SHIFTS
+#define FFAI_DM_ALU_SHIFTS 3   // how many of the three shifts per word go to the logic pipe instead of the multiplier
+#endif
 FFAI_DEVINL void unpack_word_128r(uint32_t w, uint32_t* o, uint32_t mask, uint32_t expo) {
+#ifdef FFAI_DM_EXP_NOUNPACK
+    o[0] = w; o[1] = w ^ mask; o[2] = w ^ expo; o[3] = w; return;
+#endif
     o[0] = and_or(w, mask, expo);
-    o[1] = and_or(shr_mul(w, 1u << 28), mask, expo);
-    o[2] = and_or(shr_mul(w, 1u << 24), mask, expo);
-    o[3] = and_or(shr_mul(w, 1u << 20), mask, expo);
+    o[1] = and_or(FFAI_DM_ALU_SHIFTS >= 1 ? (w >> 4) : shr_mul(w, 1u << 28), mask, expo);
+    o[2] = and_or(FFAI_DM_ALU_SHIFTS >= 2 ? (w >> 8) : shr_mul(w, 1u << 24), mask, expo);
+    o[3] = and_or(FFAI_DM_ALU_SHIFTS >= 3 ? (w >> 12) : shr_mul(w, 1u << 20), mask, expo);
 }
 // 16-byte asynchronous copy that reads `bytes` (16 or 0) from the source and zero-fills the rest.
 FFAI_DEVINL void cp_async16_zfill(uint32_t dst, const void* src, uint32_t bytes) {
@@ -161,6 +185,7 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
                              int row0, int cnt, int tok0, int lane, float (*tot)[WarpStage<FUSED>::NP][4]) {
     using WS = WarpStage<FUSED>;
     constexpr int NP = WS::NP;
+    constexpr int DEPTH = WS::DEPTH;
     const int g = lane >> 2, t = lane & 3;
     const int K = p.K;
     const int n_runs = job.n_runs;
@@ -195,7 +220,9 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
             cp_async16_zfill(job.wdst + issue_slot + i * 8 * W_PITCH, job.wsrc[i] + issue_off, szw);
         if (job.sb_lane) cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * 2, (int)sb_run < issue_rem ? 16u : 0u);
         cp_async_commit();
+#ifndef FFAI_DM_EXP_NOW
         issue_off += 64;
+#endif
         issue_rem -= STG_RUNS;
         issue_slot = issue_slot == (DEPTH - 1) * WS::STAGE ? 0u : issue_slot + WS::STAGE;
     };
@@ -217,6 +244,9 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
     if (n_runs > 0) fetch_x(0, xbuf[0]);   // a warp without a slice must not touch the row at all
 
     uint32_t use_slot = 0;
+    // this lane's fragment words inside a stage: row g (+8h, + projection), swizzled 16-byte column of run 0 / run 1
+    const uint32_t rd0 = g * W_PITCH + (t & 1) * 8 + (((t >> 1) ^ (((g >> 1) & 1) << 1)) << 4);
+    const uint32_t rd[STG_RUNS] = {rd0, rd0 ^ 32u};
     const float* xs_run = xs_sm + job.G0 * 16 + 2 * t;           // 16 floats (one per activation row of the pass) per run
     for (int st = 0; st < n_stages; ++st) {
         cp_async_wait<DEPTH - 2>();   // this lane's copies of the stage have landed
@@ -229,7 +259,9 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
             // this run's activations are in set Gi; start fetching the next run's into the other set
             uint4 (*xc)[2] = xbuf[Gi];
             x_off = min(x_off + 128u, x_last);
+#ifndef FFAI_DM_EXP_NOX
             fetch_x(x_off, xbuf[(Gi + 1) % STG_RUNS]);
+#endif
             float2 sx[NT];
 #pragma unroll
             for (int j = 0; j < NT; ++j) sx[j] = *reinterpret_cast<const float2*>(xs_run + Gi * 16 + 8 * j);
@@ -249,7 +281,7 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
                 uint32_t af[2][2][4];
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const uint2 wv = *reinterpret_cast<const uint2*>(stage + (q * 16 + g + 8 * h) * W_PITCH + Gi * 32 + t * 8);
+                    const uint2 wv = *reinterpret_cast<const uint2*>(stage + (q * 16 + 8 * h) * W_PITCH + rd[Gi]);
                     unpack_word_128r(wv.x, af[0][h], mask, expo);
                     unpack_word_128r(wv.y, af[1][h], mask, expo);
                 }
@@ -279,6 +311,137 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
     cp_async_wait<0>();
 }
 
+// The same pass with the activation rows staged once per CTA: the four warps of a CTA work on the same
+// expert, the same rows and (no split) the same 128-k stage, so the rows travel from L2 once per CTA
+// instead of once per warp.  All threads copy (weights into their warp's ring, activations into the
+// shared ring) and meet at one barrier per stage, which both publishes the stage and frees the slot
+// of the previous one.  The loop count is the CTA's (n64), so warps without rows still take part.
+template <bool FUSED, int NT>
+FFAI_DEVINL void decode_pass_shared(const Params& p, const WarpJob<FUSED>& job, uint8_t* wsm, uint8_t* xring,
+                                    const float* xs_sm, int row0, int cnt, int tok0, int n64, int lane,
+                                    float (*tot)[WarpStage<FUSED>::NP][4]) {
+    using WS = WarpStage<FUSED>;
+    constexpr int NP = WS::NP;
+    constexpr int DEPTH = WS::DEPTH;
+    const int g = lane >> 2, t = lane & 3;
+    const int K = p.K;
+    const int n_stages = (n64 + STG_RUNS - 1) / STG_RUNS;
+    uint32_t mask, expo;
+    asm volatile("mov.u32 %0, 0x000F000F;" : "=r"(mask));
+    asm volatile("mov.u32 %0, 0x43004300;" : "=r"(expo));
+
+    // activation chunks this thread copies per stage: chunk c = tid + 128 i -> row c / 16, 16-byte column c % 16
+    const uint8_t* xsrc[NT];
+    uint32_t xdst[NT];
+    const uint32_t xcol_run = (threadIdx.x & 15) >> 3;
+    {
+        const uint32_t xring_u32 = (uint32_t)__cvta_generic_to_shared(xring);
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            const int c = threadIdx.x + 128 * i, row = c >> 4, col = c & 15;
+            xsrc[i] = reinterpret_cast<const uint8_t*>(p.x + (size_t)(row0 + min(tok0 + row, cnt - 1)) * K) + col * 16;
+            xdst[i] = xring_u32 + row * X_PITCH + col * 16;
+        }
+    }
+
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int q = 0; q < NP; ++q)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tot[j][q][i] = 0.0f;
+
+    const uint32_t col_run = (uint32_t)(lane & 3) >> 1;
+    const uint32_t sb_run = (uint32_t)(lane & 7) >> 2;
+    uint32_t issue_off = 0, issue_slot = 0, issue_xslot = 0;
+    int issue_rem = job.n_runs;       // this warp's weight runs not yet issued (0 for a warp without rows)
+    int issue_rem_x = n64;            // the CTA's activation runs not yet issued
+    auto issue_stage = [&]() {
+        const uint32_t szw = (int)col_run < issue_rem ? 16u : 0u;
+#pragma unroll
+        for (int i = 0; i < NP * 2; ++i)
+            cp_async16_zfill(job.wdst + issue_slot + i * 8 * W_PITCH, job.wsrc[i] + issue_off, szw);
+        if (job.sb_lane) cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * 2, (int)sb_run < issue_rem ? 16u : 0u);
+        const uint32_t szx = (int)xcol_run < issue_rem_x ? 16u : 0u;
+#pragma unroll
+        for (int i = 0; i < NT; ++i) cp_async16_zfill(xdst[i] + issue_xslot, xsrc[i] + issue_off * 4, szx);
+        cp_async_commit();
+        issue_off += 64;
+        issue_rem -= STG_RUNS;
+        issue_rem_x -= STG_RUNS;
+        issue_slot = issue_slot == (DEPTH - 1) * WS::STAGE ? 0u : issue_slot + WS::STAGE;
+        issue_xslot = issue_xslot == (DEPTH - 1) * X_STAGE ? 0u : issue_xslot + X_STAGE;
+    };
+
+#pragma unroll
+    for (int st = 0; st < DEPTH - 1; ++st) issue_stage();
+
+    uint32_t use_slot = 0, use_xslot = 0;
+    const uint32_t rd0 = g * W_PITCH + (t & 1) * 8 + (((t >> 1) ^ (((g >> 1) & 1) << 1)) << 4);
+    const uint32_t rd[STG_RUNS] = {rd0, rd0 ^ 32u};
+    const uint32_t xrd = g * X_PITCH + t * 32;
+    const float* xs_run = xs_sm + 2 * t;
+    for (int st = 0; st < n_stages; ++st) {
+        cp_async_wait<DEPTH - 2>();   // this thread's copies of the stage have landed
+        __syncthreads();              // ... and everybody's; the slots of the previous stage are free again
+        issue_stage();
+        const uint8_t* stage = wsm + use_slot;
+        const uint8_t* xstage = xring + use_xslot + xrd;
+        use_slot = use_slot == (DEPTH - 1) * WS::STAGE ? 0u : use_slot + WS::STAGE;
+        use_xslot = use_xslot == (DEPTH - 1) * X_STAGE ? 0u : use_xslot + X_STAGE;
+#pragma unroll
+        for (int Gi = 0; Gi < STG_RUNS; ++Gi) {
+            uint4 xc[NT][2];
+            float2 sx[NT];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                xc[j][0] = *reinterpret_cast<const uint4*>(xstage + j * 8 * X_PITCH + Gi * 128);
+                xc[j][1] = *reinterpret_cast<const uint4*>(xstage + j * 8 * X_PITCH + Gi * 128 + 16);
+                sx[j] = *reinterpret_cast<const float2*>(xs_run + Gi * 16 + 8 * j);
+            }
+#pragma unroll
+            for (int q = 0; q < NP; ++q) {
+                float sc[2], bm[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t v = *reinterpret_cast<const uint32_t*>(
+                        stage + WS::W_BYTES + q * (STG_RUNS * 64) + Gi * 64 + (g + 8 * h) * 4);
+                    const float s = __uint_as_float(v << 16), b = __uint_as_float(v & 0xFFFF0000u);
+                    sc[h] = s;
+                    bm[h] = fmaf(-128.0f, s, b);
+                }
+                uint32_t af[2][2][4];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint2 wv = *reinterpret_cast<const uint2*>(stage + (q * 16 + 8 * h) * W_PITCH + rd[Gi]);
+                    unpack_word_128r(wv.x, af[0][h], mask, expo);
+                    unpack_word_128r(wv.y, af[1][h], mask, expo);
+                }
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const uint32_t xb[2][4] = {{xc[j][0].x, xc[j][0].y, xc[j][0].z, xc[j][0].w},
+                                               {xc[j][1].x, xc[j][1].y, xc[j][1].z, xc[j][1].w}};
+                    float c[4];
+#pragma unroll
+                    for (int w = 0; w < 2; ++w)
+#pragma unroll
+                        for (int hp = 0; hp < 2; ++hp) {
+                            const uint32_t a[4] = {af[w][0][2 * hp], af[w][1][2 * hp], af[w][0][2 * hp + 1], af[w][1][2 * hp + 1]};
+                            if (w == 0 && hp == 0) mma_bf16_16816_zero(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
+                            else mma_bf16_16816(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
+                        }
+                    tot[j][q][0] = fmaf(sc[0], c[0], fmaf(bm[0], sx[j].x, tot[j][q][0]));
+                    tot[j][q][1] = fmaf(sc[0], c[1], fmaf(bm[0], sx[j].y, tot[j][q][1]));
+                    tot[j][q][2] = fmaf(sc[1], c[2], fmaf(bm[1], sx[j].x, tot[j][q][2]));
+                    tot[j][q][3] = fmaf(sc[1], c[3], fmaf(bm[1], sx[j].y, tot[j][q][3]));
+                }
+            }
+        }
+        xs_run += STG_RUNS * 16;
+    }
+    cp_async_wait<0>();
+}
+
 // grid: (ceil(N / 16 / (4 / KSPLIT)), E); block: 128 threads = 4 warps.
 // Warp w works on 16-row block (w / KSPLIT) of the CTA and on the (w % KSPLIT)-th slice of the
 // reduction axis; with KSPLIT > 1 the slices are summed in a fixed order through shared memory at
@@ -290,7 +453,7 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
 // Shared memory: the rings, then 16 floats per 64-run (rounded up to whole stages, plus one stage)
 // holding the 64-run sums of the pass's activation rows, transposed so a lane reads its two rows at once.
 template <bool FUSED, int NT, int KSPLIT>
-__global__ void __launch_bounds__(128, 4)
+__global__ void __launch_bounds__(128, FFAI_DM_MIN_BLOCKS)
 grouped_mma_decode_kernel(const Params p) {
     using WS = WarpStage<FUSED>;
     constexpr int NP = WS::NP;
@@ -310,7 +473,8 @@ grouped_mma_decode_kernel(const Params p) {
     const int G0 = min(ks * per, n64), G1 = min(G0 + per, n64);
 
     uint8_t* wsm = smem + warp * WS::PER_WARP;
-    float* xs_sm = reinterpret_cast<float*>(smem + WS::TOTAL);
+    uint8_t* xring = smem + WS::TOTAL;   // present only without a split reduction axis
+    float* xs_sm = reinterpret_cast<float*>(smem + WS::TOTAL + (KSPLIT == 1 ? WS::X_RING : 0));
     const int xs_runs = xs_sm_runs(n64);
 
     WarpJob<FUSED> job;
@@ -330,7 +494,7 @@ grouped_mma_decode_kernel(const Params p) {
         job.sbsrc = reinterpret_cast<const uint8_t*>(
             ((sb_q == 1 && FUSED) ? p.sb2 : p.sb1) + (((size_t)e * (p.N / 16) + (warp_active ? rb : 0)) * n64 + G0) * 16) + (lane & 7) * 16;
         const uint32_t wsm_u32 = (uint32_t)__cvta_generic_to_shared(wsm);
-        job.wdst = wsm_u32 + (lane >> 2) * W_PITCH + col * 16;
+        job.wdst = wsm_u32 + (lane >> 2) * W_PITCH + ((col ^ (((lane >> 3) & 1) << 1)) << 4);
         job.sbdst = wsm_u32 + WS::W_BYTES + (sb_q & (NP - 1)) * (STG_RUNS * 64) + (lane & 7) * 16;
     }
 
@@ -348,7 +512,8 @@ grouped_mma_decode_kernel(const Params p) {
 
         float tot[NT][NP][4];
         if (NT == 1 || cnt - tok0 <= 8) {
-            decode_pass<FUSED, 1>(p, job, wsm, xs_sm, row0, cnt, tok0, lane, tot);
+            if (KSPLIT == 1) decode_pass_shared<FUSED, 1>(p, job, wsm, xring, xs_sm, row0, cnt, tok0, n64, lane, tot);
+            else decode_pass<FUSED, 1>(p, job, wsm, xs_sm, row0, cnt, tok0, lane, tot);
 #pragma unroll
             for (int j = 1; j < NT; ++j)
 #pragma unroll
@@ -356,7 +521,8 @@ grouped_mma_decode_kernel(const Params p) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) tot[j][q][i] = 0.0f;
         } else {
-            decode_pass<FUSED, NT>(p, job, wsm, xs_sm, row0, cnt, tok0, lane, tot);
+            if (KSPLIT == 1) decode_pass_shared<FUSED, NT>(p, job, wsm, xring, xs_sm, row0, cnt, tok0, n64, lane, tot);
+            else decode_pass<FUSED, NT>(p, job, wsm, xs_sm, row0, cnt, tok0, lane, tot);
         }
 
         if (KSPLIT > 1) {

@@ -350,7 +350,7 @@ template <bool FUSED, int NT, int KSPLIT>
 void launch_mma_decode_k(const dmma::Params& p, int n_experts, cudaStream_t st) {
     using WS = dmma::WarpStage<FUSED>;
     auto k = dmma::grouped_mma_decode_kernel<FUSED, NT, KSPLIT>;
-    const int smem = WS::TOTAL + dmma::xs_sm_runs(p.K / 64) * 64;
+    const int smem = WS::smem_bytes(p.K / 64, KSPLIT);
     static int attr_smem = 0;
     if (smem > attr_smem) {
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
