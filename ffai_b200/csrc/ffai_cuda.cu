@@ -71,6 +71,7 @@ struct ffai_moe_layer {
     uint32_t* sb_down = nullptr;
     uint32_t* tile_offsets = nullptr;    // [E+1]
     uint16_t* sh_x = nullptr;        // [T,H]  shared expert input (8-run permuted)
+    uint16_t* sh_wbf[3] = {nullptr, nullptr, nullptr};  // shared expert expanded to bf16 (bit widths other than 4): gate, up, down
     uint16_t* sh_inner_bf = nullptr; // [T,Is]
     uint32_t* sh_sched = nullptr;    // offsets[2] + tile_offsets[2]
     uint32_t* error_word = nullptr;
@@ -394,6 +395,90 @@ __global__ void dense_rowdot_kernel(const TW* __restrict__ w, const uint16_t* __
     if (lane == 0) out[t] = acc;
 }
 
+// One projection expanded to bf16 in the tensor-core operand's K order: w = fma(q, scale, bias) rounded
+// once, every 8-run stored as 0,4,1,5,2,6,3,7.  One thread per 8-run.  Runs once, at load time.
+template <int BITS>
+__global__ void expand_to_bf16_perm8_kernel(const uint32_t* __restrict__ weight, const uint16_t* __restrict__ scales,
+                                            const uint16_t* __restrict__ biases, uint16_t* __restrict__ out,
+                                            size_t rows, int K, int group_size) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int runs = K / 8;
+    if (i >= rows * runs) return;
+    const size_t row = i / runs;
+    const int run = (int)(i - row * runs);
+    const uint32_t* w = weight + row * ((size_t)K * BITS / 32);
+    const int gpr = K / group_size;
+    const float s = bf16_bits_to_f32(scales[row * gpr + (run * 8) / group_size]);
+    const float b = bf16_bits_to_f32(biases[row * gpr + (run * 8) / group_size]);
+    uint16_t v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = f32_to_bf16_bits(fmaf((float)unpack_at<BITS>(w, run * 8 + j), s, b));
+    uint4 o;
+    o.x = (uint32_t)v[0] | ((uint32_t)v[4] << 16);
+    o.y = (uint32_t)v[1] | ((uint32_t)v[5] << 16);
+    o.z = (uint32_t)v[2] | ((uint32_t)v[6] << 16);
+    o.w = (uint32_t)v[3] | ((uint32_t)v[7] << 16);
+    *reinterpret_cast<uint4*>(out + row * K + run * 8) = o;
+}
+
+int launch_expand_to_bf16(const ffai_qproj& q, uint16_t* out, size_t rows, int K, int bits, int gs) {
+    const size_t n = rows * (K / 8);
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    switch (bits) {
+        case 2: expand_to_bf16_perm8_kernel<2><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
+        case 3: expand_to_bf16_perm8_kernel<3><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
+        case 4: expand_to_bf16_perm8_kernel<4><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
+        case 5: expand_to_bf16_perm8_kernel<5><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
+        case 6: expand_to_bf16_perm8_kernel<6><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
+        case 8: expand_to_bf16_perm8_kernel<8><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
+        default: return FFAI_ERR_INVALID_ARG;
+    }
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}
+
+// [1,H] affine-quantized projection per token (the shared expert's sigmoid gate): one warp per token,
+// fp32 accumulation, lanes take 8-runs round robin, fixed-shape warp reduction.
+template <int BITS>
+__global__ void affine_rowdot_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales,
+                                     const uint16_t* __restrict__ biases, const uint16_t* __restrict__ x,
+                                     float* __restrict__ out, int n_tokens, int hidden, int group_size) {
+    const int warps = blockDim.x / 32;
+    const int t = blockIdx.x * warps + threadIdx.x / 32;
+    if (t >= n_tokens) return;
+    const int lane = threadIdx.x & 31;
+    const uint16_t* xr = x + (size_t)t * hidden;
+    float acc = 0.0f;
+    for (int k0 = lane * 8; k0 < hidden; k0 += 256) {
+        const float s = bf16_bits_to_f32(scales[k0 / group_size]);
+        const float b = bf16_bits_to_f32(biases[k0 / group_size]);
+        const uint4 xv = *reinterpret_cast<const uint4*>(xr + k0);
+        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float wv = fmaf((float)unpack_at<BITS>(w, k0 + j), s, b);
+            const float xf = (j & 1) ? bf16hi(xw[j >> 1]) : bf16lo(xw[j >> 1]);
+            acc = fmaf(wv, xf, acc);
+        }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[t] = acc;
+}
+
+int launch_affine_rowdot(const ffai_linear& g, int bits, int gs, const uint16_t* x, float* out, int T, int H, cudaStream_t st) {
+    const uint32_t* w = (const uint32_t*)g.weight;
+    const unsigned blocks = (unsigned)((T + 3) / 4);
+    switch (bits) {
+        case 2: affine_rowdot_kernel<2><<<blocks, 128, 0, st>>>(w, g.scales, g.biases, x, out, T, H, gs); break;
+        case 3: affine_rowdot_kernel<3><<<blocks, 128, 0, st>>>(w, g.scales, g.biases, x, out, T, H, gs); break;
+        case 4: affine_rowdot_kernel<4><<<blocks, 128, 0, st>>>(w, g.scales, g.biases, x, out, T, H, gs); break;
+        case 5: affine_rowdot_kernel<5><<<blocks, 128, 0, st>>>(w, g.scales, g.biases, x, out, T, H, gs); break;
+        case 6: affine_rowdot_kernel<6><<<blocks, 128, 0, st>>>(w, g.scales, g.biases, x, out, T, H, gs); break;
+        case 8: affine_rowdot_kernel<8><<<blocks, 128, 0, st>>>(w, g.scales, g.biases, x, out, T, H, gs); break;
+        default: return FFAI_ERR_INVALID_ARG;
+    }
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}
+
 enum Stage { ST_ROUTER = 0, ST_PLAN, ST_GATHER, ST_GATE_UP, ST_DOWN, ST_COMBINE, ST_SHARED, ST_EXCHANGE };
 
 // A stage may run in up to two segments per forward (the exchange does).
@@ -539,7 +624,7 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
     // 256-k packed TMA box.
     const bool tc_shapes = H >= 256 && I >= 256 && (c.shared_intermediate == 0 || c.shared_intermediate >= 256);
     const bool want_tc = cc_major == 10 && tc_shapes;
-    if (c.expert_bits == 4 || (want_tc && c.shared_intermediate > 0 && c.shared_bits == 4)) {
+    if (c.expert_bits == 4 || (want_tc && c.shared_intermediate > 0)) {
         const size_t Mp = Mx < 128 ? 128 : Mx, Tp = T < 128 ? 128 : T;  // at least one full TMA box of rows
         if ((rc = ws_alloc(L, &L->xg, Mp * H))) return rc;
         if ((rc = ws_alloc(L, &L->inner_bf, Mp * I))) return rc;
@@ -550,7 +635,7 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
         if (want_tc) {
             if (world == 1 && (rc = ws_alloc(L, &L->y_bf, M * H))) return rc;
             if ((rc = ws_alloc(L, &L->tile_offsets, E + 1))) return rc;
-            if (c.shared_intermediate > 0 && c.shared_bits == 4) {
+            if (c.shared_intermediate > 0) {
                 if ((rc = ws_alloc(L, &L->sh_x, Tp * H))) return rc;
                 if ((rc = ws_alloc(L, &L->sh_inner_bf, Tp * c.shared_intermediate))) return rc;
                 if ((rc = ws_alloc(L, &L->sh_sched, 4))) return rc;
@@ -571,6 +656,7 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
     const ffai_moe_config& c = L->cfg;
     CUDA_TRY(L, cudaSetDevice(L->device));
     free_list(L->owned_weights);
+    L->sh_wbf[0] = L->sh_wbf[1] = L->sh_wbf[2] = nullptr;
     L->weights_set = false;
     L->w = ffai_moe_weights{};
     int rc;
@@ -617,9 +703,29 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
         }
         if (L->sh_x) {
             const int Is = c.shared_intermediate;
-            ok = ok && make_weight_map(&L->tm_sh_gate, L->w.shared_gate_proj.weight, Is, c.hidden / 8);
-            ok = ok && make_weight_map(&L->tm_sh_up, L->w.shared_up_proj.weight, Is, c.hidden / 8);
-            ok = ok && make_weight_map(&L->tm_sh_down, L->w.shared_down_proj.weight, c.hidden, Is / 8);
+            if (c.shared_bits == 4) {
+                ok = ok && make_weight_map(&L->tm_sh_gate, L->w.shared_gate_proj.weight, Is, c.hidden / 8);
+                ok = ok && make_weight_map(&L->tm_sh_up, L->w.shared_up_proj.weight, Is, c.hidden / 8);
+                ok = ok && make_weight_map(&L->tm_sh_down, L->w.shared_down_proj.weight, c.hidden, Is / 8);
+            } else {
+                // other bit widths: expand the one shared expert to bf16 once (2 bytes per weight) and let the
+                // tensor-core kernel read it without a dequant stage
+                const ffai_qproj* q[3] = {&L->w.shared_gate_proj, &L->w.shared_up_proj, &L->w.shared_down_proj};
+                const size_t rows[3] = {(size_t)Is, (size_t)Is, (size_t)c.hidden};
+                const int kk[3] = {c.hidden, c.hidden, Is};
+                for (int i = 0; i < 3; ++i) {
+                    void* buf = nullptr;
+                    CUDA_TRY(L, cudaMalloc(&buf, rows[i] * kk[i] * 2));
+                    L->owned_weights.push_back(buf);
+                    L->sh_wbf[i] = static_cast<uint16_t*>(buf);
+                    if ((rc = launch_expand_to_bf16(*q[i], L->sh_wbf[i], rows[i], kk[i], c.shared_bits, c.shared_group_size)))
+                        return fail(L, rc, "expanding the shared expert to bf16 failed");
+                }
+                CUDA_TRY(L, cudaDeviceSynchronize());
+                ok = ok && make_act_map(&L->tm_sh_gate, L->sh_wbf[0], Is, c.hidden, BM);
+                ok = ok && make_act_map(&L->tm_sh_up, L->sh_wbf[1], Is, c.hidden, BM);
+                ok = ok && make_act_map(&L->tm_sh_down, L->sh_wbf[2], c.hidden, Is, BM);
+            }
             ok = ok && make_act_map(&L->tm_sh_x, L->sh_x, Tcap, c.hidden, BM);
             ok = ok && make_act_map(&L->tm_sh_inner, L->sh_inner_bf, Tcap, Is, BM);
         }
@@ -1203,13 +1309,16 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
             p.scales2 = L->w.shared_up_proj.scales; p.biases2 = L->w.shared_up_proj.biases;
             p.n_out = Is; p.K = H; p.m_tiles = (Is + BN / 2 - 1) / (BN / 2);
             p.out = L->sh_inner_bf; p.out_ld = Is; p.out_permute8 = 1;
-            if (launch_grouped_gemm<true, uint16_t>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x, p, L->n_sms, st))
+            const bool wbf = L->sh_wbf[0] != nullptr;
+            if (wbf ? launch_grouped_gemm<true, uint16_t, true>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x, p, L->n_sms, st)
+                    : launch_grouped_gemm<true, uint16_t>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x, p, L->n_sms, st))
                 return fail(L, FFAI_ERR_CUDA, "shared gate/up grouped GEMM launch failed");
             p.scales = L->w.shared_down_proj.scales; p.biases = L->w.shared_down_proj.biases;
             p.scales2 = nullptr; p.biases2 = nullptr;
             p.n_out = H; p.K = Is; p.m_tiles = (H + BN - 1) / BN;
             p.out = L->sh_y; p.out_ld = H; p.out_permute8 = 0;
-            if (launch_grouped_gemm<false, float>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner, p, L->n_sms, st))
+            if (wbf ? launch_grouped_gemm<false, float, true>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner, p, L->n_sms, st)
+                    : launch_grouped_gemm<false, float>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner, p, L->n_sms, st))
                 return fail(L, FFAI_ERR_CUDA, "shared down grouped GEMM launch failed");
             L->launches += 4;
         } else {
@@ -1226,10 +1335,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         }
         sh_y = L->sh_y;
         if (c.shared_gate_kind == FFAI_LINEAR_AFFINE) {
-            ffai_qproj g{(const uint32_t*)L->w.shared_gate.weight, L->w.shared_gate.scales, L->w.shared_gate.biases, nullptr};
-            GemvParams gp = gemv_params(g, nullptr, 1, H, c.shared_gate_group_size, 1);
-            gp.n_rows = T;
-            if ((rc = launch_grouped_gemv<uint16_t, float, false>(gp, c.shared_gate_bits, x, L->sh_gate, 1, st)))
+            if ((rc = launch_affine_rowdot(L->w.shared_gate, c.shared_gate_bits, c.shared_gate_group_size, x, L->sh_gate, T, H, st)))
                 return fail(L, rc, "shared gate launch failed");
             L->launches += 1;
             sh_gate = L->sh_gate;

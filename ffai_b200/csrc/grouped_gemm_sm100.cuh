@@ -298,7 +298,11 @@ struct SmemLayout {
 // FUSED:  the 256 weight rows are 128 gate rows and the 128 matching up rows of one expert;
 //         out[row, n] = act(Wg[e][n]·x[row] + bg, Wu[e][n]·x[row] + bu), bf16, optionally 8-run permuted
 // !FUSED: 256 consecutive rows of one projection;  out[row, n] = W[e][n]·x[row] + b, TOut
-template <bool FUSED, typename TOut>
+// WBF16: the weights are already bf16 in the operand's K order ([rows, K], 8-runs permuted like the
+//         activations): the weight producer copies them by TMA straight into the operand ring and the
+//         dequant warps have nothing to do.  Used for projections that were expanded once at load time
+//         (bit widths other than 4).
+template <bool FUSED, typename TOut, bool WBF16>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
                     const __grid_constant__ CUtensorMap tm_x, const Params p) {
@@ -329,7 +333,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     if (threadIdx.x == 0) {
         for (int s = 0; s < L::NW; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), N_DEQ_WARPS); }
         for (int s = 0; s < L::NX; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 1); }
-        for (int s = 0; s < NB; ++s) { mbar_init(b_full(s), N_DEQ_WARPS); mbar_init(b_empty(s), 1); }
+        for (int s = 0; s < NB; ++s) { mbar_init(b_full(s), WBF16 ? 1 : N_DEQ_WARPS); mbar_init(b_empty(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
         *abort_flag = 0;
         fence_barrier_init();
@@ -346,7 +350,35 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == W_WARP) {
+    if (warp == W_WARP && WBF16) {
+        // ───────────── TMA producer, bf16 weights: two 128-row x 128-byte boxes per 64 k, into the operand ring ─────────────
+        if (lane == 0) {
+            RingPos bp{0, 0};
+            uint32_t issued = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const TileCoord c = decode_tile(p, tile, BM);
+                const int wrow = c.expert * p.n_out + c.m_tile * ROWS_PER_TILE;
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!mbar_wait<64>(b_empty(bp.stage), bp.phase ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t stage = sbase + L::OFF_B + bp.stage * L::B_STAGE;
+                    mbar_arrive_expect_tx(b_full(bp.stage), L::B_STAGE);
+                    tma_load_2d(stage, &tm_w, kb * BK, wrow, b_full(bp.stage));
+                    if (FUSED) tma_load_2d(stage + L::B_STAGE / 2, &tm_w2, kb * BK, wrow, b_full(bp.stage));
+                    else tma_load_2d(stage + L::B_STAGE / 2, &tm_w, kb * BK, wrow + BN / 2, b_full(bp.stage));
+                    bp.advance(NB);
+                    ++issued;
+                }
+            }
+            if (!ok) {
+                const uint32_t first = issued > (uint32_t)NB ? issued - NB : 0;
+                for (uint32_t j = first; j < issued; ++j) {
+                    const uint64_t t0 = global_timer_ns();
+                    while (!mbar_try_wait(b_full(j % NB), (j / NB) & 1) && global_timer_ns() - t0 < 2000000ull) {}
+                }
+            }
+        }
+    } else if (warp == W_WARP) {
         // ───────────── TMA producer, packed weights: two 128-row x 128-byte boxes per 256 k ─────────────
         if (lane == 0) {
             RingPos wp{0, 0};
@@ -437,7 +469,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                 if (ok) umma_commit(acc_full(buf));
             }
         }
-    } else if (warp >= DEQ_WARP0 && warp < DEQ_WARP0 + N_DEQ_WARPS) {
+    } else if (!WBF16 && warp >= DEQ_WARP0 && warp < DEQ_WARP0 + N_DEQ_WARPS) {
         // ───────────── dequant: 512 threads, thread = (weight row r of 256, 32-k half of a 64-k block) ─────────────
         // A warp covers 16 rows x 2 halves, eight consecutive rows per quarter-warp, so both the 16-byte
         // reads of the 128-byte-swizzled packed tile and the 16-byte stores into the 128-byte-swizzled
