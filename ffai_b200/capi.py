@@ -73,7 +73,8 @@ class MoEConfig(C.Structure):
         ("max_tokens", C.c_int32),
         ("ep_rank", C.c_int32),
         ("ep_world", C.c_int32),
-        ("reserved", C.c_int32 * 8),
+        ("prefill_weight_cache", C.c_int32),
+        ("reserved", C.c_int32 * 7),
     ]
 
     def __init__(self, **kw):

@@ -67,6 +67,21 @@ FFAI_DEVINL float small_uint_to_float(uint32_t q) {
     return __uint_as_float(0x4B000000u | q) - 8388608.0f;
 }
 
+// The same activations with the kind fixed at compile time, for loops that branch once outside.
+template <int ACT>
+FFAI_DEVINL float glu_activation_t(float g, float u, float limit, float alpha) {
+    if (ACT == 1) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return __fdividef(g, 1.0f + __expf(-alpha * g)) * (u + 1.0f);
+    }
+    if (ACT == 2) {
+        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        return 0.5f * g * (1.0f + tanhf(inner)) * u;
+    }
+    return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
 FFAI_DEVINL float warp_sum(float v) {
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, m);

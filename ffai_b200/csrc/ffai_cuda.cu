@@ -71,6 +71,10 @@ struct ffai_moe_layer {
     uint32_t* sb_down = nullptr;
     uint32_t* tile_offsets = nullptr;    // [E+1]
     uint16_t* sh_x = nullptr;        // [T,H]  shared expert input (8-run permuted)
+    uint16_t* exp_wbf[3] = {nullptr, nullptr, nullptr}; // routed experts expanded to bf16 (prefill weight cache): gate, up, down
+    bool cache_planned = false;
+    CUtensorMap tm_gate_bf{}, tm_up_bf{}, tm_down_bf{};
+    int opt_tc_weights = 0;          // tensor-core path reads: 0 the bf16 cache when there is one, 1 always the packed weights
     uint16_t* sh_wbf[3] = {nullptr, nullptr, nullptr};  // shared expert expanded to bf16 (bit widths other than 4): gate, up, down
     uint16_t* sh_inner_bf = nullptr; // [T,Is]
     uint32_t* sh_sched = nullptr;    // offsets[2] + tile_offsets[2]
@@ -624,7 +628,13 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
     // 256-k packed TMA box.
     const bool tc_shapes = H >= 256 && I >= 256 && (c.shared_intermediate == 0 || c.shared_intermediate >= 256);
     const bool want_tc = cc_major == 10 && tc_shapes;
-    if (c.expert_bits == 4 || (want_tc && c.shared_intermediate > 0)) {
+    {
+        const double cache_bytes = 3.0 * (double)L->e_local * H * I * 2.0;
+        const bool prefill_sized = (double)T * K / E >= 32.0;
+        L->cache_planned = want_tc && c.prefill_weight_cache != 1 &&
+                           (c.prefill_weight_cache == 2 || (prefill_sized && cache_bytes <= 4.0 * 1073741824.0));
+    }
+    if (c.expert_bits == 4 || (want_tc && (c.shared_intermediate > 0 || L->cache_planned))) {
         const size_t Mp = Mx < 128 ? 128 : Mx, Tp = T < 128 ? 128 : T;  // at least one full TMA box of rows
         if ((rc = ws_alloc(L, &L->xg, Mp * H))) return rc;
         if ((rc = ws_alloc(L, &L->inner_bf, Mp * I))) return rc;
@@ -657,6 +667,7 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
     CUDA_TRY(L, cudaSetDevice(L->device));
     free_list(L->owned_weights);
     L->sh_wbf[0] = L->sh_wbf[1] = L->sh_wbf[2] = nullptr;
+    L->exp_wbf[0] = L->exp_wbf[1] = L->exp_wbf[2] = nullptr;
     L->weights_set = false;
     L->w = ffai_moe_weights{};
     int rc;
@@ -700,6 +711,27 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
             ok = ok && make_weight_map(&L->tm_down, L->w.down_proj.weight, (uint64_t)El * c.hidden, c.intermediate / 8);
             ok = ok && make_act_map(&L->tm_xg, L->xg, Mcap, c.hidden, BM);
             ok = ok && make_act_map(&L->tm_inner, L->inner_bf, Mcap, c.intermediate, BM);
+        }
+        if (L->cache_planned) {
+            const ffai_qproj* q[3] = {&L->w.gate_proj, &L->w.up_proj, &L->w.down_proj};
+            const size_t rows[3] = {(size_t)El * c.intermediate, (size_t)El * c.intermediate, (size_t)El * c.hidden};
+            const int kk[3] = {c.hidden, c.hidden, c.intermediate};
+            for (int i = 0; i < 3; ++i) {
+                void* buf = nullptr;
+                CUDA_TRY(L, cudaMalloc(&buf, rows[i] * kk[i] * 2));
+                L->owned_weights.push_back(buf);
+                L->exp_wbf[i] = static_cast<uint16_t*>(buf);
+                if ((rc = launch_expand_to_bf16(*q[i], L->exp_wbf[i], rows[i], kk[i], c.expert_bits, c.expert_group_size)))
+                    return fail(L, rc, "expanding the experts to bf16 failed");
+            }
+            CUDA_TRY(L, cudaDeviceSynchronize());
+            ok = ok && make_act_map(&L->tm_gate_bf, L->exp_wbf[0], rows[0], c.hidden, BM);
+            ok = ok && make_act_map(&L->tm_up_bf, L->exp_wbf[1], rows[1], c.hidden, BM);
+            ok = ok && make_act_map(&L->tm_down_bf, L->exp_wbf[2], rows[2], c.intermediate, BM);
+            if (c.expert_bits != 4) {
+                ok = ok && make_act_map(&L->tm_xg, L->xg, Mcap, c.hidden, BM);
+                ok = ok && make_act_map(&L->tm_inner, L->inner_bf, Mcap, c.intermediate, BM);
+            }
         }
         if (L->sh_x) {
             const int Is = c.shared_intermediate;
@@ -819,6 +851,11 @@ extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name,
     if (!strcmp(name, "tc_min_rows")) {
         if (value < 0) return fail(L, FFAI_ERR_INVALID_ARG, "option tc_min_rows must be >= 0");
         L->opt_tc_min_rows = value;
+        return FFAI_OK;
+    }
+    if (!strcmp(name, "tc_weights")) {
+        if (value < 0 || value > 1) return fail(L, FFAI_ERR_INVALID_ARG, "tc_weights must be 0 (cache when present) or 1 (packed)");
+        L->opt_tc_weights = value;
         return FFAI_OK;
     }
     if (!strcmp(name, "ksplit")) {
@@ -966,9 +1003,23 @@ int ep_all_to_all(ffai_moe_layer* L, const uint8_t* send, const size_t* off_s, c
     return FFAI_OK;
 }
 
+// The two grouped GEMMs of the tensor-core path, from the bf16 weight cache when the layer keeps one,
+// else from the packed 4-bit weights with the in-kernel dequant stage.
+bool tc_reads_cache(const ffai_moe_layer* L) { return L->exp_wbf[0] && (L->opt_tc_weights == 0 || L->cfg.expert_bits != 4); }
+bool tc_possible(const ffai_moe_layer* L) { return L->tc_ok && (L->cfg.expert_bits == 4 || L->exp_wbf[0]); }
+int tc_gate_up(ffai_moe_layer* L, const g100::Params& p, cudaStream_t st) {
+    return tc_reads_cache(L) ? g100::launch_grouped_gemm<true, uint16_t, true>(L->tm_gate_bf, L->tm_up_bf, L->tm_xg, p, L->n_sms, st)
+                             : g100::launch_grouped_gemm<true, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg, p, L->n_sms, st);
+}
+template <typename TOut>
+int tc_down(ffai_moe_layer* L, const g100::Params& p, cudaStream_t st) {
+    return tc_reads_cache(L) ? g100::launch_grouped_gemm<false, TOut, true>(L->tm_down_bf, L->tm_down_bf, L->tm_inner, p, L->n_sms, st)
+                             : g100::launch_grouped_gemm<false, TOut>(L->tm_down, L->tm_down, L->tm_inner, p, L->n_sms, st);
+}
+
 // Whether rows travel 8-run permuted (the layout both 4-bit kernels read).  Every rank must agree, so
 // the rule looks only at the layer's configuration and options.
-bool ep_rows_perm8(const ffai_moe_layer* L) { return L->mma_ok && L->opt_path != 1; }
+bool ep_rows_perm8(const ffai_moe_layer* L) { return (L->mma_ok || tc_possible(L)) && L->opt_path != 1; }
 
 // Routed experts over rows that are already expert-contiguous in L->xg (bf16; 8-run permuted when the layer's
 // experts are 4-bit with group 64/128, plain otherwise).  Output: fp32 rows in L->y.
@@ -977,12 +1028,14 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
     const int H = c.hidden, I = c.intermediate;
     if (n_rows <= 0) return FFAI_OK;
     const double rpe = (double)n_rows / n_exp;
-    const bool can_tc = L->tc_ok && c.expert_bits == 4;
+    const bool can_tc = tc_possible(L);
     bool use_mma = false, use_tc = false;
-    if (ep_rows_perm8(L)) {   // the rows arrived 8-run permuted: one of the two 4-bit kernels must take them
-        if (L->opt_path == 3) use_mma = true;
+    if (ep_rows_perm8(L)) {   // the rows arrived 8-run permuted: the streaming or the tensor-core kernels must take them
+        if (L->opt_path == 3) use_tc = !L->mma_ok;
         else if (L->opt_path == 2) use_tc = can_tc;
-        else use_tc = can_tc && rpe > 12.0;
+        else use_tc = can_tc && (rpe > 12.0 || !L->mma_ok);
+        if (!L->mma_ok) use_tc = true;
+        if (!can_tc) use_tc = false;
         use_mma = !use_tc;
     }
     if (use_mma) {
@@ -1022,17 +1075,19 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         stage_begin(L, ST_GATE_UP, st);
         p.scales = L->w.gate_proj.scales; p.biases = L->w.gate_proj.biases; p.row_bias = L->w.gate_proj.row_bias;
         p.scales2 = L->w.up_proj.scales; p.biases2 = L->w.up_proj.biases; p.row_bias2 = L->w.up_proj.row_bias;
+        p.sb = L->sb_gate; p.sb2 = L->sb_up;
         p.n_out = I; p.K = H; p.m_tiles = (I + BN / 2 - 1) / (BN / 2);
         p.out = L->inner_bf; p.out_ld = I; p.out_permute8 = 1;
-        if (launch_grouped_gemm<true, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg, p, L->n_sms, st))
+        if (tc_gate_up(L, p, st))
             return fail(L, FFAI_ERR_CUDA, "gate/up grouped GEMM launch failed");
         stage_end(L, ST_GATE_UP, st);
         stage_begin(L, ST_DOWN, st);
         p.scales = L->w.down_proj.scales; p.biases = L->w.down_proj.biases; p.row_bias = L->w.down_proj.row_bias;
         p.scales2 = nullptr; p.biases2 = nullptr; p.row_bias2 = nullptr;
+        p.sb = L->sb_down; p.sb2 = nullptr;
         p.n_out = H; p.K = I; p.m_tiles = (H + BN - 1) / BN;
         p.out = L->y; p.out_ld = H; p.out_permute8 = 0;
-        if (launch_grouped_gemm<false, float>(L->tm_down, L->tm_down, L->tm_inner, p, L->n_sms, st))
+        if (tc_down<float>(L, p, st))
             return fail(L, FFAI_ERR_CUDA, "down grouped GEMM launch failed");
         stage_end(L, ST_DOWN, st);
         L->launches += 3;
@@ -1177,7 +1232,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     //   tcgen05 grouped GEMM            4-bit, many rows per expert (prefill): bound by the tensor cores
     //   CUDA-core grouped GEMV          any bit width / group size, and shapes the others do not take
     const double rows_per_expert = (double)M / E;
-    const bool can_tc = L->tc_ok && c.expert_bits == 4;
+    const bool can_tc = tc_possible(L);
     bool mma_experts = false, tc_experts = false;
     if (ep_on) { /* done above */ }
     else if (L->opt_path == 3) mma_experts = L->mma_ok;
@@ -1245,9 +1300,10 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         stage_begin(L, ST_GATE_UP, st);
         p.scales = L->w.gate_proj.scales; p.biases = L->w.gate_proj.biases; p.row_bias = L->w.gate_proj.row_bias;
         p.scales2 = L->w.up_proj.scales; p.biases2 = L->w.up_proj.biases; p.row_bias2 = L->w.up_proj.row_bias;
+        p.sb = L->sb_gate; p.sb2 = L->sb_up;
         p.n_out = I; p.K = H; p.m_tiles = (I + BN / 2 - 1) / (BN / 2);
         p.out = L->inner_bf; p.out_ld = I; p.out_permute8 = 1;
-        if (launch_grouped_gemm<true, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg, p, L->n_sms, st))
+        if (tc_gate_up(L, p, st))
             return fail(L, FFAI_ERR_CUDA, "gate/up grouped GEMM launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += 1;
         stage_end(L, ST_GATE_UP, st);
@@ -1256,9 +1312,10 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         p.timeline = nullptr;
         p.scales = L->w.down_proj.scales; p.biases = L->w.down_proj.biases; p.row_bias = L->w.down_proj.row_bias;
         p.scales2 = nullptr; p.biases2 = nullptr; p.row_bias2 = nullptr;
+        p.sb = L->sb_down; p.sb2 = nullptr;
         p.n_out = H; p.K = I; p.m_tiles = (H + BN - 1) / BN;
         p.out = L->y_bf; p.out_ld = H; p.out_permute8 = 0;
-        if (launch_grouped_gemm<false, uint16_t>(L->tm_down, L->tm_down, L->tm_inner, p, L->n_sms, st))
+        if (tc_down<uint16_t>(L, p, st))
             return fail(L, FFAI_ERR_CUDA, "down grouped GEMM launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += 1;
         stage_end(L, ST_DOWN, st);

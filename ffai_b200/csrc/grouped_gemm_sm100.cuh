@@ -61,6 +61,8 @@ struct Params {
     const uint16_t* scales2;   // second projection (fused gate/up)
     const uint16_t* biases2;
     const uint16_t* row_bias2;
+    const uint32_t* sb;        // nullable: (scale | bias << 16) words re-tiled [E, n_out/16, K/64, 16] (group 64 or 128)
+    const uint32_t* sb2;
     int n_out;                 // output rows per expert
     int K;
     int group_size;
@@ -276,14 +278,18 @@ FFAI_DEVINL TileCoord decode_tile(const Params& p, int tile, int ntok) {
     return c;
 }
 
-template <bool FUSED>
+// Ring depths.  Both TMA-fed rings must hold enough 64-k stages to cover the latency of a bulk copy
+// (a few thousand cycles) at one stage per ~540 cycles of tensor-pipe time, or the MMA issuer idles.
+//   packed weights: operand ring 3 x 32 KB (filled by the dequant warps), packed ring 2 x 32 KB, activations 4 x 16 KB
+//   bf16 weights:   operand ring 4 x 32 KB (filled by TMA), no packed ring, activations 5 x 16 KB
+template <bool WBF16>
 struct SmemLayout {
-    static constexpr int B_STAGE = BN * BK * 2;            // 32 KB: 256 weight rows x 64 k, bf16, dequantised
-    static constexpr int NB = 3;                           // dequantised-operand ring
+    static constexpr int B_STAGE = BN * BK * 2;            // 32 KB: 256 weight rows x 64 k, bf16
+    static constexpr int NB = WBF16 ? 4 : 3;               // operand ring
     static constexpr int W_STAGE = BN * (KS / 2);          // 32 KB: 256 weight rows x 256 k, packed 4-bit
-    static constexpr int NW = 2;                           // packed-weight ring (256-k super blocks)
+    static constexpr int NW = WBF16 ? 0 : 2;               // packed-weight ring (256-k super blocks)
     static constexpr int X_TILE = BM * BK * 2;             // 16 KB: 128 activation rows x 64 k
-    static constexpr int NX = 3;                           // activation ring
+    static constexpr int NX = WBF16 ? 5 : 4;               // activation ring
     static constexpr int OFF_B = 0;
     static constexpr int OFF_W = OFF_B + NB * B_STAGE;
     static constexpr int OFF_X = OFF_W + NW * W_STAGE;
@@ -306,7 +312,7 @@ template <bool FUSED, typename TOut, bool WBF16>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
                     const __grid_constant__ CUtensorMap tm_x, const Params p) {
-    using L = SmemLayout<FUSED>;
+    using L = SmemLayout<WBF16>;
     constexpr int NB = L::NB;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
@@ -402,10 +408,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             }
             if (!ok) {
                 // copies already issued still land in this CTA's shared memory: wait for them (bounded, 2 ms each)
-                const uint32_t first = issued > (uint32_t)L::NW ? issued - L::NW : 0;
+                constexpr uint32_t NWd = L::NW > 0 ? L::NW : 1;   // (this branch is never taken without a packed ring)
+                const uint32_t first = issued > NWd ? issued - NWd : 0;
                 for (uint32_t j = first; j < issued; ++j) {
                     const uint64_t t0 = global_timer_ns();
-                    while (!mbar_try_wait(w_full(j % L::NW), (j / L::NW) & 1) && global_timer_ns() - t0 < 2000000ull) {}
+                    while (!mbar_try_wait(w_full(j % NWd), (j / NWd) & 1) && global_timer_ns() - t0 < 2000000ull) {}
                 }
             }
         }
@@ -474,66 +481,93 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         // A warp covers 16 rows x 2 halves, eight consecutive rows per quarter-warp, so both the 16-byte
         // reads of the 128-byte-swizzled packed tile and the 16-byte stores into the 128-byte-swizzled
         // operand tile touch eight distinct chunk columns: no bank conflicts either way.
+        // Per 64-k block a thread turns 4 packed words into 32 bf16: per word 4 logic ops (mask and
+        // exponent held in registers so each pair is one instruction), 3 shifts, 4 subtract-128 and
+        // 4 fused multiply-adds on bf16 pairs, one 16-byte shared-space store.
         const int dw = warp - DEQ_WARP0;
         const int half = (lane >> 3) & 1;
         const int r = dw * 16 + (lane & 7) + ((lane >> 4) << 3);   // 0..255
         const int gpr = p.K / p.group_size;
         const int gshift = p.group_size == 32 ? 5 : (p.group_size == 64 ? 6 : 7);
-        const long total_rows = (long)p.n_experts * p.n_out;
         const bool second = FUSED && r >= BN / 2;                   // the up projection's half of the tile
         const uint16_t* sbase_ptr = second ? p.scales2 : p.scales;
         const uint16_t* bbase_ptr = second ? p.biases2 : p.biases;
+        const uint32_t* sbw_ptr = second ? p.sb2 : p.sb;            // nullable: repacked (scale | bias << 16) words
         const int r_in_proj = FUSED ? (r & (BN / 2 - 1)) : r;
+        uint32_t mask, expo;
+        asm volatile("mov.u32 %0, 0x000F000F;" : "=r"(mask));
+        asm volatile("mov.u32 %0, 0x43004300;" : "=r"(expo));       // also the bf16 pair (128, 128)
+        // shared-window addresses of this thread's row in stage 0 of both rings, and its four swizzled chunks
+        const uint32_t w_row0 = sbase + L::OFF_W + r * 128;
+        const uint32_t b_row0 = sbase + L::OFF_B + r * 128;
+        uint32_t w_chunk[SUB], b_chunk[4];
+#pragma unroll
+        for (int j = 0; j < SUB; ++j) w_chunk[j] = (uint32_t)(((2 * j + half) ^ (r & 7)) << 4);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) b_chunk[jj] = (uint32_t)(((half * 4 + jj) ^ (r & 7)) << 4);
         RingPos wp{0, 0}, bp{0, 0};
         bool ok = true;
         int gk = 0;
         const bool tl_on = (warp == DEQ_WARP0 && lane == 0);
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const TileCoord c = decode_tile(p, tile, BM);
-            long grow = (long)c.expert * p.n_out + c.m_tile * ROWS_PER_TILE + r_in_proj;
-            if (grow >= total_rows) grow = total_rows - 1;  // rows past the tensor: zero-filled by TMA, masked at store
+            int prow = c.m_tile * ROWS_PER_TILE + r_in_proj;        // row within the expert's projection
+            if (prow >= p.n_out) prow = p.n_out - 1;                // rows past the projection: zero-filled by TMA, masked at store
+            const long grow = (long)c.expert * p.n_out + prow;
             const uint16_t* sp = sbase_ptr + grow * gpr;
             const uint16_t* bq = bbase_ptr + grow * gpr;
+            const uint32_t* sw = sbw_ptr ? sbw_ptr + (((size_t)c.expert * (p.n_out >> 4) + (prow >> 4)) * KB) * 16 + (prow & 15) : nullptr;
             // scale and bias per 64-k block, fetched one super block ahead.  The loaded values are left
             // untouched until the next super block: an instruction that consumes a load stalls the warp
             // until the data arrives, which would put the memory latency back on the critical path.
-            uint16_t s_nxt[SUB], b_nxt[SUB];
+            uint32_t s_nxt[SUB], b_nxt[SUB];
             auto fetch_scales = [&](int kb0) {
 #pragma unroll
                 for (int j = 0; j < SUB; ++j) {
                     const int kb = min(kb0 + j, KB - 1);
-                    const int g = (kb * BK + half * 32) >> gshift;
-                    s_nxt[j] = sp[g];
-                    b_nxt[j] = bq[g];
+                    if (sw) {
+                        s_nxt[j] = __ldg(sw + (size_t)kb * 16);
+                    } else {
+                        const int g = (kb * BK + half * 32) >> gshift;
+                        s_nxt[j] = sp[g];
+                        b_nxt[j] = bq[g];
+                    }
                 }
             };
             fetch_scales(0);
             for (int sb = 0; sb < SB && ok; ++sb) {
                 uint32_t sb_cur[SUB];
 #pragma unroll
-                for (int j = 0; j < SUB; ++j) sb_cur[j] = (uint32_t)s_nxt[j] | ((uint32_t)b_nxt[j] << 16);
+                for (int j = 0; j < SUB; ++j) sb_cur[j] = sw ? s_nxt[j] : (s_nxt[j] | (b_nxt[j] << 16));
                 fetch_scales((sb + 1) * SUB);
                 if (tl_on) tl_mark(p, TL_DEQ, gk, 0);
                 if (!mbar_wait<0>(w_full(wp.stage), wp.phase, abort_flag)) { ok = false; break; }
                 if (tl_on) tl_mark(p, TL_DEQ, gk, 1);
-                const uint8_t* wrow_s = smem + L::OFF_W + wp.stage * L::W_STAGE + r * 128;
+                const uint32_t w_row = w_row0 + wp.stage * L::W_STAGE;
 #pragma unroll
                 for (int j = 0; j < SUB; ++j) {
                     if (sb * SUB + j >= KB) break;
                     if (!mbar_wait<0>(b_empty(bp.stage), bp.phase ^ 1, abort_flag)) { ok = false; break; }
                     if (tl_on) tl_mark(p, TL_DEQ, gk, 2);
-                    uint8_t* row = smem + L::OFF_B + bp.stage * L::B_STAGE + r * 128;
-                    // logical 16-byte chunk 2j+half of the packed row, at its swizzled position
-                    const uint4 wv = *reinterpret_cast<const uint4*>(wrow_s + (((2 * j + half) ^ (r & 7)) << 4));
+                    const uint32_t b_row = b_row0 + bp.stage * L::B_STAGE;
+                    uint32_t w4[4];
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(w4[0]), "=r"(w4[1]), "=r"(w4[2]), "=r"(w4[3]) : "r"(w_row + w_chunk[j]));
                     const uint32_t sbv = sb_cur[j];
-                    __nv_bfloat162 s2, b2;
-                    *reinterpret_cast<uint32_t*>(&s2) = __byte_perm(sbv, sbv, 0x1010);
-                    *reinterpret_cast<uint32_t*>(&b2) = __byte_perm(sbv, sbv, 0x3232);
-                    const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+                    const uint32_t s2 = __byte_perm(sbv, sbv, 0x1010), b2 = __byte_perm(sbv, sbv, 0x3232);
 #pragma unroll
                     for (int jj = 0; jj < 4; ++jj) {
-                        const int chunk = (half * 4 + jj) ^ (r & 7);
-                        *reinterpret_cast<uint4*>(row + chunk * 16) = dequant_word_bf16(words[jj], s2, b2);
+                        const uint32_t w = w4[jj];
+                        uint32_t o[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t t, q;
+                            asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(i == 0 ? w : (w >> (4 * i))), "r"(mask), "r"(expo));
+                            asm("sub.bf16x2 %0, %1, %2;" : "=r"(q) : "r"(t), "r"(expo));
+                            asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[i]) : "r"(q), "r"(s2), "r"(b2));
+                        }
+                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
+                                     ::"r"(b_row + b_chunk[jj]), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
                     }
                     fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
                     __syncwarp();
@@ -569,22 +603,40 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             for (int c0 = 0; c0 < ROWS_PER_TILE; c0 += 16) {
                 if (n0 + c0 >= p.n_out) break;                  // n_out is a multiple of 16: a chunk is all in or all out
                 uint32_t a[16], b[16];
+                const bool tl_e = (warp == EPI_WARP0 && lane == 0);
+                if (tl_e) tl_mark(p, TL_XPROD, (int)tcount * 16 + c0 / 16, 0);
                 tmem_ld16(t0 + c0, a);
                 if (FUSED) tmem_ld16(t0 + BN / 2 + c0, b);
                 tmem_ld_wait();
+                if (tl_e) tl_mark(p, TL_XPROD, (int)tcount * 16 + c0 / 16, 1);
                 if (tok_ok) {
                     float v[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        float x = __uint_as_float(a[j]);
-                        if (p.row_bias) x += bf16_bits_to_f32(p.row_bias[ebase + n0 + c0 + j]);
-                        if (FUSED) {
-                            float u = __uint_as_float(b[j]);
-                            if (p.row_bias2) u += bf16_bits_to_f32(p.row_bias2[ebase + n0 + c0 + j]);
-                            x = glu_activation(x, u, p.activation, p.limit, p.alpha);
-                        }
-                        v[j] = x;
+                        v[j] = __uint_as_float(a[j]);
+                        if (p.row_bias) v[j] += bf16_bits_to_f32(p.row_bias[ebase + n0 + c0 + j]);
                     }
+                    if (FUSED) {
+                        float u[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            u[j] = __uint_as_float(b[j]);
+                            if (p.row_bias2) u[j] += bf16_bits_to_f32(p.row_bias2[ebase + n0 + c0 + j]);
+                        }
+                        // one branch per chunk, outside the element loop: with the kind tested per element the
+                        // compiler predicates all three bodies and every element pays for the tanh
+                        if (p.activation == 1) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] = glu_activation_t<1>(v[j], u[j], p.limit, p.alpha);
+                        } else if (p.activation == 2) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] = glu_activation_t<2>(v[j], u[j], p.limit, p.alpha);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] = glu_activation_t<0>(v[j], u[j], p.limit, p.alpha);
+                        }
+                    }
+                    if (tl_e) tl_mark(p, TL_XPROD, (int)tcount * 16 + c0 / 16, 2);
                     if (sizeof(TOut) == 2) {
                         // 16 bf16 = two 16-byte stores; with the 8-run permutation, run positions hold k = 0,4,1,5,2,6,3,7
                         uint32_t w8[8];
@@ -608,6 +660,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                         for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                     }
                 }
+                if (tl_e) tl_mark(p, TL_XPROD, (int)tcount * 16 + c0 / 16, 3);
             }
             tc_fence_before();
             __syncwarp();

@@ -58,7 +58,7 @@ inline bool make_act_map(CUtensorMap* m, const uint16_t* x, uint64_t rows, uint6
 template <bool FUSED, typename TOut, bool WBF16 = false>
 int launch_grouped_gemm(const CUtensorMap& w, const CUtensorMap& w2, const CUtensorMap& x, const Params& p,
                         int n_ctas, cudaStream_t st) {
-    using L = SmemLayout<FUSED>;
+    using L = SmemLayout<WBF16>;
     auto k = grouped_gemm_kernel<FUSED, TOut, WBF16>;
     static bool attr_set = false;
     if (!attr_set) {

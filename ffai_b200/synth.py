@@ -121,6 +121,7 @@ class LayerSpec:
     shared_gate_kind: int = capi.LINEAR_NONE
     shared_gate_bits: int = 0
     shared_gate_group_size: int = 0
+    prefill_weight_cache: int = 0  # 0 automatic, 1 never, 2 always (bf16 copy of the experts for the tensor-core path)
     zipf_s: float = 0.0          # > 0: additive per-expert router bias with a Zipf profile
     zipf_strength: float = 1.0
 
@@ -134,7 +135,7 @@ class LayerSpec:
                   "router_bits", "router_group_size", "router_has_bias", "router_logits_bf16",
                   "expert_bits", "expert_group_size", "expert_row_bias", "shared_intermediate",
                   "shared_bits", "shared_group_size", "shared_gate_kind", "shared_gate_bits",
-                  "shared_gate_group_size"):
+                  "shared_gate_group_size", "prefill_weight_cache"):
             setattr(cfg, f, getattr(self, f))
         cfg.max_tokens = max_tokens
         cfg.ep_rank = ep_rank

@@ -125,7 +125,12 @@ typedef struct ffai_moe_config {
     int32_t max_tokens;        /* largest T a forward call may pass                   */
     int32_t ep_rank;           /* expert parallelism: this rank, 0 when ep_world<=1   */
     int32_t ep_world;          /* 0 or 1: single GPU                                  */
-    int32_t reserved[8];
+    int32_t prefill_weight_cache; /* bf16 copy of the routed experts (2 bytes per weight, beside the  */
+                               /* packed ones) that the tensor-core prefill path reads without a   */
+                               /* dequant stage: 0 automatic (kept when max_tokens*top_k/n_experts */
+                               /* >= 32 and the copy is at most 4 GiB), 1 never, 2 always.  Decode   */
+                               /* batches always stream the packed weights.                         */
+    int32_t reserved[7];
 } ffai_moe_config;
 
 /* One stacked quantized projection: weight [n, out, in*bits/32] u32,

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 
 def run_and_check(oracle_mod, spec, T, seed=0, residual=False, max_tokens=None, layer=None, host=None,
-                  token_mask=None, rel_rms_tol=5e-3, max_abs_norm_tol=2e-2, path=None):
+                  token_mask=None, rel_rms_tol=5e-3, max_abs_norm_tol=2e-2, path=None, options=None):
     host = host or synth.make_layer(spec, seed)
     x = synth.make_tokens(T, spec.hidden, seed)
     res = synth.make_tokens(T, spec.hidden, seed + 17) if residual else None
@@ -22,6 +22,8 @@ def run_and_check(oracle_mod, spec, T, seed=0, residual=False, max_tokens=None, 
     try:
         if path is not None:
             layer.set_option("path", path)
+        for name, value in (options or {}).items():
+            layer.set_option(name, value)
         out, dbg = layer.forward_host(x, residual=res, debug=True)
     finally:
         if own:
@@ -226,6 +228,38 @@ def test_tc_cfg3_full_prefill_sampled(oracle_mod):
     mask = np.zeros(2048, dtype=np.uint8)
     mask[np.random.default_rng(1).choice(2048, size=64, replace=False)] = 1
     run_and_check(oracle_mod, synth.cfg3_qwen(), 2048, token_mask=mask, path=TC)
+
+
+def test_tc_cfg3_full_prefill_packed_weights(oracle_mod):
+    """The same prefill with the tensor-core kernel dequantising the packed weights itself
+    (the automatic choice at this size is the bf16 weight cache)."""
+    mask = np.zeros(2048, dtype=np.uint8)
+    mask[np.random.default_rng(2).choice(2048, size=64, replace=False)] = 1
+    run_and_check(oracle_mod, synth.cfg3_qwen(), 2048, token_mask=mask, path=TC, options={"tc_weights": 1})
+
+
+@pytest.mark.parametrize("bits", [3, 4, 5, 6, 8])
+def test_tc_bf16_weight_cache_any_bit_width(oracle_mod, bits):
+    """With the cache the tensor-core path takes every bit width: the experts are expanded once."""
+    spec = synth.LayerSpec(f"cache_bits{bits}", 512, 256, 16, 4, expert_bits=bits, prefill_weight_cache=2)
+    run_and_check(oracle_mod, spec, 300, path=TC)
+    run_and_check(oracle_mod, spec, 300)          # automatic choice
+
+
+def test_tc_cache_and_packed_weights_agree(oracle_mod):
+    spec = synth.LayerSpec("cache_vs_packed", 512, 256, 16, 4, prefill_weight_cache=2)
+    host = synth.make_layer(spec, 3)
+    x = synth.make_tokens(400, spec.hidden, 3)
+    layer = MoELayer(host, 400)
+    try:
+        layer.set_option("path", TC)
+        a, _ = layer.forward_host(x)
+        layer.set_option("tc_weights", 1)
+        b, _ = layer.forward_host(x)
+    finally:
+        layer.close()
+    # both round fma(q, scale, bias) to bf16 once and run the same MMA sequence
+    assert np.array_equal(a, b)
 
 
 @pytest.mark.parametrize("gs", [32, 128])
