@@ -43,6 +43,7 @@ constexpr int BN = 256;        // weight rows per tile (the MMA's N: one fp32 TM
 constexpr int BK = 64;         // k per MMA stage (one 128-byte swizzle row of bf16)
 constexpr int KS = 256;        // k per packed-weight TMA box (one 128-byte row of 4-bit values)
 constexpr int SUB = KS / BK;   // MMA stages per packed-weight stage
+constexpr int SPF = 4;         // 64-k blocks of scale words a dequant thread fetches ahead
 constexpr int THREADS = 768;   // 24 warps
 constexpr int W_WARP = 0;      // packed-weight TMA producer
 constexpr int MMA_WARP = 1;    // MMA issuer, owns TMEM
@@ -281,6 +282,7 @@ FFAI_DEVINL TileCoord decode_tile(const Params& p, int tile, int ntok) {
 // Ring depths.  Both TMA-fed rings must hold enough 64-k stages to cover the latency of a bulk copy
 // (a few thousand cycles) at one stage per ~540 cycles of tensor-pipe time, or the MMA issuer idles.
 //   packed weights: operand ring 3 x 32 KB (filled by the dequant warps), packed ring 2 x 32 KB, activations 4 x 16 KB
+//                   (a packed ring of 4 x 16 KB with 64-byte unswizzled boxes measured slower)
 //   bf16 weights:   operand ring 4 x 32 KB (filled by TMA), no packed ring, activations 5 x 16 KB
 template <bool WBF16>
 struct SmemLayout {
@@ -498,7 +500,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         asm volatile("mov.u32 %0, 0x000F000F;" : "=r"(mask));
         asm volatile("mov.u32 %0, 0x43004300;" : "=r"(expo));       // also the bf16 pair (128, 128)
         // shared-window addresses of this thread's row in stage 0 of both rings, and its four swizzled chunks
-        const uint32_t w_row0 = sbase + L::OFF_W + r * 128;
+        const uint32_t w_row0 = sbase + L::OFF_W + r * (KS / 2);     // packed stage: 128-byte rows, 16-byte pieces XOR-swizzled by row
         const uint32_t b_row0 = sbase + L::OFF_B + r * 128;
         uint32_t w_chunk[SUB], b_chunk[4];
 #pragma unroll
@@ -520,10 +522,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             // scale and bias per 64-k block, fetched one super block ahead.  The loaded values are left
             // untouched until the next super block: an instruction that consumes a load stalls the warp
             // until the data arrives, which would put the memory latency back on the critical path.
-            uint32_t s_nxt[SUB], b_nxt[SUB];
+            uint32_t s_nxt[SPF], b_nxt[SPF];
             auto fetch_scales = [&](int kb0) {
 #pragma unroll
-                for (int j = 0; j < SUB; ++j) {
+                for (int j = 0; j < SPF; ++j) {
                     const int kb = min(kb0 + j, KB - 1);
                     if (sw) {
                         s_nxt[j] = __ldg(sw + (size_t)kb * 16);
@@ -535,50 +537,55 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                 }
             };
             fetch_scales(0);
-            for (int sb = 0; sb < SB && ok; ++sb) {
-                uint32_t sb_cur[SUB];
+            for (int kb0 = 0; kb0 < KB && ok; kb0 += SPF) {
+                uint32_t sb_cur[SPF];
 #pragma unroll
-                for (int j = 0; j < SUB; ++j) sb_cur[j] = sw ? s_nxt[j] : (s_nxt[j] | (b_nxt[j] << 16));
-                fetch_scales((sb + 1) * SUB);
-                if (tl_on) tl_mark(p, TL_DEQ, gk, 0);
-                if (!mbar_wait<0>(w_full(wp.stage), wp.phase, abort_flag)) { ok = false; break; }
-                if (tl_on) tl_mark(p, TL_DEQ, gk, 1);
-                const uint32_t w_row = w_row0 + wp.stage * L::W_STAGE;
+                for (int j = 0; j < SPF; ++j) sb_cur[j] = sw ? s_nxt[j] : (s_nxt[j] | (b_nxt[j] << 16));
+                fetch_scales(kb0 + SPF);
 #pragma unroll
-                for (int j = 0; j < SUB; ++j) {
-                    if (sb * SUB + j >= KB) break;
-                    if (!mbar_wait<0>(b_empty(bp.stage), bp.phase ^ 1, abort_flag)) { ok = false; break; }
-                    if (tl_on) tl_mark(p, TL_DEQ, gk, 2);
-                    const uint32_t b_row = b_row0 + bp.stage * L::B_STAGE;
-                    uint32_t w4[4];
-                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(w4[0]), "=r"(w4[1]), "=r"(w4[2]), "=r"(w4[3]) : "r"(w_row + w_chunk[j]));
-                    const uint32_t sbv = sb_cur[j];
-                    const uint32_t s2 = __byte_perm(sbv, sbv, 0x1010), b2 = __byte_perm(sbv, sbv, 0x3232);
+                for (int ws = 0; ws < SPF / SUB; ++ws) {
+                    if (kb0 + ws * SUB >= KB) break;
+                    if (tl_on) tl_mark(p, TL_DEQ, gk, 0);
+                    if (!mbar_wait<0>(w_full(wp.stage), wp.phase, abort_flag)) { ok = false; break; }
+                    if (tl_on) tl_mark(p, TL_DEQ, gk, 1);
+                    const uint32_t w_row = w_row0 + wp.stage * L::W_STAGE;
 #pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        const uint32_t w = w4[jj];
-                        uint32_t o[4];
+                    for (int j = 0; j < SUB; ++j) {
+                        if (kb0 + ws * SUB + j >= KB) break;
+                        if (!mbar_wait<0>(b_empty(bp.stage), bp.phase ^ 1, abort_flag)) { ok = false; break; }
+                        if (tl_on) tl_mark(p, TL_DEQ, gk, 2);
+                        const uint32_t b_row = b_row0 + bp.stage * L::B_STAGE;
+                        uint32_t w4[4];
+                        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(w4[0]), "=r"(w4[1]), "=r"(w4[2]), "=r"(w4[3]) : "r"(w_row + w_chunk[j]));
+                        const uint32_t sbv = sb_cur[ws * SUB + j];
+                        const uint32_t s2 = __byte_perm(sbv, sbv, 0x1010), b2 = __byte_perm(sbv, sbv, 0x3232);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint32_t t, q;
-                            asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(i == 0 ? w : (w >> (4 * i))), "r"(mask), "r"(expo));
-                            asm("sub.bf16x2 %0, %1, %2;" : "=r"(q) : "r"(t), "r"(expo));
-                            asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[i]) : "r"(q), "r"(s2), "r"(b2));
+                        for (int jj = 0; jj < 4; ++jj) {
+                            const uint32_t w = w4[jj];
+                            uint32_t o[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                uint32_t t, q;
+                                asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(i == 0 ? w : (w >> (4 * i))), "r"(mask), "r"(expo));
+                                asm("sub.bf16x2 %0, %1, %2;" : "=r"(q) : "r"(t), "r"(expo));
+                                asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[i]) : "r"(q), "r"(s2), "r"(b2));
+                            }
+                            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
+                                         ::"r"(b_row + b_chunk[jj]), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
                         }
-                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
-                                     ::"r"(b_row + b_chunk[jj]), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                        fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(b_full(bp.stage));
+                        if (tl_on) tl_mark(p, TL_DEQ, gk, 3);
+                        ++gk;
+                        bp.advance(NB);
                     }
-                    fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+                    if (!ok) break;
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(b_full(bp.stage));
-                    if (tl_on) tl_mark(p, TL_DEQ, gk, 3);
-                    ++gk;
-                    bp.advance(NB);
+                    if (lane == 0) mbar_arrive(w_empty(wp.stage));  // this warp is done reading the packed stage
+                    wp.advance(L::NW);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(w_empty(wp.stage));  // this warp is done reading the packed stage
-                wp.advance(L::NW);
             }
         }
     } else if (warp >= EPI_WARP0) {
