@@ -39,6 +39,7 @@ namespace ffai {
 namespace g100 {
 
 constexpr int BM = 128;        // activation rows per tile (the MMA's M: one TMEM lane each)
+constexpr int PAIR = 2 * BM;   // activation rows per work item: up to two token tiles share one pass over the weights
 constexpr int BN = 256;        // weight rows per tile (the MMA's N: one fp32 TMEM column each)
 constexpr int BK = 64;         // k per MMA stage (one 128-byte swizzle row of bf16)
 constexpr int KS = 256;        // k per packed-weight TMA box (one 128-byte row of 4-bit values)
@@ -71,6 +72,7 @@ struct Params {
     const uint32_t* offsets;       // [E+1] row ranges per expert in the sorted row space
     const uint32_t* tile_offsets;  // [E+1] prefix sum of token tiles per expert
     int m_tiles;                   // ceil(n_out / 128)
+    int group_rows;                // routed rows per work item: BM (one token tile) or PAIR (two tiles share a pass over the weights)
     int activation;
     float limit, alpha;
     void* out;                 // [rows, out_ld]
@@ -202,6 +204,17 @@ FFAI_DEVINL void tmem_ld16(uint32_t taddr, uint32_t* r) {
         : "r"(taddr)
         : "memory");
 }
+FFAI_DEVINL void tmem_ld8(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr)
+        : "memory");
+}
+template <int N>
+FFAI_DEVINL void tmem_ld_n(uint32_t taddr, uint32_t* r) {
+    if (N == 8) tmem_ld8(taddr, r); else tmem_ld16(taddr, r);
+}
 FFAI_DEVINL void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes (64 bf16),
@@ -258,8 +271,11 @@ FFAI_DEVINL int permute8_store_col(int n) {
     return (n & ~7) | (((k & 3) << 1) | (k >> 2));
 }
 
-// Tile index -> (expert, token-tile, row-tile).  Consecutive tiles share the token tile so the
-// activation tile stays hot in L2 across the CTAs that work on one expert.
+// Work item index -> (expert, group of up to 256 routed rows, weight-row tile).  An item holds one or
+// two 128-row token tiles that are multiplied against the same dequantised weight tile (each weight
+// tile is produced once per item, not once per token tile).  Consecutive items share the rows so
+// the activation tiles stay hot in L2 across the CTAs that work on one expert.
+// n_cols_valid counts the item's rows (1..256); tiles = 1 + (n_cols_valid > 128).
 struct TileCoord {
     int expert, row_begin, n_cols_valid, m_tile;
 };
@@ -287,11 +303,17 @@ FFAI_DEVINL TileCoord decode_tile(const Params& p, int tile, int ntok) {
 template <bool WBF16>
 struct SmemLayout {
     static constexpr int B_STAGE = BN * BK * 2;            // 32 KB: 256 weight rows x 64 k, bf16
-    static constexpr int NB = WBF16 ? 4 : 3;               // operand ring
+#ifndef FFAI_G100_NB_PACKED
+#define FFAI_G100_NB_PACKED 3
+#define FFAI_G100_NX_PACKED 4
+#define FFAI_G100_NB_BF16 4
+#define FFAI_G100_NX_BF16 5
+#endif
+    static constexpr int NB = WBF16 ? FFAI_G100_NB_BF16 : FFAI_G100_NB_PACKED;   // operand ring
     static constexpr int W_STAGE = BN * (KS / 2);          // 32 KB: 256 weight rows x 256 k, packed 4-bit
     static constexpr int NW = WBF16 ? 0 : 2;               // packed-weight ring (256-k super blocks)
     static constexpr int X_TILE = BM * BK * 2;             // 16 KB: 128 activation rows x 64 k
-    static constexpr int NX = WBF16 ? 5 : 4;               // activation ring
+    static constexpr int NX = WBF16 ? FFAI_G100_NX_BF16 : FFAI_G100_NX_PACKED;   // activation ring
     static constexpr int OFF_B = 0;
     static constexpr int OFF_W = OFF_B + NB * B_STAGE;
     static constexpr int OFF_X = OFF_W + NW * W_STAGE;
@@ -365,7 +387,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             uint32_t issued = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileCoord c = decode_tile(p, tile, BM);
+                const TileCoord c = decode_tile(p, tile, p.group_rows);
                 const int wrow = c.expert * p.n_out + c.m_tile * ROWS_PER_TILE;
                 for (int kb = 0; kb < KB; ++kb) {
                     if (!mbar_wait<64>(b_empty(bp.stage), bp.phase ^ 1, abort_flag)) { ok = false; break; }
@@ -393,7 +415,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             uint32_t issued = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileCoord c = decode_tile(p, tile, BM);
+                const TileCoord c = decode_tile(p, tile, p.group_rows);
                 const int wrow = c.expert * p.n_out + c.m_tile * ROWS_PER_TILE;
                 for (int sb = 0; sb < SB; ++sb) {
                     tl_mark(p, TL_WPROD, (int)issued, 0);
@@ -425,13 +447,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             uint32_t issued = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileCoord c = decode_tile(p, tile, BM);
-                for (int kb = 0; kb < KB; ++kb) {
-                    if (!mbar_wait<32>(x_empty(xp.stage), xp.phase ^ 1, abort_flag)) { ok = false; break; }
-                    mbar_arrive_expect_tx(x_full(xp.stage), L::X_TILE);
-                    tma_load_2d(sbase + L::OFF_X + xp.stage * L::X_TILE, &tm_x, kb * BK, c.row_begin, x_full(xp.stage));
-                    xp.advance(L::NX);
-                    ++issued;
+                const TileCoord c = decode_tile(p, tile, p.group_rows);
+                const int nt = c.n_cols_valid > BM ? 2 : 1;
+                for (int kb = 0; kb < KB && ok; ++kb) {
+                    for (int t = 0; t < nt; ++t) {
+                        if (!mbar_wait<32>(x_empty(xp.stage), xp.phase ^ 1, abort_flag)) { ok = false; break; }
+                        mbar_arrive_expect_tx(x_full(xp.stage), L::X_TILE);
+                        tma_load_2d(sbase + L::OFF_X + xp.stage * L::X_TILE, &tm_x, kb * BK, c.row_begin + t * BM, x_full(xp.stage));
+                        xp.advance(L::NX);
+                        ++issued;
+                    }
                 }
             }
             if (!ok) {
@@ -450,32 +475,43 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             int gk = 0;
             bool ok = true;
             const uint32_t idesc = make_idesc_bf16(BM, BN);
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-                const int buf = tcount & 1;
-                const uint32_t acc_ph = (tcount >> 1) & 1;
-                if (!mbar_wait<32>(acc_empty(buf), acc_ph ^ 1, abort_flag)) { ok = false; break; }
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const TileCoord c = decode_tile(p, tile, p.group_rows);
+                const int nt = c.n_cols_valid > BM ? 2 : 1;
+                // token tile t of the item accumulates in TMEM buffer (tcount + t) & 1
+                uint32_t d0[2];
+                for (int t = 0; t < nt; ++t) {
+                    const uint32_t tc = tcount + t;
+                    if (!mbar_wait<32>(acc_empty(tc & 1), ((tc >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    d0[t] = tmem_base + (uint32_t)((tc & 1) * BN);
+                }
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t d0 = tmem_base + (uint32_t)(buf * BN);
-                for (int kb = 0; kb < KB; ++kb, ++gk) {
-                    if (!mbar_wait<0>(x_full(xp.stage), xp.phase, abort_flag)) { ok = false; break; }
+                for (int kb = 0; kb < KB && ok; ++kb, ++gk) {
                     if (!mbar_wait<0>(b_full(bp.stage), bp.phase, abort_flag)) { ok = false; break; }
-                    tl_mark(p, TL_MMA, gk, 0);
-                    tc_fence_after();
-                    const uint64_t ad0 = make_kmajor_sw128_desc(sbase + L::OFF_X + xp.stage * L::X_TILE);
                     const uint64_t bd0 = make_kmajor_sw128_desc(sbase + L::OFF_B + bp.stage * L::B_STAGE);
+                    for (int t = 0; t < nt; ++t) {
+                        if (!mbar_wait<0>(x_full(xp.stage), xp.phase, abort_flag)) { ok = false; break; }
+                        if (t == 0) tl_mark(p, TL_MMA, gk, 0);
+                        tc_fence_after();
+                        const uint64_t ad0 = make_kmajor_sw128_desc(sbase + L::OFF_X + xp.stage * L::X_TILE);
 #pragma unroll
-                    for (int k16 = 0; k16 < BK / 16; ++k16) {
-                        // advancing 16 k inside the swizzled row = +32 bytes = +2 in the (addr >> 4) field
-                        umma_bf16(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, (kb | k16) != 0 ? 1u : 0u);
+                        for (int k16 = 0; k16 < BK / 16; ++k16) {
+                            // advancing 16 k inside the swizzled row = +32 bytes = +2 in the (addr >> 4) field
+                            umma_bf16(d0[t], ad0 + 2 * k16, bd0 + 2 * k16, idesc, (kb | k16) != 0 ? 1u : 0u);
+                        }
+                        umma_commit(x_empty(xp.stage));
+                        xp.advance(L::NX);
                     }
+                    if (!ok) break;
                     tl_mark(p, TL_MMA, gk, 1);
                     umma_commit(b_empty(bp.stage));
-                    umma_commit(x_empty(xp.stage));
                     tl_mark(p, TL_MMA, gk, 3);
-                    xp.advance(L::NX);
                     bp.advance(NB);
                 }
-                if (ok) umma_commit(acc_full(buf));
+                if (ok)
+                    for (int t = 0; t < nt; ++t) umma_commit(acc_full((tcount + t) & 1));
+                tcount += nt;
             }
         }
     } else if (!WBF16 && warp >= DEQ_WARP0 && warp < DEQ_WARP0 + N_DEQ_WARPS) {
@@ -512,7 +548,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         int gk = 0;
         const bool tl_on = (warp == DEQ_WARP0 && lane == 0);
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const TileCoord c = decode_tile(p, tile, BM);
+            const TileCoord c = decode_tile(p, tile, p.group_rows);
             int prow = c.m_tile * ROWS_PER_TILE + r_in_proj;        // row within the expert's projection
             if (prow >= p.n_out) prow = p.n_out - 1;                // rows past the projection: zero-filled by TMA, masked at store
             const long grow = (long)c.expert * p.n_out + prow;
@@ -593,8 +629,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
         uint32_t tcount = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-            const TileCoord c = decode_tile(p, tile, BM);
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
+          for (int tt = 0; tt < 2 && ok; ++tt) {
+            TileCoord c = decode_tile(p, tile, p.group_rows);
+            if (tt == 1 && c.n_cols_valid <= BM) break;
+            c.row_begin += tt * BM;                               // this token tile's rows
+            c.n_cols_valid = min(BM, c.n_cols_valid - tt * BM);
             const int buf = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1;
             if (warp == EPI_WARP0 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 0);
@@ -607,73 +647,78 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             const size_t ebase = (size_t)c.expert * p.n_out;
             uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + (size_t)(c.row_begin + tok) * p.out_ld * sizeof(TOut);
-            for (int c0 = 0; c0 < ROWS_PER_TILE; c0 += 16) {
-                if (n0 + c0 >= p.n_out) break;                  // n_out is a multiple of 16: a chunk is all in or all out
-                uint32_t a[16], b[16];
-                const bool tl_e = (warp == EPI_WARP0 && lane == 0);
-                if (tl_e) tl_mark(p, TL_XPROD, (int)tcount * 16 + c0 / 16, 0);
-                tmem_ld16(t0 + c0, a);
-                if (FUSED) tmem_ld16(t0 + BN / 2 + c0, b);
-                tmem_ld_wait();
-                if (tl_e) tl_mark(p, TL_XPROD, (int)tcount * 16 + c0 / 16, 1);
-                if (tok_ok) {
-                    float v[16];
+            // One chunk of CH accumulator columns: bias, activation, pack, 16-byte stores.  CH = 8 for gate/up
+            // (two accumulator halves are read per output column, so 8 keeps both register sets small), else 16.
+            constexpr int CH = FUSED ? 8 : 16;
+            auto finish_chunk = [&](int c0, uint32_t* a, uint32_t* b) {
+                if (!tok_ok || n0 + c0 >= p.n_out) return;      // n_out is a multiple of 16: a chunk is all in or all out
+                float v[CH];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        v[j] = __uint_as_float(a[j]);
-                        if (p.row_bias) v[j] += bf16_bits_to_f32(p.row_bias[ebase + n0 + c0 + j]);
+                for (int j = 0; j < CH; ++j) {
+                    v[j] = __uint_as_float(a[j]);
+                    if (p.row_bias) v[j] += bf16_bits_to_f32(p.row_bias[ebase + n0 + c0 + j]);
+                }
+                if (FUSED) {
+                    float u[CH];
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) {
+                        u[j] = __uint_as_float(b[j]);
+                        if (p.row_bias2) u[j] += bf16_bits_to_f32(p.row_bias2[ebase + n0 + c0 + j]);
                     }
-                    if (FUSED) {
-                        float u[16];
+                    // one branch per chunk, outside the element loop: with the kind tested per element the
+                    // compiler predicates all three bodies and every element pays for all of them
+                    if (p.activation == 1) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            u[j] = __uint_as_float(b[j]);
-                            if (p.row_bias2) u[j] += bf16_bits_to_f32(p.row_bias2[ebase + n0 + c0 + j]);
-                        }
-                        // one branch per chunk, outside the element loop: with the kind tested per element the
-                        // compiler predicates all three bodies and every element pays for the tanh
-                        if (p.activation == 1) {
+                        for (int j = 0; j < CH; ++j) v[j] = glu_activation_fast<1>(v[j], u[j], p.limit, p.alpha);
+                    } else if (p.activation == 2) {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] = glu_activation_t<1>(v[j], u[j], p.limit, p.alpha);
-                        } else if (p.activation == 2) {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] = glu_activation_t<2>(v[j], u[j], p.limit, p.alpha);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] = glu_activation_t<0>(v[j], u[j], p.limit, p.alpha);
-                        }
-                    }
-                    if (tl_e) tl_mark(p, TL_XPROD, (int)tcount * 16 + c0 / 16, 2);
-                    if (sizeof(TOut) == 2) {
-                        // 16 bf16 = two 16-byte stores; with the 8-run permutation, run positions hold k = 0,4,1,5,2,6,3,7
-                        uint32_t w8[8];
-                        if (p.out_permute8) {
-#pragma unroll
-                            for (int h8 = 0; h8 < 2; ++h8)
-#pragma unroll
-                                for (int pp = 0; pp < 4; ++pp)
-                                    w8[h8 * 4 + pp] = pack_bf16x2(v[h8 * 8 + pp], v[h8 * 8 + pp + 4]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                w8[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>(orow + (size_t)(n0 + c0) * 2);
-                        dst[0] = make_uint4(w8[0], w8[1], w8[2], w8[3]);
-                        dst[1] = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+                        for (int j = 0; j < CH; ++j) v[j] = glu_activation_fast<2>(v[j], u[j], p.limit, p.alpha);
                     } else {
-                        float4* dst = reinterpret_cast<float4*>(orow + (size_t)(n0 + c0) * 4);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                        for (int j = 0; j < CH; ++j) v[j] = glu_activation_fast<0>(v[j], u[j], p.limit, p.alpha);
                     }
                 }
-                if (tl_e) tl_mark(p, TL_XPROD, (int)tcount * 16 + c0 / 16, 3);
+                if (sizeof(TOut) == 2) {
+                    // 8 bf16 per 16-byte store; with the 8-run permutation, run positions hold k = 0,4,1,5,2,6,3,7
+                    uint32_t w8[CH / 2];
+#pragma unroll
+                    for (int h8 = 0; h8 < CH / 8; ++h8)
+#pragma unroll
+                        for (int pp = 0; pp < 4; ++pp)
+                            w8[h8 * 4 + pp] = p.out_permute8 ? pack_bf16x2(v[h8 * 8 + pp], v[h8 * 8 + pp + 4])
+                                                             : pack_bf16x2(v[h8 * 8 + 2 * pp], v[h8 * 8 + 2 * pp + 1]);
+                    uint4* dst = reinterpret_cast<uint4*>(orow + (size_t)(n0 + c0) * 2);
+#pragma unroll
+                    for (int i = 0; i < CH / 8; ++i) dst[i] = make_uint4(w8[4 * i], w8[4 * i + 1], w8[4 * i + 2], w8[4 * i + 3]);
+                } else {
+                    float4* dst = reinterpret_cast<float4*>(orow + (size_t)(n0 + c0) * 4);
+#pragma unroll
+                    for (int i = 0; i < CH / 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                }
+            };
+            // Two register sets: the TMEM loads of the next chunk are in flight while this one is finished.
+            // (tcgen05.wait::ld waits for every outstanding load, so the next load is issued right after it.)
+            uint32_t a0[CH], b0[CH], a1[CH], b1[CH];
+            tmem_ld_n<CH>(t0, a0);
+            if (FUSED) tmem_ld_n<CH>(t0 + BN / 2, b0);
+            for (int c0 = 0; c0 < ROWS_PER_TILE; c0 += 2 * CH) {
+                tmem_ld_wait();
+                tmem_ld_n<CH>(t0 + c0 + CH, a1);
+                if (FUSED) tmem_ld_n<CH>(t0 + BN / 2 + c0 + CH, b1);
+                finish_chunk(c0, a0, b0);
+                tmem_ld_wait();
+                if (c0 + 2 * CH < ROWS_PER_TILE) {
+                    tmem_ld_n<CH>(t0 + c0 + 2 * CH, a0);
+                    if (FUSED) tmem_ld_n<CH>(t0 + BN / 2 + c0 + 2 * CH, b0);
+                }
+                finish_chunk(c0 + CH, a1, b1);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty(buf));
             if (warp == EPI_WARP0 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 2);
-        }
+            ++tcount;
+          }
     }
 
     tc_fence_before();
