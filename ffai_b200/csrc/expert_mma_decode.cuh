@@ -47,6 +47,9 @@ struct Params {
     const uint16_t* x;        // [rows, K] bf16, 8-run permuted
     const float* xsum;        // [rows, xsum_pitch] sum of each 64-run of x; pitch = K/64 rounded up to 4
     int xsum_pitch;
+    const float* xsum_parts;  // alternative to xsum (when non-null): [rows, K/16] sums of 16-runs, four per 64-run,
+                              // as written by the gate/up kernel; added in ascending order
+    float* out_parts;         // FUSED, nullable: [rows, N/16] sum of each warp's 16 rounded outputs per activation row
     void* out;                // FUSED: bf16 [rows, N] 8-run permuted;  else fp32 [rows, N]
     int activation;
     float limit, alpha;
@@ -505,7 +508,14 @@ grouped_mma_decode_kernel(const Params p) {
         for (int i = threadIdx.x; i < xs_runs * 16; i += 128) {
             const int r = i / xs_runs, G = i - r * xs_runs;
             float v = 0.0f;
-            if (tok0 + r < cnt && G < n64) v = __ldg(p.xsum + (size_t)(row0 + tok0 + r) * p.xsum_pitch + G);
+            if (tok0 + r < cnt && G < n64) {
+                if (p.xsum_parts) {
+                    const float4 q4 = __ldg(reinterpret_cast<const float4*>(p.xsum_parts + (size_t)(row0 + tok0 + r) * (K / 16)) + G);
+                    v = ((q4.x + q4.y) + q4.z) + q4.w;
+                } else {
+                    v = __ldg(p.xsum + (size_t)(row0 + tok0 + r) * p.xsum_pitch + G);
+                }
+            }
             xs_sm[G * 16 + r] = v;
         }
         __syncthreads();
@@ -552,6 +562,9 @@ grouped_mma_decode_kernel(const Params p) {
 
         // results: value i -> (row g + 8*(i>>1), activation row tok0 + 8j + 2t + (i&1))
         if (warp_active && ks == 0) {
+            float rsum[NT][2];   // FUSED: this lane's two rows' share of sum over the warp's 16 outputs, per activation row
+#pragma unroll
+            for (int j = 0; j < NT; ++j) rsum[j][0] = rsum[j][1] = 0.0f;
 #pragma unroll
             for (int j = 0; j < NT; ++j)
 #pragma unroll
@@ -566,11 +579,27 @@ grouped_mma_decode_kernel(const Params p) {
                         float u = tot[j][NP - 1][i];
                         if (p.rb2) u += bf16_bits_to_f32(p.rb2[rr]);
                         v = glu_activation(v, u, p.activation, p.limit, p.alpha);
-                        reinterpret_cast<uint16_t*>(p.out)[(size_t)(row0 + tok) * p.N + permute8_col(n)] = f32_to_bf16_bits(v);
+                        const uint16_t vb = f32_to_bf16_bits(v);
+                        reinterpret_cast<uint16_t*>(p.out)[(size_t)(row0 + tok) * p.N + permute8_col(n)] = vb;
+                        rsum[j][i & 1] += bf16_bits_to_f32(vb);
                     } else {
                         reinterpret_cast<float*>(p.out)[(size_t)(row0 + tok) * p.N + n] = v;
                     }
                 }
+            if (FUSED && p.out_parts) {
+                // sum over the warp's 16 output rows (the lanes that share t), fixed butterfly; lanes g == 0 write
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        float v = rsum[j][h];
+                        v += __shfl_xor_sync(0xFFFFFFFFu, v, 4);
+                        v += __shfl_xor_sync(0xFFFFFFFFu, v, 8);
+                        v += __shfl_xor_sync(0xFFFFFFFFu, v, 16);
+                        const int tok = tok0 + 8 * j + 2 * t + h;
+                        if (g == 0 && tok < cnt) p.out_parts[(size_t)(row0 + tok) * (p.N / 16) + rb] = v;
+                    }
+            }
         }
     }
 }

@@ -64,6 +64,7 @@ struct ffai_moe_layer {
     uint16_t* inner_bf = nullptr;    // [M,I]  activation output (8-run permuted)
     uint16_t* y_bf = nullptr;        // [M,H]
     float* xsum = nullptr;           // [M, H/64]  64-run sums of xg rows
+    float* inner_parts = nullptr;    // [M, I/16]  16-run sums of inner rows, written by the gate/up streaming kernel
     float* inner_sum = nullptr;      // [M, I/64]  64-run sums of inner rows
     bool mma_ok = false;             // register-streaming decode kernels usable (4-bit, group 64/128)
     uint32_t* sb_gate = nullptr;     // repacked (scale | bias << 16) words of the expert projections
@@ -311,11 +312,11 @@ int launch_router_batched(const RouterParams& p, const uint16_t* x, int T, uint3
 // shape does not fit (the caller then uses router_token_kernel).
 template <int KIND>
 int launch_router_rows(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w, float* logits,
-                       uint32_t* tickets, cudaStream_t st) {
+                       uint32_t* tickets, const PlanOut& plan, cudaStream_t st) {
     const int wbytes = KIND == 1 ? 4 : 2;
     const size_t smem = (size_t)ROUTER_ROWS * p.hidden * wbytes + (size_t)p.hidden * 2 +
                         (size_t)ROUTER_ROWS * (p.hidden / 64) * 4 + 2 * (size_t)p.n_experts * 4;
-    if (smem > 200 * 1024 || p.hidden % 64) return -1;
+    if (smem > 200 * 1024 || p.hidden % 64 || T > ROUTER_BATCH_TICKET) return -1;
     auto k = router_rows_kernel<KIND>;
     static size_t attr = 0;
     if (smem > 48 * 1024 && smem > attr) {
@@ -323,7 +324,7 @@ int launch_router_rows(const RouterParams& p, const uint16_t* x, int T, uint32_t
         attr = smem;
     }
     dim3 grid((p.n_experts + ROUTER_ROWS - 1) / ROUTER_ROWS, T);
-    k<<<grid, 256, smem, st>>>(p, x, T, idx, w, logits, tickets);
+    k<<<grid, 256, smem, st>>>(p, x, T, idx, w, logits, tickets, plan);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -597,8 +598,8 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
         L->router_partials_cap = T * E * (H / 64);
         if ((rc = ws_alloc(L, &L->router_partials, L->router_partials_cap))) return rc;
     }
-    if ((rc = ws_alloc(L, &L->tickets, 96))) return rc;
-    CUDA_TRY(L, cudaMemset(L->tickets, 0, 96 * sizeof(uint32_t)));
+    if ((rc = ws_alloc(L, &L->tickets, ROUTER_TICKETS))) return rc;
+    CUDA_TRY(L, cudaMemset(L->tickets, 0, ROUTER_TICKETS * sizeof(uint32_t)));
     if ((rc = ws_alloc(L, &L->inner, Mx * I))) return rc;
     if ((rc = ws_alloc(L, &L->y, Mx * H))) return rc;
     if (world > 1) {
@@ -642,6 +643,7 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
         // 64-run sums, row pitch rounded up to 4 floats (16-byte rows for cp.async), + one spare row
         if ((rc = ws_alloc(L, &L->xsum, (Mx + 1) * (size_t)((H / 64 + 3) & ~3)))) return rc;
         if ((rc = ws_alloc(L, &L->inner_sum, (Mx + 1) * (size_t)((I / 64 + 3) & ~3)))) return rc;
+        if ((rc = ws_alloc(L, &L->inner_parts, (Mx + 1) * (size_t)(I / 16)))) return rc;
         L->mma_ok = c.expert_bits == 4 && (c.expert_group_size == 64 || c.expert_group_size == 128);
         if (want_tc) {
             if (world == 1 && (rc = ws_alloc(L, &L->y_bf, M * H))) return rc;
@@ -1059,17 +1061,18 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         p.w2 = L->w.up_proj.weight; p.s2 = L->w.up_proj.scales; p.b2 = L->w.up_proj.biases; p.rb2 = L->w.up_proj.row_bias;
         p.sb1 = L->sb_gate; p.sb2 = L->sb_up;
         p.N = I; p.K = H; p.x = L->xg; p.xsum = L->xsum; p.xsum_pitch = xp_h; p.out = L->inner_bf;
+        p.out_parts = L->inner_parts;
         launch_mma_decode<true>(p, n_exp, nt, ksplit, st);
-        sum64_rows_kernel<<<(n_rows + 7) / 8, 256, 0, st>>>(L->inner_bf, L->inner_sum, n_rows, I, xp_i);
         stage_end(L, ST_GATE_UP, st);
         stage_begin(L, ST_DOWN, st);
         p.w1 = L->w.down_proj.weight; p.s1 = L->w.down_proj.scales; p.b1 = L->w.down_proj.biases; p.rb1 = L->w.down_proj.row_bias;
         p.w2 = nullptr; p.s2 = nullptr; p.b2 = nullptr; p.rb2 = nullptr;
         p.sb1 = L->sb_down; p.sb2 = nullptr;
-        p.N = H; p.K = I; p.x = L->inner_bf; p.xsum = L->inner_sum; p.xsum_pitch = xp_i; p.out = L->y;
+        p.N = H; p.K = I; p.x = L->inner_bf; p.xsum = nullptr; p.xsum_parts = L->inner_parts; p.xsum_pitch = xp_i; p.out = L->y;
+        p.out_parts = nullptr;
         launch_mma_decode<false>(p, n_exp, nt, ksplit, st);
         stage_end(L, ST_DOWN, st);
-        L->launches += 4;
+        L->launches += 3;
     } else if (use_tc) {
         using namespace g100;
         tile_schedule_kernel<<<1, 32, 0, st>>>(offsets_dev, n_exp, tc_group_rows(L), L->tile_offsets);
@@ -1207,14 +1210,18 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     // stage 0: router (projection + bias + top-k + softmax)
     stage_begin(L, ST_ROUTER, st);
     RouterParams rp = router_params(L);
+    // small batches: the router kernel's last block also builds the dispatch plan
+    const PlanOut fused_plan = (M <= PLAN_ENTRIES_PER_WARP) ? PlanOut{L->counts, L->offsets, L->perm, L->inv_perm} : PlanOut{nullptr, nullptr, nullptr, nullptr};
+    bool plan_done = false;
     if (T >= 96) {
         int nr = launch_router_batched(rp, x, T, L->indices, L->rweights, L->logits, L->router_partials,
                                        L->router_partials_cap, L->n_sms, st);
         if (nr < 0) return fail(L, FFAI_ERR_CUDA, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += nr;
-    } else if ((rp.kind == FFAI_LINEAR_F32 && launch_router_rows<1>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, st) == 0) ||
-               (rp.kind == FFAI_LINEAR_BF16 && launch_router_rows<2>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, st) == 0)) {
+    } else if ((rp.kind == FFAI_LINEAR_F32 && launch_router_rows<1>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, fused_plan, st) == 0) ||
+               (rp.kind == FFAI_LINEAR_BF16 && launch_router_rows<2>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, fused_plan, st) == 0)) {
         L->launches += 1;
+        plan_done = fused_plan.perm != nullptr;
     } else {
         if ((rc = launch_router(rp, x, T, L->indices, L->rweights, L->logits, st)))
             return fail(L, rc, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -1224,9 +1231,11 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
 
     // stage 1: dispatch plan
     stage_begin(L, ST_PLAN, st);
-    int nl = launch_plan(L->indices, M, E, L->counts, L->offsets, L->perm, L->inv_perm, L->block_hist, st);
-    if (nl < 0) return fail(L, FFAI_ERR_CUDA, "plan launch failed: %s", cudaGetErrorString(cudaGetLastError()));
-    L->launches += nl;
+    if (!plan_done) {
+        int nl = launch_plan(L->indices, M, E, L->counts, L->offsets, L->perm, L->inv_perm, L->block_hist, st);
+        if (nl < 0) return fail(L, FFAI_ERR_CUDA, "plan launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += nl;
+    }
     stage_end(L, ST_PLAN, st);
 
     const bool ep_on = c.ep_world > 1;
@@ -1271,16 +1280,17 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         p.w2 = L->w.up_proj.weight; p.s2 = L->w.up_proj.scales; p.b2 = L->w.up_proj.biases; p.rb2 = L->w.up_proj.row_bias;
         p.sb1 = L->sb_gate; p.sb2 = L->sb_up;
         p.N = I; p.K = H; p.x = L->xg; p.xsum = L->xsum; p.xsum_pitch = xp_h; p.out = L->inner_bf;
+        p.out_parts = L->inner_parts;
         launch_mma_decode<true>(p, E, nt, ksplit, st);
-        sum64_rows_kernel<<<(M + 7) / 8, 256, 0, st>>>(L->inner_bf, L->inner_sum, M, I, xp_i);
-        L->launches += 2;
+        L->launches += 1;
         stage_end(L, ST_GATE_UP, st);
 
         stage_begin(L, ST_DOWN, st);
         p.w1 = L->w.down_proj.weight; p.s1 = L->w.down_proj.scales; p.b1 = L->w.down_proj.biases; p.rb1 = L->w.down_proj.row_bias;
         p.w2 = nullptr; p.s2 = nullptr; p.b2 = nullptr; p.rb2 = nullptr;
         p.sb1 = L->sb_down; p.sb2 = nullptr;
-        p.N = H; p.K = I; p.x = L->inner_bf; p.xsum = L->inner_sum; p.xsum_pitch = xp_i; p.out = L->y;
+        p.N = H; p.K = I; p.x = L->inner_bf; p.xsum = nullptr; p.xsum_parts = L->inner_parts; p.xsum_pitch = xp_i; p.out = L->y;
+        p.out_parts = nullptr;
         launch_mma_decode<false>(p, E, nt, ksplit, st);
         L->launches += 1;
         stage_end(L, ST_DOWN, st);

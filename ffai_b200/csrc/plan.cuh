@@ -103,19 +103,23 @@ __global__ void plan_scatter_kernel(const uint32_t* __restrict__ indices, int n_
     }
 }
 
-// Single-launch variant for small row counts (decode): one warp does all three
-// passes.  n_rows <= PLAN_ENTRIES_PER_WARP.
-__global__ void plan_small_kernel(const uint32_t* __restrict__ indices, int n_rows, int n_experts,
-                                  uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets,
-                                  uint32_t* __restrict__ perm, uint32_t* __restrict__ inv_perm) {
-    extern __shared__ uint32_t sm[];  // hist[E], cursor[E]
-    uint32_t* hist = sm;
-    uint32_t* cursor = sm + n_experts;
-    const int lane = threadIdx.x;
+// Where a plan goes (all device pointers).
+struct PlanOut {
+    uint32_t* counts;    // [E]
+    uint32_t* offsets;   // [E+1]
+    uint32_t* perm;      // [n_rows]
+    uint32_t* inv_perm;  // [n_rows]
+};
+
+// The whole plan by one warp, for small row counts (decode): histogram, exclusive scan, stable scatter.
+// hist and cursor: n_experts words of shared memory each.  indices are read past L1 (they may have
+// been written by other blocks of the same launch).  n_rows <= PLAN_ENTRIES_PER_WARP.
+FFAI_DEVINL void plan_small_warp(const uint32_t* indices, int n_rows, int n_experts, const PlanOut& o,
+                                 uint32_t* hist, uint32_t* cursor, int lane) {
     for (int e = lane; e < n_experts; e += 32) hist[e] = 0;
     __syncwarp();
     for (int i = lane; i < n_rows; i += 32) {
-        uint32_t e = indices[i];
+        uint32_t e = __ldcg(indices + i);
         if (e < (uint32_t)n_experts) atomicAdd(&hist[e], 1u);
     }
     __syncwarp();
@@ -127,22 +131,22 @@ __global__ void plan_small_kernel(const uint32_t* __restrict__ indices, int n_ro
         uint32_t incl = c;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
-            uint32_t o = __shfl_up_sync(0xFFFFFFFFu, incl, d);
-            if (lane >= d) incl += o;
+            uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += v;
         }
         if (e < n_experts) {
-            counts[e] = c;
-            offsets[e] = carry + incl - c;
+            o.counts[e] = c;
+            o.offsets[e] = carry + incl - c;
             cursor[e] = carry + incl - c;
         }
         carry += __shfl_sync(0xFFFFFFFFu, incl, 31);
     }
-    if (lane == 0) offsets[n_experts] = carry;
+    if (lane == 0) o.offsets[n_experts] = carry;
     __syncwarp();
     for (int i0 = 0; i0 < n_rows; i0 += 32) {
         const int i = i0 + lane;
         const bool valid = i < n_rows;
-        uint32_t e = valid ? indices[i] : 0xFFFFFFFFu;
+        uint32_t e = valid ? __ldcg(indices + i) : 0xFFFFFFFFu;
         if (valid && e >= (uint32_t)n_experts) e = 0xFFFFFFFEu;
         const uint32_t peers = __match_any_sync(0xFFFFFFFFu, e);
         const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
@@ -153,10 +157,19 @@ __global__ void plan_small_kernel(const uint32_t* __restrict__ indices, int n_ro
         if (real && rank == 0) cursor[e] += __popc(peers);
         __syncwarp();
         if (real) {
-            perm[pos] = (uint32_t)i;
-            inv_perm[i] = pos;
+            o.perm[pos] = (uint32_t)i;
+            o.inv_perm[i] = pos;
         }
     }
+}
+
+// Single-launch variant for small row counts (decode): one warp does all three passes.
+__global__ void plan_small_kernel(const uint32_t* __restrict__ indices, int n_rows, int n_experts,
+                                  uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets,
+                                  uint32_t* __restrict__ perm, uint32_t* __restrict__ inv_perm) {
+    extern __shared__ uint32_t sm[];  // hist[E], cursor[E]
+    const PlanOut o{counts, offsets, perm, inv_perm};
+    plan_small_warp(indices, n_rows, n_experts, o, sm, sm + n_experts, threadIdx.x);
 }
 
 // Ops.gather (FFAI Ops.swift:308-346) specialised to the dispatch: row `pos` of the

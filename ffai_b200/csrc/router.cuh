@@ -11,6 +11,7 @@
 // then added in ascending chunk order.  Top-k orders by (value desc, index asc).
 #pragma once
 #include "common.cuh"
+#include "plan.cuh"
 
 namespace ffai {
 
@@ -225,15 +226,19 @@ router_token_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens
 // lane touch its own 128-byte line: tag-lookup bound on one SM), then each thread folds one
 // (expert, chunk) pair from shared memory in the fixed order, one thread per expert adds the chunk
 // sums, and the last block to finish a token (a ticket counter that resets itself) routes it.
+// With a plan destination, the block that routes the last token of the batch (a second ticket, in
+// the last slot of the ticket array) also builds the dispatch plan, which saves a launch per step.
 // Shared-memory rows are stored with the 16-byte pieces of each 64-value line XOR-swizzled by the
 // line index, so threads that read consecutive lines hit distinct banks.
 constexpr int ROUTER_ROWS = 8;
+constexpr int ROUTER_TICKETS = 96;             // per-token tickets; the last slot counts routed tokens of the batch
+constexpr int ROUTER_BATCH_TICKET = ROUTER_TICKETS - 1;
 
 template <int KIND>  // 1: fp32 weights, 2: bf16 weights
 __global__ void __launch_bounds__(256)
 router_rows_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
                    uint32_t* __restrict__ indices, float* __restrict__ weights,
-                   float* __restrict__ logits_out, uint32_t* __restrict__ tickets) {
+                   float* __restrict__ logits_out, uint32_t* __restrict__ tickets, PlanOut plan) {
     constexpr int WBYTES = KIND == 1 ? 4 : 2;
     constexpr int LINE16 = 64 * WBYTES / 16;   // 16-byte pieces per 64-value line of a weight row
     extern __shared__ __align__(16) uint8_t rsm[];
@@ -316,8 +321,22 @@ router_rows_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
     for (int e = threadIdx.x; e < E; e += blockDim.x) lsm[e] = __ldcg(logits_out + (size_t)t * E + e);
     if (threadIdx.x == 0) tickets[t] = 0;  // ready for the next call
     __syncthreads();
-    if (threadIdx.x < 32)
+    if (threadIdx.x < 32) {
         route_token_warp(p, lsm, lsm + E, threadIdx.x, indices + (size_t)t * p.top_k, weights + (size_t)t * p.top_k);
+        if (plan.perm) {
+            __syncwarp();
+            __threadfence();                       // this token's indices are visible before the batch ticket moves
+            uint32_t done = 0;
+            if (threadIdx.x == 0) done = atomicAdd(&tickets[ROUTER_BATCH_TICKET], 1u);
+            done = __shfl_sync(0xFFFFFFFFu, done, 0);
+            if (done == (uint32_t)n_tokens - 1) {  // every token of the batch is routed
+                if (threadIdx.x == 0) tickets[ROUTER_BATCH_TICKET] = 0;
+                __threadfence();
+                uint32_t* hist = reinterpret_cast<uint32_t*>(lsm);
+                plan_small_warp(indices, n_tokens * p.top_k, E, plan, hist, hist + E, threadIdx.x);
+            }
+        }
+    }
 }
 
 // Batched router projection for many tokens: a TB-token x 64-expert tile per block (TB = 64, 32 or
