@@ -45,6 +45,8 @@ struct Params {
     int N, K, group_size;  // group_size 64 or 128
     const uint32_t* offsets;  // [E+1] rows per expert in the sorted row space
     const uint16_t* x;        // [rows, K] bf16, 8-run permuted
+    const uint32_t* row_src;  // nullable: sorted row r reads x (and xsum) at row row_src[r] / row_div instead of r
+    int row_div;              //           (the dispatch permutation over per-token rows: no gathered copy is made)
     const float* xsum;        // [rows, xsum_pitch] sum of each 64-run of x; pitch = K/64 rounded up to 4
     int xsum_pitch;
     const float* xsum_parts;  // alternative to xsum (when non-null): [rows, K/16] sums of 16-runs, four per 64-run,
@@ -60,6 +62,11 @@ FFAI_DEVINL void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Row of x / xsum that sorted row r reads.
+FFAI_DEVINL size_t src_row(const Params& p, int r) {
+    return p.row_src ? (size_t)(__ldg(p.row_src + r) / (uint32_t)p.row_div) : (size_t)r;
 }
 
 // One packed word -> 4 bf16 pairs (128+n0,128+n4), (128+n1,128+n5), (128+n2,128+n6), (128+n3,128+n7).
@@ -201,7 +208,7 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
     const uint8_t* xrow[NT];
 #pragma unroll
     for (int j = 0; j < NT; ++j)
-        xrow[j] = reinterpret_cast<const uint8_t*>(p.x + (size_t)(row0 + min(tok0 + 8 * j + g, cnt - 1)) * K + 16 * t) + (size_t)job.G0 * 128;
+        xrow[j] = reinterpret_cast<const uint8_t*>(p.x + src_row(p, row0 + min(tok0 + 8 * j + g, cnt - 1)) * K + 16 * t) + (size_t)job.G0 * 128;
     const uint32_t x_last = (uint32_t)(n_runs > 0 ? n_runs - 1 : 0) * 128u;
 
 #pragma unroll
@@ -342,7 +349,7 @@ FFAI_DEVINL void decode_pass_shared(const Params& p, const WarpJob<FUSED>& job, 
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
             const int c = threadIdx.x + 128 * i, row = c >> 4, col = c & 15;
-            xsrc[i] = reinterpret_cast<const uint8_t*>(p.x + (size_t)(row0 + min(tok0 + row, cnt - 1)) * K) + col * 16;
+            xsrc[i] = reinterpret_cast<const uint8_t*>(p.x + src_row(p, row0 + min(tok0 + row, cnt - 1)) * K) + col * 16;
             xdst[i] = xring_u32 + row * X_PITCH + col * 16;
         }
     }
@@ -513,7 +520,7 @@ grouped_mma_decode_kernel(const Params p) {
                     const float4 q4 = __ldg(reinterpret_cast<const float4*>(p.xsum_parts + (size_t)(row0 + tok0 + r) * (K / 16)) + G);
                     v = ((q4.x + q4.y) + q4.z) + q4.w;
                 } else {
-                    v = __ldg(p.xsum + (size_t)(row0 + tok0 + r) * p.xsum_pitch + G);
+                    v = __ldg(p.xsum + src_row(p, row0 + tok0 + r) * p.xsum_pitch + G);
                 }
             }
             xs_sm[G * 16 + r] = v;

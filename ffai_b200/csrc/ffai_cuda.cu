@@ -64,6 +64,8 @@ struct ffai_moe_layer {
     uint16_t* inner_bf = nullptr;    // [M,I]  activation output (8-run permuted)
     uint16_t* y_bf = nullptr;        // [M,H]
     float* xsum = nullptr;           // [M, H/64]  64-run sums of xg rows
+    uint16_t* x_tok = nullptr;       // [T, H] token rows, 8-run permuted (streaming kernels read them through perm)
+    float* xsum_tok = nullptr;       // [T, H/64 rounded up to 4] their 64-run sums
     float* inner_parts = nullptr;    // [M, I/16]  16-run sums of inner rows, written by the gate/up streaming kernel
     float* inner_sum = nullptr;      // [M, I/64]  64-run sums of inner rows
     bool mma_ok = false;             // register-streaming decode kernels usable (4-bit, group 64/128)
@@ -312,7 +314,7 @@ int launch_router_batched(const RouterParams& p, const uint16_t* x, int T, uint3
 // shape does not fit (the caller then uses router_token_kernel).
 template <int KIND>
 int launch_router_rows(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w, float* logits,
-                       uint32_t* tickets, const PlanOut& plan, cudaStream_t st) {
+                       uint32_t* tickets, const PlanOut& plan, uint16_t* x_perm8, float* x_sum64, int sum_pitch, cudaStream_t st) {
     const int wbytes = KIND == 1 ? 4 : 2;
     const size_t smem = (size_t)ROUTER_ROWS * p.hidden * wbytes + (size_t)p.hidden * 2 +
                         (size_t)ROUTER_ROWS * (p.hidden / 64) * 4 + 2 * (size_t)p.n_experts * 4;
@@ -324,7 +326,7 @@ int launch_router_rows(const RouterParams& p, const uint16_t* x, int T, uint32_t
         attr = smem;
     }
     dim3 grid((p.n_experts + ROUTER_ROWS - 1) / ROUTER_ROWS, T);
-    k<<<grid, 256, smem, st>>>(p, x, T, idx, w, logits, tickets, plan);
+    k<<<grid, 256, smem, st>>>(p, x, T, idx, w, logits, tickets, plan, x_perm8, x_sum64, sum_pitch);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -644,6 +646,8 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
         if ((rc = ws_alloc(L, &L->xsum, (Mx + 1) * (size_t)((H / 64 + 3) & ~3)))) return rc;
         if ((rc = ws_alloc(L, &L->inner_sum, (Mx + 1) * (size_t)((I / 64 + 3) & ~3)))) return rc;
         if ((rc = ws_alloc(L, &L->inner_parts, (Mx + 1) * (size_t)(I / 16)))) return rc;
+        if ((rc = ws_alloc(L, &L->x_tok, (T + 1) * H))) return rc;
+        if ((rc = ws_alloc(L, &L->xsum_tok, (T + 1) * (size_t)((H / 64 + 3) & ~3)))) return rc;
         L->mma_ok = c.expert_bits == 4 && (c.expert_group_size == 64 || c.expert_group_size == 128);
         if (want_tc) {
             if (world == 1 && (rc = ws_alloc(L, &L->y_bf, M * H))) return rc;
@@ -1213,15 +1217,21 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     // small batches: the router kernel's last block also builds the dispatch plan
     const PlanOut fused_plan = (M <= PLAN_ENTRIES_PER_WARP) ? PlanOut{L->counts, L->offsets, L->perm, L->inv_perm} : PlanOut{nullptr, nullptr, nullptr, nullptr};
     bool plan_done = false;
+    // 4-bit streaming kernels read per-token rows through the permutation: the rows (8-run permuted) and their
+    // 64-run sums are written once per token, by the router kernel when it is the small-batch one
+    uint16_t* tok_x = (L->mma_ok && c.ep_world <= 1) ? L->x_tok : nullptr;
+    const int xp_tok = (H / 64 + 3) & ~3;
+    bool tok_rows_done = false;
     if (T >= 96) {
         int nr = launch_router_batched(rp, x, T, L->indices, L->rweights, L->logits, L->router_partials,
                                        L->router_partials_cap, L->n_sms, st);
         if (nr < 0) return fail(L, FFAI_ERR_CUDA, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += nr;
-    } else if ((rp.kind == FFAI_LINEAR_F32 && launch_router_rows<1>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, fused_plan, st) == 0) ||
-               (rp.kind == FFAI_LINEAR_BF16 && launch_router_rows<2>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, fused_plan, st) == 0)) {
+    } else if ((rp.kind == FFAI_LINEAR_F32 && launch_router_rows<1>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, fused_plan, tok_x, L->xsum_tok, xp_tok, st) == 0) ||
+               (rp.kind == FFAI_LINEAR_BF16 && launch_router_rows<2>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, fused_plan, tok_x, L->xsum_tok, xp_tok, st) == 0)) {
         L->launches += 1;
         plan_done = fused_plan.perm != nullptr;
+        tok_rows_done = tok_x != nullptr;
     } else {
         if ((rc = launch_router(rp, x, T, L->indices, L->rweights, L->logits, st)))
             return fail(L, rc, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -1263,8 +1273,10 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         using namespace dmma;
         stage_begin(L, ST_GATHER, st);
         const int xp_h = (H / 64 + 3) & ~3, xp_i = (I / 64 + 3) & ~3;
-        gather_perm8_sum64_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, K, L->xg, L->xsum, M, H, xp_h);
-        L->launches += 1;
+        if (!tok_rows_done) {   // one row per token (not per routed row); the kernels follow the permutation themselves
+            gather_perm8_sum64_kernel<<<(T + 7) / 8, 256, 0, st>>>(x, nullptr, 1, L->x_tok, L->xsum_tok, T, H, xp_h);
+            L->launches += 1;
+        }
         stage_end(L, ST_GATHER, st);
 
         Params p{};
@@ -1279,9 +1291,11 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         p.w1 = L->w.gate_proj.weight; p.s1 = L->w.gate_proj.scales; p.b1 = L->w.gate_proj.biases; p.rb1 = L->w.gate_proj.row_bias;
         p.w2 = L->w.up_proj.weight; p.s2 = L->w.up_proj.scales; p.b2 = L->w.up_proj.biases; p.rb2 = L->w.up_proj.row_bias;
         p.sb1 = L->sb_gate; p.sb2 = L->sb_up;
-        p.N = I; p.K = H; p.x = L->xg; p.xsum = L->xsum; p.xsum_pitch = xp_h; p.out = L->inner_bf;
+        p.N = I; p.K = H; p.x = L->x_tok; p.xsum = L->xsum_tok; p.xsum_pitch = xp_h; p.out = L->inner_bf;
+        p.row_src = L->perm; p.row_div = K;
         p.out_parts = L->inner_parts;
         launch_mma_decode<true>(p, E, nt, ksplit, st);
+        p.row_src = nullptr; p.row_div = 1;
         L->launches += 1;
         stage_end(L, ST_GATE_UP, st);
 

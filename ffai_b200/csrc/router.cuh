@@ -226,6 +226,9 @@ router_token_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens
 // lane touch its own 128-byte line: tag-lookup bound on one SM), then each thread folds one
 // (expert, chunk) pair from shared memory in the fixed order, one thread per expert adds the chunk
 // sums, and the last block to finish a token (a ticket counter that resets itself) routes it.
+// With a destination for it, block 0 of a token also writes the token's row in the order the 4-bit
+// expert kernels read (every 8-run as 0,4,1,5,2,6,3,7) and the fp32 sum of every 64-run, from the
+// copy it staged anyway.
 // With a plan destination, the block that routes the last token of the batch (a second ticket, in
 // the last slot of the ticket array) also builds the dispatch plan, which saves a launch per step.
 // Shared-memory rows are stored with the 16-byte pieces of each 64-value line XOR-swizzled by the
@@ -238,7 +241,8 @@ template <int KIND>  // 1: fp32 weights, 2: bf16 weights
 __global__ void __launch_bounds__(256)
 router_rows_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
                    uint32_t* __restrict__ indices, float* __restrict__ weights,
-                   float* __restrict__ logits_out, uint32_t* __restrict__ tickets, PlanOut plan) {
+                   float* __restrict__ logits_out, uint32_t* __restrict__ tickets, PlanOut plan,
+                   uint16_t* __restrict__ x_perm8, float* __restrict__ x_sum64, int sum_pitch) {
     constexpr int WBYTES = KIND == 1 ? 4 : 2;
     constexpr int LINE16 = 64 * WBYTES / 16;   // 16-byte pieces per 64-value line of a weight row
     extern __shared__ __align__(16) uint8_t rsm[];
@@ -271,6 +275,32 @@ router_rows_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
+
+    if (x_perm8 && blockIdx.x == 0) {
+        // 16-byte piece i of the row (8 values): permuted copy + its share of the 64-run sum; the eight
+        // pieces of a run sit in eight consecutive lanes
+        uint4* d = reinterpret_cast<uint4*>(x_perm8 + (size_t)t * H);
+        for (int i0 = 0; i0 < nchunks * 8; i0 += blockDim.x) {
+            const int i = i0 + threadIdx.x;
+            float part = 0.0f;
+            if (i < nchunks * 8) {
+                const int line = i >> 3, j = i & 7;
+                const uint4 v = *reinterpret_cast<const uint4*>(xsm + (size_t)(line * 8 + (j ^ (line & 7))) * 16);
+                uint4 o;
+                o.x = __byte_perm(v.x, v.z, 0x5410);
+                o.y = __byte_perm(v.x, v.z, 0x7632);
+                o.z = __byte_perm(v.y, v.w, 0x5410);
+                o.w = __byte_perm(v.y, v.w, 0x7632);
+                d[i] = o;
+                part = ((bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y))) +
+                       ((bf16lo(v.z) + bf16hi(v.z)) + (bf16lo(v.w) + bf16hi(v.w)));
+            }
+            part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
+            part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
+            part += __shfl_xor_sync(0xFFFFFFFFu, part, 4);
+            if ((threadIdx.x & 7) == 0 && i < nchunks * 8) x_sum64[(size_t)t * sum_pitch + (i >> 3)] = part;
+        }
+    }
 
     // one (row, chunk) pair per thread: 64 fused multiply-adds in ascending k
     for (int i = threadIdx.x; i < rows * nchunks; i += blockDim.x) {
