@@ -42,6 +42,10 @@ import numpy as np
 
 from ffai_b200 import capi, synth
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu captures
+# summarised in profiles/ (same workload, same command); None where no capture exists
+NCU_TRAFFIC_BYTES = {"cfg2_b64": 306.2e6 + 5.1e6, "cfg3": 883.0e6 + 24.4e6}
+
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -316,7 +320,7 @@ def main():
             achieved = alg_bytes / (kms * 1e-3) / 1e9
             roofline = {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peaks["hbm_gbs"],
                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                        "traffic": None, "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kms}
+                        "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kms}
             layer_bytes = spec.decode_bytes(n_tokens, mean_distinct)
             layer_frac = layer_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"]
         else:
@@ -326,7 +330,7 @@ def main():
             achieved = alg / (kms * 1e-3) / 1e12
             roofline = {"bound": "tensor", "kernel": kernel, "achieved": achieved, "peak": peaks["bf16_tflops"],
                         "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "peak_source": peaks["source"],
-                        "traffic": None, "algorithmic_flops_per_launch": alg, "kernel_ms": kms}
+                        "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "algorithmic_flops_per_launch": alg, "kernel_ms": kms}
             layer_frac = (fl["routed"] + fl["shared"] + fl["router"]) / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"]
         line = {
             "metric": METRIC, "value": world * n_tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
