@@ -184,6 +184,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--option", action="append", default=[], help="name=value execution option (experiments)")
+    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
+                    help="*_ep workloads: row exchange over peer memory (CUDA IPC, fused into gather and combine) or NCCL send/recv")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -214,10 +216,16 @@ def main():
     if ep_mode:
         from ffai_b200 import ep
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        uid = [ep.unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(uid, src=0)
-        ep_comm = ep.comm_create(uid[0], rank, world)
-        layer = MoELayer(host, n_tokens, ep_rank=rank, ep_world=world, ep_comm=ep_comm)
+        if args.ep_exchange == "nccl":
+            uid = [ep.unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(uid, src=0)
+            ep_comm = ep.comm_create(uid[0], rank, world)
+            layer = MoELayer(host, n_tokens, ep_rank=rank, ep_world=world, ep_comm=ep_comm)
+        else:
+            layer = MoELayer(host, n_tokens, ep_rank=rank, ep_world=world)
+            blobs = [None] * world
+            dist.all_gather_object(blobs, layer.ep_export())
+            layer.ep_import(blobs)
     else:
         layer = MoELayer(host, n_tokens)
     layer.set_stage_timing(False)
@@ -357,10 +365,16 @@ def main():
             off_rank = (world - 1) / world      # share of a rank's rows whose expert lives on another rank (uniform routing)
             line["ep"] = {"exchange_ms": stage_mean["exchange"], "rows_per_rank": rows,
                           "dispatch_bytes_per_rank": rows * H * 2 * off_rank, "return_bytes_per_rank": rows * H * 4 * off_rank,
-                          "transport": "NCCL send/recv groups over NVLink, one host sync per step for the sizes"}
+                          "transport": ("peer memory over NVLink (CUDA IPC): gather fused with dispatch, combine fused with "
+                                        "return, three flag barriers, no host synchronisation" if args.ep_exchange == "peer"
+                                        else "NCCL send/recv groups over NVLink, one host sync per step for the sizes")}
         if not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_baseline(spec, n_tokens, args.seed, args.cpu_seconds)
         print(json.dumps(line), flush=True)
+    if ep_mode and ep_comm is None:
+        sync_all()
+        layer.ep_release()
+        sync_all()
     layer.close()
     if ep_comm is not None:
         sync_all()

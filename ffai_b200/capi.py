@@ -38,6 +38,7 @@ LINEAR_AFFINE = 3
 MEM_HOST = 0
 MEM_DEVICE = 1
 
+EP_EXPORT_BYTES = 192
 N_STAGES = 8
 STAGE_NAMES = ("router", "plan", "gather", "gate_up", "down", "combine", "shared", "exchange")
 MAX_TOP_K = 32
@@ -147,6 +148,9 @@ SIGNATURES = {
     "ffai_moe_forward": (C.c_int, [_P, _P, _I, _P, _P, C.POINTER(MoEDebug), _P]),
     "ffai_moe_forward_host": (C.c_int, [_P, _P, _I, _P, _P, C.POINTER(MoEDebug)]),
     "ffai_moe_set_nccl_comm": (C.c_int, [_P, _P]),
+    "ffai_moe_ep_export": (C.c_int, [_P, _P]),
+    "ffai_moe_ep_import": (C.c_int, [_P, _P]),
+    "ffai_moe_ep_release": (C.c_int, [_P]),
     "ffai_ep_get_unique_id": (C.c_int, [_P]),
     "ffai_ep_comm_create": (C.c_int, [_P, _I, _I, C.POINTER(_P)]),
     "ffai_ep_comm_destroy": (C.c_int, [_P]),

@@ -102,5 +102,201 @@ __global__ void copy_segments_kernel(const uint8_t* __restrict__ src, uint8_t* _
     }
 }
 
+// ───────────────────── exchange over peer memory (no NCCL, no host round trip) ─────────────────────
+//
+// Every rank exports three allocations to the others (CUDA IPC; one process per GPU): its row buffer
+// (rows it will compute on, expert-contiguous), its result buffer, and a small control window that
+// holds the counts matrix [world][n_experts] and the barrier flags.  Per step, all on the stream:
+//   publish   every rank stores its per-expert row counts into row `rank` of every peer's matrix; barrier 0
+//   layout    every rank derives, from the same matrix, where each (source, expert) segment lives in each
+//             receiver's row buffer: its own expert offsets, and the base of its own segments elsewhere
+//   dispatch  the gather writes each routed row (8-run permuted) straight into its owner's row buffer
+//             over NVLink; barrier 1
+//   experts   unchanged kernels over the local rows; barrier 2
+//   combine   each token pulls its k result rows from the owners' result buffers while it sums them
+// so the gather is fused with the dispatch and the combine with the return.  A barrier is a flag per
+// (barrier, source rank) holding the step number, written into every peer's window and polled locally
+// with a time limit; on expiry the kernel records an error word and returns.
+constexpr int EP_MAX_WORLD = 16;
+constexpr int EP_BARRIERS = 3;
+constexpr uint64_t EP_WAIT_LIMIT_NS = 2000000000ull;
+enum : uint32_t { EP_ERR_BARRIER_TIMEOUT = 16, EP_ERR_CAPACITY = 17 };
+
+struct PeerPtrs {
+    void* p[EP_MAX_WORLD];
+};
+
+// control window, in 32-bit words: flags[EP_BARRIERS][EP_MAX_WORLD], then the counts matrix [world][n_experts]
+__host__ __device__ __forceinline__ uint32_t* win_flags(void* win, int barrier) { return static_cast<uint32_t*>(win) + barrier * EP_MAX_WORLD; }
+__host__ __device__ __forceinline__ uint32_t* win_matrix(void* win) { return static_cast<uint32_t*>(win) + EP_BARRIERS * EP_MAX_WORLD; }
+inline size_t win_words(int world, int n_experts) { return (size_t)EP_BARRIERS * EP_MAX_WORLD + (size_t)world * n_experts; }
+
+// Tell every peer this rank reached `barrier` of step `epoch`, then wait (bounded) for all of them.
+// Called by one block; threads 0..world-1 take one peer each.  Writes before the call are made
+// visible system-wide first.
+FFAI_DEVINL void peer_barrier(const PeerPtrs& win, int me, int world, int barrier, uint32_t epoch, uint32_t* error_word) {
+    __threadfence_system();
+    __syncthreads();
+    if ((int)threadIdx.x < world) {
+        volatile uint32_t* theirs = win_flags(win.p[threadIdx.x], barrier) + me;
+        *theirs = epoch;
+        volatile uint32_t* mine = win_flags(win.p[me], barrier) + threadIdx.x;
+        uint64_t t0 = 0;
+        for (uint32_t spin = 0;; ++spin) {
+            if ((int32_t)(*mine - epoch) >= 0) break;
+            if ((spin & 255u) == 255u) {
+                uint64_t now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > EP_WAIT_LIMIT_NS) {
+                    atomicExch(error_word, EP_ERR_BARRIER_TIMEOUT);
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    __threadfence_system();
+}
+
+__global__ void __launch_bounds__(256)
+ep_publish_counts_kernel(const uint32_t* __restrict__ counts, int n_experts, int me, int world, PeerPtrs win,
+                         uint32_t epoch, uint32_t* error_word) {
+    for (int d = 0; d < world; ++d) {
+        uint32_t* row = win_matrix(win.p[d]) + (size_t)me * n_experts;
+        for (int e = threadIdx.x; e < n_experts; e += blockDim.x) row[e] = counts[e];
+    }
+    peer_barrier(win, me, world, 0, epoch, error_word);
+}
+
+__global__ void __launch_bounds__(32)
+ep_barrier_kernel(int barrier, int me, int world, PeerPtrs win, uint32_t epoch, uint32_t* error_word) {
+    peer_barrier(win, me, world, barrier, epoch, error_word);
+}
+
+// From the counts matrix (identical on every rank after barrier 0):
+//   local_off[e_local+1]  row ranges of this rank's experts in its own row buffer (all sources, ascending rank)
+//   send_base[n_experts]  where this rank's rows for expert e start in the owner's row buffer
+__global__ void __launch_bounds__(256)
+ep_layout_kernel(const uint32_t* __restrict__ matrix, int n_experts, int e_local, int me, int world,
+                 uint32_t* __restrict__ local_off, uint32_t* __restrict__ send_base) {
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        const int first = (e / e_local) * e_local;   // first expert of the owner
+        uint32_t base = 0;
+        for (int ee = first; ee < e; ++ee)
+            for (int s = 0; s < world; ++s) base += matrix[(size_t)s * n_experts + ee];
+        for (int s = 0; s < me; ++s) base += matrix[(size_t)s * n_experts + e];
+        send_base[e] = base;
+    }
+    for (int el = threadIdx.x; el <= e_local; el += blockDim.x) {
+        uint32_t run = 0;
+        for (int ee = 0; ee < el; ++ee)
+            for (int s = 0; s < world; ++s) run += matrix[(size_t)s * n_experts + me * e_local + ee];
+        local_off[el] = run;
+    }
+}
+
+// Gather fused with the dispatch: sorted row r of this rank (token perm[r]/k, expert indices[perm[r]])
+// is written, 8-run permuted, into the row buffer of the rank that owns the expert.  One warp per row.
+__global__ void __launch_bounds__(256)
+ep_dispatch_kernel(const uint16_t* __restrict__ x, const uint32_t* __restrict__ perm, const uint32_t* __restrict__ indices,
+                   const uint32_t* __restrict__ offsets, const uint32_t* __restrict__ send_base, int k, int e_local,
+                   int n_rows, int hidden, PeerPtrs rows_of, uint32_t capacity, uint32_t* error_word) {
+    const int warps = blockDim.x / 32;
+    const int r = blockIdx.x * warps + threadIdx.x / 32;
+    if (r >= n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const uint32_t pe = perm[r];
+    const uint32_t e = indices[pe];
+    const uint32_t pos = send_base[e] + ((uint32_t)r - offsets[e]);
+    if (pos >= capacity) {
+        if (lane == 0) atomicExch(error_word, EP_ERR_CAPACITY);
+        return;
+    }
+    const uint4* s = reinterpret_cast<const uint4*>(x + (size_t)(pe / (uint32_t)k) * hidden);
+    uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(rows_of.p[e / (uint32_t)e_local]) + (size_t)pos * hidden);
+    for (int i = lane; i < hidden / 8; i += 32) {
+        const uint4 v = s[i];
+        uint4 o;
+        o.x = __byte_perm(v.x, v.z, 0x5410);
+        o.y = __byte_perm(v.x, v.z, 0x7632);
+        o.z = __byte_perm(v.y, v.w, 0x5410);
+        o.w = __byte_perm(v.y, v.w, 0x7632);
+        d[i] = o;
+    }
+}
+
+// Combine fused with the return: as combine_kernel<bf16, float>, but slot s of token t reads its
+// result row (bf16: half the bytes over NVLink) from the owner of its expert.  One block per token; a thread owns 4 hidden positions.
+__global__ void __launch_bounds__(256)
+combine_peer_kernel(PeerPtrs y_of, const uint32_t* __restrict__ inv_perm, const uint32_t* __restrict__ indices,
+                    const uint32_t* __restrict__ offsets, const uint32_t* __restrict__ send_base, int e_local,
+                    const float* __restrict__ weights, int k, const float* __restrict__ shared_y,
+                    const float* __restrict__ shared_gate_logit, const uint16_t* __restrict__ residual,
+                    uint16_t* __restrict__ out, int hidden) {
+    const int t = blockIdx.x;
+    __shared__ const uint16_t* row_s[32];
+    __shared__ float w_s[32];
+    __shared__ float sig_s;
+    if ((int)threadIdx.x < k) {
+        const size_t slot = (size_t)t * k + threadIdx.x;
+        const uint32_t e = indices[slot];
+        const uint32_t pos = send_base[e] + (inv_perm[slot] - offsets[e]);
+        row_s[threadIdx.x] = static_cast<const uint16_t*>(y_of.p[e / (uint32_t)e_local]) + (size_t)pos * hidden;
+        w_s[threadIdx.x] = weights[slot];
+    }
+    if (threadIdx.x == 0) {
+        float sig = 1.0f;
+        if (shared_gate_logit) sig = 1.0f / (1.0f + __expf(-shared_gate_logit[t]));
+        sig_s = sig;
+    }
+    __syncthreads();
+    for (int h = threadIdx.x * 4; h < hidden; h += blockDim.x * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < k; ++s) {
+            const float w = w_s[s];
+            const uint2 u = *reinterpret_cast<const uint2*>(row_s[s] + h);
+            acc.x += w * bf16lo(u.x); acc.y += w * bf16hi(u.x); acc.z += w * bf16lo(u.y); acc.w += w * bf16hi(u.y);
+        }
+        if (shared_y) {
+            const float sig = sig_s;
+            const float4 v = *reinterpret_cast<const float4*>(shared_y + (size_t)t * hidden + h);
+            acc.x += sig * v.x; acc.y += sig * v.y; acc.z += sig * v.z; acc.w += sig * v.w;
+        }
+        if (residual) {
+            const uint2 u = *reinterpret_cast<const uint2*>(residual + (size_t)t * hidden + h);
+            acc.x += bf16lo(u.x); acc.y += bf16hi(u.x); acc.z += bf16lo(u.y); acc.w += bf16hi(u.y);
+        }
+        uint2 o;
+        o.x = (uint32_t)f32_to_bf16_bits(acc.x) | ((uint32_t)f32_to_bf16_bits(acc.y) << 16);
+        o.y = (uint32_t)f32_to_bf16_bits(acc.z) | ((uint32_t)f32_to_bf16_bits(acc.w) << 16);
+        *reinterpret_cast<uint2*>(out + (size_t)t * hidden + h) = o;
+    }
+}
+
+// 64-run sums of the first *n_rows_dev rows (the count lives on the device); grid sized for the capacity.
+__global__ void sum64_rows_counted_kernel(const uint16_t* __restrict__ rows, float* __restrict__ sums,
+                                          const uint32_t* __restrict__ n_rows_dev, int row_len, int sum_pitch) {
+    const int warps = blockDim.x / 32;
+    const int row = blockIdx.x * warps + threadIdx.x / 32;
+    if (row >= (int)*n_rows_dev) return;
+    const int lane = threadIdx.x & 31;
+    const uint4* s = reinterpret_cast<const uint4*>(rows + (size_t)row * row_len);
+    const int chunks = row_len / 8;
+    for (int i0 = 0; i0 < chunks; i0 += 32) {
+        const int i = i0 + lane;
+        float part = 0.0f;
+        if (i < chunks) {
+            const uint4 v = s[i];
+            part = ((bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y))) +
+                   ((bf16lo(v.z) + bf16hi(v.z)) + (bf16lo(v.w) + bf16hi(v.w)));
+        }
+        part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
+        part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
+        part += __shfl_xor_sync(0xFFFFFFFFu, part, 4);
+        if ((lane & 7) == 0 && i < chunks) sums[(size_t)row * sum_pitch + (i >> 3)] = part;
+    }
+}
+
 }  // namespace ep
 }  // namespace ffai

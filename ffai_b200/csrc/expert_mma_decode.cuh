@@ -52,7 +52,8 @@ struct Params {
     const float* xsum_parts;  // alternative to xsum (when non-null): [rows, K/16] sums of 16-runs, four per 64-run,
                               // as written by the gate/up kernel; added in ascending order
     float* out_parts;         // FUSED, nullable: [rows, N/16] sum of each warp's 16 rounded outputs per activation row
-    void* out;                // FUSED: bf16 [rows, N] 8-run permuted;  else fp32 [rows, N]
+    void* out;                // FUSED: bf16 [rows, N] 8-run permuted;  else fp32 [rows, N] (bf16 when out_bf16)
+    int out_bf16;             // !FUSED: store bf16 in plain column order instead of fp32
     int activation;
     float limit, alpha;
 };
@@ -589,6 +590,8 @@ grouped_mma_decode_kernel(const Params p) {
                         const uint16_t vb = f32_to_bf16_bits(v);
                         reinterpret_cast<uint16_t*>(p.out)[(size_t)(row0 + tok) * p.N + permute8_col(n)] = vb;
                         rsum[j][i & 1] += bf16_bits_to_f32(vb);
+                    } else if (p.out_bf16) {
+                        reinterpret_cast<uint16_t*>(p.out)[(size_t)(row0 + tok) * p.N + n] = f32_to_bf16_bits(v);
                     } else {
                         reinterpret_cast<float*>(p.out)[(size_t)(row0 + tok) * p.N + n] = v;
                     }

@@ -3,6 +3,7 @@
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -94,6 +95,15 @@ struct ffai_moe_layer {
     float* ep_home_y = nullptr;      // [M,H]   my rows' outputs, in my sorted order
     uint32_t* ep_recv_counts = nullptr;  // [world][E_local] rows per (source, local expert)
     uint32_t* ep_plan_dev = nullptr;     // local_offsets[E_local+1] | seg_src | seg_dst  (each world*E_local)
+    // exchange over peer memory (CUDA IPC): control window, peers' windows / row buffers / result buffers
+    uint32_t* ep_win = nullptr;          // flags + counts matrix (exported)
+    uint16_t* ep_y_bf = nullptr;         // [mx_rows, H] bf16 results of this rank's experts (exported; peers pull from it)
+    uint32_t* ep_send_base = nullptr;    // [E] base of this rank's rows for expert e in the owner's row buffer
+    ep::PeerPtrs ep_peer_win{}, ep_peer_rows{}, ep_peer_y{};
+    std::vector<void*> ep_opened;        // IPC mappings to close
+    bool ep_peer_on = false;
+    const uint32_t* ep_rows_dev = nullptr;   // set while the experts run on rows whose count only the device knows
+    uint32_t ep_epoch = 0;
     uint32_t* ep_pin = nullptr;          // pinned: recv_counts | offsets[E+1] | plan upload staging
 
     // host-buffer entry point
@@ -612,6 +622,13 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
         if ((rc = ws_alloc(L, &L->ep_home_y, M * H))) return rc;
         if ((rc = ws_alloc(L, &L->ep_recv_counts, W * El))) return rc;
         if ((rc = ws_alloc(L, &L->ep_plan_dev, (El + 1) + 2 * W * El))) return rc;
+        if (W > (size_t)ep::EP_MAX_WORLD) return fail(L, FFAI_ERR_INVALID_ARG, "ep_world %zu exceeds %d", W, ep::EP_MAX_WORLD);
+        // exported to the peers: a whole 2 MiB granule of its own, so the mapping a peer opens holds nothing else
+        const size_t win_words = std::max(ep::win_words((int)W, (int)E), (size_t)(2u << 20) / sizeof(uint32_t));
+        if ((rc = ws_alloc(L, &L->ep_win, win_words))) return rc;
+        CUDA_TRY(L, cudaMemset(L->ep_win, 0, win_words * sizeof(uint32_t)));
+        if ((rc = ws_alloc(L, &L->ep_send_base, E))) return rc;
+        if ((rc = ws_alloc(L, &L->ep_y_bf, Mx * H))) return rc;
         void* pin = nullptr;
         CUDA_TRY(L, cudaMallocHost(&pin, sizeof(uint32_t) * (W * El + (E + 1) + (El + 1) + 2 * W * El)));
         L->owned_pinned.push_back(pin);
@@ -796,6 +813,7 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
 extern "C" FFAI_API int ffai_moe_destroy(ffai_moe_layer* L) {
     if (!L) return FFAI_OK;
     if (L->device >= 0) cudaSetDevice(L->device);
+    for (void* p : L->ep_opened) cudaIpcCloseMemHandle(p);
     free_list(L->owned_weights);
     free_list(L->owned_ws);
     for (void* p : L->owned_pinned) cudaFreeHost(p);
@@ -811,6 +829,54 @@ extern "C" FFAI_API const char* ffai_moe_last_error(const ffai_moe_layer* L) { r
 extern "C" FFAI_API int ffai_moe_set_nccl_comm(ffai_moe_layer* L, void* comm) {
     if (!L) return FFAI_ERR_INVALID_ARG;
     L->nccl_comm = comm;
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_moe_ep_export(ffai_moe_layer* L, uint8_t out_blob[FFAI_EP_EXPORT_BYTES]) {
+    if (!L || !out_blob) return FFAI_ERR_INVALID_ARG;
+    if (L->cfg.ep_world <= 1 || !L->ep_win) return fail(L, FFAI_ERR_INVALID_ARG, "layer was not created with ep_world > 1");
+    static_assert(3 * sizeof(cudaIpcMemHandle_t) == FFAI_EP_EXPORT_BYTES, "export blob size");
+    CUDA_TRY(L, cudaSetDevice(L->device));
+    cudaIpcMemHandle_t h[3];
+    CUDA_TRY(L, cudaIpcGetMemHandle(&h[0], L->ep_win));
+    CUDA_TRY(L, cudaIpcGetMemHandle(&h[1], L->xg));
+    CUDA_TRY(L, cudaIpcGetMemHandle(&h[2], L->ep_y_bf));
+    memcpy(out_blob, h, sizeof(h));
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_moe_ep_import(ffai_moe_layer* L, const uint8_t* blobs) {
+    if (!L || !blobs) return FFAI_ERR_INVALID_ARG;
+    const int W = L->cfg.ep_world, me = L->cfg.ep_rank;
+    if (W <= 1 || !L->ep_win) return fail(L, FFAI_ERR_INVALID_ARG, "layer was not created with ep_world > 1");
+    if (L->ep_peer_on) return fail(L, FFAI_ERR_INVALID_ARG, "peer buffers were already imported");
+    CUDA_TRY(L, cudaSetDevice(L->device));
+    for (int r = 0; r < W; ++r) {
+        if (r == me) {
+            L->ep_peer_win.p[r] = L->ep_win; L->ep_peer_rows.p[r] = L->xg; L->ep_peer_y.p[r] = L->ep_y_bf;
+            continue;
+        }
+        cudaIpcMemHandle_t h[3];
+        memcpy(h, blobs + (size_t)r * FFAI_EP_EXPORT_BYTES, sizeof(h));
+        void* ptr[3] = {nullptr, nullptr, nullptr};
+        for (int i = 0; i < 3; ++i) {
+            CUDA_TRY(L, cudaIpcOpenMemHandle(&ptr[i], h[i], cudaIpcMemLazyEnablePeerAccess));
+            L->ep_opened.push_back(ptr[i]);
+        }
+        L->ep_peer_win.p[r] = ptr[0]; L->ep_peer_rows.p[r] = ptr[1]; L->ep_peer_y.p[r] = ptr[2];
+    }
+    L->ep_peer_on = true;
+    L->ep_epoch = 0;
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_moe_ep_release(ffai_moe_layer* L) {
+    if (!L) return FFAI_ERR_INVALID_ARG;
+    CUDA_TRY(L, cudaSetDevice(L->device));
+    CUDA_TRY(L, cudaDeviceSynchronize());
+    for (void* p : L->ep_opened) cudaIpcCloseMemHandle(p);
+    L->ep_opened.clear();
+    L->ep_peer_on = false;
     return FFAI_OK;
 }
 
@@ -1053,7 +1119,10 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
     if (use_mma) {
         using namespace dmma;
         const int xp_h = (H / 64 + 3) & ~3, xp_i = (I / 64 + 3) & ~3;
-        sum64_rows_kernel<<<(n_rows + 7) / 8, 256, 0, st>>>(L->xg, L->xsum, n_rows, H, xp_h);
+        if (L->ep_rows_dev)
+            ep::sum64_rows_counted_kernel<<<(unsigned)((L->mx_rows + 7) / 8), 256, 0, st>>>(L->xg, L->xsum, L->ep_rows_dev, H, xp_h);
+        else
+            sum64_rows_kernel<<<(n_rows + 7) / 8, 256, 0, st>>>(L->xg, L->xsum, n_rows, H, xp_h);
         Params p{};
         p.group_size = c.expert_group_size;
         p.offsets = offsets_dev;
@@ -1073,6 +1142,7 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         p.w2 = nullptr; p.s2 = nullptr; p.b2 = nullptr; p.rb2 = nullptr;
         p.sb1 = L->sb_down; p.sb2 = nullptr;
         p.N = H; p.K = I; p.x = L->inner_bf; p.xsum = nullptr; p.xsum_parts = L->inner_parts; p.xsum_pitch = xp_i; p.out = L->y;
+        if (L->ep_peer_on) { p.out = L->ep_y_bf; p.out_bf16 = 1; }
         p.out_parts = nullptr;
         launch_mma_decode<false>(p, n_exp, nt, ksplit, st);
         stage_end(L, ST_DOWN, st);
@@ -1100,7 +1170,8 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         p.sb = L->sb_down; p.sb2 = nullptr;
         p.n_out = H; p.K = I; p.m_tiles = (H + BN - 1) / BN;
         p.out = L->y; p.out_ld = H; p.out_permute8 = 0;
-        if (tc_down<float>(L, p, st))
+        if (L->ep_peer_on) p.out = L->ep_y_bf;
+        if (L->ep_peer_on ? tc_down<uint16_t>(L, p, st) : tc_down<float>(L, p, st))
             return fail(L, FFAI_ERR_CUDA, "down grouped GEMM launch failed");
         stage_end(L, ST_DOWN, st);
         L->launches += 3;
@@ -1197,6 +1268,41 @@ int forward_experts_ep(ffai_moe_layer* L, const uint16_t* x, int T, cudaStream_t
     return FFAI_OK;
 }
 
+// The routed experts under expert parallelism with the exchange over peer memory: no NCCL call and no
+// host synchronisation inside the step.  On return the result rows are in their owners' result
+// buffers; the combine pulls them (combine_peer_kernel).
+int forward_experts_ep_peer(ffai_moe_layer* L, const uint16_t* x, int T, cudaStream_t st) {
+    const ffai_moe_config& c = L->cfg;
+    const int H = c.hidden, E = c.n_experts, K = c.top_k, W = c.ep_world, me = c.ep_rank, El = L->e_local;
+    const int M = T * K;
+    if (!ep_rows_perm8(L)) return fail(L, FFAI_ERR_UNSUPPORTED, "the peer-memory exchange needs the 4-bit or cached-bf16 expert kernels");
+    const uint32_t epoch = ++L->ep_epoch;
+    int rc;
+    stage_begin(L, ST_EXCHANGE, st);
+    ep::ep_publish_counts_kernel<<<1, 256, 0, st>>>(L->counts, E, me, W, L->ep_peer_win, epoch, L->error_word);
+    uint32_t* local_off = L->ep_plan_dev;
+    ep::ep_layout_kernel<<<1, 256, 0, st>>>(ep::win_matrix(L->ep_win), E, El, me, W, local_off, L->ep_send_base);
+    if (M > 0)
+        ep::ep_dispatch_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, L->indices, L->offsets, L->ep_send_base, K, El, M, H,
+                                                            L->ep_peer_rows, (uint32_t)L->mx_rows, L->error_word);
+    ep::ep_barrier_kernel<<<1, 32, 0, st>>>(1, me, W, L->ep_peer_win, epoch, L->error_word);
+    L->launches += M > 0 ? 4 : 3;
+    stage_end(L, ST_EXCHANGE, st);
+    if (cudaGetLastError() != cudaSuccess) return fail(L, FFAI_ERR_CUDA, "exchange kernels launch failed");
+
+    // the row count is known on the device only: kernels take their ranges from local_off; the path is
+    // chosen for a balanced share
+    L->ep_rows_dev = local_off + El;
+    if ((rc = run_experts_on_rows(L, M > 0 ? M : 1, El, local_off, st))) return rc;
+    L->ep_rows_dev = nullptr;
+
+    stage_begin(L, ST_EXCHANGE, st);
+    ep::ep_barrier_kernel<<<1, 32, 0, st>>>(2, me, W, L->ep_peer_win, epoch, L->error_word);
+    L->launches += 1;
+    stage_end(L, ST_EXCHANGE, st);
+    return FFAI_OK;
+}
+
 int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, const uint16_t* residual,
                    cudaStream_t st) {
     const ffai_moe_config& c = L->cfg;
@@ -1208,7 +1314,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     if (T == 0) {   // expert parallelism only: no rows of its own, but its experts serve the other ranks
         CUDA_TRY(L, cudaMemsetAsync(L->counts, 0, sizeof(uint32_t) * E, st));
         CUDA_TRY(L, cudaMemsetAsync(L->offsets, 0, sizeof(uint32_t) * (E + 1), st));
-        return forward_experts_ep(L, x, 0, st);
+        return L->ep_peer_on ? forward_experts_ep_peer(L, x, 0, st) : forward_experts_ep(L, x, 0, st);
     }
 
     // stage 0: router (projection + bias + top-k + softmax)
@@ -1250,7 +1356,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
 
     const bool ep_on = c.ep_world > 1;
     if (ep_on) {
-        if ((rc = forward_experts_ep(L, x, T, st))) return rc;
+        if ((rc = L->ep_peer_on ? forward_experts_ep_peer(L, x, T, st) : forward_experts_ep(L, x, T, st))) return rc;
     }
     // Path choice for the routed experts:
     //   register-streaming mma kernels  4-bit, few rows per expert (decode): bound by HBM
@@ -1438,7 +1544,10 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     }
     stage_end(L, ST_SHARED, st);
     stage_begin(L, ST_COMBINE, st);
-    if (ep_on)
+    if (ep_on && L->ep_peer_on)
+        ep::combine_peer_kernel<<<T, 256, 0, st>>>(L->ep_peer_y, L->inv_perm, L->indices, L->offsets, L->ep_send_base, L->e_local,
+                                                   L->rweights, K, sh_y, sh_gate, residual, out, H);
+    else if (ep_on)
         combine_kernel<float, float><<<T, 256, 0, st>>>(L->ep_home_y, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
     else if (tc_experts)
         combine_kernel<uint16_t, float><<<T, 256, 0, st>>>(L->y_bf, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);

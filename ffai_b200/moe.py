@@ -92,6 +92,20 @@ class MoELayer:
                                        C.byref(debug) if debug is not None else None, stream or None)
         capi.check(rc, "ffai_moe_forward", self.handle)
 
+    # exchange over peer memory (expert parallelism without NCCL): export, hand every rank's blob to all, import
+    def ep_export(self) -> bytes:
+        buf = (C.c_uint8 * capi.EP_EXPORT_BYTES)()
+        capi.check(self.lib.ffai_moe_ep_export(self.handle, buf), "ffai_moe_ep_export", self.handle)
+        return bytes(buf)
+
+    def ep_import(self, blobs) -> None:
+        joined = b"".join(blobs)
+        buf = (C.c_uint8 * len(joined)).from_buffer_copy(joined)
+        capi.check(self.lib.ffai_moe_ep_import(self.handle, buf), "ffai_moe_ep_import", self.handle)
+
+    def ep_release(self) -> None:
+        capi.check(self.lib.ffai_moe_ep_release(self.handle), "ffai_moe_ep_release", self.handle)
+
     def set_option(self, name: str, value: int) -> None:
         capi.check(self.lib.ffai_moe_set_option(self.handle, name.encode(), int(value)), "ffai_moe_set_option", self.handle)
 

@@ -229,6 +229,19 @@ FFAI_API int ffai_moe_set_nccl_comm(ffai_moe_layer* layer, void* nccl_comm);
 FFAI_API int ffai_ep_get_unique_id(uint8_t out_id[128]);
 FFAI_API int ffai_ep_comm_create(const uint8_t id[128], int32_t rank, int32_t world, void** out_comm);
 FFAI_API int ffai_ep_comm_destroy(void* comm);
+/* Exchange over peer memory instead of NCCL (one process per GPU on one node, every GPU reachable over
+ * NVLink): each rank exports three of its buffers as CUDA IPC handles, the host code hands every
+ * rank's blob to every rank (rank order, any transport), each rank imports.  From then on a step
+ * makes no NCCL call and no host synchronisation: the row gather stores straight into the owners'
+ * buffers, the combine loads result rows from them, three flag barriers (time-limited) order the
+ * phases.  Needs the 4-bit expert kernels (or the bf16 weight cache); all ranks call forward for every
+ * step, with the same max_tokens.  No reference counterpart. */
+#define FFAI_EP_EXPORT_BYTES 192
+FFAI_API int ffai_moe_ep_export(ffai_moe_layer* layer, uint8_t out_blob[FFAI_EP_EXPORT_BYTES]);
+FFAI_API int ffai_moe_ep_import(ffai_moe_layer* layer, const uint8_t* blobs /* [ep_world][FFAI_EP_EXPORT_BYTES] */);
+/* Unmaps the peers' buffers (after the last step; before any rank destroys its layer, so that no
+ * exported buffer is freed while a peer still maps it). */
+FFAI_API int ffai_moe_ep_release(ffai_moe_layer* layer);
 /* Host-side plan of one exchange from the per-(source rank, local expert) row counts
  * recv_counts[world][e_local]: where each source's rows start in the receive buffer
  * (rank_offsets[world+1]), the expert-contiguous layout after regrouping (local_offsets[e_local+1]),

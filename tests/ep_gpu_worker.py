@@ -45,6 +45,11 @@ def main():
     torch.zeros(1, device="cuda")
     store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=120))
     comm = ep.comm_from_store(store, rank, world)
+
+    def meet(tag):
+        store.set(f"{tag}/{rank}", b"1")
+        store.wait([f"{tag}/{r}" for r in range(world)])
+
     results = []
     try:
         for name, spec, tokens_of, path in CASES:
@@ -72,6 +77,31 @@ def main():
                     rec["rel_rms_vs_single_gpu"] = parity(out, synth.bf16_to_f32(solo))["rel_rms"]
                     rec["repeatable"] = bool(np.array_equal(out, out2))
                 rec["launches"] = lay.launch_count()
+                # the same step with the exchange over peer memory (result rows travel as bf16 there)
+                if spec.expert_bits == 4 and path != 1:
+                    peer = MoELayer(host, max_t, ep_rank=rank, ep_world=world)
+                    try:
+                        if path is not None:
+                            peer.set_option("path", path)
+                        store.set(f"blob/{name}/{rank}", peer.ep_export())
+                        peer.ep_import([bytes(store.get(f"blob/{name}/{r}")) for r in range(world)])
+                        meet(f"go1/{name}")       # the barriers inside a step are time-limited: enter it together
+                        pout, pdbg = peer.forward_host(x, debug=True)
+                        meet(f"go2/{name}")
+                        pout2, _ = peer.forward_host(x)
+                        peer.check_device_status()
+                        rec["peer_launches"] = peer.launch_count()
+                        if T:
+                            rec["peer_rel_rms_vs_nccl"] = parity(pout, synth.bf16_to_f32(out))["rel_rms"]
+                            ppar = parity(pout, ref.out_f32)
+                            rec["peer_rel_rms"], rec["peer_max_abs_norm"] = ppar["rel_rms"], ppar["max_abs_norm"]
+                            rec["peer_routing_exact"] = bool(np.array_equal(pdbg.indices, ref.indices) and np.array_equal(pdbg.perm, ref.perm))
+                            rec["peer_repeatable"] = bool(np.array_equal(pout, pout2))
+                        meet(f"done/{name}")      # nobody unmaps while a peer may still be reading
+                        peer.ep_release()
+                        meet(f"released/{name}")  # nobody frees while a peer still maps
+                    finally:
+                        peer.close()
             finally:
                 lay.close()
                 one.close()

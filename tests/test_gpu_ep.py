@@ -47,3 +47,7 @@ def test_two_gpu_expert_parallel_matches_oracle_and_single_gpu(tmp_path, ffai_li
             assert c["repeatable"], c
             assert c["rel_rms"] <= 5e-3 and c["max_abs_norm"] <= 2e-2, c
             assert c["rel_rms_vs_single_gpu"] <= 5e-3, c
+            if "peer_equals_nccl" in c:
+                assert c["peer_repeatable"] and c["peer_routing_exact"], c
+                assert c["peer_rel_rms"] <= 5e-3 and c["peer_max_abs_norm"] <= 2e-2, c
+        assert sum("peer_launches" in c for c in res["cases"]) >= 4
