@@ -7,6 +7,7 @@ Workloads (seeded synthetic weights and activations, shapes of the benchmark con
     cfg2_b64 (default), cfg2_b1, cfg2_b8, cfg2_b32   GPT-OSS-20B-shaped decode batches
     cfg3                                            Qwen3-30B-A3B-shaped 2048-token prefill
     cfg1                                            tiny layer
+    prep_mxfp4, prep_quant4                         load-time weight preparation kernels (own metric: bytes/s)
     cfg4_ep, cfg3_ep                                256- / 128-expert layers, 2048 tokens per rank, experts
                                                     sharded over the N ranks (expert parallelism: two NCCL
                                                     all-to-all exchanges inside the timed step); N = 1 runs
@@ -173,6 +174,59 @@ def run_reference(args, spec, n_tokens, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_prep(args):
+    """--workload prep_mxfp4 | prep_quant4: the load-time weight preparation kernels on one GPT-OSS-20B-sized
+    stacked projection (32 x 2880 x 2880), GB/s against the HBM roofline (bytes read + written)."""
+    import torch
+    lib = capi.load()
+    if lib.ffai_cuda_device_count() <= 0:
+        raise SystemExit("bench.py needs a CUDA device: libffai_cuda has no CPU fallback")
+    rows, K = 32 * 2880, 2880
+    g = torch.Generator(device="cuda").manual_seed(args.seed)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    if args.workload == "prep_mxfp4":
+        n_groups = rows * K // 32
+        src = torch.randint(0, 256, (n_groups * 16,), dtype=torch.uint8, device="cuda", generator=g)
+        e8 = torch.randint(110, 130, (n_groups,), dtype=torch.uint8, device="cuda", generator=g)
+        ow = torch.empty_like(src)
+        osc = torch.empty(n_groups, dtype=torch.int16, device="cuda")
+        obi = torch.empty(n_groups, dtype=torch.int16, device="cuda")
+        nbytes = n_groups * (16 + 1 + 16 + 4)
+        call = lambda: lib.ffai_op_mxfp4_to_affine_int4(src.data_ptr(), e8.data_ptr(), n_groups, ow.data_ptr(), osc.data_ptr(),
+                                                        obi.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        kernel = "mxfp4_to_affine4_kernel"
+    else:
+        w = torch.randn(rows * K, device="cuda", generator=g).to(torch.bfloat16)
+        ow = torch.empty(rows * K // 8, dtype=torch.int32, device="cuda")
+        osc = torch.empty(rows * K // 64, dtype=torch.int16, device="cuda")
+        obi = torch.empty(rows * K // 64, dtype=torch.int16, device="cuda")
+        nbytes = rows * K * 2 + rows * K // 2 + rows * K // 64 * 4
+        call = lambda: lib.ffai_op_affine_quantize(w.data_ptr(), rows, K, 4, 64, ow.data_ptr(), osc.data_ptr(), obi.data_ptr(),
+                                                   torch.cuda.current_stream().cuda_stream)
+        kernel = "affine_quantize_kernel<4>"
+    times = []
+    for i in range(args.warmup + args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        capi.check(call(), kernel)
+        e1.record()
+        e1.synchronize()
+        if i >= args.warmup:
+            times.append(e0.elapsed_time(e1))
+    ms = statistics.mean(times)
+    peaks = measured_peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "weight_prep_bytes_per_s", "value": gbs * 1e9, "unit": "bytes/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "u4 codes, bf16 scales", "data": "synthetic (seeded)",
+                      "config": {"workload": args.workload, "rows": rows, "in_dim": K, "l2": "256 MiB buffer overwritten between steps (not timed)"},
+                      "gpu_launches": args.steps + args.warmup,
+                      "roofline": {"bound": "hbm", "kernel": kernel, "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                   "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"], "traffic": None,
+                                   "algorithmic_bytes_per_launch": nbytes, "kernel_ms": ms}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -192,6 +246,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.workload.startswith("prep_"):
+        if rank == 0:
+            run_prep(args)
+        return
     spec, n_tokens, regime = workload(args.workload)
 
     if args.impl == "reference":

@@ -20,6 +20,7 @@
 #include "plan.cuh"
 #include "router.cuh"
 #include "tc_path.cuh"
+#include "weight_prep.cuh"
 
 using namespace ffai;
 
@@ -1810,6 +1811,40 @@ extern "C" FFAI_API int ffai_op_moe_unpermute(const uint16_t* expert_out, const 
     int rc;
     if ((rc = need_device())) return rc;
     combine_kernel<uint16_t, float><<<T, 256, 0, (cudaStream_t)stream>>>(expert_out, inv_perm, weights, k, nullptr, nullptr, nullptr, out, hidden);
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}
+
+extern "C" FFAI_API int ffai_op_mxfp4_to_affine_int4(const uint32_t* packed, const uint8_t* e8m0, int64_t n_groups,
+                                                     uint32_t* out_weight, uint16_t* out_scales, uint16_t* out_biases,
+                                                     void* stream) {
+    if (!packed || !e8m0 || !out_weight || !out_scales || !out_biases || n_groups <= 0) return FFAI_ERR_INVALID_ARG;
+    if (!aligned16(packed) || !aligned16(out_weight)) return FFAI_ERR_INVALID_ARG;
+    int rc;
+    if ((rc = need_device())) return rc;
+    const unsigned blocks = (unsigned)((n_groups + 255) / 256);
+    prep::mxfp4_to_affine4_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const uint4*>(packed), e8m0, (long)n_groups, reinterpret_cast<uint4*>(out_weight), out_scales, out_biases);
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}
+
+extern "C" FFAI_API int ffai_op_affine_quantize(const uint16_t* w, int64_t rows, int32_t in_dim, int32_t bits, int32_t gs,
+                                                uint32_t* out_weight, uint16_t* out_scales, uint16_t* out_biases, void* stream) {
+    if (!w || !out_weight || !out_scales || !out_biases || rows <= 0) return FFAI_ERR_INVALID_ARG;
+    int rc = op_check_quant(bits, gs, in_dim);
+    if (rc) return rc;
+    if ((rc = need_device())) return rc;
+    const long n_groups = (long)rows * (in_dim / gs);
+    const unsigned blocks = (unsigned)((n_groups + 127) / 128);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (bits) {
+        case 2: prep::affine_quantize_kernel<2><<<blocks, 128, 0, st>>>(w, n_groups, gs, out_weight, out_scales, out_biases); break;
+        case 3: prep::affine_quantize_kernel<3><<<blocks, 128, 0, st>>>(w, n_groups, gs, out_weight, out_scales, out_biases); break;
+        case 4: prep::affine_quantize_kernel<4><<<blocks, 128, 0, st>>>(w, n_groups, gs, out_weight, out_scales, out_biases); break;
+        case 5: prep::affine_quantize_kernel<5><<<blocks, 128, 0, st>>>(w, n_groups, gs, out_weight, out_scales, out_biases); break;
+        case 6: prep::affine_quantize_kernel<6><<<blocks, 128, 0, st>>>(w, n_groups, gs, out_weight, out_scales, out_biases); break;
+        case 8: prep::affine_quantize_kernel<8><<<blocks, 128, 0, st>>>(w, n_groups, gs, out_weight, out_scales, out_biases); break;
+        default: return FFAI_ERR_INVALID_ARG;
+    }
     return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
 }
 

@@ -362,6 +362,20 @@ FFAI_API int ffai_op_moe_unpermute(const uint16_t* expert_out, const uint32_t* i
                           const float* weights, uint16_t* out, int32_t n_tokens,
                           int32_t hidden, int32_t k, void* stream);
 
+/* Weight preparation (rows either side of the block).
+ * ffai_op_mxfp4_to_affine_int4: the load-time transcode of GPT-OSS experts
+ *   (GPTOSSText.swift:1071-1244, a host loop there): per group of 32 fp4 (e2m1) codes and one e8m0
+ *   scale byte, fit an affine 16-level grid to the group's own min/max and remap the codes nibble for
+ *   nibble.  packed: n_groups*4 words; out_weight the same size (bits 4, group size 32); scales and
+ *   biases bf16, one per group.  Bit-identical to the host version.
+ * ffai_op_affine_quantize: MLX affine quantization of a [rows, in_dim] bf16 matrix into the packed
+ *   layout this library reads (QuantizedOps.swift:229-388); bits in {2,3,4,5,6,8}, gs in {32,64,128}. */
+FFAI_API int ffai_op_mxfp4_to_affine_int4(const uint32_t* packed, const uint8_t* e8m0, int64_t n_groups,
+                                          uint32_t* out_weight, uint16_t* out_scales, uint16_t* out_biases,
+                                          void* stream);
+FFAI_API int ffai_op_affine_quantize(const uint16_t* w, int64_t rows, int32_t in_dim, int32_t bits, int32_t gs,
+                                     uint32_t* out_weight, uint16_t* out_scales, uint16_t* out_biases, void* stream);
+
 /* Ops.sigmoidScalarFMA / sigmoidScalarFMAResidual — Ops.swift:6255-6334,
  * OpsFused.swift:699-753, batched over rows:
  * out[t,:] = [residual[t,:] +] base[t,:] + sigmoid(gate[t]) * value[t,:]. */

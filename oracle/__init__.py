@@ -121,6 +121,29 @@ def unpermute(expert_out, inv_perm, weights, n_tokens, hidden, k):
     return out
 
 
+def mxfp4_to_affine4(packed_bytes, e8m0):
+    """MXFP4 codes [n_groups, 16] u8 + scale bytes [n_groups] -> (packed u8 [n_groups,16], scales, biases bf16)."""
+    packed_bytes = np.ascontiguousarray(packed_bytes, dtype=np.uint8)
+    e8m0 = np.ascontiguousarray(e8m0, dtype=np.uint8)
+    n = int(e8m0.size)
+    out = np.zeros((n, 16), dtype=np.uint8)
+    sc = np.zeros(n, dtype=np.uint16)
+    bi = np.zeros(n, dtype=np.uint16)
+    lib().orc_mxfp4_to_affine4(_p(packed_bytes), _p(e8m0), C.c_int64(n), _p(out), _p(sc), _p(bi))
+    return out, sc, bi
+
+
+def affine_quantize(w_bf16, bits, gs):
+    """[rows, K] bf16 bit patterns -> (packed u32 [rows, K*bits/32], scales, biases bf16 [rows, K/gs])."""
+    w_bf16 = np.ascontiguousarray(w_bf16, dtype=np.uint16)
+    rows, K = w_bf16.shape
+    out = np.zeros((rows, K * bits // 32), dtype=np.uint32)
+    sc = np.zeros((rows, K // gs), dtype=np.uint16)
+    bi = np.zeros((rows, K // gs), dtype=np.uint16)
+    lib().orc_affine_quantize(_p(w_bf16), C.c_int64(rows), C.c_int(K), C.c_int(bits), C.c_int(gs), _p(out), _p(sc), _p(bi))
+    return out, sc, bi
+
+
 def router_logits(host_layer, x):
     """Router logits [T, E] in the oracle's fixed accumulation order."""
     spec = host_layer.spec

@@ -578,3 +578,102 @@ ORC_EXPORT int orc_num_threads(void) {
     return 1;
 #endif
 }
+
+/* ───────────────────────── weight preparation (next rows) ───────────────────────── */
+
+/* MXFP4 -> affine int4, group 32, as GPT-OSS checkpoints are transcoded at load time
+ * (GPTOSSText.swift:943-956 constants, :1150-1226 the per-group fit).  Per group of 32 fp4 codes
+ * (16 bytes, low nibble first) and one e8m0 byte:
+ *   micro = 2^(e8m0 - 127); lo, hi = min / max of the code values (scan order: bytes ascending, low
+ *   nibble then high nibble; strict comparisons, so the first zero met decides the sign of a zero
+ *   minimum); bias = lo * micro; scale = (hi - lo) * micro / 15 (0 for a flat group);
+ *   q = clamp(round_half_away(((value - lo) * (micro * (1 / scale)))), 0, 15), nibble for nibble.
+ * Scale and bias are stored as bf16 (round to nearest even). */
+static const float MXFP4_LUT[16] = {+0.0f, +0.5f, +1.0f, +1.5f, +2.0f, +3.0f, +4.0f, +6.0f,
+                                    -0.0f, -0.5f, -1.0f, -1.5f, -2.0f, -3.0f, -4.0f, -6.0f};
+
+ORC_EXPORT void orc_mxfp4_to_affine4(const uint8_t* packed, const uint8_t* e8m0, int64_t n_groups, uint8_t* out_packed,
+                          uint16_t* out_scales, uint16_t* out_biases) {
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < n_groups; ++g) {
+        const float micro = (float)exp2((double)((int)e8m0[g] - 127));
+        const uint8_t* src = packed + g * 16;
+        float lo = 1e30f, hi = -1e30f;
+        for (int b = 0; b < 16; ++b) {
+            const float v0 = MXFP4_LUT[src[b] & 0x0F], v1 = MXFP4_LUT[src[b] >> 4];
+            if (v0 < lo) lo = v0;
+            if (v0 > hi) hi = v0;
+            if (v1 < lo) lo = v1;
+            if (v1 > hi) hi = v1;
+        }
+        const float aff_bias = lo * micro;
+        const float span = (hi - lo) * micro;
+        const float aff_scale = span > 0.0f ? span / 15.0f : 0.0f;
+        const float inv_scale = aff_scale > 0.0f ? 1.0f / aff_scale : 0.0f;
+        out_scales[g] = orc_f32_to_bf16(aff_scale);
+        out_biases[g] = orc_f32_to_bf16(aff_bias);
+        const float code_scale = micro * inv_scale;
+        for (int b = 0; b < 16; ++b) {
+            int q0 = (int)roundf((MXFP4_LUT[src[b] & 0x0F] - lo) * code_scale);
+            int q1 = (int)roundf((MXFP4_LUT[src[b] >> 4] - lo) * code_scale);
+            if (q0 < 0) q0 = 0;
+            if (q0 > 15) q0 = 15;
+            if (q1 < 0) q1 = 0;
+            if (q1 > 15) q1 = 15;
+            out_packed[g * 16 + b] = (uint8_t)(q0 | (q1 << 4));
+        }
+    }
+}
+
+/* MLX affine quantization of one [rows, K] matrix, bits in {2,3,4,5,6,8}, group size gs
+ * (wrapper and shape rules: QuantizedOps.swift:229-388, QuantizedOpsValidation.swift:132-146).
+ * The reference's kernel body is in the un-vendored metaltile project; what follows is MLX's published
+ * affine_quantize (the algorithm the reference's format comes from), which the reference's own
+ * tests constrain only through round-trip error bounds (QuantizedOpsAffineTests.swift:19-381):
+ *   n = 2^bits - 1; scale = max((max - min) / n, 1e-7); the edge with the larger magnitude is kept
+ *   exact: side = |min| > |max|; scale = side ? scale : -scale; edge = side ? min : max;
+ *   q0 = round(edge / scale); if q0 != 0 { scale = edge / q0; bias = edge } else bias = 0;
+ *   q = min(round((w - bias) / scale), n)   (fp32 scale and bias; bf16 copies are stored)
+ * Values are packed LSB first.  Input and scale/bias are bf16 bit patterns. */
+ORC_EXPORT void orc_affine_quantize(const uint16_t* w, int64_t rows, int K, int bits, int gs, uint32_t* out_packed,
+                         uint16_t* out_scales, uint16_t* out_biases) {
+    const int gpr = K / gs;
+    const int64_t words_per_row = (int64_t)K * bits / 32;
+    const float n_bins = (float)((1 << bits) - 1);
+    memset(out_packed, 0, (size_t)(rows * words_per_row) * 4);
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        for (int g = 0; g < gpr; ++g) {
+            const uint16_t* src = w + r * K + (int64_t)g * gs;
+            float w_min = INFINITY, w_max = -INFINITY;
+            for (int i = 0; i < gs; ++i) {
+                const float v = orc_bf16_to_f32(src[i]);
+                w_min = fminf(w_min, v);
+                w_max = fmaxf(w_max, v);
+            }
+            float scale = fmaxf((w_max - w_min) / n_bins, 1e-7f);
+            const int side = fabsf(w_min) > fabsf(w_max);
+            scale = side ? scale : -scale;
+            const float edge = side ? w_min : w_max;
+            const float q0 = roundf(edge / scale);
+            float bias = 0.0f;
+            if (q0 != 0.0f) {
+                scale = edge / q0;
+                bias = edge;
+            }
+            out_scales[r * gpr + g] = orc_f32_to_bf16(scale);
+            out_biases[r * gpr + g] = orc_f32_to_bf16(bias);
+            for (int i = 0; i < gs; ++i) {
+                const float v = orc_bf16_to_f32(src[i]);
+                float q = roundf((v - bias) / scale);
+                if (q > n_bins) q = n_bins;
+                if (!(q >= 0.0f)) q = 0.0f;
+                const uint32_t qi = (uint32_t)q;
+                const int64_t bit = (int64_t)(g * gs + i) * bits;
+                uint32_t* row = out_packed + r * words_per_row;
+                row[bit >> 5] |= qi << (bit & 31);
+                if ((bit & 31) + bits > 32) row[(bit >> 5) + 1] |= qi >> (32 - (bit & 31));
+            }
+        }
+    }
+}
