@@ -5,6 +5,7 @@
 
 Workloads (seeded synthetic weights and activations, shapes of the benchmark configurations):
     cfg2_b64 (default), cfg2_b1, cfg2_b8, cfg2_b32   GPT-OSS-20B-shaped decode batches
+    cfg2g32_b64, cfg2g32_b1, ...                     the same with group-32 experts and row biases (transcoded checkpoints)
     cfg3                                            Qwen3-30B-A3B-shaped 2048-token prefill
     cfg1                                            tiny layer
     prep_mxfp4, prep_quant4                         load-time weight preparation kernels (own metric: bytes/s)
@@ -57,6 +58,9 @@ def workload(name: str):
         return synth.cfg4_shared(), 2048, "prefill"
     if name == "cfg3_ep":
         return synth.cfg3_qwen(), 2048, "prefill"
+    if name.startswith("cfg2g32"):   # GPT-OSS experts as the MXFP4 transcode leaves them: group 32, row biases
+        b = int(name.split("_b")[1]) if "_b" in name else 64
+        return synth.cfg2_gptoss().with_(name="cfg2_gptoss20b_gs32", expert_group_size=32, expert_row_bias=1), b, "decode"
     if name.startswith("cfg2"):
         b = int(name.split("_b")[1]) if "_b" in name else 64
         return synth.cfg2_gptoss(), b, "decode"
@@ -230,7 +234,7 @@ def run_prep(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="cfg2_b64")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

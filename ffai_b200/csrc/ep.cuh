@@ -274,7 +274,7 @@ combine_peer_kernel(PeerPtrs y_of, const uint32_t* __restrict__ inv_perm, const 
     }
 }
 
-// 64-run sums of the first *n_rows_dev rows (the count lives on the device); grid sized for the capacity.
+// 32-run sums of the first *n_rows_dev rows (the count lives on the device); grid sized for the capacity.
 __global__ void sum64_rows_counted_kernel(const uint16_t* __restrict__ rows, float* __restrict__ sums,
                                           const uint32_t* __restrict__ n_rows_dev, int row_len, int sum_pitch) {
     const int warps = blockDim.x / 32;
@@ -293,8 +293,7 @@ __global__ void sum64_rows_counted_kernel(const uint16_t* __restrict__ rows, flo
         }
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
-        part += __shfl_xor_sync(0xFFFFFFFFu, part, 4);
-        if ((lane & 7) == 0 && i < chunks) sums[(size_t)row * sum_pitch + (i >> 3)] = part;
+        if ((lane & 3) == 0 && i < chunks) sums[(size_t)row * sum_pitch + (i >> 2)] = part;
     }
 }
 

@@ -129,6 +129,7 @@ constexpr int W_PITCH = 64;
 #endif
 
 // Runs of 64-run sums kept in shared memory per pass: whole stages, plus one stage that the look-ahead may touch.
+// (With group size 32 the sums are kept per 32-run: twice as many entries.)
 __host__ __device__ inline int xs_sm_runs(int n64) { return ((n64 + STG_RUNS - 1) / STG_RUNS + 1) * STG_RUNS; }
 
 // Block-shared activation ring (kernels without a split reduction axis): per stage 16 rows x 256 bytes
@@ -136,18 +137,20 @@ __host__ __device__ inline int xs_sm_runs(int n64) { return ((n64 + STG_RUNS - 1
 constexpr int X_PITCH = 272;
 constexpr int X_STAGE = 16 * X_PITCH;
 
-template <bool FUSED>
+// G32: quantization groups of 32 (two scale words per row and 64-run instead of one).
+template <bool FUSED, bool G32 = false>
 struct WarpStage {
     static constexpr int NP = FUSED ? 2 : 1;
+    static constexpr int SBW = G32 ? 2 : 1;            // scale words per row and 64-run
     static constexpr int DEPTH = FUSED ? FFAI_DM_DEPTH_FUSED : FFAI_DM_DEPTH_PLAIN;   // ring slots per warp; DEPTH-1 stages in flight
     static constexpr int W_BYTES = NP * 16 * W_PITCH;
-    static constexpr int SB_BYTES = NP * STG_RUNS * 64;
+    static constexpr int SB_BYTES = NP * STG_RUNS * 64 * SBW;
     static constexpr int STAGE = W_BYTES + SB_BYTES;
     static constexpr int PER_WARP = DEPTH * STAGE;
     static constexpr int TOTAL = 4 * PER_WARP;
     static constexpr int X_RING = DEPTH * X_STAGE;
     // dynamic shared memory of a launch: weight rings, [activation ring], 64-run sums
-    static int smem_bytes(int n64, int ksplit) { return TOTAL + (ksplit == 1 ? X_RING : 0) + xs_sm_runs(n64) * 64; }
+    static int smem_bytes(int n64, int ksplit) { return TOTAL + (ksplit == 1 ? X_RING : 0) + xs_sm_runs(n64) * 64 * SBW; }
 };
 
 // (w & mask) | expo with both constants held in registers: with immediates the compiler has to emit two
@@ -178,7 +181,7 @@ FFAI_DEVINL void cp_async16_zfill(uint32_t dst, const void* src, uint32_t bytes)
 // What a warp knows about its slice of the weights; does not change between passes over the activations.
 template <bool FUSED>
 struct WarpJob {
-    const uint8_t* wsrc[WarpStage<FUSED>::NP * 2];  // this lane's 16-byte column of the rows it copies, at the slice start
+    const uint8_t* wsrc[WarpStage<FUSED, false>::NP * 2];  // this lane's 16-byte column of the rows it copies, at the slice start
     const uint8_t* sbsrc;                           // this lane's chunk of scale words, at the slice start
     bool sb_lane;                                   // lane copies scale words
     uint32_t wdst;                                  // shared-memory address of this lane's first weight chunk in slot 0
@@ -187,16 +190,105 @@ struct WarpJob {
     int G0;                                         // first run of the slice
 };
 
+// One 64-run of a stage: scale words, A fragments from the staged packed rows, MMAs against the B
+// fragments in xc, fold into tot.
+//   group 64/128: a lane's two packed words are k 16t..16t+15 of the run (one 8-byte read); one fold per run
+//   group 32:     word 0 is k 8t..8t+7 of the first half, word 1 the same of the second half (two 4-byte
+//                 reads), so the two MMAs of a word stay inside one quantization group; one fold per half
+// rd: this lane's byte offsets into a weight row of the stage ([Gi] for group 64, [2 Gi + word] for group 32);
+// xs: the lane's 64-run sums for this run (16 floats per run; per 32-run with group 32).
+template <bool FUSED, int NT, bool G32, int Gi>
+FFAI_DEVINL void compute_run(const uint8_t* stage, const uint32_t* rd, const uint4 (*xc)[2], const float* xs,
+                             uint32_t mask, uint32_t expo, int g, float (*tot)[WarpStage<FUSED, G32>::NP][4]) {
+    using WS = WarpStage<FUSED, G32>;
+    constexpr int NP = WS::NP;
+    constexpr int SBW = WS::SBW;
+    float2 sx[SBW][NT];
+#pragma unroll
+    for (int hf = 0; hf < SBW; ++hf)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) sx[hf][j] = *reinterpret_cast<const float2*>(xs + hf * 16 + 8 * j);
+#pragma unroll
+    for (int q = 0; q < NP; ++q) {
+        // scale and (bias - 128*scale) of the two rows this lane's results belong to
+        float sc[SBW][2], bm[SBW][2];
+#pragma unroll
+        for (int hf = 0; hf < SBW; ++hf)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t v = *reinterpret_cast<const uint32_t*>(
+                    stage + WS::W_BYTES + q * (STG_RUNS * 64 * SBW) + (Gi * SBW + hf) * 64 + (g + 8 * h) * 4);
+                const float s = __uint_as_float(v << 16), b = __uint_as_float(v & 0xFFFF0000u);
+                sc[hf][h] = s;
+                bm[hf][h] = fmaf(-128.0f, s, b);
+            }
+        // A fragments: [word 0/1][row lo/hi][pair 0..3]
+        uint32_t af[2][2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (G32) {
+                const uint32_t w0 = *reinterpret_cast<const uint32_t*>(stage + (q * 16 + 8 * h) * W_PITCH + rd[2 * Gi]);
+                const uint32_t w1 = *reinterpret_cast<const uint32_t*>(stage + (q * 16 + 8 * h) * W_PITCH + rd[2 * Gi + 1]);
+                unpack_word_128r(w0, af[0][h], mask, expo);
+                unpack_word_128r(w1, af[1][h], mask, expo);
+            } else {
+                const uint2 wv = *reinterpret_cast<const uint2*>(stage + (q * 16 + 8 * h) * W_PITCH + rd[Gi]);
+                unpack_word_128r(wv.x, af[0][h], mask, expo);
+                unpack_word_128r(wv.y, af[1][h], mask, expo);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const uint32_t xb[2][4] = {{xc[j][0].x, xc[j][0].y, xc[j][0].z, xc[j][0].w},
+                                       {xc[j][1].x, xc[j][1].y, xc[j][1].z, xc[j][1].w}};
+            float c[4];
+#pragma unroll
+            for (int w = 0; w < 2; ++w) {
+#pragma unroll
+                for (int hp = 0; hp < 2; ++hp) {
+                    // k-slots (2t,2t+1) <- pair 2hp, (2t+8,2t+9) <- pair 2hp+1 of word w
+                    const uint32_t a[4] = {af[w][0][2 * hp], af[w][1][2 * hp], af[w][0][2 * hp + 1], af[w][1][2 * hp + 1]};
+                    if ((G32 || w == 0) && hp == 0) mma_bf16_16816_zero(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
+                    else mma_bf16_16816(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
+                }
+                if (G32 || w == 1) {
+                    constexpr int dummy = 0; (void)dummy;
+                    const int hf = G32 ? w : 0;
+                    tot[j][q][0] = fmaf(sc[hf][0], c[0], fmaf(bm[hf][0], sx[hf][j].x, tot[j][q][0]));
+                    tot[j][q][1] = fmaf(sc[hf][0], c[1], fmaf(bm[hf][0], sx[hf][j].y, tot[j][q][1]));
+                    tot[j][q][2] = fmaf(sc[hf][1], c[2], fmaf(bm[hf][1], sx[hf][j].x, tot[j][q][2]));
+                    tot[j][q][3] = fmaf(sc[hf][1], c[3], fmaf(bm[hf][1], sx[hf][j].y, tot[j][q][3]));
+                }
+            }
+        }
+    }
+}
+
+// This lane's byte offsets into a weight row of a stage (see compute_run).
+template <bool G32>
+FFAI_DEVINL void weight_read_offsets(int g, int t, uint32_t* rd) {
+    const uint32_t swz = ((g >> 1) & 1) << 1;                     // 16-byte columns are XOR-swizzled with bit 1 of the row
+    if (G32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) rd[i] = g * W_PITCH + (((uint32_t)i ^ swz) << 4) + 4 * t;   // i = 2 Gi + word
+    } else {
+        const uint32_t rd0 = g * W_PITCH + (t & 1) * 8 + ((((uint32_t)t >> 1) ^ swz) << 4);
+        rd[0] = rd0;
+        rd[1] = rd0 ^ 32u;
+    }
+}
+
 // One pass over the weights of a warp's 16-row block for up to 8*NT activation rows.
 // All stages have the same shape: the second run of an odd tail (and every stage issued past the
 // end) is copied with zero source bytes, so its weights and scale words read as zero and add nothing;
 // its activations are read from the last real run (finite values).
-template <bool FUSED, int NT>
+template <bool FUSED, int NT, bool G32>
 FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t* wsm, const float* xs_sm,
-                             int row0, int cnt, int tok0, int lane, float (*tot)[WarpStage<FUSED>::NP][4]) {
-    using WS = WarpStage<FUSED>;
+                             int row0, int cnt, int tok0, int lane, float (*tot)[WarpStage<FUSED, G32>::NP][4]) {
+    using WS = WarpStage<FUSED, G32>;
     constexpr int NP = WS::NP;
     constexpr int DEPTH = WS::DEPTH;
+    constexpr int SBW = WS::SBW;
     const int g = lane >> 2, t = lane & 3;
     const int K = p.K;
     const int n_runs = job.n_runs;
@@ -205,11 +297,13 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
     asm volatile("mov.u32 %0, 0x000F000F;" : "=r"(mask));
     asm volatile("mov.u32 %0, 0x43004300;" : "=r"(expo));
 
-    // B-operand rows of this lane (column g of each 8-wide tile), clamped to the last valid row
+    // B-operand rows of this lane (column g of each 8-wide tile), clamped to the last valid row; the lane's
+    // k range inside a run: 16t.. (one 32-byte piece) or, with group 32, 8t.. of each half (two 16-byte pieces)
     const uint8_t* xrow[NT];
 #pragma unroll
     for (int j = 0; j < NT; ++j)
-        xrow[j] = reinterpret_cast<const uint8_t*>(p.x + src_row(p, row0 + min(tok0 + 8 * j + g, cnt - 1)) * K + 16 * t) + (size_t)job.G0 * 128;
+        xrow[j] = reinterpret_cast<const uint8_t*>(p.x + src_row(p, row0 + min(tok0 + 8 * j + g, cnt - 1)) * K + (G32 ? 8 : 16) * t) +
+                  (size_t)job.G0 * 128;
     const uint32_t x_last = (uint32_t)(n_runs > 0 ? n_runs - 1 : 0) * 128u;
 
 #pragma unroll
@@ -220,7 +314,7 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
             for (int i = 0; i < 4; ++i) tot[j][q][i] = 0.0f;
 
     const uint32_t col_run = (uint32_t)(lane & 3) >> 1;          // which run of a stage this lane's weight column belongs to
-    const uint32_t sb_run = (uint32_t)(lane & 7) >> 2;           // ... and its scale chunk
+    const uint32_t sb_run = G32 ? (uint32_t)(lane & 15) >> 3 : (uint32_t)(lane & 7) >> 2;   // ... and its scale chunk
     uint32_t issue_off = 0;                                      // byte offset of the next stage in the source rows
     uint32_t issue_slot = 0;                                     // byte offset of the ring slot it goes to
     int issue_rem = n_runs;                                      // runs not yet issued (may go negative)
@@ -229,7 +323,7 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
 #pragma unroll
         for (int i = 0; i < NP * 2; ++i)
             cp_async16_zfill(job.wdst + issue_slot + i * 8 * W_PITCH, job.wsrc[i] + issue_off, szw);
-        if (job.sb_lane) cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * 2, (int)sb_run < issue_rem ? 16u : 0u);
+        if (job.sb_lane) cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * (2 * SBW), (int)sb_run < issue_rem ? 16u : 0u);
         cp_async_commit();
 #ifndef FFAI_DM_EXP_NOW
         issue_off += 64;
@@ -248,76 +342,34 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
         for (int j = 0; j < NT; ++j) {
             const uint4* src = reinterpret_cast<const uint4*>(xrow[j] + off);
             xd[j][0] = __ldg(src);
-            xd[j][1] = __ldg(src + 1);
+            xd[j][1] = __ldg(src + (G32 ? 4 : 1));
         }
     };
     uint32_t x_off = 0;
     if (n_runs > 0) fetch_x(0, xbuf[0]);   // a warp without a slice must not touch the row at all
 
     uint32_t use_slot = 0;
-    // this lane's fragment words inside a stage: row g (+8h, + projection), swizzled 16-byte column of run 0 / run 1
-    const uint32_t rd0 = g * W_PITCH + (t & 1) * 8 + (((t >> 1) ^ (((g >> 1) & 1) << 1)) << 4);
-    const uint32_t rd[STG_RUNS] = {rd0, rd0 ^ 32u};
-    const float* xs_run = xs_sm + job.G0 * 16 + 2 * t;           // 16 floats (one per activation row of the pass) per run
+    uint32_t rd[4];
+    weight_read_offsets<G32>(g, t, rd);
+    const float* xs_run = xs_sm + job.G0 * 16 * SBW + 2 * t;     // 16 floats (one per activation row of the pass) per (half) run
     for (int st = 0; st < n_stages; ++st) {
         cp_async_wait<DEPTH - 2>();   // this lane's copies of the stage have landed
         __syncwarp();                 // ... and the other lanes'; the slot of the previous stage is free again
         issue_stage();
         const uint8_t* stage = wsm + use_slot;
         use_slot = use_slot == (DEPTH - 1) * WS::STAGE ? 0u : use_slot + WS::STAGE;
-#pragma unroll
-        for (int Gi = 0; Gi < STG_RUNS; ++Gi) {
-            // this run's activations are in set Gi; start fetching the next run's into the other set
-            uint4 (*xc)[2] = xbuf[Gi];
-            x_off = min(x_off + 128u, x_last);
+        // run 0 of the stage: its activations are in set 0; start fetching run 1's into set 1, and so on
+        x_off = min(x_off + 128u, x_last);
 #ifndef FFAI_DM_EXP_NOX
-            fetch_x(x_off, xbuf[(Gi + 1) % STG_RUNS]);
+        fetch_x(x_off, xbuf[1]);
 #endif
-            float2 sx[NT];
-#pragma unroll
-            for (int j = 0; j < NT; ++j) sx[j] = *reinterpret_cast<const float2*>(xs_run + Gi * 16 + 8 * j);
-#pragma unroll
-            for (int q = 0; q < NP; ++q) {
-                // scale and (bias - 128*scale) of the two rows this lane's results belong to
-                float sc[2], bm[2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint32_t v = *reinterpret_cast<const uint32_t*>(
-                        stage + WS::W_BYTES + q * (STG_RUNS * 64) + Gi * 64 + (g + 8 * h) * 4);
-                    const float s = __uint_as_float(v << 16), b = __uint_as_float(v & 0xFFFF0000u);
-                    sc[h] = s;
-                    bm[h] = fmaf(-128.0f, s, b);
-                }
-                // A fragments: [word 0/1][row lo/hi][pair 0..3]
-                uint32_t af[2][2][4];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint2 wv = *reinterpret_cast<const uint2*>(stage + (q * 16 + 8 * h) * W_PITCH + rd[Gi]);
-                    unpack_word_128r(wv.x, af[0][h], mask, expo);
-                    unpack_word_128r(wv.y, af[1][h], mask, expo);
-                }
-#pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    const uint32_t xb[2][4] = {{xc[j][0].x, xc[j][0].y, xc[j][0].z, xc[j][0].w},
-                                               {xc[j][1].x, xc[j][1].y, xc[j][1].z, xc[j][1].w}};
-                    float c[4];
-#pragma unroll
-                    for (int w = 0; w < 2; ++w)
-#pragma unroll
-                        for (int hp = 0; hp < 2; ++hp) {
-                            // k-slots (2t,2t+1) <- pair 2hp, (2t+8,2t+9) <- pair 2hp+1 of word w
-                            const uint32_t a[4] = {af[w][0][2 * hp], af[w][1][2 * hp], af[w][0][2 * hp + 1], af[w][1][2 * hp + 1]};
-                            if (w == 0 && hp == 0) mma_bf16_16816_zero(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
-                            else mma_bf16_16816(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
-                        }
-                    tot[j][q][0] = fmaf(sc[0], c[0], fmaf(bm[0], sx[j].x, tot[j][q][0]));
-                    tot[j][q][1] = fmaf(sc[0], c[1], fmaf(bm[0], sx[j].y, tot[j][q][1]));
-                    tot[j][q][2] = fmaf(sc[1], c[2], fmaf(bm[1], sx[j].x, tot[j][q][2]));
-                    tot[j][q][3] = fmaf(sc[1], c[3], fmaf(bm[1], sx[j].y, tot[j][q][3]));
-                }
-            }
-        }
-        xs_run += STG_RUNS * 16;
+        compute_run<FUSED, NT, G32, 0>(stage, rd, xbuf[0], xs_run, mask, expo, g, tot);
+        x_off = min(x_off + 128u, x_last);
+#ifndef FFAI_DM_EXP_NOX
+        fetch_x(x_off, xbuf[0]);
+#endif
+        compute_run<FUSED, NT, G32, 1>(stage, rd, xbuf[1], xs_run + 16 * SBW, mask, expo, g, tot);
+        xs_run += STG_RUNS * 16 * SBW;
     }
     cp_async_wait<0>();
 }
@@ -327,13 +379,14 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
 // instead of once per warp.  All threads copy (weights into their warp's ring, activations into the
 // shared ring) and meet at one barrier per stage, which both publishes the stage and frees the slot
 // of the previous one.  The loop count is the CTA's (n64), so warps without rows still take part.
-template <bool FUSED, int NT>
+template <bool FUSED, int NT, bool G32>
 FFAI_DEVINL void decode_pass_shared(const Params& p, const WarpJob<FUSED>& job, uint8_t* wsm, uint8_t* xring,
                                     const float* xs_sm, int row0, int cnt, int tok0, int n64, int lane,
-                                    float (*tot)[WarpStage<FUSED>::NP][4]) {
-    using WS = WarpStage<FUSED>;
+                                    float (*tot)[WarpStage<FUSED, G32>::NP][4]) {
+    using WS = WarpStage<FUSED, G32>;
     constexpr int NP = WS::NP;
     constexpr int DEPTH = WS::DEPTH;
+    constexpr int SBW = WS::SBW;
     const int g = lane >> 2, t = lane & 3;
     const int K = p.K;
     const int n_stages = (n64 + STG_RUNS - 1) / STG_RUNS;
@@ -363,7 +416,7 @@ FFAI_DEVINL void decode_pass_shared(const Params& p, const WarpJob<FUSED>& job, 
             for (int i = 0; i < 4; ++i) tot[j][q][i] = 0.0f;
 
     const uint32_t col_run = (uint32_t)(lane & 3) >> 1;
-    const uint32_t sb_run = (uint32_t)(lane & 7) >> 2;
+    const uint32_t sb_run = G32 ? (uint32_t)(lane & 15) >> 3 : (uint32_t)(lane & 7) >> 2;
     uint32_t issue_off = 0, issue_slot = 0, issue_xslot = 0;
     int issue_rem = job.n_runs;       // this warp's weight runs not yet issued (0 for a warp without rows)
     int issue_rem_x = n64;            // the CTA's activation runs not yet issued
@@ -372,7 +425,7 @@ FFAI_DEVINL void decode_pass_shared(const Params& p, const WarpJob<FUSED>& job, 
 #pragma unroll
         for (int i = 0; i < NP * 2; ++i)
             cp_async16_zfill(job.wdst + issue_slot + i * 8 * W_PITCH, job.wsrc[i] + issue_off, szw);
-        if (job.sb_lane) cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * 2, (int)sb_run < issue_rem ? 16u : 0u);
+        if (job.sb_lane) cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * (2 * SBW), (int)sb_run < issue_rem ? 16u : 0u);
         const uint32_t szx = (int)xcol_run < issue_rem_x ? 16u : 0u;
 #pragma unroll
         for (int i = 0; i < NT; ++i) cp_async16_zfill(xdst[i] + issue_xslot, xsrc[i] + issue_off * 4, szx);
@@ -388,9 +441,10 @@ FFAI_DEVINL void decode_pass_shared(const Params& p, const WarpJob<FUSED>& job, 
     for (int st = 0; st < DEPTH - 1; ++st) issue_stage();
 
     uint32_t use_slot = 0, use_xslot = 0;
-    const uint32_t rd0 = g * W_PITCH + (t & 1) * 8 + (((t >> 1) ^ (((g >> 1) & 1) << 1)) << 4);
-    const uint32_t rd[STG_RUNS] = {rd0, rd0 ^ 32u};
-    const uint32_t xrd = g * X_PITCH + t * 32;
+    uint32_t rd[4];
+    weight_read_offsets<G32>(g, t, rd);
+    const uint32_t xrd = g * X_PITCH + t * (G32 ? 16 : 32);   // the lane's k range inside a run (see decode_pass)
+    constexpr int X2 = G32 ? 64 : 16;                         // byte distance of its second 16-byte piece
     const float* xs_run = xs_sm + 2 * t;
     for (int st = 0; st < n_stages; ++st) {
         cp_async_wait<DEPTH - 2>();   // this thread's copies of the stage have landed
@@ -400,55 +454,20 @@ FFAI_DEVINL void decode_pass_shared(const Params& p, const WarpJob<FUSED>& job, 
         const uint8_t* xstage = xring + use_xslot + xrd;
         use_slot = use_slot == (DEPTH - 1) * WS::STAGE ? 0u : use_slot + WS::STAGE;
         use_xslot = use_xslot == (DEPTH - 1) * X_STAGE ? 0u : use_xslot + X_STAGE;
+        uint4 xc[NT][2];
 #pragma unroll
-        for (int Gi = 0; Gi < STG_RUNS; ++Gi) {
-            uint4 xc[NT][2];
-            float2 sx[NT];
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                xc[j][0] = *reinterpret_cast<const uint4*>(xstage + j * 8 * X_PITCH + Gi * 128);
-                xc[j][1] = *reinterpret_cast<const uint4*>(xstage + j * 8 * X_PITCH + Gi * 128 + 16);
-                sx[j] = *reinterpret_cast<const float2*>(xs_run + Gi * 16 + 8 * j);
-            }
-#pragma unroll
-            for (int q = 0; q < NP; ++q) {
-                float sc[2], bm[2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint32_t v = *reinterpret_cast<const uint32_t*>(
-                        stage + WS::W_BYTES + q * (STG_RUNS * 64) + Gi * 64 + (g + 8 * h) * 4);
-                    const float s = __uint_as_float(v << 16), b = __uint_as_float(v & 0xFFFF0000u);
-                    sc[h] = s;
-                    bm[h] = fmaf(-128.0f, s, b);
-                }
-                uint32_t af[2][2][4];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint2 wv = *reinterpret_cast<const uint2*>(stage + (q * 16 + 8 * h) * W_PITCH + rd[Gi]);
-                    unpack_word_128r(wv.x, af[0][h], mask, expo);
-                    unpack_word_128r(wv.y, af[1][h], mask, expo);
-                }
-#pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    const uint32_t xb[2][4] = {{xc[j][0].x, xc[j][0].y, xc[j][0].z, xc[j][0].w},
-                                               {xc[j][1].x, xc[j][1].y, xc[j][1].z, xc[j][1].w}};
-                    float c[4];
-#pragma unroll
-                    for (int w = 0; w < 2; ++w)
-#pragma unroll
-                        for (int hp = 0; hp < 2; ++hp) {
-                            const uint32_t a[4] = {af[w][0][2 * hp], af[w][1][2 * hp], af[w][0][2 * hp + 1], af[w][1][2 * hp + 1]};
-                            if (w == 0 && hp == 0) mma_bf16_16816_zero(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
-                            else mma_bf16_16816(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
-                        }
-                    tot[j][q][0] = fmaf(sc[0], c[0], fmaf(bm[0], sx[j].x, tot[j][q][0]));
-                    tot[j][q][1] = fmaf(sc[0], c[1], fmaf(bm[0], sx[j].y, tot[j][q][1]));
-                    tot[j][q][2] = fmaf(sc[1], c[2], fmaf(bm[1], sx[j].x, tot[j][q][2]));
-                    tot[j][q][3] = fmaf(sc[1], c[3], fmaf(bm[1], sx[j].y, tot[j][q][3]));
-                }
-            }
+        for (int j = 0; j < NT; ++j) {
+            xc[j][0] = *reinterpret_cast<const uint4*>(xstage + j * 8 * X_PITCH);
+            xc[j][1] = *reinterpret_cast<const uint4*>(xstage + j * 8 * X_PITCH + X2);
         }
-        xs_run += STG_RUNS * 16;
+        compute_run<FUSED, NT, G32, 0>(stage, rd, xc, xs_run, mask, expo, g, tot);
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            xc[j][0] = *reinterpret_cast<const uint4*>(xstage + j * 8 * X_PITCH + 128);
+            xc[j][1] = *reinterpret_cast<const uint4*>(xstage + j * 8 * X_PITCH + 128 + X2);
+        }
+        compute_run<FUSED, NT, G32, 1>(stage, rd, xc, xs_run + 16 * SBW, mask, expo, g, tot);
+        xs_run += STG_RUNS * 16 * SBW;
     }
     cp_async_wait<0>();
 }
@@ -463,11 +482,12 @@ FFAI_DEVINL void decode_pass_shared(const Params& p, const WarpJob<FUSED>& job, 
 // fewer left runs the one-tile body whatever NT is.
 // Shared memory: the rings, then 16 floats per 64-run (rounded up to whole stages, plus one stage)
 // holding the 64-run sums of the pass's activation rows, transposed so a lane reads its two rows at once.
-template <bool FUSED, int NT, int KSPLIT>
+template <bool FUSED, int NT, int KSPLIT, bool G32>
 __global__ void __launch_bounds__(128, FFAI_DM_MIN_BLOCKS)
 grouped_mma_decode_kernel(const Params p) {
-    using WS = WarpStage<FUSED>;
+    using WS = WarpStage<FUSED, G32>;
     constexpr int NP = WS::NP;
+    constexpr int SBW = WS::SBW;
     constexpr int RBW = 4 / KSPLIT;  // 16-row blocks per CTA
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -486,7 +506,7 @@ grouped_mma_decode_kernel(const Params p) {
     uint8_t* wsm = smem + warp * WS::PER_WARP;
     uint8_t* xring = smem + WS::TOTAL;   // present only without a split reduction axis
     float* xs_sm = reinterpret_cast<float*>(smem + WS::TOTAL + (KSPLIT == 1 ? WS::X_RING : 0));
-    const int xs_runs = xs_sm_runs(n64);
+    const int xs_runs = xs_sm_runs(n64) * SBW;   // entries of the sums table: per 64-run, or per 32-run with group 32
 
     WarpJob<FUSED> job;
     job.n_runs = warp_active ? G1 - G0 : 0;
@@ -500,38 +520,54 @@ grouped_mma_decode_kernel(const Params p) {
             const size_t row = (size_t)e * p.N + (warp_active ? rb_row : 0) + (ridx & 15);
             job.wsrc[i] = reinterpret_cast<const uint8_t*>(base + row * wpr) + G0 * 32 + col * 16;
         }
-        const int sb_q = lane >> 3;  // projection whose scale words this lane copies (valid when < NP)
+        // scale words of a stage: per projection 8 (16 with group 32) 16-byte chunks; lane -> (projection, chunk)
+        constexpr int SB_CHUNKS = 8 * SBW;
+        const int sb_q = lane / SB_CHUNKS;  // projection whose scale words this lane copies (valid when < NP)
+        const int sb_c = lane % SB_CHUNKS;
         job.sb_lane = sb_q < NP;
         job.sbsrc = reinterpret_cast<const uint8_t*>(
-            ((sb_q == 1 && FUSED) ? p.sb2 : p.sb1) + (((size_t)e * (p.N / 16) + (warp_active ? rb : 0)) * n64 + G0) * 16) + (lane & 7) * 16;
+            ((sb_q == 1 && FUSED) ? p.sb2 : p.sb1) + (((size_t)e * (p.N / 16) + (warp_active ? rb : 0)) * (n64 * SBW) + G0 * SBW) * 16) + sb_c * 16;
         const uint32_t wsm_u32 = (uint32_t)__cvta_generic_to_shared(wsm);
         job.wdst = wsm_u32 + (lane >> 2) * W_PITCH + ((col ^ (((lane >> 3) & 1) << 1)) << 4);
-        job.sbdst = wsm_u32 + WS::W_BYTES + (sb_q & (NP - 1)) * (STG_RUNS * 64) + (lane & 7) * 16;
+        job.sbdst = wsm_u32 + WS::W_BYTES + (sb_q & (NP - 1)) * (STG_RUNS * 64 * SBW) + sb_c * 16;
     }
 
     for (int tok0 = 0; tok0 < cnt; tok0 += 8 * NT) {
         // 64-run sums of the pass's activation rows -> shared memory, [run][row]; rows past the end and
         // the padding runs read as zero
         __syncthreads();   // the previous pass (or the reduction below) is done with shared memory
+        // p.xsum holds sums of 32-runs (two per 64-run); p.xsum_parts sums of 16-runs (four per 64-run)
         for (int i = threadIdx.x; i < xs_runs * 16; i += 128) {
-            const int r = i / xs_runs, G = i - r * xs_runs;
+            const int r = i / xs_runs, R = i - r * xs_runs;   // R: 64-run index, or 32-run index with group 32
             float v = 0.0f;
-            if (tok0 + r < cnt && G < n64) {
+            if (tok0 + r < cnt && R < n64 * SBW) {
                 if (p.xsum_parts) {
-                    const float4 q4 = __ldg(reinterpret_cast<const float4*>(p.xsum_parts + (size_t)(row0 + tok0 + r) * (K / 16)) + G);
-                    v = ((q4.x + q4.y) + q4.z) + q4.w;
+                    const float* q = p.xsum_parts + (size_t)(row0 + tok0 + r) * (K / 16);
+                    if (G32) {
+                        const float2 q2 = __ldg(reinterpret_cast<const float2*>(q) + R);
+                        v = q2.x + q2.y;
+                    } else {
+                        const float4 q4 = __ldg(reinterpret_cast<const float4*>(q) + R);
+                        v = (q4.x + q4.y) + (q4.z + q4.w);
+                    }
                 } else {
-                    v = __ldg(p.xsum + src_row(p, row0 + tok0 + r) * p.xsum_pitch + G);
+                    const float* q = p.xsum + src_row(p, row0 + tok0 + r) * p.xsum_pitch;
+                    if (G32) {
+                        v = __ldg(q + R);
+                    } else {
+                        const float2 q2 = __ldg(reinterpret_cast<const float2*>(q) + R);
+                        v = q2.x + q2.y;
+                    }
                 }
             }
-            xs_sm[G * 16 + r] = v;
+            xs_sm[R * 16 + r] = v;
         }
         __syncthreads();
 
         float tot[NT][NP][4];
         if (NT == 1 || cnt - tok0 <= 8) {
-            if (KSPLIT == 1) decode_pass_shared<FUSED, 1>(p, job, wsm, xring, xs_sm, row0, cnt, tok0, n64, lane, tot);
-            else decode_pass<FUSED, 1>(p, job, wsm, xs_sm, row0, cnt, tok0, lane, tot);
+            if (KSPLIT == 1) decode_pass_shared<FUSED, 1, G32>(p, job, wsm, xring, xs_sm, row0, cnt, tok0, n64, lane, tot);
+            else decode_pass<FUSED, 1, G32>(p, job, wsm, xs_sm, row0, cnt, tok0, lane, tot);
 #pragma unroll
             for (int j = 1; j < NT; ++j)
 #pragma unroll
@@ -539,8 +575,8 @@ grouped_mma_decode_kernel(const Params p) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) tot[j][q][i] = 0.0f;
         } else {
-            if (KSPLIT == 1) decode_pass_shared<FUSED, NT>(p, job, wsm, xring, xs_sm, row0, cnt, tok0, n64, lane, tot);
-            else decode_pass<FUSED, NT>(p, job, wsm, xs_sm, row0, cnt, tok0, lane, tot);
+            if (KSPLIT == 1) decode_pass_shared<FUSED, NT, G32>(p, job, wsm, xring, xs_sm, row0, cnt, tok0, n64, lane, tot);
+            else decode_pass<FUSED, NT, G32>(p, job, wsm, xs_sm, row0, cnt, tok0, lane, tot);
         }
 
         if (KSPLIT > 1) {
@@ -615,26 +651,27 @@ grouped_mma_decode_kernel(const Params p) {
 }
 
 // Scale and bias of a stacked projection repacked for the streaming kernels:
-//   out[((e * N/16 + rb) * K/64 + G) * 16 + r] = scale | bias << 16   of row rb*16 + r, 64-run G
+//   out[((e * N/16 + rb) * K/run + G) * 16 + r] = scale | bias << 16   of row rb*16 + r, run G
+// (run = 64 for group sizes 64 and 128, 32 for group size 32)
 // so that the 16 rows of a block are contiguous per run and a warp's stage is one 128-byte copy.
 __global__ void repack_scale_bias_kernel(const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
-                                         uint32_t* __restrict__ out, int n_experts, int N, int K, int group_size) {
-    const size_t total = (size_t)n_experts * N * (K / 64);
+                                         uint32_t* __restrict__ out, int n_experts, int N, int K, int group_size, int run) {
+    const size_t total = (size_t)n_experts * N * (K / run);
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const int r = (int)(i & 15);
     const size_t rest = i >> 4;
-    const int n64 = K / 64;
-    const int G = (int)(rest % n64);
-    const size_t blk = rest / n64;  // e * N/16 + rb
+    const int nr = K / run;
+    const int G = (int)(rest % nr);
+    const size_t blk = rest / nr;  // e * N/16 + rb
     const size_t row = blk * 16 + r;  // e * N + rb*16 + r
     const int gpr = K / group_size;
-    const size_t src = row * gpr + (size_t)(G * 64 / group_size);
+    const size_t src = row * gpr + (size_t)(G * run / group_size);
     out[i] = (uint32_t)scales[src] | ((uint32_t)biases[src] << 16);
 }
 
 // Gather rows into expert-sorted order with the 8-run permutation, and write the sum of every
-// 64-run (fp32).  One warp per output row.  ids nullable (identity), id_div as in Ops.gather use.
+// 32-run (fp32; a 64-run's sum is the sum of its two halves).  One warp per output row.  ids nullable (identity), id_div as in Ops.gather use.
 __global__ void gather_perm8_sum64_kernel(const uint16_t* __restrict__ table, const uint32_t* __restrict__ ids,
                                           int id_div, uint16_t* __restrict__ out, float* __restrict__ sums,
                                           int n_rows, int row_len, int sum_pitch) {
@@ -660,11 +697,10 @@ __global__ void gather_perm8_sum64_kernel(const uint16_t* __restrict__ table, co
             part = ((bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y))) +
                    ((bf16lo(v.z) + bf16hi(v.z)) + (bf16lo(v.w) + bf16hi(v.w)));
         }
-        // 8 consecutive lanes hold one 64-run: fixed-shape tree over them
+        // 4 consecutive lanes hold one 32-run: fixed-shape tree over them
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
-        part += __shfl_xor_sync(0xFFFFFFFFu, part, 4);
-        if ((lane & 7) == 0 && i < chunks) sums[(size_t)row * sum_pitch + (i >> 3)] = part;
+        if ((lane & 3) == 0 && i < chunks) sums[(size_t)row * sum_pitch + (i >> 2)] = part;
     }
 }
 
@@ -688,8 +724,7 @@ __global__ void sum64_rows_kernel(const uint16_t* __restrict__ rows, float* __re
         }
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
         part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
-        part += __shfl_xor_sync(0xFFFFFFFFu, part, 4);
-        if ((lane & 7) == 0 && i < chunks) sums[(size_t)row * sum_pitch + (i >> 3)] = part;
+        if ((lane & 3) == 0 && i < chunks) sums[(size_t)row * sum_pitch + (i >> 2)] = part;
     }
 }
 

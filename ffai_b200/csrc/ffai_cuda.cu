@@ -366,10 +366,10 @@ int launch_plan(const uint32_t* indices, int n_rows, int E, uint32_t* counts, ui
     return cudaGetLastError() == cudaSuccess ? 3 : -1;
 }
 
-template <bool FUSED, int NT, int KSPLIT>
+template <bool FUSED, int NT, int KSPLIT, bool G32>
 void launch_mma_decode_k(const dmma::Params& p, int n_experts, cudaStream_t st) {
-    using WS = dmma::WarpStage<FUSED>;
-    auto k = dmma::grouped_mma_decode_kernel<FUSED, NT, KSPLIT>;
+    using WS = dmma::WarpStage<FUSED, G32>;
+    auto k = dmma::grouped_mma_decode_kernel<FUSED, NT, KSPLIT, G32>;
     const int smem = WS::smem_bytes(p.K / 64, KSPLIT);
     static int attr_smem = 0;
     if (smem > attr_smem) {
@@ -381,18 +381,25 @@ void launch_mma_decode_k(const dmma::Params& p, int n_experts, cudaStream_t st) 
     k<<<grid, 128, smem, st>>>(p);
 }
 
-// nt: 8-row activation tiles per pass (1 or 2); ksplit: slices of the reduction axis per 16-row block (1, 2, 4)
+template <bool FUSED, bool G32>
+void launch_mma_decode_g(const dmma::Params& p, int n_experts, int nt, int ksplit, cudaStream_t st) {
+    if (nt == 2) {
+        if (ksplit == 4) launch_mma_decode_k<FUSED, 2, 4, G32>(p, n_experts, st);
+        else if (ksplit == 2) launch_mma_decode_k<FUSED, 2, 2, G32>(p, n_experts, st);
+        else launch_mma_decode_k<FUSED, 2, 1, G32>(p, n_experts, st);
+    } else {
+        if (ksplit == 4) launch_mma_decode_k<FUSED, 1, 4, G32>(p, n_experts, st);
+        else if (ksplit == 2) launch_mma_decode_k<FUSED, 1, 2, G32>(p, n_experts, st);
+        else launch_mma_decode_k<FUSED, 1, 1, G32>(p, n_experts, st);
+    }
+}
+
+// nt: 8-row activation tiles per pass (1 or 2); ksplit: slices of the reduction axis per 16-row block (1, 2, 4);
+// the group size (p.group_size) picks the 32-run variant
 template <bool FUSED>
 void launch_mma_decode(const dmma::Params& p, int n_experts, int nt, int ksplit, cudaStream_t st) {
-    if (nt == 2) {
-        if (ksplit == 4) launch_mma_decode_k<FUSED, 2, 4>(p, n_experts, st);
-        else if (ksplit == 2) launch_mma_decode_k<FUSED, 2, 2>(p, n_experts, st);
-        else launch_mma_decode_k<FUSED, 2, 1>(p, n_experts, st);
-    } else {
-        if (ksplit == 4) launch_mma_decode_k<FUSED, 1, 4>(p, n_experts, st);
-        else if (ksplit == 2) launch_mma_decode_k<FUSED, 1, 2>(p, n_experts, st);
-        else launch_mma_decode_k<FUSED, 1, 1>(p, n_experts, st);
-    }
+    if (p.group_size == 32) launch_mma_decode_g<FUSED, true>(p, n_experts, nt, ksplit, st);
+    else launch_mma_decode_g<FUSED, false>(p, n_experts, nt, ksplit, st);
 }
 
 // dense [1,H] projection per token (shared-expert gate stored as f32 / bf16)
@@ -661,12 +668,12 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
         if ((rc = ws_alloc(L, &L->xg, Mp * H))) return rc;
         if ((rc = ws_alloc(L, &L->inner_bf, Mp * I))) return rc;
         // 64-run sums, row pitch rounded up to 4 floats (16-byte rows for cp.async), + one spare row
-        if ((rc = ws_alloc(L, &L->xsum, (Mx + 1) * (size_t)((H / 64 + 3) & ~3)))) return rc;
-        if ((rc = ws_alloc(L, &L->inner_sum, (Mx + 1) * (size_t)((I / 64 + 3) & ~3)))) return rc;
+        if ((rc = ws_alloc(L, &L->xsum, (Mx + 1) * (size_t)((H / 32 + 3) & ~3)))) return rc;
+        if ((rc = ws_alloc(L, &L->inner_sum, (Mx + 1) * (size_t)((I / 32 + 3) & ~3)))) return rc;
         if ((rc = ws_alloc(L, &L->inner_parts, (Mx + 1) * (size_t)(I / 16)))) return rc;
         if ((rc = ws_alloc(L, &L->x_tok, (T + 1) * H))) return rc;
-        if ((rc = ws_alloc(L, &L->xsum_tok, (T + 1) * (size_t)((H / 64 + 3) & ~3)))) return rc;
-        L->mma_ok = c.expert_bits == 4 && (c.expert_group_size == 64 || c.expert_group_size == 128);
+        if ((rc = ws_alloc(L, &L->xsum_tok, (T + 1) * (size_t)((H / 32 + 3) & ~3)))) return rc;
+        L->mma_ok = c.expert_bits == 4;   // every group size the format allows (32, 64, 128)
         if (want_tc) {
             if (world == 1 && (rc = ws_alloc(L, &L->y_bf, M * H))) return rc;
             if ((rc = ws_alloc(L, &L->tile_offsets, E + 1))) return rc;
@@ -793,12 +800,13 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
     L->sb_gate = L->sb_up = L->sb_down = nullptr;
     if (L->mma_ok) {
         auto repack = [&](const ffai_qproj& q, int N, int K, uint32_t** out) -> int {
-            const size_t total = (size_t)El * N * (K / 64);
+            const int run = c.expert_group_size == 32 ? 32 : 64;
+            const size_t total = (size_t)El * N * (K / run);
             void* p = nullptr;
             CUDA_TRY(L, cudaMalloc(&p, total * 4));
             L->owned_weights.push_back(p);
             *out = static_cast<uint32_t*>(p);
-            dmma::repack_scale_bias_kernel<<<(unsigned)((total + 255) / 256), 256>>>(q.scales, q.biases, *out, El, N, K, c.expert_group_size);
+            dmma::repack_scale_bias_kernel<<<(unsigned)((total + 255) / 256), 256>>>(q.scales, q.biases, *out, El, N, K, c.expert_group_size, run);
             CUDA_TRY(L, cudaGetLastError());
             return FFAI_OK;
         };
@@ -1119,7 +1127,7 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
     }
     if (use_mma) {
         using namespace dmma;
-        const int xp_h = (H / 64 + 3) & ~3, xp_i = (I / 64 + 3) & ~3;
+        const int xp_h = (H / 32 + 3) & ~3, xp_i = (I / 32 + 3) & ~3;
         if (L->ep_rows_dev)
             ep::sum64_rows_counted_kernel<<<(unsigned)((L->mx_rows + 7) / 8), 256, 0, st>>>(L->xg, L->xsum, L->ep_rows_dev, H, xp_h);
         else
@@ -1159,7 +1167,7 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         stage_begin(L, ST_GATE_UP, st);
         p.scales = L->w.gate_proj.scales; p.biases = L->w.gate_proj.biases; p.row_bias = L->w.gate_proj.row_bias;
         p.scales2 = L->w.up_proj.scales; p.biases2 = L->w.up_proj.biases; p.row_bias2 = L->w.up_proj.row_bias;
-        p.sb = L->sb_gate; p.sb2 = L->sb_up;
+        if (c.expert_group_size != 32) { p.sb = L->sb_gate; p.sb2 = L->sb_up; }
         p.n_out = I; p.K = H; p.m_tiles = (I + BN / 2 - 1) / (BN / 2);
         p.out = L->inner_bf; p.out_ld = I; p.out_permute8 = 1;
         if (tc_gate_up(L, p, st))
@@ -1168,7 +1176,7 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         stage_begin(L, ST_DOWN, st);
         p.scales = L->w.down_proj.scales; p.biases = L->w.down_proj.biases; p.row_bias = L->w.down_proj.row_bias;
         p.scales2 = nullptr; p.biases2 = nullptr; p.row_bias2 = nullptr;
-        p.sb = L->sb_down; p.sb2 = nullptr;
+        p.sb = c.expert_group_size != 32 ? L->sb_down : nullptr; p.sb2 = nullptr;
         p.n_out = H; p.K = I; p.m_tiles = (H + BN - 1) / BN;
         p.out = L->y; p.out_ld = H; p.out_permute8 = 0;
         if (L->ep_peer_on) p.out = L->ep_y_bf;
@@ -1327,7 +1335,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     // 4-bit streaming kernels read per-token rows through the permutation: the rows (8-run permuted) and their
     // 64-run sums are written once per token, by the router kernel when it is the small-batch one
     uint16_t* tok_x = (L->mma_ok && c.ep_world <= 1) ? L->x_tok : nullptr;
-    const int xp_tok = (H / 64 + 3) & ~3;
+    const int xp_tok = (H / 32 + 3) & ~3;
     bool tok_rows_done = false;
     if (T >= 96) {
         int nr = launch_router_batched(rp, x, T, L->indices, L->rweights, L->logits, L->router_partials,
@@ -1379,7 +1387,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     if (mma_experts) {
         using namespace dmma;
         stage_begin(L, ST_GATHER, st);
-        const int xp_h = (H / 64 + 3) & ~3, xp_i = (I / 64 + 3) & ~3;
+        const int xp_h = (H / 32 + 3) & ~3, xp_i = (I / 32 + 3) & ~3;
         if (!tok_rows_done) {   // one row per token (not per routed row); the kernels follow the permutation themselves
             gather_perm8_sum64_kernel<<<(T + 7) / 8, 256, 0, st>>>(x, nullptr, 1, L->x_tok, L->xsum_tok, T, H, xp_h);
             L->launches += 1;
@@ -1437,7 +1445,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         stage_begin(L, ST_GATE_UP, st);
         p.scales = L->w.gate_proj.scales; p.biases = L->w.gate_proj.biases; p.row_bias = L->w.gate_proj.row_bias;
         p.scales2 = L->w.up_proj.scales; p.biases2 = L->w.up_proj.biases; p.row_bias2 = L->w.up_proj.row_bias;
-        p.sb = L->sb_gate; p.sb2 = L->sb_up;
+        if (c.expert_group_size != 32) { p.sb = L->sb_gate; p.sb2 = L->sb_up; }
         p.n_out = I; p.K = H; p.m_tiles = (I + BN / 2 - 1) / (BN / 2);
         p.out = L->inner_bf; p.out_ld = I; p.out_permute8 = 1;
         if (tc_gate_up(L, p, st))
@@ -1449,7 +1457,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         p.timeline = nullptr;
         p.scales = L->w.down_proj.scales; p.biases = L->w.down_proj.biases; p.row_bias = L->w.down_proj.row_bias;
         p.scales2 = nullptr; p.biases2 = nullptr; p.row_bias2 = nullptr;
-        p.sb = L->sb_down; p.sb2 = nullptr;
+        p.sb = c.expert_group_size != 32 ? L->sb_down : nullptr; p.sb2 = nullptr;
         p.n_out = H; p.K = I; p.m_tiles = (H + BN - 1) / BN;
         p.out = L->y_bf; p.out_ld = H; p.out_permute8 = 0;
         if (tc_down<uint16_t>(L, p, st))

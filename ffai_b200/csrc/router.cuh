@@ -227,7 +227,7 @@ router_token_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens
 // (expert, chunk) pair from shared memory in the fixed order, one thread per expert adds the chunk
 // sums, and the last block to finish a token (a ticket counter that resets itself) routes it.
 // With a destination for it, block 0 of a token also writes the token's row in the order the 4-bit
-// expert kernels read (every 8-run as 0,4,1,5,2,6,3,7) and the fp32 sum of every 64-run, from the
+// expert kernels read (every 8-run as 0,4,1,5,2,6,3,7) and the fp32 sum of every 32-run, from the
 // copy it staged anyway.
 // With a plan destination, the block that routes the last token of the batch (a second ticket, in
 // the last slot of the ticket array) also builds the dispatch plan, which saves a launch per step.
@@ -277,8 +277,8 @@ router_rows_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
     __syncthreads();
 
     if (x_perm8 && blockIdx.x == 0) {
-        // 16-byte piece i of the row (8 values): permuted copy + its share of the 64-run sum; the eight
-        // pieces of a run sit in eight consecutive lanes
+        // 16-byte piece i of the row (8 values): permuted copy + its share of the 32-run sum; the four
+        // pieces of a run sit in four consecutive lanes
         uint4* d = reinterpret_cast<uint4*>(x_perm8 + (size_t)t * H);
         for (int i0 = 0; i0 < nchunks * 8; i0 += blockDim.x) {
             const int i = i0 + threadIdx.x;
@@ -297,8 +297,7 @@ router_rows_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
             }
             part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
             part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
-            part += __shfl_xor_sync(0xFFFFFFFFu, part, 4);
-            if ((threadIdx.x & 7) == 0 && i < nchunks * 8) x_sum64[(size_t)t * sum_pitch + (i >> 3)] = part;
+            if ((threadIdx.x & 3) == 0 && i < nchunks * 8) x_sum64[(size_t)t * sum_pitch + (i >> 2)] = part;
         }
     }
 

@@ -325,6 +325,21 @@ def test_mma_group_size_128_and_many_rows_per_expert(oracle_mod):
     run_and_check(oracle_mod, synth.LayerSpec("mma_small", 64, 64, 4, 2), 5, path=MMA)
 
 
+@pytest.mark.parametrize("T", [1, 4, 8, 20, 64])
+def test_mma_group_size_32_gptoss_as_transcoded(oracle_mod, T):
+    """GPT-OSS experts as the MXFP4 transcode leaves them: 4-bit, group 32, row biases.  All three
+    reduction splits (1, 4 and 8 tokens give split 4 / 2 / 1) and both pass widths."""
+    spec = synth.cfg2_gptoss().with_(name="gptoss_gs32", expert_group_size=32, expert_row_bias=1)
+    run_and_check(oracle_mod, spec, T, path=MMA)
+    run_and_check(oracle_mod, spec, T)                      # the automatic choice takes the same kernels
+
+
+def test_mma_group_size_32_small_shapes(oracle_mod):
+    run_and_check(oracle_mod, synth.LayerSpec("mma_gs32", 512, 256, 8, 2, expert_group_size=32), 70, path=MMA)
+    run_and_check(oracle_mod, synth.LayerSpec("mma_gs32_small", 64, 64, 4, 2, expert_group_size=32), 5, path=MMA)
+    run_and_check(oracle_mod, synth.LayerSpec("mma_gs32_odd_runs", 320, 192, 4, 2, expert_group_size=32), 11, path=MMA)
+
+
 def test_auto_path_is_deterministic_and_matches_forced_paths(oracle_mod):
     spec = synth.cfg2_gptoss()
     host = synth.make_layer(spec, 0)
