@@ -171,6 +171,7 @@ SIGNATURES = {
     "ffai_op_moe_gather_dequant_gemm": (C.c_int, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "ffai_op_glu_activation": (C.c_int, [_P, _P, _P, C.c_int64, _I, C.c_float, C.c_float, _P]),
     "ffai_op_moe_unpermute": (C.c_int, [_P, _P, _P, _P, _I, _I, _I, _P]),
+    "ffai_op_add_rmsnorm": (C.c_int, [_P, _P, _P, C.c_float, _I, _I, _P, _P, _P]),
     "ffai_op_mxfp4_to_affine_int4": (C.c_int, [_P, _P, C.c_int64, _P, _P, _P, _P]),
     "ffai_op_affine_quantize": (C.c_int, [_P, C.c_int64, _I, _I, _I, _P, _P, _P, _P]),
     "ffai_op_sigmoid_scalar_fma": (C.c_int, [_P, _P, _P, _P, _P, _I, _I, _P]),

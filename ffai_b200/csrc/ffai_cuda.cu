@@ -1822,6 +1822,16 @@ extern "C" FFAI_API int ffai_op_moe_unpermute(const uint16_t* expert_out, const 
     return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
 }
 
+extern "C" FFAI_API int ffai_op_add_rmsnorm(const uint16_t* a, const uint16_t* b, const uint16_t* weight, float eps,
+                                            int32_t n_rows, int32_t n, uint16_t* residual_out, uint16_t* normed_out, void* stream) {
+    if (!a || !b || !weight || !residual_out || !normed_out || n_rows <= 0 || n <= 0 || n % 4) return FFAI_ERR_INVALID_ARG;
+    if (!aligned16(a) || !aligned16(b) || !aligned16(residual_out) || !aligned16(normed_out) || (n % 8)) return FFAI_ERR_INVALID_ARG;
+    int rc;
+    if ((rc = need_device())) return rc;
+    prep::add_rmsnorm_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(a, b, weight, eps, n, residual_out, normed_out);
+    return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
+}
+
 extern "C" FFAI_API int ffai_op_mxfp4_to_affine_int4(const uint32_t* packed, const uint8_t* e8m0, int64_t n_groups,
                                                      uint32_t* out_weight, uint16_t* out_scales, uint16_t* out_biases,
                                                      void* stream) {

@@ -125,5 +125,46 @@ affine_quantize_kernel(const uint16_t* __restrict__ w, long n_groups, int group_
     }
 }
 
+// The step in front of the block: residual = a + b, normed = RMSNorm(a + b) * weight, one pass
+// (FFAI Ops.addAndRmsNorm, Ops.swift:658-760; GPT-OSS calls it right before the MoE block,
+// GPTOSSText.swift:700-716).  bf16 in and out; the sum, the mean of squares and the scaling are fp32
+// and the norm is taken from the unrounded sum, as in the reference's CPU check
+// (OpsTests.swift:1042-1052).  One block per row; a thread owns 4 consecutive positions per step.
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, const uint16_t* __restrict__ weight,
+                   float eps, int n, uint16_t* __restrict__ residual_out, uint16_t* __restrict__ normed_out) {
+    const size_t row = blockIdx.x;
+    const uint16_t* ar = a + row * n;
+    const uint16_t* br = b + row * n;
+    __shared__ float red[8];
+    float ssq = 0.0f;
+    for (int h = threadIdx.x * 4; h < n; h += blockDim.x * 4) {
+        const uint2 ua = *reinterpret_cast<const uint2*>(ar + h), ub = *reinterpret_cast<const uint2*>(br + h);
+        const float s0 = bf16lo(ua.x) + bf16lo(ub.x), s1 = bf16hi(ua.x) + bf16hi(ub.x);
+        const float s2 = bf16lo(ua.y) + bf16lo(ub.y), s3 = bf16hi(ua.y) + bf16hi(ub.y);
+        ssq += (s0 * s0 + s1 * s1) + (s2 * s2 + s3 * s3);
+    }
+    ssq = warp_sum(ssq);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ssq;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += red[w];
+    const float inv_rms = 1.0f / sqrtf(total / (float)n + eps);
+    for (int h = threadIdx.x * 4; h < n; h += blockDim.x * 4) {
+        const uint2 ua = *reinterpret_cast<const uint2*>(ar + h), ub = *reinterpret_cast<const uint2*>(br + h);
+        const uint2 uw = *reinterpret_cast<const uint2*>(weight + h);
+        const float s0 = bf16lo(ua.x) + bf16lo(ub.x), s1 = bf16hi(ua.x) + bf16hi(ub.x);
+        const float s2 = bf16lo(ua.y) + bf16lo(ub.y), s3 = bf16hi(ua.y) + bf16hi(ub.y);
+        uint2 r, o;
+        r.x = (uint32_t)f32_to_bf16_bits(s0) | ((uint32_t)f32_to_bf16_bits(s1) << 16);
+        r.y = (uint32_t)f32_to_bf16_bits(s2) | ((uint32_t)f32_to_bf16_bits(s3) << 16);
+        o.x = (uint32_t)f32_to_bf16_bits(s0 * inv_rms * bf16lo(uw.x)) | ((uint32_t)f32_to_bf16_bits(s1 * inv_rms * bf16hi(uw.x)) << 16);
+        o.y = (uint32_t)f32_to_bf16_bits(s2 * inv_rms * bf16lo(uw.y)) | ((uint32_t)f32_to_bf16_bits(s3 * inv_rms * bf16hi(uw.y)) << 16);
+        *reinterpret_cast<uint2*>(residual_out + row * n + h) = r;
+        *reinterpret_cast<uint2*>(normed_out + row * n + h) = o;
+    }
+}
+
 }  // namespace prep
 }  // namespace ffai

@@ -370,6 +370,11 @@ FFAI_API int ffai_op_moe_unpermute(const uint16_t* expert_out, const uint32_t* i
  *   biases bf16, one per group.  Bit-identical to the host version.
  * ffai_op_affine_quantize: MLX affine quantization of a [rows, in_dim] bf16 matrix into the packed
  *   layout this library reads (QuantizedOps.swift:229-388); bits in {2,3,4,5,6,8}, gs in {32,64,128}. */
+/* The step in front of the block (Ops.addAndRmsNorm, Ops.swift:658-760; called right before the MoE
+ * block in GPTOSSText.swift:700-716): residual_out = a + b, normed_out = RMSNorm(a + b) * weight, rows of
+ * n bf16 (n a multiple of 8; no upper limit, unlike the reference's 4096), fp32 arithmetic inside. */
+FFAI_API int ffai_op_add_rmsnorm(const uint16_t* a, const uint16_t* b, const uint16_t* weight, float eps,
+                                 int32_t n_rows, int32_t n, uint16_t* residual_out, uint16_t* normed_out, void* stream);
 FFAI_API int ffai_op_mxfp4_to_affine_int4(const uint32_t* packed, const uint8_t* e8m0, int64_t n_groups,
                                           uint32_t* out_weight, uint16_t* out_scales, uint16_t* out_biases,
                                           void* stream);

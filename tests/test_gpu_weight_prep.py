@@ -83,3 +83,23 @@ def test_affine_quantizer_bit_exact(ffai_lib, oracle_mod, bits, gs):
 def test_weight_prep_rejects_bad_arguments(ffai_lib):
     assert ffai_lib.ffai_op_mxfp4_to_affine_int4(None, None, 4, None, None, None, None) == capi.FFAI_ERR_INVALID_ARG
     assert ffai_lib.ffai_op_affine_quantize(None, 1, 64, 4, 64, None, None, None, None) == capi.FFAI_ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize("rows,n", [(1, 2880), (2, 128), (7, 2048), (64, 5376)])
+def test_add_rmsnorm_matches_oracle(ffai_lib, oracle_mod, rows, n):
+    import torch
+    rng = np.random.default_rng(rows * 31 + n)
+    a = synth.f32_to_bf16(rng.standard_normal((rows, n)).astype(np.float32) * 3)
+    b = synth.f32_to_bf16(rng.standard_normal((rows, n)).astype(np.float32))
+    w = synth.f32_to_bf16((1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32))
+    da, db, dw = to_dev(a.reshape(-1)), to_dev(b.reshape(-1)), to_dev(w)
+    res = torch.zeros(rows * n, dtype=torch.int16, device="cuda")
+    nrm = torch.zeros(rows * n, dtype=torch.int16, device="cuda")
+    capi.check(ffai_lib.ffai_op_add_rmsnorm(da.data_ptr(), db.data_ptr(), dw.data_ptr(), 1e-6, rows, n, res.data_ptr(), nrm.data_ptr(), None),
+               "ffai_op_add_rmsnorm")
+    torch.cuda.synchronize()
+    ores, onrm, onf = oracle_mod.add_rmsnorm(a, b, w, 1e-6)
+    assert np.array_equal(from_dev(res, np.uint16).reshape(rows, n), ores)          # the sum is exact in fp32: same bits
+    got = synth.bf16_to_f32(from_dev(nrm, np.uint16)).reshape(rows, n)
+    # the sum of squares is reduced in another order: at most one bf16 step from the fp32 oracle value
+    assert np.all(np.abs(got - onf) <= 2.0 ** -7 * np.abs(onf) + 1e-6)

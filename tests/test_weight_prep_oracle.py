@@ -116,3 +116,19 @@ def test_quantizer_flat_and_zero_groups(oracle_mod):
     q = np.stack([synth.unpack_bits(packed[r], 4, 64) for r in range(2)]).astype(np.float64)
     deq = q * synth.bf16_to_f32(sc).astype(np.float64) + synth.bf16_to_f32(bi).astype(np.float64)
     assert np.all(np.isfinite(deq)) and np.allclose(deq, w, atol=1e-6)
+
+
+def test_add_rmsnorm_oracle_on_the_reference_pattern(oracle_mod):
+    """The inputs of the reference's own check (OpsTests.swift:1017-1019: index patterns, not data), in bf16."""
+    rows, n, eps = 2, 128, 1e-6
+    i = np.arange(rows * n)
+    a = ((i % 19) - 9).astype(np.float32) * np.float32(0.31)
+    b = ((i % 13) - 6).astype(np.float32) * np.float32(0.17)
+    w = (1.0 + (np.arange(n) % 7) * 0.05).astype(np.float32)
+    ab, bb, wb = (synth.f32_to_bf16(v) for v in (a.reshape(rows, n), b.reshape(rows, n), w))
+    res, nrm, nf = oracle_mod.add_rmsnorm(ab, bb, wb, eps)
+    s = synth.bf16_to_f32(ab).astype(np.float64) + synth.bf16_to_f32(bb).astype(np.float64)
+    ref = s / np.sqrt((s * s).mean(axis=1, keepdims=True) + eps) * synth.bf16_to_f32(wb).astype(np.float64)
+    assert np.abs(synth.bf16_to_f32(res) - s).max() < 1e-3 * 32      # the reference's 1e-3, widened for bf16 storage
+    assert np.abs(nf - ref).max() < 1e-5
+    assert np.abs(synth.bf16_to_f32(nrm) - ref).max() < 1e-2
