@@ -75,7 +75,8 @@ class MoEConfig(C.Structure):
         ("ep_rank", C.c_int32),
         ("ep_world", C.c_int32),
         ("prefill_weight_cache", C.c_int32),
-        ("reserved", C.c_int32 * 7),
+        ("router_logit_scale", C.c_float),
+        ("reserved", C.c_int32 * 6),
     ]
 
     def __init__(self, **kw):
@@ -114,6 +115,7 @@ class MoEWeights(C.Structure):
         ("shared_up_proj", QProj),
         ("shared_down_proj", QProj),
         ("shared_gate", Linear),
+        ("router_per_expert_scale", C.c_void_p),
     ]
 
     def __init__(self, **kw):
@@ -146,6 +148,10 @@ SIGNATURES = {
     "ffai_moe_destroy": (C.c_int, [_P]),
     "ffai_moe_last_error": (C.c_char_p, [_P]),
     "ffai_moe_forward": (C.c_int, [_P, _P, _I, _P, _P, C.POINTER(MoEDebug), _P]),
+    "ffai_moe_forward_split": (C.c_int, [_P, _P, _P, _I, _P, _P, _P, _P]),
+    "ffai_moe_forward_host_split": (C.c_int, [_P, _P, _P, _I, _P, _P, _P]),
+    "ffai_moe_forward_split": (C.c_int, [_P, _P, _P, _I, _P, _P, C.POINTER(MoEDebug), _P]),
+    "ffai_moe_forward_host_split": (C.c_int, [_P, _P, _P, _I, _P, _P, C.POINTER(MoEDebug)]),
     "ffai_moe_forward_host": (C.c_int, [_P, _P, _I, _P, _P, C.POINTER(MoEDebug)]),
     "ffai_moe_set_nccl_comm": (C.c_int, [_P, _P]),
     "ffai_moe_ep_export": (C.c_int, [_P, _P]),

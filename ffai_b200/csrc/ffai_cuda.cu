@@ -70,6 +70,8 @@ struct ffai_moe_layer {
     float* xsum_tok = nullptr;       // [T, H/64 rounded up to 4] their 64-run sums
     float* inner_parts = nullptr;    // [M, I/16]  16-run sums of inner rows, written by the gate/up streaming kernel
     float* inner_sum = nullptr;      // [M, I/64]  64-run sums of inner rows
+    const uint16_t* router_x = nullptr;  // set for the duration of a split forward: the router's own input rows
+    uint16_t* dev_xr = nullptr;          // host-buffer entry point: device copy of the router input
     bool mma_ok = false;             // register-streaming decode kernels usable (4-bit, group 64/128)
     uint32_t* sb_gate = nullptr;     // repacked (scale | bias << 16) words of the expert projections
     uint32_t* sb_up = nullptr;
@@ -713,6 +715,8 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
         if (!w->router_expert_bias) return fail(L, FFAI_ERR_INVALID_ARG, "router_expert_bias set but pointer is null");
         if ((rc = upload(L, w->router_expert_bias, (size_t)c.n_experts * 4, loc, (const void**)&L->w.router_expert_bias))) return rc;
     }
+    if (w->router_per_expert_scale)
+        if ((rc = upload(L, w->router_per_expert_scale, (size_t)c.n_experts * 4, loc, (const void**)&L->w.router_per_expert_scale))) return rc;
     const int El = L->e_local;
     if ((rc = upload_qproj(L, w->gate_proj, El, c.intermediate, c.hidden, c.expert_bits, c.expert_group_size, loc, &L->w.gate_proj, "gate_proj"))) return rc;
     if ((rc = upload_qproj(L, w->up_proj, El, c.intermediate, c.hidden, c.expert_bits, c.expert_group_size, loc, &L->w.up_proj, "up_proj"))) return rc;
@@ -1035,6 +1039,8 @@ RouterParams router_params(const ffai_moe_layer* L) {
     p.gating_mode = c.gating_mode;
     p.norm_topk_prob = c.norm_topk_prob;
     p.logits_bf16 = c.router_logits_bf16;
+    p.logit_scale = c.router_logit_scale != 0.0f ? c.router_logit_scale : 1.0f;
+    p.per_expert_scale = L->w.router_per_expert_scale;
     return p;
 }
 
@@ -1334,21 +1340,22 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     bool plan_done = false;
     // 4-bit streaming kernels read per-token rows through the permutation: the rows (8-run permuted) and their
     // 64-run sums are written once per token, by the router kernel when it is the small-batch one
-    uint16_t* tok_x = (L->mma_ok && c.ep_world <= 1) ? L->x_tok : nullptr;
+    const uint16_t* xr = L->router_x ? L->router_x : x;   // the router's input rows (its own under a split forward)
+    uint16_t* tok_x = (L->mma_ok && c.ep_world <= 1 && xr == x) ? L->x_tok : nullptr;
     const int xp_tok = (H / 32 + 3) & ~3;
     bool tok_rows_done = false;
     if (T >= 96) {
-        int nr = launch_router_batched(rp, x, T, L->indices, L->rweights, L->logits, L->router_partials,
+        int nr = launch_router_batched(rp, xr, T, L->indices, L->rweights, L->logits, L->router_partials,
                                        L->router_partials_cap, L->n_sms, st);
         if (nr < 0) return fail(L, FFAI_ERR_CUDA, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += nr;
-    } else if ((rp.kind == FFAI_LINEAR_F32 && launch_router_rows<1>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, fused_plan, tok_x, L->xsum_tok, xp_tok, st) == 0) ||
-               (rp.kind == FFAI_LINEAR_BF16 && launch_router_rows<2>(rp, x, T, L->indices, L->rweights, L->logits, L->tickets, fused_plan, tok_x, L->xsum_tok, xp_tok, st) == 0)) {
+    } else if ((rp.kind == FFAI_LINEAR_F32 && launch_router_rows<1>(rp, xr, T, L->indices, L->rweights, L->logits, L->tickets, fused_plan, tok_x, L->xsum_tok, xp_tok, st) == 0) ||
+               (rp.kind == FFAI_LINEAR_BF16 && launch_router_rows<2>(rp, xr, T, L->indices, L->rweights, L->logits, L->tickets, fused_plan, tok_x, L->xsum_tok, xp_tok, st) == 0)) {
         L->launches += 1;
         plan_done = fused_plan.perm != nullptr;
         tok_rows_done = tok_x != nullptr;
     } else {
-        if ((rc = launch_router(rp, x, T, L->indices, L->rweights, L->logits, st)))
+        if ((rc = launch_router(rp, xr, T, L->indices, L->rweights, L->logits, st)))
             return fail(L, rc, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += 1;
     }
@@ -1590,6 +1597,33 @@ extern "C" FFAI_API int ffai_moe_forward(ffai_moe_layer* L, const uint16_t* x, i
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if ((rc = forward_device(L, x, T, out, residual, st))) return rc;
     return copy_debug(L, debug, T, st, cudaMemcpyDeviceToDevice);
+}
+
+extern "C" FFAI_API int ffai_moe_forward_split(ffai_moe_layer* L, const uint16_t* x, const uint16_t* x_router, int32_t T,
+                                               uint16_t* out, const uint16_t* residual, const ffai_moe_debug* debug, void* stream) {
+    if (!L) return FFAI_ERR_INVALID_ARG;
+    if (x_router && !aligned16(x_router)) return fail(L, FFAI_ERR_INVALID_ARG, "x_router must be 16-byte aligned");
+    L->router_x = x_router;
+    const int rc = ffai_moe_forward(L, x, T, out, residual, debug, stream);
+    L->router_x = nullptr;
+    return rc;
+}
+
+extern "C" FFAI_API int ffai_moe_forward_host(ffai_moe_layer* L, const uint16_t* x, int32_t T, uint16_t* out,
+                                              const uint16_t* residual, const ffai_moe_debug* debug);
+
+extern "C" FFAI_API int ffai_moe_forward_host_split(ffai_moe_layer* L, const uint16_t* x, const uint16_t* x_router, int32_t T,
+                                                    uint16_t* out, const uint16_t* residual, const ffai_moe_debug* debug) {
+    int rc = check_forward_args(L, x, T, out);
+    if (rc) return rc;
+    if (!x_router || T == 0) return ffai_moe_forward_host(L, x, T, out, residual, debug);
+    CUDA_TRY(L, cudaSetDevice(L->device));
+    if (!L->dev_xr && (rc = ws_alloc(L, &L->dev_xr, (size_t)L->cfg.max_tokens * L->cfg.hidden))) return rc;
+    CUDA_TRY(L, cudaMemcpy(L->dev_xr, x_router, (size_t)T * L->cfg.hidden * 2, cudaMemcpyHostToDevice));
+    L->router_x = L->dev_xr;
+    rc = ffai_moe_forward_host(L, x, T, out, residual, debug);
+    L->router_x = nullptr;
+    return rc;
 }
 
 extern "C" FFAI_API int ffai_moe_forward_host(ffai_moe_layer* L, const uint16_t* x, int32_t T, uint16_t* out,

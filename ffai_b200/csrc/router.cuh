@@ -26,6 +26,8 @@ struct RouterParams {
     int hidden, n_experts, top_k;
     int gating_mode, norm_topk_prob;
     int logits_bf16;
+    float logit_scale;               // logits are multiplied by this before routing (1 unless the model says otherwise)
+    const float* per_expert_scale;   // nullable [E]: combine weight *= scale[expert]
 };
 
 // One 64-wide chunk of dot(x[t], W[e]) in ascending k with fused multiply-add.
@@ -140,6 +142,10 @@ FFAI_DEVINL void route_token_warp(const RouterParams& p, float* logits_s, float*
     const int E = p.n_experts, K = p.top_k;
     int my_idx;
     float my_val;
+    if (p.logit_scale != 1.0f && p.logit_scale != 0.0f) {   // (0: unset) Gemma 4: hidden^-0.5 folded into the logits (Gemma4Text.swift:937-943)
+        for (int e = lane; e < E; e += 32) logits_s[e] = __fmul_rn(logits_s[e], p.logit_scale);
+        __syncwarp();
+    }
     const bool fast = (p.gating_mode == 1) ||
                       (p.gating_mode == 0 && p.norm_topk_prob && p.expert_bias == nullptr);
     if (fast) {
@@ -150,6 +156,7 @@ FFAI_DEVINL void route_token_warp(const RouterParams& p, float* logits_s, float*
         float sum = 0.0f;
         for (int j = 0; j < K; ++j) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, ex, j));
         float w = (sum > 0.0f) ? __fdiv_rn(ex, sum) : __fdiv_rn(1.0f, (float)K);
+        if (p.per_expert_scale && lane < K) w = __fmul_rn(w, p.per_expert_scale[my_idx]);
         if (lane < K) { idx_out[lane] = (uint32_t)my_idx; w_out[lane] = w; }
         return;
     }
@@ -176,6 +183,7 @@ FFAI_DEVINL void route_token_warp(const RouterParams& p, float* logits_s, float*
         for (int j = 0; j < K; ++j) s2 = __fadd_rn(s2, __shfl_sync(0xFFFFFFFFu, my_val, j));
         if (s2 > 0.0f) w = __fdiv_rn(my_val, s2);
     }
+    if (p.per_expert_scale && lane < K) w = __fmul_rn(w, p.per_expert_scale[my_idx]);
     if (lane < K) { idx_out[lane] = (uint32_t)my_idx; w_out[lane] = w; }
 }
 

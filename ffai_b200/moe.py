@@ -67,7 +67,8 @@ class MoELayer:
 
     # host buffers in, host buffers out (copies inside the call)
     def forward_host(self, x: np.ndarray, residual: Optional[np.ndarray] = None,
-                     debug: bool = False, out: Optional[np.ndarray] = None
+                     debug: bool = False, out: Optional[np.ndarray] = None,
+                     x_router: Optional[np.ndarray] = None
                      ) -> Tuple[np.ndarray, Optional[DebugBuffers]]:
         x = np.ascontiguousarray(x, dtype=np.uint16)
         T = int(x.shape[0]) if x.ndim == 2 else 0
@@ -79,9 +80,16 @@ class MoELayer:
         if residual is not None:
             residual = np.ascontiguousarray(residual, dtype=np.uint16)
             res_p = residual.ctypes.data
-        rc = self.lib.ffai_moe_forward_host(self.handle, x.ctypes.data if T else None, T,
-                                            out.ctypes.data if T else None, res_p,
-                                            C.byref(dstruct) if dstruct else None)
+        if x_router is not None:   # the router reads its own rows (Gemma 4)
+            x_router = np.ascontiguousarray(x_router, dtype=np.uint16)
+            rc = self.lib.ffai_moe_forward_host_split(self.handle, x.ctypes.data if T else None,
+                                                      x_router.ctypes.data if T else None, T,
+                                                      out.ctypes.data if T else None, res_p,
+                                                      C.byref(dstruct) if dstruct else None)
+        else:
+            rc = self.lib.ffai_moe_forward_host(self.handle, x.ctypes.data if T else None, T,
+                                                out.ctypes.data if T else None, res_p,
+                                                C.byref(dstruct) if dstruct else None)
         capi.check(rc, "ffai_moe_forward_host", self.handle)
         return out, dbg
 

@@ -121,6 +121,8 @@ class LayerSpec:
     shared_gate_kind: int = capi.LINEAR_NONE
     shared_gate_bits: int = 0
     shared_gate_group_size: int = 0
+    router_logit_scale: float = 0.0     # logits are multiplied by this before routing (0: no scaling)
+    router_per_expert_scale: int = 0    # 1: a per-expert factor on the combine weights (Gemma 4)
     prefill_weight_cache: int = 0  # 0 automatic, 1 never, 2 always (bf16 copy of the experts for the tensor-core path)
     zipf_s: float = 0.0          # > 0: additive per-expert router bias with a Zipf profile
     zipf_strength: float = 1.0
@@ -135,7 +137,7 @@ class LayerSpec:
                   "router_bits", "router_group_size", "router_has_bias", "router_logits_bf16",
                   "expert_bits", "expert_group_size", "expert_row_bias", "shared_intermediate",
                   "shared_bits", "shared_group_size", "shared_gate_kind", "shared_gate_bits",
-                  "shared_gate_group_size", "prefill_weight_cache"):
+                  "shared_gate_group_size", "prefill_weight_cache", "router_logit_scale"):
             setattr(cfg, f, getattr(self, f))
         cfg.max_tokens = max_tokens
         cfg.ep_rank = ep_rank
@@ -199,6 +201,13 @@ def cfg5_skewed(bits: int) -> LayerSpec:
                              zipf_s=1.1)
 
 
+def gemma4_style() -> LayerSpec:
+    """Gemma-4-style block: top-k then softmax, logits scaled by hidden^-0.5, per-expert combine scale,
+    GELU-GLU experts (Gemma4Text.swift:928-980); the router reads its own normalised input."""
+    return LayerSpec("gemma4_style", 1024, 512, 32, 4, gating_mode=capi.GATING_TOPK_THEN_SOFTMAX,
+                     activation=capi.ACT_GELU_GLU, router_logit_scale=1024 ** -0.5, router_per_expert_scale=1)
+
+
 CONFIGS = {"cfg1": cfg1_tiny, "cfg2": cfg2_gptoss, "cfg3": cfg3_qwen, "cfg4": cfg4_shared}
 
 
@@ -240,6 +249,7 @@ class HostLayer:
 
         w.router = lin("gate")
         w.router_expert_bias = ptr(a.get("gate.expert_bias"))
+        w.router_per_expert_scale = ptr(a.get("gate.per_expert_scale"))
         w.gate_proj = qproj("experts.gate_proj", True)
         w.up_proj = qproj("experts.up_proj", True)
         w.down_proj = qproj("experts.down_proj", True)
@@ -322,6 +332,8 @@ def make_layer(spec: LayerSpec, seed: int = 0) -> HostLayer:
         if spec.shared_gate_kind != capi.LINEAR_NONE:
             _rand_linear(rng, 1, H, spec.shared_gate_kind, spec.shared_gate_bits,
                          spec.shared_gate_group_size, "shared_expert_gate", a)
+    if spec.router_per_expert_scale:   # drawn last so that every other array of a seed stays as it was
+        a["gate.per_expert_scale"] = (0.5 + rng.random(E, dtype=np.float32)).astype(np.float32)
     return HostLayer(spec, a)
 
 

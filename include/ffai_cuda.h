@@ -130,7 +130,9 @@ typedef struct ffai_moe_config {
                                /* dequant stage: 0 automatic (kept when max_tokens*top_k/n_experts */
                                /* >= 32 and the copy is at most 4 GiB), 1 never, 2 always.  Decode   */
                                /* batches always stream the packed weights.                         */
-    int32_t reserved[7];
+    float router_logit_scale;  /* the logits are multiplied by this (fp32) before top-k / softmax; 0 means 1.   */
+                               /* Gemma 4 folds hidden^-0.5 into the logits here (Gemma4Text.swift:937-943). */
+    int32_t reserved[6];
 } ffai_moe_config;
 
 /* One stacked quantized projection: weight [n, out, in*bits/32] u32,
@@ -163,6 +165,8 @@ typedef struct ffai_moe_weights {
     ffai_qproj shared_up_proj;   /* [1, I_s, H]                                  */
     ffai_qproj shared_down_proj; /* [1, H, I_s]                                  */
     ffai_linear shared_gate;  /* [1, H]                                         */
+    const float* router_per_expert_scale; /* nullable [E] f32: combine weight of a slot *= scale[its expert] */
+                                          /* (Gemma 4 router.per_expert_scale, Gemma4Text.swift:944-949)     */
 } ffai_moe_weights;
 
 /* Optional per-call routing/dispatch outputs (device pointers for
@@ -214,6 +218,13 @@ FFAI_API int ffai_moe_forward(ffai_moe_layer* layer, const uint16_t* x, int32_t 
  * forward, copies out (and debug outputs) back, and waits.  This is what a
  * caller holding host tensors uses, as the reference's callers do with
  * shared-storage MTLBuffers (Sources/FFAI/Device.swift:23-64). */
+/* As ffai_moe_forward / ffai_moe_forward_host, with the router reading its own input rows x_router
+ * [T, hidden] while the experts (and the shared expert) read x: Gemma 4 normalises the two branches
+ * differently (Gemma4Text.swift:929-933, 957).  x_router == NULL means x. */
+FFAI_API int ffai_moe_forward_split(ffai_moe_layer* layer, const uint16_t* x, const uint16_t* x_router, int32_t n_tokens,
+                                    uint16_t* out, const uint16_t* residual, const ffai_moe_debug* debug, void* stream);
+FFAI_API int ffai_moe_forward_host_split(ffai_moe_layer* layer, const uint16_t* x, const uint16_t* x_router, int32_t n_tokens,
+                                         uint16_t* out, const uint16_t* residual, const ffai_moe_debug* debug);
 FFAI_API int ffai_moe_forward_host(ffai_moe_layer* layer, const uint16_t* x, int32_t n_tokens,
                           uint16_t* out, const uint16_t* residual,
                           const ffai_moe_debug* debug);

@@ -174,7 +174,7 @@ class Result:
 
 
 def moe_forward(host_layer, x, residual=None, token_mask=None, round_stages=False, n_threads=0,
-                compute_output=True) -> Result:
+                compute_output=True, x_router=None) -> Result:
     """The whole block on the CPU.  `x`: uint16 bf16 bit patterns [T, H]."""
     spec = host_layer.spec
     T = int(x.shape[0])
@@ -197,7 +197,8 @@ def moe_forward(host_layer, x, residual=None, token_mask=None, round_stages=Fals
                         r.inv_perm.ctypes.data)
     res = None if residual is None else np.ascontiguousarray(residual, dtype=np.uint16)
     mask = None if token_mask is None else np.ascontiguousarray(token_mask, dtype=np.uint8)
-    rc = lib().orc_moe_forward(C.byref(cfg), C.byref(w), _p(x), C.c_int(T), _p(r.out_f32),
+    xr = None if x_router is None else np.ascontiguousarray(x_router, dtype=np.uint16)
+    rc = lib().orc_moe_forward_split(C.byref(cfg), C.byref(w), _p(x), _p(xr), C.c_int(T), _p(r.out_f32),
                                _p(r.out_bf16), _p(res), C.byref(dbg), _p(mask),
                                C.c_int(1 if round_stages else 0), C.c_int(n_threads))
     if rc != 0:

@@ -416,11 +416,28 @@ static void run_expert(const ffai_moe_config* c, const proj_view* pg, const proj
  * for tokens with a non-zero mask; routing and the plan always cover all tokens.
  * out_f32 (nullable) receives the un-rounded fp32 result, out_bf16 (nullable) the rounded one.
  */
+ORC_EXPORT int orc_moe_forward_split(const ffai_moe_config* c, const ffai_moe_weights* w,
+                                     const uint16_t* x, const uint16_t* x_router, int n_tokens, float* out_f32,
+                                     uint16_t* out_bf16, const uint16_t* residual,
+                                     const ffai_moe_debug* dbg, const uint8_t* token_mask,
+                                     int round_stages, int n_threads);
+
 ORC_EXPORT int orc_moe_forward(const ffai_moe_config* c, const ffai_moe_weights* w,
                                const uint16_t* x, int n_tokens, float* out_f32,
                                uint16_t* out_bf16, const uint16_t* residual,
                                const ffai_moe_debug* dbg, const uint8_t* token_mask,
                                int round_stages, int n_threads) {
+    return orc_moe_forward_split(c, w, x, x, n_tokens, out_f32, out_bf16, residual, dbg, token_mask, round_stages, n_threads);
+}
+
+/* x_router: the rows the router reads (Gemma 4 normalises the router input and the expert input
+ * differently, Gemma4Text.swift:929-933, 957); the logits are scaled by router_logit_scale before
+ * routing (:937-943) and each combine weight by router_per_expert_scale[expert] (:944-949). */
+ORC_EXPORT int orc_moe_forward_split(const ffai_moe_config* c, const ffai_moe_weights* w,
+                                     const uint16_t* x, const uint16_t* x_router, int n_tokens, float* out_f32,
+                                     uint16_t* out_bf16, const uint16_t* residual,
+                                     const ffai_moe_debug* dbg, const uint8_t* token_mask,
+                                     int round_stages, int n_threads) {
     const int H = c->hidden, I = c->intermediate, E = c->n_experts, K = c->top_k, T = n_tokens;
     if (T <= 0) return 0;
 #ifdef _OPENMP
@@ -437,14 +454,22 @@ ORC_EXPORT int orc_moe_forward(const ffai_moe_config* c, const ffai_moe_weights*
     uint32_t* perm = (uint32_t*)malloc(4 * (size_t)M);
     uint32_t* inv_perm = (uint32_t*)malloc(4 * (size_t)M);
 
-    orc_router_logits(c, &w->router, x, T, logits);
+    orc_router_logits(c, &w->router, x_router ? x_router : x, T, logits);
+    const float logit_scale = c->router_logit_scale != 0.0f ? c->router_logit_scale : 1.0f;
+    float* scaled = logit_scale != 1.0f ? (float*)malloc(sizeof(float) * (size_t)T * E) : NULL;
+    if (scaled)
+        for (int64_t i = 0; i < (int64_t)T * E; ++i) scaled[i] = logits[i] * logit_scale;
 #pragma omp parallel for schedule(static)
     for (int t = 0; t < T; ++t) {
         int32_t idx[FFAI_MAX_TOP_K];
-        orc_route(logits + (int64_t)t * E, E, K, c->gating_mode, c->norm_topk_prob,
+        orc_route((scaled ? scaled : logits) + (int64_t)t * E, E, K, c->gating_mode, c->norm_topk_prob,
                   c->router_expert_bias ? w->router_expert_bias : NULL, idx, rw + (int64_t)t * K);
-        for (int s = 0; s < K; ++s) indices[(int64_t)t * K + s] = (uint32_t)idx[s];
+        for (int s = 0; s < K; ++s) {
+            indices[(int64_t)t * K + s] = (uint32_t)idx[s];
+            if (w->router_per_expert_scale) rw[(int64_t)t * K + s] *= w->router_per_expert_scale[idx[s]];
+        }
     }
+    free(scaled);
     orc_plan(indices, T, K, E, counts, offsets, perm, inv_perm);
     if (dbg) {
         if (dbg->logits) memcpy(dbg->logits, logits, sizeof(float) * (size_t)T * E);

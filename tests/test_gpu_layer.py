@@ -353,3 +353,30 @@ def test_auto_path_is_deterministic_and_matches_forced_paths(oracle_mod):
     finally:
         layer.close()
     assert np.array_equal(a, b) and np.array_equal(a, c)   # small batches take the streaming kernels
+
+
+# ── Gemma-4-style routing: scaled logits, per-expert combine scale, GELU-GLU, the router's own input ──
+
+@pytest.mark.parametrize("T,path", [(1, None), (6, None), (40, None), (150, None), (300, 2), (9, 1)])
+def test_gemma4_style_block(oracle_mod, T, path):
+    spec = synth.gemma4_style()
+    host = synth.make_layer(spec, 4)
+    x = synth.make_tokens(T, spec.hidden, 4)
+    xr = synth.make_tokens(T, spec.hidden, 40)          # stands for rmsNorm(h, router.scale)
+    layer = MoELayer(host, T)
+    try:
+        if path is not None:
+            layer.set_option("path", path)
+        out, dbg = layer.forward_host(x, debug=True, x_router=xr)
+        same, _ = layer.forward_host(x, x_router=xr)
+        plain, pdbg = layer.forward_host(x, debug=True)           # router reading x: a different routing
+    finally:
+        layer.close()
+    ref = oracle_mod.moe_forward(host, x, x_router=xr)
+    assert np.array_equal(dbg.indices, ref.indices) and np.array_equal(dbg.weights, ref.weights)
+    assert np.array_equal(dbg.perm, ref.perm) and np.array_equal(out, same)
+    assert_parity(out, ref.out_f32, what=spec.name)
+    ref_plain = oracle_mod.moe_forward(host, x)
+    assert np.array_equal(pdbg.indices, ref_plain.indices) and np.array_equal(pdbg.weights, ref_plain.weights)
+    # the per-expert scale really is in the weights: they no longer sum to one
+    assert np.abs(ref.weights.sum(axis=1) - 1.0).max() > 1e-2
