@@ -68,6 +68,7 @@ struct ffai_moe_layer {
     float* xsum = nullptr;           // [M, H/64]  64-run sums of xg rows
     uint16_t* x_tok = nullptr;       // [T, H] token rows, 8-run permuted (streaming kernels read them through perm)
     float* xsum_tok = nullptr;       // [T, H/64 rounded up to 4] their 64-run sums
+    float* router_f32 = nullptr;     // quantized router expanded to fp32 (owned with the weights)
     float* inner_parts = nullptr;    // [M, I/16]  16-run sums of inner rows, written by the gate/up streaming kernel
     float* inner_sum = nullptr;      // [M, I/64]  64-run sums of inner rows
     const uint16_t* router_x = nullptr;  // set for the duration of a split forward: the router's own input rows
@@ -423,6 +424,22 @@ __global__ void dense_rowdot_kernel(const TW* __restrict__ w, const uint16_t* __
     if (lane == 0) out[t] = acc;
 }
 
+// A quantized router expanded to fp32 once at load time: w = fma(scale, q, bias), the value the
+// quantized projection uses for every product (FFAI Layers.swift:201-210), so the dense fp32 router
+// kernels give the same logits bit for bit and the per-use unpacking disappears (E*H*4 bytes).
+template <int BITS>
+__global__ void expand_router_f32_kernel(const uint32_t* __restrict__ weight, const uint16_t* __restrict__ scales,
+                                         const uint16_t* __restrict__ biases, float* __restrict__ out,
+                                         int rows, int K, int group_size) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * K) return;
+    const size_t row = i / K;
+    const int k = (int)(i - row * K);
+    const uint32_t* w = weight + row * ((size_t)K * BITS / 32);
+    const size_t g = row * (K / group_size) + k / group_size;
+    out[i] = __fmaf_rn(bf16_bits_to_f32(scales[g]), (float)unpack_at<BITS>(w, k), bf16_bits_to_f32(biases[g]));
+}
+
 // One projection expanded to bf16 in the tensor-core operand's K order: w = fma(q, scale, bias) rounded
 // once, every 8-run stored as 0,4,1,5,2,6,3,7.  One thread per 8-run.  Runs once, at load time.
 template <int BITS>
@@ -709,6 +726,20 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
     if ((rc = upload_linear(L, w->router, c.router_kind, c.n_experts, c.hidden, c.router_bits,
                             c.router_group_size, loc, &L->w.router, "router")))
         return rc;
+    L->router_f32 = nullptr;
+    if (c.router_kind == FFAI_LINEAR_AFFINE) {
+        void* buf = nullptr;
+        const size_t n = (size_t)c.n_experts * c.hidden;
+        CUDA_TRY(L, cudaMalloc(&buf, n * sizeof(float)));
+        L->owned_weights.push_back(buf);
+        L->router_f32 = static_cast<float*>(buf);
+        const unsigned blocks = (unsigned)((n + 255) / 256);
+        const uint32_t* rw = static_cast<const uint32_t*>(L->w.router.weight);
+        BITS_SWITCH(c.router_bits, (expand_router_f32_kernel<B><<<blocks, 256>>>(rw, L->w.router.scales, L->w.router.biases, L->router_f32,
+                                                                                c.n_experts, c.hidden, c.router_group_size)));
+        CUDA_TRY(L, cudaGetLastError());
+        CUDA_TRY(L, cudaDeviceSynchronize());
+    }
     if (c.router_has_bias && !w->router.bias) return fail(L, FFAI_ERR_INVALID_ARG, "router_has_bias set but router.bias is null");
     if (!c.router_has_bias) L->w.router.bias = nullptr;
     if (c.router_expert_bias) {
@@ -1031,6 +1062,10 @@ RouterParams router_params(const ffai_moe_layer* L) {
     p.bias = L->w.router.bias;
     p.expert_bias = c.router_expert_bias ? L->w.router_expert_bias : nullptr;
     p.kind = c.router_kind;
+    if (L->router_f32) {   // quantized router: its fp32 expansion through the dense kernels (same bits, no per-use unpacking)
+        p.weight = L->router_f32;
+        p.kind = FFAI_LINEAR_F32;
+    }
     p.bits = c.router_bits;
     p.group_size = c.router_group_size;
     p.hidden = c.hidden;
