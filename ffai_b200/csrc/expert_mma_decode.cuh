@@ -44,6 +44,7 @@ struct Params {
     const uint32_t* sb2;
     int N, K, group_size;  // group_size 64 or 128
     const uint32_t* offsets;  // [E+1] rows per expert in the sorted row space
+    const uint32_t* order;    // nullable [E]: expert handled by grid row y (longest first); identity when null
     const uint16_t* x;        // [rows, K] bf16, 8-run permuted
     const uint32_t* row_src;  // nullable: sorted row r reads x (and xsum) at row row_src[r] / row_div instead of r
     int row_div;              //           (the dispatch permutation over per-token rows: no gathered copy is made)
@@ -492,7 +493,7 @@ grouped_mma_decode_kernel(const Params p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int e = blockIdx.y;
+    const int e = p.order ? (int)p.order[blockIdx.y] : (int)blockIdx.y;
     const int row0 = (int)p.offsets[e], cnt = (int)p.offsets[e + 1] - row0;
     if (cnt <= 0) return;
     const int K = p.K, wpr = K / 8, n64 = K / 64;

@@ -68,6 +68,7 @@ struct ffai_moe_layer {
     float* xsum = nullptr;           // [M, H/64]  64-run sums of xg rows
     uint16_t* x_tok = nullptr;       // [T, H] token rows, 8-run permuted (streaming kernels read them through perm)
     float* xsum_tok = nullptr;       // [T, H/64 rounded up to 4] their 64-run sums
+    uint32_t* expert_order = nullptr; // [E] experts by descending row count, written with the fused small-batch plan
     float* router_f32 = nullptr;     // quantized router expanded to fp32 (owned with the weights)
     float* inner_parts = nullptr;    // [M, I/16]  16-run sums of inner rows, written by the gate/up streaming kernel
     float* inner_sum = nullptr;      // [M, I/64]  64-run sums of inner rows
@@ -637,6 +638,7 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
         L->router_partials_cap = T * E * (H / 64);
         if ((rc = ws_alloc(L, &L->router_partials, L->router_partials_cap))) return rc;
     }
+    if ((rc = ws_alloc(L, &L->expert_order, E))) return rc;
     if ((rc = ws_alloc(L, &L->tickets, ROUTER_TICKETS))) return rc;
     CUDA_TRY(L, cudaMemset(L->tickets, 0, ROUTER_TICKETS * sizeof(uint32_t)));
     if ((rc = ws_alloc(L, &L->inner, Mx * I))) return rc;
@@ -1371,7 +1373,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     stage_begin(L, ST_ROUTER, st);
     RouterParams rp = router_params(L);
     // small batches: the router kernel's last block also builds the dispatch plan
-    const PlanOut fused_plan = (M <= PLAN_ENTRIES_PER_WARP) ? PlanOut{L->counts, L->offsets, L->perm, L->inv_perm} : PlanOut{nullptr, nullptr, nullptr, nullptr};
+    const PlanOut fused_plan = (M <= PLAN_ENTRIES_PER_WARP) ? PlanOut{L->counts, L->offsets, L->perm, L->inv_perm, L->expert_order} : PlanOut{nullptr, nullptr, nullptr, nullptr, nullptr};
     bool plan_done = false;
     // 4-bit streaming kernels read per-token rows through the permutation: the rows (8-run permuted) and their
     // 64-run sums are written once per token, by the router kernel when it is the small-batch one
@@ -1439,6 +1441,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         Params p{};
         p.group_size = c.expert_group_size;
         p.offsets = L->offsets;
+        p.order = plan_done ? L->expert_order : nullptr;   // longest experts first shortens the tail of the grid
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
         const int nt = rows_per_expert > 4.0 ? 2 : 1;  // 16 activation rows per pass instead of 8
         // few routed rows -> few active experts -> slice the reduction axis to keep every SM busy

@@ -109,6 +109,8 @@ struct PlanOut {
     uint32_t* offsets;   // [E+1]
     uint32_t* perm;      // [n_rows]
     uint32_t* inv_perm;  // [n_rows]
+    uint32_t* order;     // nullable [E]: experts by descending row count (ties: ascending index), for kernels that
+                         // want their longest work items scheduled first
 };
 
 // The whole plan by one warp, for small row counts (decode): histogram, exclusive scan, stable scatter.
@@ -143,6 +145,17 @@ FFAI_DEVINL void plan_small_warp(const uint32_t* indices, int n_rows, int n_expe
     }
     if (lane == 0) o.offsets[n_experts] = carry;
     __syncwarp();
+    if (o.order) {   // rank of expert e = experts with more rows, or as many and a smaller index (E^2 / 32 compares per lane)
+        for (int e = lane; e < n_experts; e += 32) {
+            const uint32_t c = hist[e];
+            int rank = 0;
+            for (int f = 0; f < n_experts; ++f) {
+                const uint32_t d = hist[f];
+                rank += (d > c) || (d == c && f < e);
+            }
+            o.order[rank] = (uint32_t)e;
+        }
+    }
     for (int i0 = 0; i0 < n_rows; i0 += 32) {
         const int i = i0 + lane;
         const bool valid = i < n_rows;
@@ -168,7 +181,7 @@ __global__ void plan_small_kernel(const uint32_t* __restrict__ indices, int n_ro
                                   uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets,
                                   uint32_t* __restrict__ perm, uint32_t* __restrict__ inv_perm) {
     extern __shared__ uint32_t sm[];  // hist[E], cursor[E]
-    const PlanOut o{counts, offsets, perm, inv_perm};
+    const PlanOut o{counts, offsets, perm, inv_perm, nullptr};
     plan_small_warp(indices, n_rows, n_experts, o, sm, sm + n_experts, threadIdx.x);
 }
 
