@@ -177,6 +177,12 @@ SIGNATURES = {
     "ffai_op_moe_gather_dequant_gemm": (C.c_int, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "ffai_op_glu_activation": (C.c_int, [_P, _P, _P, C.c_int64, _I, C.c_float, C.c_float, _P]),
     "ffai_op_moe_unpermute": (C.c_int, [_P, _P, _P, _P, _I, _I, _I, _P]),
+    "ffai_st_open": (C.c_int, [C.c_char_p, C.POINTER(_P)]),
+    "ffai_st_close": (None, [_P]),
+    "ffai_st_last_error": (C.c_char_p, [_P]),
+    "ffai_st_tensor": (C.c_int, [_P, C.c_char_p, C.POINTER(_P), C.POINTER(C.c_uint64), C.c_char_p, C.POINTER(C.c_int64 * 8), C.POINTER(C.c_int32)]),
+    "ffai_st_derive_bits": (C.c_int32, [C.c_int64, C.c_int64, C.c_int32]),
+    "ffai_st_moe_weights": (C.c_int, [_P, C.c_char_p, C.c_int32, C.POINTER(MoEConfig), C.POINTER(MoEWeights)]),
     "ffai_op_add_rmsnorm": (C.c_int, [_P, _P, _P, C.c_float, _I, _I, _P, _P, _P]),
     "ffai_op_mxfp4_to_affine_int4": (C.c_int, [_P, _P, C.c_int64, _P, _P, _P, _P]),
     "ffai_op_affine_quantize": (C.c_int, [_P, C.c_int64, _I, _I, _I, _P, _P, _P, _P]),

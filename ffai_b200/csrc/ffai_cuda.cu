@@ -19,6 +19,7 @@
 #include "expert_mma_decode.cuh"
 #include "plan.cuh"
 #include "router.cuh"
+#include "safetensors.hpp"
 #include "tc_path.cuh"
 #include "weight_prep.cuh"
 
@@ -1721,6 +1722,166 @@ extern "C" FFAI_API int ffai_moe_forward_host(ffai_moe_layer* L, const uint16_t*
         return fail(L, FFAI_ERR_DEVICE_CHECK, "a kernel gave up a bounded wait (code %u)", *pin_err);
     }
     if (!out_pinned && bytes) memcpy(out, L->pin_out, bytes);
+    return FFAI_OK;
+}
+
+
+// ───────────────────────────── safetensors -> ffai_moe_weights ─────────────────────────────
+
+struct ffai_st_file {
+    ffai::st::File* f = nullptr;
+    std::string error;
+};
+
+extern "C" FFAI_API int ffai_st_open(const char* path, ffai_st_file** out) {
+    if (!path || !out) return FFAI_ERR_INVALID_ARG;
+    ffai_st_file* h = new (std::nothrow) ffai_st_file();
+    if (!h) return FFAI_ERR_CUDA;
+    h->f = ffai::st::open_file(path, &h->error);
+    *out = h;
+    return h->f ? FFAI_OK : FFAI_ERR_INVALID_ARG;
+}
+
+extern "C" FFAI_API void ffai_st_close(ffai_st_file* h) {
+    if (!h) return;
+    ffai::st::close_file(h->f);
+    delete h;
+}
+
+extern "C" FFAI_API const char* ffai_st_last_error(const ffai_st_file* h) { return h ? h->error.c_str() : "null handle"; }
+
+extern "C" FFAI_API int ffai_st_tensor(const ffai_st_file* h, const char* name, const void** data, uint64_t* n_bytes,
+                                       char dtype[8], int64_t shape[8], int32_t* n_dims) {
+    if (!h || !h->f || !name) return FFAI_ERR_INVALID_ARG;
+    const ffai::st::Tensor* t = ffai::st::find(h->f, name);
+    if (!t) return FFAI_ERR_INVALID_ARG;
+    if (data) *data = h->f->data + t->begin;
+    if (n_bytes) *n_bytes = t->end - t->begin;
+    if (dtype) { memset(dtype, 0, 8); strncpy(dtype, t->dtype.c_str(), 7); }
+    if (n_dims) *n_dims = (int32_t)t->shape.size();
+    if (shape) for (size_t i = 0; i < t->shape.size() && i < 8; ++i) shape[i] = t->shape[i];
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int32_t ffai_st_derive_bits(int64_t weight_packed_cols, int64_t scale_cols, int32_t group_size) {
+    const int64_t in_features = scale_cols * group_size;   // Layers.swift:348-363
+    if (in_features <= 0 || (32 * weight_packed_cols) % in_features) return 0;
+    return (int32_t)((32 * weight_packed_cols) / in_features);
+}
+
+namespace {
+int st_fail(ffai_st_file* h, const std::string& msg) {
+    h->error = msg;
+    return FFAI_ERR_INVALID_ARG;
+}
+
+// One stacked quantized projection <base>.{weight,scales,biases}: shapes [n, out, in*bits/32] and [n, out, in/gs].
+int st_qproj(ffai_st_file* h, const std::string& base, int gs, ffai_qproj* q, int64_t* n, int64_t* out_dim, int64_t* in_dim, int* bits) {
+    const ffai::st::Tensor* w = ffai::st::find(h->f, base + ".weight");
+    const ffai::st::Tensor* s = ffai::st::find(h->f, base + ".scales");
+    const ffai::st::Tensor* b = ffai::st::find(h->f, base + ".biases");
+    if (!w || !s || !b) return st_fail(h, "missing " + base + ".{weight,scales,biases}");
+    if (w->dtype != "U32") return st_fail(h, base + ".weight is not U32");
+    if (s->dtype != "BF16" || b->dtype != "BF16") return st_fail(h, base + ": scales/biases must be BF16");
+    if (w->shape.size() < 2 || s->shape != b->shape || s->shape.size() != w->shape.size()) return st_fail(h, base + ": shapes do not match");
+    const size_t r = w->shape.size();
+    const int64_t wcols = w->shape[r - 1], scols = s->shape[r - 1];
+    const int bt = ffai_st_derive_bits(wcols, scols, gs);
+    if (!valid_bits(bt)) return st_fail(h, base + ": shapes do not describe an affine-quantized tensor at this group size");
+    for (size_t i = 0; i + 1 < r; ++i)
+        if (w->shape[i] != s->shape[i]) return st_fail(h, base + ": leading dimensions differ");
+    *n = r == 3 ? w->shape[0] : 1;
+    *out_dim = w->shape[r - 2];
+    *in_dim = scols * gs;
+    *bits = bt;
+    q->weight = reinterpret_cast<const uint32_t*>(h->f->data + w->begin);
+    q->scales = reinterpret_cast<const uint16_t*>(h->f->data + s->begin);
+    q->biases = reinterpret_cast<const uint16_t*>(h->f->data + b->begin);
+    q->row_bias = nullptr;
+    return FFAI_OK;
+}
+
+// A router / gate projection <base>.weight [+ .scales/.biases]: dense F32 / BF16, or affine.
+int st_linear(ffai_st_file* h, const std::string& base, int gs, ffai_linear* lin, int* kind, int* bits, int64_t* out_dim, int64_t* in_dim) {
+    const ffai::st::Tensor* w = ffai::st::find(h->f, base + ".weight");
+    if (!w || w->shape.size() != 2) return st_fail(h, "missing or non-2-D " + base + ".weight");
+    *lin = ffai_linear{};
+    lin->weight = h->f->data + w->begin;
+    *out_dim = w->shape[0];
+    if (w->dtype == "F32") { *kind = FFAI_LINEAR_F32; *bits = 0; *in_dim = w->shape[1]; }
+    else if (w->dtype == "BF16") { *kind = FFAI_LINEAR_BF16; *bits = 0; *in_dim = w->shape[1]; }
+    else if (w->dtype == "U32") {
+        const ffai::st::Tensor* s = ffai::st::find(h->f, base + ".scales");
+        const ffai::st::Tensor* b = ffai::st::find(h->f, base + ".biases");
+        if (!s || !b || s->shape.size() != 2) return st_fail(h, base + ": packed weight without scales/biases");
+        *bits = ffai_st_derive_bits(w->shape[1], s->shape[1], gs);
+        if (!valid_bits(*bits)) return st_fail(h, base + ": shapes do not describe an affine-quantized tensor at this group size");
+        *kind = FFAI_LINEAR_AFFINE;
+        *in_dim = s->shape[1] * gs;
+        lin->scales = reinterpret_cast<const uint16_t*>(h->f->data + s->begin);
+        lin->biases = reinterpret_cast<const uint16_t*>(h->f->data + b->begin);
+    } else return st_fail(h, base + ".weight has an unsupported dtype " + w->dtype);
+    if (const ffai::st::Tensor* bias = ffai::st::find(h->f, base + ".bias"))
+        if (bias->dtype == "BF16") lin->bias = reinterpret_cast<const uint16_t*>(h->f->data + bias->begin);
+    return FFAI_OK;
+}
+}  // namespace
+
+extern "C" FFAI_API int ffai_st_moe_weights(ffai_st_file* h, const char* prefix, int32_t scheme, ffai_moe_config* cfg,
+                                            ffai_moe_weights* out) {
+    if (!h || !h->f || !prefix || !cfg || !out) return FFAI_ERR_INVALID_ARG;
+    if (scheme != FFAI_ST_SWITCH_MLP && scheme != FFAI_ST_SWITCH_GLU) return st_fail(h, "unknown naming scheme");
+    const std::string p = prefix;
+    const std::string ex = p + (scheme == FFAI_ST_SWITCH_MLP ? ".switch_mlp" : ".experts.switch_glu");
+    const std::string router = p + (scheme == FFAI_ST_SWITCH_MLP ? ".gate" : ".router.proj");
+    if (!valid_gs(cfg->expert_group_size)) return st_fail(h, "config.expert_group_size must be 32, 64 or 128");
+    *out = ffai_moe_weights{};
+    out->struct_size = sizeof(ffai_moe_weights);
+    out->location = FFAI_MEM_HOST;
+    int rc, bits[3];
+    int64_t n[3], od[3], id[3];
+    if ((rc = st_qproj(h, ex + ".gate_proj", cfg->expert_group_size, &out->gate_proj, &n[0], &od[0], &id[0], &bits[0]))) return rc;
+    if ((rc = st_qproj(h, ex + ".up_proj", cfg->expert_group_size, &out->up_proj, &n[1], &od[1], &id[1], &bits[1]))) return rc;
+    if ((rc = st_qproj(h, ex + ".down_proj", cfg->expert_group_size, &out->down_proj, &n[2], &od[2], &id[2], &bits[2]))) return rc;
+    if (n[0] != n[1] || n[0] != n[2] || od[0] != od[1] || id[0] != id[1] || od[2] != id[0] || id[2] != od[0])
+        return st_fail(h, "gate/up/down shapes are inconsistent");
+    if (bits[0] != bits[1] || bits[0] != bits[2]) return st_fail(h, "gate/up/down use different bit widths (not supported in one block)");
+    cfg->n_experts = (int32_t)n[0];
+    cfg->intermediate = (int32_t)od[0];
+    cfg->hidden = (int32_t)id[0];
+    cfg->expert_bits = bits[0];
+    int64_t ro, ri;
+    const int rgs = cfg->router_group_size ? cfg->router_group_size : cfg->expert_group_size;
+    if ((rc = st_linear(h, router, rgs, &out->router, &cfg->router_kind, &cfg->router_bits, &ro, &ri))) return rc;
+    if (ro != n[0] || ri != id[0]) return st_fail(h, "router shape does not match the experts");
+    cfg->router_group_size = cfg->router_kind == FFAI_LINEAR_AFFINE ? rgs : 0;
+    cfg->router_has_bias = out->router.bias != nullptr;
+    if (const ffai::st::Tensor* t = ffai::st::find(h->f, p + ".router.per_expert_scale"))
+        if (t->dtype == "F32" && t->end - t->begin == (uint64_t)n[0] * 4)
+            out->router_per_expert_scale = reinterpret_cast<const float*>(h->f->data + t->begin);
+    // optional shared expert (Qwen3xText.swift:626-650): <prefix>.shared_expert.* and <prefix>.shared_expert_gate
+    cfg->shared_intermediate = 0;
+    if (ffai::st::find(h->f, p + ".shared_expert.gate_proj.weight")) {
+        const int sgs = cfg->shared_group_size ? cfg->shared_group_size : cfg->expert_group_size;
+        int sb[3];
+        int64_t sn[3], so[3], si[3];
+        if ((rc = st_qproj(h, p + ".shared_expert.gate_proj", sgs, &out->shared_gate_proj, &sn[0], &so[0], &si[0], &sb[0]))) return rc;
+        if ((rc = st_qproj(h, p + ".shared_expert.up_proj", sgs, &out->shared_up_proj, &sn[1], &so[1], &si[1], &sb[1]))) return rc;
+        if ((rc = st_qproj(h, p + ".shared_expert.down_proj", sgs, &out->shared_down_proj, &sn[2], &so[2], &si[2], &sb[2]))) return rc;
+        if (si[0] != id[0] || so[2] != id[0] || so[0] != so[1] || si[2] != so[0] || sb[0] != sb[1] || sb[0] != sb[2])
+            return st_fail(h, "shared expert shapes are inconsistent");
+        cfg->shared_intermediate = (int32_t)so[0];
+        cfg->shared_bits = sb[0];
+        cfg->shared_group_size = sgs;
+        cfg->shared_gate_kind = FFAI_LINEAR_NONE;
+        if (ffai::st::find(h->f, p + ".shared_expert_gate.weight")) {
+            int64_t go, gi;
+            const int ggs = cfg->shared_gate_group_size ? cfg->shared_gate_group_size : sgs;
+            if ((rc = st_linear(h, p + ".shared_expert_gate", ggs, &out->shared_gate, &cfg->shared_gate_kind, &cfg->shared_gate_bits, &go, &gi))) return rc;
+            if (go != 1 || gi != id[0]) return st_fail(h, "shared_expert_gate must be [1, hidden]");
+            cfg->shared_gate_group_size = cfg->shared_gate_kind == FFAI_LINEAR_AFFINE ? ggs : 0;
+        }
+    }
     return FFAI_OK;
 }
 

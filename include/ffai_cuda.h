@@ -373,6 +373,28 @@ FFAI_API int ffai_op_moe_unpermute(const uint16_t* expert_out, const uint32_t* i
                           const float* weights, uint16_t* out, int32_t n_tokens,
                           int32_t hidden, int32_t k, void* stream);
 
+/* Reading a block's weights from a .safetensors file (host code; no GPU needed).  The file is mapped
+ * read-only and ffai_moe_weights is filled with HOST pointers into the mapping, valid until
+ * ffai_st_close; hand it to ffai_moe_set_weights (which copies to the device) before closing.
+ * Replaces the reference's loader path for the block (Loader/SafeTensors.swift:377-396; stacked triplets
+ * Qwen3xText.swift:605-650, Gemma4Text.swift:540-554; bit widths derived per tensor from the shapes,
+ * Layers.swift:340-363).  ffai_st_moe_weights takes the group sizes from `config` (expert_group_size
+ * must be set; router / shared ones default to it), and fills in from the file: n_experts, hidden,
+ * intermediate, the bit widths, the router kind and bias flag, the shared expert's sizes.  Routing
+ * mode, activation, top_k and max_tokens stay the caller's.  GPT-OSS checkpoints (MXFP4 experts) go
+ * through ffai_st_tensor + ffai_op_mxfp4_to_affine_int4 instead. */
+typedef struct ffai_st_file ffai_st_file;
+enum { FFAI_ST_SWITCH_MLP = 0,   /* <prefix>.switch_mlp.{gate,up,down}_proj.*, router <prefix>.gate.*             */
+       FFAI_ST_SWITCH_GLU = 1 }; /* <prefix>.experts.switch_glu.*, router <prefix>.router.proj.* (+ per_expert_scale) */
+FFAI_API int ffai_st_open(const char* path, ffai_st_file** out_file);
+FFAI_API void ffai_st_close(ffai_st_file* file);
+FFAI_API const char* ffai_st_last_error(const ffai_st_file* file);
+FFAI_API int ffai_st_tensor(const ffai_st_file* file, const char* name, const void** data, uint64_t* n_bytes,
+                            char dtype[8], int64_t shape[8], int32_t* n_dims);
+FFAI_API int32_t ffai_st_derive_bits(int64_t weight_packed_cols, int64_t scale_cols, int32_t group_size);
+FFAI_API int ffai_st_moe_weights(ffai_st_file* file, const char* prefix, int32_t scheme, ffai_moe_config* config,
+                                 ffai_moe_weights* out_weights);
+
 /* Weight preparation (rows either side of the block).
  * ffai_op_mxfp4_to_affine_int4: the load-time transcode of GPT-OSS experts
  *   (GPTOSSText.swift:1071-1244, a host loop there): per group of 32 fp4 (e2m1) codes and one e8m0
