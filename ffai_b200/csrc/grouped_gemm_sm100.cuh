@@ -13,16 +13,18 @@
 // element in its own TMEM lane.  (Measured with the device timeline: one tcgen05.mma costs its
 // issuing thread 80-100 clk whatever its N; only N = 256 keeps the tensor pipe busy that long.)
 //
-// Warp roles in a 768-thread CTA (persistent; tiles are (expert, 128-row token tile, weight-row tile)):
-//   warp 0       TMA producer of packed weights: two boxes of [128 rows x 128 B] (256 k) per stage,
-//                128-byte swizzle, ring "W"
+// Warp roles in a 768-thread CTA (persistent; work items are (expert, 128 routed rows, weight-row tile)):
+//   warp 0       TMA producer of weights.  Packed 4-bit: two boxes of [128 rows x 128 B] (256 k) per stage,
+//                128-byte swizzle, ring "W".  bf16 weights (WBF16: expanded once at load time): two boxes of
+//                [128 rows x 64 k] per 64 k straight into the operand ring "B".
 //   warp 2       TMA producer of activations: [128 rows x 128 B] per 64 k, 128-byte swizzle, ring "X"
 //   warp 1       MMA issuer (one thread): 4 x tcgen05.mma (M128 N256 K16) per 64 k; owns TMEM
 //                (two accumulators of 256 columns, so the epilogue of a tile overlaps the next tile)
-//   warps 4-19   dequant: 512 threads, thread = (weight row, half of a 64-k block); unpack 4-bit to
-//                bf16 (w = fma(q, scale, bias) rounded once), store into the 128-byte-swizzled K-major
-//                operand tile, ring "B"
-//   warps 20-23  epilogue: tcgen05.ld 16 columns at a time, bias + activation, 16-byte stores
+//   warps 4-19   dequant (packed weights only): 512 threads, thread = (weight row, half of a 64-k block);
+//                unpack 4-bit to bf16 (w = fma(q, scale, bias) rounded once), store into the
+//                128-byte-swizzled K-major operand tile, ring "B"
+//   warps 20-23  epilogue: tcgen05.ld 8 or 16 columns at a time with the next chunk's load in flight,
+//                bias + activation (one special-function op per element), 16-byte stores
 // Every mbarrier wait is bounded (about one second); on expiry the kernel raises an error
 // word, stops issuing work, waits (bounded) for its own copies in flight, frees TMEM and returns.
 //
