@@ -137,12 +137,13 @@ def cpu_baseline(spec, n_tokens: int, seed: int, min_seconds: float, impl_line: 
     host = synth.make_layer(spec, seed)
     sample_tokens = min(n_tokens, 64)
     x = synth.make_tokens(sample_tokens, spec.hidden, seed)
-    threads = oracle.lib().orc_num_threads()
-    oracle.moe_forward(host, x[:1])  # touch the weights once
+    # every core this process may run on, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for its ranks)
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    oracle.moe_forward(host, x[:1], n_threads=threads)  # touch the weights once
     t0 = time.perf_counter()
     reps = 0
     while True:
-        oracle.moe_forward(host, x)
+        oracle.moe_forward(host, x, n_threads=threads)
         reps += 1
         if time.perf_counter() - t0 >= min_seconds or reps >= 50:
             break
