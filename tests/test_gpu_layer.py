@@ -380,3 +380,22 @@ def test_gemma4_style_block(oracle_mod, T, path):
     assert np.array_equal(pdbg.indices, ref_plain.indices) and np.array_equal(pdbg.weights, ref_plain.weights)
     # the per-expert scale really is in the weights: they no longer sum to one
     assert np.abs(ref.weights.sum(axis=1) - 1.0).max() > 1e-2
+
+
+# ── the remaining benchmark configurations at their full sizes (outputs on a token sample: the oracle is scalar) ──
+
+def test_cfg4_full_prefill_sampled(oracle_mod):
+    """256 experts, top-8, sigmoid-gated 8-bit shared expert, 8-bit router, 2048 tokens: routing and
+    the plan for every token, outputs for 48 sampled tokens."""
+    mask = np.zeros(2048, dtype=np.uint8)
+    mask[np.random.default_rng(4).choice(2048, size=48, replace=False)] = 1
+    run_and_check(oracle_mod, synth.cfg4_shared(), 2048, token_mask=mask)
+
+
+@pytest.mark.parametrize("bits", [3, 4, 5, 6, 8])
+def test_cfg5_skewed_routing_every_bit_width(oracle_mod, bits):
+    """cfg3 shape with a Zipf(1.1) router bias (a few hot experts with many token tiles, most experts
+    nearly empty) at every bit width; 1024 tokens, outputs for 32 sampled tokens."""
+    mask = np.zeros(1024, dtype=np.uint8)
+    mask[np.random.default_rng(bits).choice(1024, size=32, replace=False)] = 1
+    run_and_check(oracle_mod, synth.cfg5_skewed(bits), 1024, token_mask=mask)
