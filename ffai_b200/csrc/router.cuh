@@ -525,9 +525,7 @@ __global__ void route_from_partials_kernel(RouterParams p, const float* __restri
     float* logits_s = smem + (size_t)warp * 2 * E;
     float* scratch = logits_s + E;
     if (t >= n_tokens) return;
-    for (int e = lane; e < E; e += 32) {
-        float total = 0.0f;
-        for (int c = 0; c < n_chunks; ++c) total = __fadd_rn(total, partials[((size_t)c * n_tokens + t) * E + e]);
+    auto finish = [&](int e, float total) {
         if (p.logits_bf16) total = bf16_round(total);
         if (p.bias) {
             total = __fadd_rn(total, bf16_bits_to_f32(p.bias[e]));
@@ -535,6 +533,33 @@ __global__ void route_from_partials_kernel(RouterParams p, const float* __restri
         }
         logits_s[e] = total;
         if (logits_out) logits_out[(size_t)t * E + e] = total;
+    };
+    if ((E & 3) == 0) {
+        // a lane owns four consecutive experts; eight chunk loads are issued before the first add so the
+        // (ordered) additions do not wait for one memory latency each
+        constexpr int U = 8;
+        for (int e = lane * 4; e < E; e += 128) {
+            float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c0 = 0; c0 < n_chunks; c0 += U) {
+                float4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (c0 + u < n_chunks) v[u] = __ldg(reinterpret_cast<const float4*>(partials + ((size_t)(c0 + u) * n_tokens + t) * E + e));
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (c0 + u < n_chunks) {
+                        total.x = __fadd_rn(total.x, v[u].x); total.y = __fadd_rn(total.y, v[u].y);
+                        total.z = __fadd_rn(total.z, v[u].z); total.w = __fadd_rn(total.w, v[u].w);
+                    }
+            }
+            finish(e, total.x); finish(e + 1, total.y); finish(e + 2, total.z); finish(e + 3, total.w);
+        }
+    } else {
+        for (int e = lane; e < E; e += 32) {
+            float total = 0.0f;
+            for (int c = 0; c < n_chunks; ++c) total = __fadd_rn(total, partials[((size_t)c * n_tokens + t) * E + e]);
+            finish(e, total);
+        }
     }
     __syncwarp();
     route_token_warp(p, logits_s, scratch, lane, indices + (size_t)t * p.top_k, weights + (size_t)t * p.top_k);
