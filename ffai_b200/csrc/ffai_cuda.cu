@@ -1164,7 +1164,7 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
     if (ep_rows_perm8(L)) {   // the rows arrived 8-run permuted: the streaming or the tensor-core kernels must take them
         if (L->opt_path == 3) use_tc = !L->mma_ok;
         else if (L->opt_path == 2) use_tc = can_tc;
-        else use_tc = can_tc && (rpe > 12.0 || !L->mma_ok);
+        else use_tc = can_tc && (rpe > 16.0 || !L->mma_ok);
         if (!L->mma_ok) use_tc = true;
         if (!can_tc) use_tc = false;
         use_mma = !use_tc;
@@ -1423,7 +1423,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     else if (L->opt_path == 3) mma_experts = L->mma_ok;
     else if (L->opt_path == 2) tc_experts = can_tc;
     else if (L->opt_path == 0) {
-        if (L->mma_ok && (rows_per_expert <= 12.0 || !can_tc)) mma_experts = rows_per_expert <= 48.0;
+        if (L->mma_ok && (rows_per_expert <= 16.0 || !can_tc)) mma_experts = rows_per_expert <= 48.0;
         if (!mma_experts && can_tc) tc_experts = M >= (L->opt_tc_min_rows > 0 ? L->opt_tc_min_rows : 64);
         if (!mma_experts && !tc_experts && L->mma_ok && rows_per_expert <= 48.0) mma_experts = true;
     }
