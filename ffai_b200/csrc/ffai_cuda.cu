@@ -1181,7 +1181,7 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         p.offsets = offsets_dev;
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
         const int nt = rpe > 4.0 ? 2 : 1;
-        const int ksplit = L->opt_ksplit > 0 ? L->opt_ksplit : (n_rows <= 8 ? 4 : (n_rows <= 24 ? 2 : 1));
+        const int ksplit = L->opt_ksplit > 0 ? L->opt_ksplit : (n_rows <= 4 ? 2 : 1);
         stage_begin(L, ST_GATE_UP, st);
         p.w1 = L->w.gate_proj.weight; p.s1 = L->w.gate_proj.scales; p.b1 = L->w.gate_proj.biases; p.rb1 = L->w.gate_proj.row_bias;
         p.w2 = L->w.up_proj.weight; p.s2 = L->w.up_proj.scales; p.b2 = L->w.up_proj.biases; p.rb2 = L->w.up_proj.row_bias;
@@ -1446,7 +1446,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
         const int nt = rows_per_expert > 4.0 ? 2 : 1;  // 16 activation rows per pass instead of 8
         // few routed rows -> few active experts -> slice the reduction axis to keep every SM busy
-        const int ksplit = L->opt_ksplit > 0 ? L->opt_ksplit : (M <= 8 ? 4 : (M <= 24 ? 2 : 1));
+        const int ksplit = L->opt_ksplit > 0 ? L->opt_ksplit : (M <= 4 ? 2 : 1);
 
         stage_begin(L, ST_GATE_UP, st);
         p.w1 = L->w.gate_proj.weight; p.s1 = L->w.gate_proj.scales; p.b1 = L->w.gate_proj.biases; p.rb1 = L->w.gate_proj.row_bias;

@@ -327,8 +327,7 @@ def test_mma_group_size_128_and_many_rows_per_expert(oracle_mod):
 
 @pytest.mark.parametrize("T", [1, 4, 8, 20, 64])
 def test_mma_group_size_32_gptoss_as_transcoded(oracle_mod, T):
-    """GPT-OSS experts as the MXFP4 transcode leaves them: 4-bit, group 32, row biases.  All three
-    reduction splits (1, 4 and 8 tokens give split 4 / 2 / 1) and both pass widths."""
+    """GPT-OSS experts as the MXFP4 transcode leaves them: 4-bit, group 32, row biases; both pass widths."""
     spec = synth.cfg2_gptoss().with_(name="gptoss_gs32", expert_group_size=32, expert_row_bias=1)
     run_and_check(oracle_mod, spec, T, path=MMA)
     run_and_check(oracle_mod, spec, T)                      # the automatic choice takes the same kernels
@@ -338,6 +337,16 @@ def test_mma_group_size_32_small_shapes(oracle_mod):
     run_and_check(oracle_mod, synth.LayerSpec("mma_gs32", 512, 256, 8, 2, expert_group_size=32), 70, path=MMA)
     run_and_check(oracle_mod, synth.LayerSpec("mma_gs32_small", 64, 64, 4, 2, expert_group_size=32), 5, path=MMA)
     run_and_check(oracle_mod, synth.LayerSpec("mma_gs32_odd_runs", 320, 192, 4, 2, expert_group_size=32), 11, path=MMA)
+
+
+@pytest.mark.parametrize("ksplit", [1, 2, 4])
+@pytest.mark.parametrize("gs", [32, 64])
+def test_mma_every_reduction_split(oracle_mod, ksplit, gs):
+    """The reduction axis cut into 1, 2 or 4 slices per 16-row block (the automatic choice only splits the
+    smallest batches), for both scale layouts, with one and with several rows per expert."""
+    spec = synth.cfg2_gptoss().with_(name=f"split{ksplit}_gs{gs}", expert_group_size=gs)
+    for T in (1, 3, 24):
+        run_and_check(oracle_mod, spec, T, path=MMA, options={"ksplit": ksplit})
 
 
 def test_auto_path_is_deterministic_and_matches_forced_paths(oracle_mod):
