@@ -54,7 +54,10 @@ struct Params {
                               // as written by the gate/up kernel; added in ascending order
     float* out_parts;         // FUSED, nullable: [rows, N/16] sum of each warp's 16 rounded outputs per activation row
     void* out;                // FUSED: bf16 [rows, N] 8-run permuted;  else fp32 [rows, N] (bf16 when out_bf16)
-    int out_bf16;             // !FUSED: store bf16 in plain column order instead of fp32
+    int out_bf16;             // !FUSED or pair: store bf16 in plain column order instead of fp32
+    int pair;                 // FUSED instantiation used for ONE projection: a warp owns 32 consecutive rows, the
+                              // "second projection" being rows +16 of the first (w2/s2/b2/rb2/sb2 unused); no
+                              // activation, both halves stored.  Halves the activation reads per weight byte.
     int activation;
     float limit, alpha;
 };
@@ -189,6 +192,8 @@ struct WarpJob {
     uint32_t sbdst;                                 // ... of its scale chunk in slot 0
     int n_runs;                                     // 64-runs in the slice
     int G0;                                         // first run of the slice
+    bool second_ok;                                 // pair mode: the warp's second 16 rows exist (else they are zero-filled)
+    bool sb_second;                                 // this lane's scale chunk belongs to the second projection / half
 };
 
 // One 64-run of a stage: scale words, A fragments from the staged packed rows, MMAs against the B
@@ -323,8 +328,10 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
         const uint32_t szw = (int)col_run < issue_rem ? 16u : 0u;
 #pragma unroll
         for (int i = 0; i < NP * 2; ++i)
-            cp_async16_zfill(job.wdst + issue_slot + i * 8 * W_PITCH, job.wsrc[i] + issue_off, szw);
-        if (job.sb_lane) cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * (2 * SBW), (int)sb_run < issue_rem ? 16u : 0u);
+            cp_async16_zfill(job.wdst + issue_slot + i * 8 * W_PITCH, job.wsrc[i] + issue_off, (i >= 2 && !job.second_ok) ? 0u : szw);
+        if (job.sb_lane)
+            cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * (2 * SBW),
+                             ((int)sb_run < issue_rem && !(job.sb_second && !job.second_ok)) ? 16u : 0u);
         cp_async_commit();
 #ifndef FFAI_DM_EXP_NOW
         issue_off += 64;
@@ -425,8 +432,10 @@ FFAI_DEVINL void decode_pass_shared(const Params& p, const WarpJob<FUSED>& job, 
         const uint32_t szw = (int)col_run < issue_rem ? 16u : 0u;
 #pragma unroll
         for (int i = 0; i < NP * 2; ++i)
-            cp_async16_zfill(job.wdst + issue_slot + i * 8 * W_PITCH, job.wsrc[i] + issue_off, szw);
-        if (job.sb_lane) cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * (2 * SBW), (int)sb_run < issue_rem ? 16u : 0u);
+            cp_async16_zfill(job.wdst + issue_slot + i * 8 * W_PITCH, job.wsrc[i] + issue_off, (i >= 2 && !job.second_ok) ? 0u : szw);
+        if (job.sb_lane)
+            cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * (2 * SBW),
+                             ((int)sb_run < issue_rem && !(job.sb_second && !job.second_ok)) ? 16u : 0u);
         const uint32_t szx = (int)xcol_run < issue_rem_x ? 16u : 0u;
 #pragma unroll
         for (int i = 0; i < NT; ++i) cp_async16_zfill(xdst[i] + issue_xslot, xsrc[i] + issue_off * 4, szx);
@@ -497,9 +506,10 @@ grouped_mma_decode_kernel(const Params p) {
     const int row0 = (int)p.offsets[e], cnt = (int)p.offsets[e + 1] - row0;
     if (cnt <= 0) return;
     const int K = p.K, wpr = K / 8, n64 = K / 64;
-    const int rb = blockIdx.x * RBW + warp / KSPLIT;   // 16-row block within the expert
+    const bool pair = FUSED && p.pair;                 // one projection, 32 rows per warp (see Params::pair)
+    const int rb = blockIdx.x * RBW + warp / KSPLIT;   // 16-row (pair: 32-row) block within the expert
     const int ks = warp % KSPLIT;
-    const int rb_row = rb * 16;
+    const int rb_row = rb * (pair ? 32 : 16);
     const bool warp_active = rb_row < p.N;             // N is a multiple of 16
     const int per = (n64 + KSPLIT - 1) / KSPLIT;
     const int G0 = min(ks * per, n64), G1 = min(G0 + per, n64);
@@ -512,13 +522,15 @@ grouped_mma_decode_kernel(const Params p) {
     WarpJob<FUSED> job;
     job.n_runs = warp_active ? G1 - G0 : 0;
     job.G0 = G0;
+    job.second_ok = !pair || rb_row + 16 < p.N;
     {
         const int col = lane & 3;
 #pragma unroll
         for (int i = 0; i < NP * 2; ++i) {
             const int ridx = (lane >> 2) + 8 * i;  // 0 .. NP*16-1
-            const uint32_t* base = (ridx >= 16) ? p.w2 : p.w1;
-            const size_t row = (size_t)e * p.N + (warp_active ? rb_row : 0) + (ridx & 15);
+            const uint32_t* base = (ridx >= 16 && !pair) ? p.w2 : p.w1;
+            const int half_rows = (ridx >= 16 && pair && job.second_ok) ? 16 : 0;   // second half of a pair: the next 16 rows
+            const size_t row = (size_t)e * p.N + (warp_active ? rb_row : 0) + half_rows + (ridx & 15);
             job.wsrc[i] = reinterpret_cast<const uint8_t*>(base + row * wpr) + G0 * 32 + col * 16;
         }
         // scale words of a stage: per projection 8 (16 with group 32) 16-byte chunks; lane -> (projection, chunk)
@@ -526,8 +538,11 @@ grouped_mma_decode_kernel(const Params p) {
         const int sb_q = lane / SB_CHUNKS;  // projection whose scale words this lane copies (valid when < NP)
         const int sb_c = lane % SB_CHUNKS;
         job.sb_lane = sb_q < NP;
+        job.sb_second = sb_q == 1;
+        // 16-row block whose scale words this lane copies: in pair mode the warp's two halves are blocks 2 rb, 2 rb + 1
+        const int sb_blk = !warp_active ? 0 : (pair ? 2 * rb + ((sb_q == 1 && job.second_ok) ? 1 : 0) : rb);
         job.sbsrc = reinterpret_cast<const uint8_t*>(
-            ((sb_q == 1 && FUSED) ? p.sb2 : p.sb1) + (((size_t)e * (p.N / 16) + (warp_active ? rb : 0)) * (n64 * SBW) + G0 * SBW) * 16) + sb_c * 16;
+            ((sb_q == 1 && FUSED && !pair) ? p.sb2 : p.sb1) + (((size_t)e * (p.N / 16) + sb_blk) * (n64 * SBW) + G0 * SBW) * 16) + sb_c * 16;
         const uint32_t wsm_u32 = (uint32_t)__cvta_generic_to_shared(wsm);
         job.wdst = wsm_u32 + (lane >> 2) * W_PITCH + ((col ^ (((lane >> 3) & 1) << 1)) << 4);
         job.sbdst = wsm_u32 + WS::W_BYTES + (sb_q & (NP - 1)) * (STG_RUNS * 64 * SBW) + sb_c * 16;
@@ -606,6 +621,24 @@ grouped_mma_decode_kernel(const Params p) {
         }
 
         // results: value i -> (row g + 8*(i>>1), activation row tok0 + 8j + 2t + (i&1))
+        if (FUSED && pair) {
+            if (warp_active && ks == 0) {
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int q = 0; q < NP; ++q)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int tok = tok0 + 8 * j + 2 * t + (i & 1);
+                            if (tok >= cnt || (q == 1 && !job.second_ok)) continue;
+                            const int n = rb_row + 16 * q + g + 8 * (i >> 1);
+                            float v = tot[j][q][i];
+                            if (p.rb1) v += bf16_bits_to_f32(p.rb1[(size_t)e * p.N + n]);
+                            if (p.out_bf16) reinterpret_cast<uint16_t*>(p.out)[(size_t)(row0 + tok) * p.N + n] = f32_to_bf16_bits(v);
+                            else reinterpret_cast<float*>(p.out)[(size_t)(row0 + tok) * p.N + n] = v;
+                        }
+            }
+        } else
         if (warp_active && ks == 0) {
             float rsum[NT][2];   // FUSED: this lane's two rows' share of sum over the warp's 16 outputs, per activation row
 #pragma unroll
