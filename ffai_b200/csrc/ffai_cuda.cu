@@ -1350,7 +1350,9 @@ int forward_experts_ep_peer(ffai_moe_layer* L, const uint16_t* x, int T, cudaStr
     // the row count is known on the device only: kernels take their ranges from local_off; the path is
     // chosen for a balanced share
     L->ep_rows_dev = local_off + El;
-    if ((rc = run_experts_on_rows(L, M > 0 ? M : 1, El, local_off, st))) return rc;
+    // hint for the kernel choice: this rank's own row count, but not below a small batch (a rank with few or no
+    // tokens of its own may still receive many rows)
+    if ((rc = run_experts_on_rows(L, M > 64 ? M : 64, El, local_off, st))) return rc;
     L->ep_rows_dev = nullptr;
 
     stage_begin(L, ST_EXCHANGE, st);
