@@ -8,6 +8,22 @@ namespace ffai {
 
 #define FFAI_DEVINL __device__ __forceinline__
 
+// The opt-in shared-memory size of a kernel is a per-device attribute.  One of these per kernel
+// instantiation (a function-local static) remembers the largest size set on each device, so a
+// process that drives several GPUs sets it on each of them.
+struct SmemOptIn {
+    int set[64] = {};
+    template <typename K>
+    bool ensure(K kernel, int bytes) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+        if (bytes <= set[dev]) return true;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+        set[dev] = bytes;
+        return true;
+    }
+};
+
 // bf16 bit pattern <-> fp32.  Same rule as FFAI's Tensor.swift:107-113,145-150
 // (round to nearest even on the bit pattern).
 FFAI_DEVINL float bf16_bits_to_f32(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }

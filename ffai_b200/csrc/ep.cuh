@@ -174,26 +174,33 @@ ep_barrier_kernel(int barrier, int me, int world, PeerPtrs win, uint32_t epoch, 
     peer_barrier(win, me, world, barrier, epoch, error_word);
 }
 
-// From the counts matrix (identical on every rank after barrier 0):
+// From the counts matrix [world][n_experts] (identical on every rank after barrier 0): where rank `me`'s rows
+// for expert e start in the row buffer of the rank that owns e.  Rows are grouped by expert, and inside an
+// expert by ascending source rank - the layout plan_exchange gives the NCCL mode.  Host and device share
+// these two functions; the host copy is exported for tests.
+__host__ __device__ inline uint32_t peer_send_base(const uint32_t* matrix, int n_experts, int e_local, int me, int world, int e) {
+    const int first = (e / e_local) * e_local;   // first expert of the owner
+    uint32_t base = 0;
+    for (int ee = first; ee < e; ++ee)
+        for (int s = 0; s < world; ++s) base += matrix[(size_t)s * n_experts + ee];
+    for (int s = 0; s < me; ++s) base += matrix[(size_t)s * n_experts + e];
+    return base;
+}
+// ... and where the rows of rank `me`'s own expert el (0..e_local; e_local gives the total) start in its buffer.
+__host__ __device__ inline uint32_t peer_local_offset(const uint32_t* matrix, int n_experts, int e_local, int me, int world, int el) {
+    uint32_t run = 0;
+    for (int ee = 0; ee < el; ++ee)
+        for (int s = 0; s < world; ++s) run += matrix[(size_t)s * n_experts + me * e_local + ee];
+    return run;
+}
+
 //   local_off[e_local+1]  row ranges of this rank's experts in its own row buffer (all sources, ascending rank)
 //   send_base[n_experts]  where this rank's rows for expert e start in the owner's row buffer
 __global__ void __launch_bounds__(256)
 ep_layout_kernel(const uint32_t* __restrict__ matrix, int n_experts, int e_local, int me, int world,
                  uint32_t* __restrict__ local_off, uint32_t* __restrict__ send_base) {
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-        const int first = (e / e_local) * e_local;   // first expert of the owner
-        uint32_t base = 0;
-        for (int ee = first; ee < e; ++ee)
-            for (int s = 0; s < world; ++s) base += matrix[(size_t)s * n_experts + ee];
-        for (int s = 0; s < me; ++s) base += matrix[(size_t)s * n_experts + e];
-        send_base[e] = base;
-    }
-    for (int el = threadIdx.x; el <= e_local; el += blockDim.x) {
-        uint32_t run = 0;
-        for (int ee = 0; ee < el; ++ee)
-            for (int s = 0; s < world; ++s) run += matrix[(size_t)s * n_experts + me * e_local + ee];
-        local_off[el] = run;
-    }
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) send_base[e] = peer_send_base(matrix, n_experts, e_local, me, world, e);
+    for (int el = threadIdx.x; el <= e_local; el += blockDim.x) local_off[el] = peer_local_offset(matrix, n_experts, e_local, me, world, el);
 }
 
 // Gather fused with the dispatch: sorted row r of this rank (token perm[r]/k, expert indices[perm[r]])

@@ -336,11 +336,8 @@ int launch_router_rows(const RouterParams& p, const uint16_t* x, int T, uint32_t
                         (size_t)ROUTER_ROWS * (p.hidden / 64) * 4 + 2 * (size_t)p.n_experts * 4;
     if (smem > 200 * 1024 || p.hidden % 64 || T > ROUTER_BATCH_TICKET) return -1;
     auto k = router_rows_kernel<KIND>;
-    static size_t attr = 0;
-    if (smem > 48 * 1024 && smem > attr) {
-        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
-        attr = smem;
-    }
+    static SmemOptIn opt_in;
+    if (smem > 48 * 1024 && !opt_in.ensure(k, (int)smem)) return -1;
     dim3 grid((p.n_experts + ROUTER_ROWS - 1) / ROUTER_ROWS, T);
     k<<<grid, 256, smem, st>>>(p, x, T, idx, w, logits, tickets, plan, x_perm8, x_sum64, sum_pitch);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
@@ -376,11 +373,8 @@ void launch_mma_decode_k(const dmma::Params& p, int n_experts, cudaStream_t st) 
     using WS = dmma::WarpStage<FUSED, G32>;
     auto k = dmma::grouped_mma_decode_kernel<FUSED, NT, KSPLIT, G32>;
     const int smem = WS::smem_bytes(p.K / 64, KSPLIT);
-    static int attr_smem = 0;
-    if (smem > attr_smem) {
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        attr_smem = smem;
-    }
+    static SmemOptIn opt_in;
+    opt_in.ensure(k, smem);   // a failure shows as a launch error, which the caller reports
     const int rbw = 4 / KSPLIT;
     const int row_blocks = (FUSED && p.pair) ? (p.N + 31) / 32 : p.N / 16;   // 16-row blocks, or 32-row pairs
     dim3 grid((row_blocks + rbw - 1) / rbw, n_experts);
@@ -915,6 +909,16 @@ extern "C" FFAI_API int ffai_moe_ep_import(ffai_moe_layer* L, const uint8_t* blo
     }
     L->ep_peer_on = true;
     L->ep_epoch = 0;
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_ep_peer_layout(const uint32_t* counts_matrix, int32_t world, int32_t n_experts, int32_t rank,
+                                            uint32_t* local_offsets, uint32_t* send_base) {
+    if (!counts_matrix || !local_offsets || !send_base || world < 1 || n_experts < world || n_experts % world || rank < 0 || rank >= world)
+        return FFAI_ERR_INVALID_ARG;
+    const int el = n_experts / world;
+    for (int e = 0; e < n_experts; ++e) send_base[e] = ep::peer_send_base(counts_matrix, n_experts, el, rank, world, e);
+    for (int i = 0; i <= el; ++i) local_offsets[i] = ep::peer_local_offset(counts_matrix, n_experts, el, rank, world, i);
     return FFAI_OK;
 }
 

@@ -60,11 +60,8 @@ int launch_grouped_gemm(const CUtensorMap& w, const CUtensorMap& w2, const CUten
                         int n_ctas, cudaStream_t st) {
     using L = SmemLayout<WBF16>;
     auto k = grouped_gemm_kernel<FUSED, TOut, WBF16>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) return -1;
-        attr_set = true;
-    }
+    static SmemOptIn opt_in;
+    if (!opt_in.ensure(k, L::TOTAL)) return -1;
     k<<<n_ctas, THREADS, L::TOTAL, st>>>(w, w2, x, p);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -57,3 +57,15 @@ def plan_exchange(recv_counts: np.ndarray) -> Dict[str, np.ndarray]:
                                           local_offsets.ctypes.data, seg_src.ctypes.data, seg_dst.ctypes.data)
     return {"n_rows": int(n), "rank_offsets": rank_offsets, "local_offsets": local_offsets,
             "seg_src": seg_src, "seg_dst": seg_dst}
+
+
+def peer_layout(counts_matrix: np.ndarray, rank: int) -> Dict[str, np.ndarray]:
+    """Layout of the peer-memory exchange for one rank from ``counts_matrix[world, n_experts]`` (the code the
+    device kernel runs, on the host)."""
+    m = np.ascontiguousarray(counts_matrix, dtype=np.uint32)
+    world, n_experts = m.shape
+    local = np.zeros(n_experts // world + 1, dtype=np.uint32)
+    base = np.zeros(n_experts, dtype=np.uint32)
+    capi.check(capi.load().ffai_ep_peer_layout(m.ctypes.data, world, n_experts, rank, local.ctypes.data, base.ctypes.data),
+               "ffai_ep_peer_layout")
+    return {"local_offsets": local, "send_base": base}

@@ -253,6 +253,12 @@ FFAI_API int ffai_moe_ep_import(ffai_moe_layer* layer, const uint8_t* blobs /* [
 /* Unmaps the peers' buffers (after the last step; before any rank destroys its layer, so that no
  * exported buffer is freed while a peer still maps it). */
 FFAI_API int ffai_moe_ep_release(ffai_moe_layer* layer);
+/* The layout the peer-memory exchange derives on the device, computed on the host by the same code (for
+ * tests; needs no GPU): from counts_matrix[world][n_experts] (rows every rank sends to every expert),
+ * local_offsets[n_experts/world + 1] = row ranges of `rank`'s own experts in its row buffer, and
+ * send_base[n_experts] = where `rank`'s rows for each expert start in the owner's row buffer. */
+FFAI_API int ffai_ep_peer_layout(const uint32_t* counts_matrix, int32_t world, int32_t n_experts, int32_t rank,
+                                 uint32_t* local_offsets, uint32_t* send_base);
 /* Host-side plan of one exchange from the per-(source rank, local expert) row counts
  * recv_counts[world][e_local]: where each source's rows start in the receive buffer
  * (rank_offsets[world+1]), the expert-contiguous layout after regrouping (local_offsets[e_local+1]),

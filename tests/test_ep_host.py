@@ -37,6 +37,23 @@ def test_plan_exchange_empty():
     assert p["n_rows"] == 0 and not p["local_offsets"].any() and not p["rank_offsets"].any()
 
 
+def test_peer_layout_agrees_with_the_exchange_plan():
+    """The device-side layout of the peer-memory mode (run here through its host copy) puts every
+    (source rank, expert) segment where the NCCL mode's host plan puts it."""
+    rng = np.random.default_rng(9)
+    for world, e_local in ((2, 4), (4, 8), (8, 32)):
+        E = world * e_local
+        matrix = rng.integers(0, 9, size=(world, E)).astype(np.uint32)     # matrix[s, e]: rows rank s sends to expert e
+        matrix[rng.integers(0, world)] = 0                                   # a rank without tokens
+        for d in range(world):                                               # d: the rank that owns the experts
+            plan = ep.plan_exchange(matrix[:, d * e_local:(d + 1) * e_local])
+            mine = ep.peer_layout(matrix, d)
+            assert np.array_equal(mine["local_offsets"], plan["local_offsets"])
+            for s in range(world):
+                theirs = ep.peer_layout(matrix, s)["send_base"][d * e_local:(d + 1) * e_local]
+                assert np.array_equal(theirs, plan["seg_dst"][s])
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
