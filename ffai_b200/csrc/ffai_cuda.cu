@@ -354,14 +354,33 @@ int launch_router(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx
 }
 
 // returns number of launches, or -1 on error
+// When tile_offsets is given and the one-block form ran, *tiles_done is set and tile_offsets holds the
+// token-tile schedule for tile_rows rows per tile.
 int launch_plan(const uint32_t* indices, int n_rows, int E, uint32_t* counts, uint32_t* offsets,
-                uint32_t* perm, uint32_t* inv_perm, uint32_t* block_hist, cudaStream_t st) {
+                uint32_t* perm, uint32_t* inv_perm, uint32_t* block_hist, cudaStream_t st,
+                int tile_rows = 0, uint32_t* tile_offsets = nullptr, bool* tiles_done = nullptr) {
     if (n_rows <= PLAN_ENTRIES_PER_WARP) {
         plan_small_kernel<<<1, 32, 2 * E * sizeof(uint32_t), st>>>(indices, n_rows, E, counts, offsets,
                                                                   perm, inv_perm);
         return cudaGetLastError() == cudaSuccess ? 1 : -1;
     }
     const int nb = plan_num_blocks(n_rows);
+    if (nb <= PLAN_BLOCK_MAX_WARPS) {
+        const int run_len = plan_block_run_len(n_rows);
+        const int n_warps = (n_rows + run_len - 1) / run_len;
+        const size_t lean_smem = plan_block_smem(n_warps, E, 0), staged_smem = plan_block_smem(n_warps, E, n_rows);
+        const bool staged = staged_smem <= 200 * 1024;
+        const size_t block_smem = staged ? staged_smem : lean_smem;
+        static SmemOptIn opt_in;
+        if (block_smem <= 200 * 1024 && (block_smem <= 48 * 1024 || opt_in.ensure(plan_block_kernel, (int)block_smem))) {
+            const PlanOut o{counts, offsets, perm, inv_perm, nullptr};
+            const bool tiles = tile_offsets != nullptr && tile_rows > 0;
+            plan_block_kernel<<<1, n_warps * 32, block_smem, st>>>(indices, n_rows, E, run_len, o, tile_rows,
+                                                                   tiles ? tile_offsets : nullptr, staged ? 1 : 0);
+            if (tiles && tiles_done) *tiles_done = true;
+            return cudaGetLastError() == cudaSuccess ? 1 : -1;
+        }
+    }
     plan_count_kernel<<<nb, 32, E * sizeof(uint32_t), st>>>(indices, n_rows, E, block_hist);
     plan_scan_kernel<<<1, 256, (E + 1) * sizeof(uint32_t), st>>>(block_hist, nb, E, counts, offsets);
     plan_scatter_kernel<<<nb, 32, E * sizeof(uint32_t), st>>>(indices, n_rows, E, block_hist, perm, inv_perm);
@@ -1385,7 +1404,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     RouterParams rp = router_params(L);
     // small batches: the router kernel's last block also builds the dispatch plan
     const PlanOut fused_plan = (M <= PLAN_ENTRIES_PER_WARP) ? PlanOut{L->counts, L->offsets, L->perm, L->inv_perm, L->expert_order} : PlanOut{nullptr, nullptr, nullptr, nullptr, nullptr};
-    bool plan_done = false;
+    bool plan_done = false, tiles_done = false;
     // 4-bit streaming kernels read per-token rows through the permutation: the rows (8-run permuted) and their
     // 64-run sums are written once per token, by the router kernel when it is the small-batch one
     const uint16_t* xr = L->router_x ? L->router_x : x;   // the router's input rows (its own under a split forward)
@@ -1412,7 +1431,8 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     // stage 1: dispatch plan
     stage_begin(L, ST_PLAN, st);
     if (!plan_done) {
-        int nl = launch_plan(L->indices, M, E, L->counts, L->offsets, L->perm, L->inv_perm, L->block_hist, st);
+        int nl = launch_plan(L->indices, M, E, L->counts, L->offsets, L->perm, L->inv_perm, L->block_hist, st,
+                             tc_group_rows(L), L->tile_offsets, &tiles_done);
         if (nl < 0) return fail(L, FFAI_ERR_CUDA, "plan launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += nl;
     }
@@ -1487,9 +1507,12 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     if (tc_experts) {
         using namespace g100;
         stage_begin(L, ST_GATHER, st);
-        tile_schedule_kernel<<<1, 32, 0, st>>>(L->offsets, E, tc_group_rows(L), L->tile_offsets);
+        if (!tiles_done) {
+            tile_schedule_kernel<<<1, 32, 0, st>>>(L->offsets, E, tc_group_rows(L), L->tile_offsets);
+            L->launches += 1;
+        }
         gather_rows_perm8_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, K, L->xg, M, H);
-        L->launches += 2;
+        L->launches += 1;
         stage_end(L, ST_GATHER, st);
 
         Params p{};

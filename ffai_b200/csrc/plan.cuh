@@ -176,6 +176,123 @@ FFAI_DEVINL void plan_small_warp(const uint32_t* indices, int n_rows, int n_expe
     }
 }
 
+// Medium row counts (a prefill chunk): the three passes in ONE block of up to 32 warps.  Each warp owns a
+// contiguous run of run_len entries (a multiple of 32, at most PLAN_ENTRIES_PER_WARP); the stable order
+// does not depend on how the entries are cut into runs, so the permutation equals the three-launch one.
+// Lanes that hold the same expert find each other through a per-warp word per expert that they OR their
+// lane bit into (commutative, so deterministic); this is several times cheaper than a warp match when
+// most lanes hold different experts.  Shared memory: hist[warps][E] + base[E] + mask[warps][E] words, and with
+// stage_perm another n_rows words: the permutation is then assembled in shared memory and written out in
+// order, because one SM retires scattered 4-byte global stores at about one per clock.
+// When tile_offsets is given it also receives the prefix sum of ceil(count / tile_rows) (the grouped
+// GEMM's token-tile schedule).
+constexpr int PLAN_BLOCK_MAX_WARPS = 32;
+
+__host__ __device__ inline int plan_block_run_len(int n_rows) {
+    const int per_warp = (n_rows + PLAN_BLOCK_MAX_WARPS - 1) / PLAN_BLOCK_MAX_WARPS;
+    return ((per_warp + 31) / 32) * 32;
+}
+__host__ __device__ inline size_t plan_block_smem(int n_warps, int n_experts, int staged_rows) {
+    return ((size_t)(2 * n_warps + 1) * n_experts + (size_t)staged_rows) * sizeof(uint32_t);
+}
+
+__global__ void __launch_bounds__(PLAN_BLOCK_MAX_WARPS * 32)
+plan_block_kernel(const uint32_t* __restrict__ indices, int n_rows, int n_experts, int run_len, PlanOut o,
+                  int tile_rows, uint32_t* __restrict__ tile_offsets, int stage_perm) {
+    extern __shared__ uint32_t sm[];
+    __shared__ uint32_t n_placed_s;
+    const int n_warps = blockDim.x / 32;
+    const int warp = threadIdx.x / 32, lane = threadIdx.x & 31;
+    uint32_t* hist = sm + (size_t)warp * n_experts;                       // this warp's histogram, then its cursors
+    uint32_t* base = sm + (size_t)n_warps * n_experts;                    // [E] totals, then expert offsets
+    uint32_t* mask = sm + (size_t)(n_warps + 1 + warp) * n_experts;       // this warp's lane sets per expert
+    uint32_t* perm_out = stage_perm ? sm + (size_t)(2 * n_warps + 1) * n_experts : o.perm;
+    for (int i = threadIdx.x; i < (2 * n_warps + 1) * n_experts; i += blockDim.x) sm[i] = 0;
+    __syncthreads();
+    const int begin = warp * run_len;
+    const int end = min(begin + run_len, n_rows);
+    // the warp's whole run sits in registers: one round trip to memory instead of one per 32 entries
+    constexpr int PER_LANE = PLAN_ENTRIES_PER_WARP / 32;
+    uint32_t ev[PER_LANE];
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {
+        const int i = begin + j * 32 + lane;
+        ev[j] = (i < end) ? indices[i] : 0xFFFFFFFFu;   // ids out of range (padding or corrupt) are dropped
+    }
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j)
+        if (ev[j] < (uint32_t)n_experts) atomicAdd(&hist[ev[j]], 1u);
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {   // running sum over warps, per expert
+        uint32_t run = 0;
+        for (int w = 0; w < n_warps; ++w) {
+            const uint32_t c = sm[(size_t)w * n_experts + e];
+            sm[(size_t)w * n_experts + e] = run;
+            run += c;
+        }
+        base[e] = run;
+        o.counts[e] = run;
+    }
+    __syncthreads();
+    if (warp == 0) {   // exclusive scans over experts, 32 at a time: rows and token tiles
+        uint32_t carry = 0, tcarry = 0;
+        for (int e0 = 0; e0 < n_experts; e0 += 32) {
+            const int e = e0 + lane;
+            const uint32_t c = (e < n_experts) ? base[e] : 0u;
+            const uint32_t t = tile_offsets ? (c + tile_rows - 1) / tile_rows : 0u;
+            uint32_t incl = c, tincl = t;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                const uint32_t tv = __shfl_up_sync(0xFFFFFFFFu, tincl, d);
+                if (lane >= d) { incl += v; tincl += tv; }
+            }
+            if (e < n_experts) {
+                o.offsets[e] = carry + incl - c;
+                base[e] = carry + incl - c;
+                if (tile_offsets) tile_offsets[e] = tcarry + tincl - t;
+            }
+            carry += __shfl_sync(0xFFFFFFFFu, incl, 31);
+            tcarry += __shfl_sync(0xFFFFFFFFu, tincl, 31);
+        }
+        if (lane == 0) {
+            o.offsets[n_experts] = carry;
+            n_placed_s = carry;
+            if (tile_offsets) tile_offsets[n_experts] = tcarry;
+        }
+    }
+    __syncthreads();
+    for (int e = lane; e < n_experts; e += 32) hist[e] += base[e];
+    __syncwarp();
+    const uint32_t below = (1u << lane) - 1u;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {   // stable scatter of this warp's run, 32 entries at a time
+        if (begin + j * 32 >= end) break;
+        const uint32_t e = ev[j];
+        const bool real = e < (uint32_t)n_experts;
+        if (real) atomicOr(&mask[e], 1u << lane);
+        __syncwarp();
+        const uint32_t peers = real ? mask[e] : 0u;
+        const uint32_t pos = real ? hist[e] + __popc(peers & below) : 0u;
+        __syncwarp();
+        if (real && (peers & below) == 0u) {   // the lowest lane of each expert advances its cursor
+            hist[e] += __popc(peers);
+            mask[e] = 0u;
+        }
+        __syncwarp();
+        if (real) {
+            const uint32_t i = (uint32_t)(begin + j * 32 + lane);
+            perm_out[pos] = i;
+            o.inv_perm[i] = pos;
+        }
+    }
+    if (stage_perm) {
+        __syncthreads();
+        const uint32_t n_placed = n_placed_s;
+        for (uint32_t i = threadIdx.x; i < n_placed; i += blockDim.x) o.perm[i] = perm_out[i];
+    }
+}
+
 // Single-launch variant for small row counts (decode): one warp does all three passes.
 __global__ void plan_small_kernel(const uint32_t* __restrict__ indices, int n_rows, int n_experts,
                                   uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets,

@@ -126,7 +126,7 @@ def test_router_random_bit_exact(ffai_lib, oracle_mod, E, k, mode, norm, use_bia
         assert np.array_equal(gw[t], ow), t
 
 
-@pytest.mark.parametrize("T,k,E", [(1, 8, 128), (16, 2, 8), (64, 4, 32), (300, 8, 128), (2048, 8, 128), (4100, 8, 256)])
+@pytest.mark.parametrize("T,k,E", [(1, 8, 128), (16, 2, 8), (64, 4, 32), (300, 8, 128), (2048, 8, 128), (1500, 2, 8), (4096, 8, 256), (4100, 8, 256)])
 def test_plan_matches_oracle(ffai_lib, oracle_mod, T, k, E):
     import torch
     rng = np.random.default_rng(T)
