@@ -156,18 +156,28 @@ FFAI_DEVINL void plan_small_warp(const uint32_t* indices, int n_rows, int n_expe
             o.order[rank] = (uint32_t)e;
         }
     }
+    // Stable scatter, 32 entries at a time.  Lanes with the same expert find each other by OR-ing their lane
+    // bit into the expert's word (hist, free again after the ranking above); the next 32 ids are in flight
+    // while this group is placed.
+    __syncwarp();
+    for (int e = lane; e < n_experts; e += 32) hist[e] = 0;
+    __syncwarp();
+    const uint32_t below = (1u << lane) - 1u;
+    uint32_t e_next = (lane < n_rows) ? __ldcg(indices + lane) : 0xFFFFFFFFu;
     for (int i0 = 0; i0 < n_rows; i0 += 32) {
         const int i = i0 + lane;
-        const bool valid = i < n_rows;
-        uint32_t e = valid ? __ldcg(indices + i) : 0xFFFFFFFFu;
-        if (valid && e >= (uint32_t)n_experts) e = 0xFFFFFFFEu;
-        const uint32_t peers = __match_any_sync(0xFFFFFFFFu, e);
-        const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
-        const bool real = valid && e < (uint32_t)n_experts;
-        uint32_t pos = 0;
-        if (real) pos = cursor[e] + rank;
+        const uint32_t e = e_next;
+        e_next = (i + 32 < n_rows) ? __ldcg(indices + i + 32) : 0xFFFFFFFFu;
+        const bool real = e < (uint32_t)n_experts;   // padding and corrupt ids are dropped
+        if (real) atomicOr(&hist[e], 1u << lane);
         __syncwarp();
-        if (real && rank == 0) cursor[e] += __popc(peers);
+        const uint32_t peers = real ? hist[e] : 0u;
+        const uint32_t pos = real ? cursor[e] + __popc(peers & below) : 0u;
+        __syncwarp();
+        if (real && (peers & below) == 0u) {
+            cursor[e] += __popc(peers);
+            hist[e] = 0u;
+        }
         __syncwarp();
         if (real) {
             o.perm[pos] = (uint32_t)i;
