@@ -388,6 +388,10 @@ __global__ void __launch_bounds__(TB * 4)
 router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
                            float* __restrict__ logits_out, float* __restrict__ partials) {
     constexpr int EB = 64, LD = 68, NTHR = TB * 4;  // LD: padded row length of the transposed tiles
+    // Column swizzle of the transposed tiles: row r of k-line k sits at column r ^ (((k >> 3) & 7) << 2).  A warp
+    // that stages 4 rows x 8 sixteen-byte pieces then writes 32 different banks (unswizzled it would hit 4), and
+    // a thread's 4 consecutive rows stay one aligned float4.
+    auto swz = [](int k) { return ((k >> 3) & 7) << 2; };
     __shared__ __align__(16) float xs[64 * LD];   // [k][token]
     __shared__ __align__(16) float ws[64 * LD];   // [k][expert]
     const int H = p.hidden, E = p.n_experts;
@@ -413,8 +417,8 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
             const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                xs[(c8 + 2 * j) * LD + row] = bf16lo(w4[j]);
-                xs[(c8 + 2 * j + 1) * LD + row] = bf16hi(w4[j]);
+                xs[(c8 + 2 * j) * LD + (row ^ swz(c8))] = bf16lo(w4[j]);
+                xs[(c8 + 2 * j + 1) * LD + (row ^ swz(c8))] = bf16hi(w4[j]);
             }
         }
         if (KIND == 1) {
@@ -424,8 +428,9 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
                 const int e = e0 + row;
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (e < E) v = *(const float4*)(w + (size_t)e * H + k0 + c4);
-                ws[(c4 + 0) * LD + row] = v.x; ws[(c4 + 1) * LD + row] = v.y;
-                ws[(c4 + 2) * LD + row] = v.z; ws[(c4 + 3) * LD + row] = v.w;
+                const int col = row ^ swz(c4);
+                ws[(c4 + 0) * LD + col] = v.x; ws[(c4 + 1) * LD + col] = v.y;
+                ws[(c4 + 2) * LD + col] = v.z; ws[(c4 + 3) * LD + col] = v.w;
             }
         } else if (KIND == 2) {
             const uint16_t* w = (const uint16_t*)p.weight;
@@ -437,8 +442,8 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
                 const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    ws[(c8 + 2 * j) * LD + row] = bf16lo(w4[j]);
-                    ws[(c8 + 2 * j + 1) * LD + row] = bf16hi(w4[j]);
+                    ws[(c8 + 2 * j) * LD + (row ^ swz(c8))] = bf16lo(w4[j]);
+                    ws[(c8 + 2 * j + 1) * LD + (row ^ swz(c8))] = bf16hi(w4[j]);
                 }
             }
         } else {
@@ -460,9 +465,9 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
                     words[BITS] = 0;
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        ws[(h32 + j) * LD + row] = __fmaf_rn(sc, small_uint_to_float(unpack_at<BITS>(words, j)), bi);
+                        ws[(h32 + j) * LD + (row ^ swz(h32 + j))] = __fmaf_rn(sc, small_uint_to_float(unpack_at<BITS>(words, j)), bi);
                 } else {
-                    for (int j = 0; j < 32; ++j) ws[(h32 + j) * LD + row] = 0.0f;
+                    for (int j = 0; j < 32; ++j) ws[(h32 + j) * LD + (row ^ swz(h32 + j))] = 0.0f;
                 }
             }
         }
@@ -474,8 +479,8 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
             for (int j = 0; j < 4; ++j) part[i][j] = 0.0f;
 #pragma unroll 8
         for (int k = 0; k < 64; ++k) {
-            const float4 xv = *(const float4*)(xs + k * LD + ty * 4);
-            const float4 wv = *(const float4*)(ws + k * LD + tx * 4);
+            const float4 xv = *(const float4*)(xs + k * LD + ((ty * 4) ^ swz(k)));
+            const float4 wv = *(const float4*)(ws + k * LD + ((tx * 4) ^ swz(k)));
             const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
             const float wa[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
