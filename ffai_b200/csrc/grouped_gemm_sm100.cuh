@@ -323,7 +323,7 @@ struct SmemLayout {
     static constexpr int N_BARS = 2 * NW + 2 * NX + 2 * NB + 4;
     static constexpr int TOTAL = OFF_BAR + N_BARS * 8 + 16 + 1024;  // + alignment slack
     static constexpr int TMEM_COLS = 2 * BN;               // two accumulators of 256 fp32 columns
-    static_assert(TOTAL <= 227 * 1024, "shared memory budget");
+    static_assert(TOTAL <= 227 * 1024, "shared memory limit");
 };
 
 // One CTA tile: 128 activation rows (the MMA's M, one TMEM lane each) x 256 weight rows (the MMA's N).
