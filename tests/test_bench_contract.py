@@ -1,0 +1,46 @@
+"""The benchmark's CPU arm prints the one JSON line its callers parse.
+
+`bench.py --impl reference` times the scalar restatement of the reference's arithmetic on the host cores; it
+needs no GPU, so its output contract is checked here on a one-second sample.
+"""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def run_reference_arm(*extra):
+    cmd = [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "3",
+           "--cpu-seconds", "1", *extra]
+    out = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=300, stdin=subprocess.DEVNULL)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1, out.stdout
+    return json.loads(lines[0])
+
+
+def test_reference_arm_line_has_the_contract_keys():
+    d = run_reference_arm()
+    assert d["impl"] == "reference"
+    assert d["metric"] == "moe_layer_tokens_per_s" and d["unit"] == "tokens/s"
+    assert d["higher_is_better"] is True and d["n_gpus"] == 1 and d["steps"] == 1 and d["warmup"] >= 3
+    assert d["value"] > 0 and d["ms_per_step"] > 0
+    assert d["config"]["workload"] == "cfg2_b64"          # the default workload of both arms
+    assert d["vs_baseline"] is None
+    cb = d["cpu_baseline"]
+    assert cb["kind"] in ("port", "reference") and cb["cores"] >= 1 and cb["value"] == d["value"] and cb["sample"]
+    e2e = d["e2e"]
+    assert e2e["value"] == d["value"] and e2e["unit"] == d["unit"]
+    assert e2e["h2d_bytes_per_step"] == 0 and e2e["d2h_bytes_per_step"] == 0
+
+
+def test_reference_arm_under_a_multi_rank_launch_only_rank_zero_prints():
+    env = dict(os.environ, RANK="1", LOCAL_RANK="1", WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT="29577")
+    cmd = [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
+           "--cpu-seconds", "1"]
+    out = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=300,
+                         stdin=subprocess.DEVNULL)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert not [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
