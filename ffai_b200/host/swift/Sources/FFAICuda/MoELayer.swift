@@ -73,4 +73,43 @@ public final class MoELayer {
         let rc = ffai_moe_forward(handle, hFlat, Int32(t), out, residual, nil, stream)
         if rc != 0 { throw FFAICudaError(status: rc, message: String(cString: ffai_moe_last_error(handle))) }
     }
+
+    /// Gemma4MoEFFN.forward — Gemma4Text.swift:928-980: the router reads its own normalised rows,
+    /// the experts read `hExperts`.  `hRouter == nil` means `hExperts`.
+    public func decodeManySplit(_ hExperts: UnsafePointer<UInt16>, router hRouter: UnsafePointer<UInt16>?, t: Int,
+                                out: UnsafeMutablePointer<UInt16>, residual: UnsafePointer<UInt16>? = nil,
+                                stream: UnsafeMutableRawPointer?) throws {
+        precondition(t > 0, "MoELayer.decodeManySplit: T must be positive")
+        let rc = ffai_moe_forward_split(handle, hExperts, hRouter, Int32(t), out, residual, nil, stream)
+        if rc != 0 { throw FFAICudaError(status: rc, message: String(cString: ffai_moe_last_error(handle))) }
+    }
+
+    /// Execution options ("path", "ksplit", "tc_min_rows", …) — the `FFAI_MOE_*` environment
+    /// switches of MoELayer.swift:486-497.
+    public func setOption(_ name: String, _ value: Int) throws {
+        let rc = name.withCString { ffai_moe_set_option(handle, $0, Int32(value)) }
+        if rc != 0 { throw FFAICudaError(status: rc, message: "ffai_moe_set_option(\(name))") }
+    }
+
+    /// Expert parallelism over peer memory (no counterpart in the reference): every rank exports, the
+    /// caller hands all blobs to every rank in rank order, every rank imports; release on every rank
+    /// before any rank's layer is destroyed.
+    public func exportPeerBuffers() throws -> [UInt8] {
+        var blob = [UInt8](repeating: 0, count: Int(FFAI_EP_EXPORT_BYTES))
+        let rc = ffai_moe_ep_export(handle, &blob)
+        if rc != 0 { throw FFAICudaError(status: rc, message: String(cString: ffai_moe_last_error(handle))) }
+        return blob
+    }
+
+    public func importPeerBuffers(_ allBlobs: [UInt8]) throws {
+        precondition(!allBlobs.isEmpty && allBlobs.count % Int(FFAI_EP_EXPORT_BYTES) == 0,
+                     "MoELayer.importPeerBuffers: expected ep_world blobs of FFAI_EP_EXPORT_BYTES")
+        let rc = ffai_moe_ep_import(handle, allBlobs)
+        if rc != 0 { throw FFAICudaError(status: rc, message: String(cString: ffai_moe_last_error(handle))) }
+    }
+
+    public func releasePeerBuffers() throws {
+        let rc = ffai_moe_ep_release(handle)
+        if rc != 0 { throw FFAICudaError(status: rc, message: String(cString: ffai_moe_last_error(handle))) }
+    }
 }
