@@ -27,7 +27,8 @@ def test_reference_arm_line_has_the_contract_keys():
     assert d["metric"] == "moe_layer_tokens_per_s" and d["unit"] == "tokens/s"
     assert d["higher_is_better"] is True and d["n_gpus"] == 1 and d["steps"] == 1 and d["warmup"] >= 3
     assert d["value"] > 0 and d["ms_per_step"] > 0
-    assert d["config"]["workload"] == "cfg2_b64"          # the default workload of both arms
+    assert d["config"]["workload"] == "cfg4"              # the default workload of both arms
+    assert d["scaling"] == "strong" and d["config"]["tokens_per_step"] == 8192
     assert d["vs_baseline"] is None
     cb = d["cpu_baseline"]
     assert cb["kind"] in ("port", "reference") and cb["cores"] >= 1 and cb["value"] == d["value"] and cb["sample"]

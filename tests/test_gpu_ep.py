@@ -30,7 +30,7 @@ def test_two_gpu_expert_parallel_matches_oracle_and_single_gpu(tmp_path, ffai_li
     logs = []
     for out, p in procs:
         try:
-            log, _ = p.communicate(timeout=300)
+            log, _ = p.communicate(timeout=600)
         except subprocess.TimeoutExpired:
             p.kill()
             raise
@@ -39,7 +39,7 @@ def test_two_gpu_expert_parallel_matches_oracle_and_single_gpu(tmp_path, ffai_li
     for out, _ in procs:
         res = json.loads(out.read_text())
         assert res["status"] == "ok", res["status"]
-        assert len(res["cases"]) >= 8
+        assert len(res["cases"]) >= 9
         for c in res["cases"]:
             if not c["tokens"]:
                 continue
@@ -47,7 +47,8 @@ def test_two_gpu_expert_parallel_matches_oracle_and_single_gpu(tmp_path, ffai_li
             assert c["repeatable"], c
             assert c["rel_rms"] <= 5e-3 and c["max_abs_norm"] <= 2e-2, c
             assert c["rel_rms_vs_single_gpu"] <= 5e-3, c
-            if "peer_equals_nccl" in c:
+            if "peer_launches" in c:     # the same step with the exchange over peer memory
                 assert c["peer_repeatable"] and c["peer_routing_exact"], c
                 assert c["peer_rel_rms"] <= 5e-3 and c["peer_max_abs_norm"] <= 2e-2, c
-        assert sum("peer_launches" in c for c in res["cases"]) >= 4
+                assert c["peer_rel_rms_vs_nccl"] <= 5e-3, c
+        assert sum("peer_launches" in c and c["tokens"] > 0 for c in res["cases"]) >= 5

@@ -408,3 +408,23 @@ def test_cfg5_skewed_routing_every_bit_width(oracle_mod, bits):
     mask = np.zeros(1024, dtype=np.uint8)
     mask[np.random.default_rng(bits).choice(1024, size=32, replace=False)] = 1
     run_and_check(oracle_mod, synth.cfg5_skewed(bits), 1024, token_mask=mask)
+
+
+def test_cfg4_at_its_full_size(oracle_mod):
+    """The 256-expert configuration at its 8192 tokens (65536 routed rows: the dispatch plan takes its
+    count / scan / scatter form): routing and plan for every token, outputs for 32 sampled tokens."""
+    mask = np.zeros(8192, dtype=np.uint8)
+    mask[np.random.default_rng(44).choice(8192, size=32, replace=False)] = 1
+    run_and_check(oracle_mod, synth.cfg4_shared(), 8192, token_mask=mask)
+
+
+def test_cfg5_at_its_full_size_with_requantized_experts(oracle_mod):
+    """The skewed configuration as it is described: the 4-bit layer of the cfg3 shape, its experts
+    re-quantised at another width (5 bits here) from their dequantised values, Zipf router bias, 16384
+    tokens (131072 routed rows); routing and plan for every token, outputs for 32 sampled tokens."""
+    base = synth.make_layer(synth.cfg5_skewed(4), 0)
+    host = synth.requantize_experts(base, 5)
+    assert host.spec.expert_bits == 5
+    mask = np.zeros(16384, dtype=np.uint8)
+    mask[np.random.default_rng(55).choice(16384, size=32, replace=False)] = 1
+    run_and_check(oracle_mod, host.spec, 16384, host=host, token_mask=mask)

@@ -3,8 +3,8 @@
 `ffai_op_moe_plan_static` exists for hosts that own every byte of device memory and do not let a
 plug-in call the CUDA allocator once they are serving (a server with a pre-sized arena, for
 instance).  It keeps its scratch in a fixed array inside the library instead of taking a workspace.
-Its results must be identical to `ffai_op_moe_plan` (integers: exact), on the first call and on a
-second call that finds the previous call's contents in the array.  The file name sorts last so a
+Its results must be identical to the CPU oracle's plan and to `ffai_op_moe_plan` (integers: exact), on the
+first call and on later calls that find the previous call's contents in the array.  The file name sorts last so a
 run that stops at the first failure has already run every other test.
 """
 import numpy as np
@@ -37,12 +37,18 @@ def _plan(lib, fn_static, idx, T, k, E):
     return [from_dev(t, np.uint32) for t in (counts, offsets, perm, inv)]
 
 
-def test_static_plan_matches_workspace_plan_twice_in_a_row(ffai_lib):
+def test_static_plan_matches_oracle_and_workspace_plan_twice_in_a_row(ffai_lib, oracle_mod):
+    """Both problems hold more than 32768 routed rows, so the count / scan / scatter form runs: the only
+    reader of the library-resident array.  The second problem has another shape, and each is planned twice,
+    so every call after the first finds the previous call's counters in the array."""
     rng = np.random.default_rng(11)
-    # two different problems back to back: the second call finds the first call's counters in the array
-    for T, k, E in ((3000, 8, 128), (1500, 4, 32)):
+    for T, k, E in ((8192, 8, 256), (5000, 8, 64)):
+        assert T * k > 32768
         idx = np.stack([rng.choice(E, size=k, replace=False) for _ in range(T)]).astype(np.uint32)
-        want = _plan(ffai_lib, False, idx, T, k, E)
+        want = oracle_mod.plan(idx, T, k, E)
+        regular = _plan(ffai_lib, False, idx, T, k, E)
+        for a, b in zip(regular, want):
+            assert np.array_equal(a, b)
         for _ in range(2):
             got = _plan(ffai_lib, True, idx, T, k, E)
             for a, b in zip(got, want):
