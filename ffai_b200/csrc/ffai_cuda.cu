@@ -17,6 +17,7 @@
 #include "expert_gemv.cuh"
 #include "ep.cuh"
 #include "expert_mma_decode.cuh"
+#include "expert_stream_decode.cuh"
 #include "plan.cuh"
 #include "router.cuh"
 #include "safetensors.hpp"
@@ -60,7 +61,6 @@ struct ffai_moe_layer {
     int n_sms = 0;
     int opt_path = 0;                // 0 auto, 1 CUDA-core GEMV, 2 tcgen05 grouped GEMM, 3 register-streaming decode
     int opt_tc_min_rows = 0;         // auto: smallest T*k routed through the tensor-core path
-    int opt_debug = 0;               // timing experiments (see g100::Params::debug_flags)
     int opt_ksplit = 0;              // streaming kernels: 0 automatic, else 1, 2 or 4 reduction slices
     long long* timeline = nullptr;   // device buffer for the gate/up kernel's CTA-0 timeline (option "timeline")
     uint16_t* xg = nullptr;          // [M,H]  expert-contiguous input rows (8-run permuted)
@@ -76,6 +76,11 @@ struct ffai_moe_layer {
     const uint16_t* router_x = nullptr;  // set for the duration of a split forward: the router's own input rows
     uint16_t* dev_xr = nullptr;          // host-buffer entry point: device copy of the router input
     bool mma_ok = false;             // register-streaming decode kernels usable (4-bit, group 64/128)
+    uint8_t* st_gate_up = nullptr;   // bulk-copy streams of the decode kernels: gate and up interleaved per 64-run, ...
+    uint8_t* st_down = nullptr;      // ... and down (re-tiled copies of the packed experts, owned with the weights)
+    int opt_decode = 0;              // decode kernels: 0 automatic, 1 per-lane cp.async rings, 2 bulk-copy streams
+    int opt_decode_team = 0;         // bulk-copy streams: warps per 16-row block (0 automatic, 1, 4, 16)
+    int opt_nt2_cost = 12;           // bulk-copy streams: schedule weight of an item with more than 8 rows (8 = as one with fewer)
     uint32_t* sb_gate = nullptr;     // repacked (scale | bias << 16) words of the expert projections
     uint32_t* sb_up = nullptr;
     uint32_t* sb_down = nullptr;
@@ -419,6 +424,27 @@ template <bool FUSED>
 void launch_mma_decode(const dmma::Params& p, int n_experts, int nt, int ksplit, cudaStream_t st) {
     if (p.group_size == 32) launch_mma_decode_g<FUSED, true>(p, n_experts, nt, ksplit, st);
     else launch_mma_decode_g<FUSED, false>(p, n_experts, nt, ksplit, st);
+}
+
+// Bulk-copy streamed decode kernels.  team: warps that share one 16-row block (4, or 16 for the smallest batches).
+// Returns false when the shape does not fit the kernel's shared memory (the caller then uses the cp.async kernels).
+template <bool FUSED, int TEAM, int CPU, int DEPTH>
+bool launch_stream_decode_t(const dstr::Params& p, int n_sms, cudaStream_t st) {
+    using LY = dstr::Layout<FUSED, TEAM, CPU, DEPTH>;
+    const int smem = LY::total(p.n_experts, p.K);
+    if (smem > 227 * 1024) return false;
+    auto k = dstr::stream_decode_kernel<FUSED, TEAM, CPU, DEPTH>;
+    static SmemOptIn opt_in;
+    if (!opt_in.ensure(k, smem)) return false;
+    k<<<n_sms, dstr::THREADS, smem, st>>>(p);
+    return true;
+}
+template <bool FUSED>
+bool launch_stream_decode(const dstr::Params& p, int team, int n_sms, cudaStream_t st) {
+    constexpr int CPU2 = FUSED ? 1 : 2;
+    if (team == 16) return launch_stream_decode_t<FUSED, 16, 1, 5>(p, n_sms, st) || launch_stream_decode_t<FUSED, 16, 1, 3>(p, n_sms, st);
+    if (team == 4) return launch_stream_decode_t<FUSED, 4, CPU2, 5>(p, n_sms, st) || launch_stream_decode_t<FUSED, 4, CPU2, 3>(p, n_sms, st);
+    return launch_stream_decode_t<FUSED, 1, CPU2, 6>(p, n_sms, st) || launch_stream_decode_t<FUSED, 1, CPU2, 3>(p, n_sms, st);
 }
 
 // dense [1,H] projection per token (shared-expert gate stored as f32 / bf16)
@@ -867,6 +893,30 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
         if ((rc = repack(L->w.down_proj, c.hidden, c.intermediate, &L->sb_down))) return rc;
         CUDA_TRY(L, cudaDeviceSynchronize());
     }
+    // re-tiled streams for the bulk-copy decode kernels (group 64 / 128; same bytes as the packed experts + scale words)
+    L->st_gate_up = L->st_down = nullptr;
+    if (L->mma_ok && c.expert_group_size != 32) {
+        const size_t H = c.hidden, I = c.intermediate;
+        const size_t gu_cells = (size_t)El * (I / 16) * (H / 64), dn_cells = (size_t)El * (H / 16) * (I / 64);
+        if (gu_cells < (1u << 31) && dn_cells < (1u << 31)) {
+            void* a = nullptr;
+            void* b = nullptr;
+            CUDA_TRY(L, cudaMalloc(&a, gu_cells * 2 * dstr::CELL));
+            L->owned_weights.push_back(a);
+            CUDA_TRY(L, cudaMalloc(&b, dn_cells * dstr::CELL));
+            L->owned_weights.push_back(b);
+            dstr::retile_stream_kernel<<<(unsigned)gu_cells, 96>>>(L->w.gate_proj.weight, L->w.gate_proj.scales, L->w.gate_proj.biases,
+                                                                   L->w.up_proj.weight, L->w.up_proj.scales, L->w.up_proj.biases,
+                                                                   static_cast<uint8_t*>(a), (int)I, (int)H, c.expert_group_size);
+            dstr::retile_stream_kernel<<<(unsigned)dn_cells, 64>>>(L->w.down_proj.weight, L->w.down_proj.scales, L->w.down_proj.biases,
+                                                                   nullptr, nullptr, nullptr, static_cast<uint8_t*>(b), (int)H, (int)I,
+                                                                   c.expert_group_size);
+            CUDA_TRY(L, cudaGetLastError());
+            CUDA_TRY(L, cudaDeviceSynchronize());
+            L->st_gate_up = static_cast<uint8_t*>(a);
+            L->st_down = static_cast<uint8_t*>(b);
+        }
+    }
     L->weights_set = true;
     return FFAI_OK;
 }
@@ -1011,8 +1061,19 @@ extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name,
         L->opt_ksplit = value;
         return FFAI_OK;
     }
-    if (!strcmp(name, "debug")) {
-        L->opt_debug = value;
+    if (!strcmp(name, "decode")) {
+        if (value < 0 || value > 2) return fail(L, FFAI_ERR_INVALID_ARG, "option decode must be 0 (automatic), 1 (cp.async rings) or 2 (bulk-copy streams)");
+        L->opt_decode = value;
+        return FFAI_OK;
+    }
+    if (!strcmp(name, "decode_team")) {
+        if (value != 0 && value != 1 && value != 4 && value != 16) return fail(L, FFAI_ERR_INVALID_ARG, "option decode_team must be 0, 1, 4 or 16");
+        L->opt_decode_team = value;
+        return FFAI_OK;
+    }
+    if (!strcmp(name, "nt2_cost")) {
+        if (value < 8 || value > 32) return fail(L, FFAI_ERR_INVALID_ARG, "option nt2_cost must be in 8..32");
+        L->opt_nt2_cost = value;
         return FFAI_OK;
     }
     if (!strcmp(name, "timeline")) {
@@ -1469,6 +1530,36 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         }
         stage_end(L, ST_GATHER, st);
 
+        // Which decode kernels: the bulk-copy streamed ones (a warp owns a 16-row block; the batch sizes where they
+        // measure faster on the GPT-OSS shape: more than 8 and at most 160 routed rows), else the cp.async ring kernels.
+        const bool stream = L->st_gate_up && (L->opt_decode == 2 || (L->opt_decode == 0 && M > 8 && M <= 160));
+        bool streamed = false;
+        if (stream) {
+            dstr::Params q{};
+            q.n_experts = E; q.offsets = L->offsets; q.order = plan_done ? L->expert_order : nullptr;
+            q.activation = c.activation; q.limit = c.swiglu_limit; q.alpha = c.swiglu_alpha;
+            q.nt2_cost = L->opt_nt2_cost; q.error_word = L->error_word;
+            // warps that share one 16-row block: one, unless the batch is so small that whole items are too few for the grid
+            const int team = L->opt_decode_team ? L->opt_decode_team : (M <= 8 ? 4 : 1);
+            stage_begin(L, ST_GATE_UP, st);
+            q.wt = L->st_gate_up; q.rb1 = L->w.gate_proj.row_bias; q.rb2 = L->w.up_proj.row_bias;
+            q.N = I; q.K = H; q.x = L->x_tok; q.row_src = L->perm; q.row_div = K; q.xsum = L->xsum_tok; q.xsum_pitch = xp_h;
+            q.out = L->inner_bf; q.out_parts = L->inner_parts;
+            streamed = launch_stream_decode<true>(q, team, L->n_sms, st);
+            stage_end(L, ST_GATE_UP, st);
+            if (streamed) {
+                stage_begin(L, ST_DOWN, st);
+                q.wt = L->st_down; q.rb1 = L->w.down_proj.row_bias; q.rb2 = nullptr;
+                q.N = H; q.K = I; q.x = L->inner_bf; q.row_src = nullptr; q.row_div = 1; q.xsum = nullptr; q.xsum_parts = L->inner_parts;
+                q.out = L->y; q.out_parts = nullptr;
+                streamed = launch_stream_decode<false>(q, team, L->n_sms, st);
+                stage_end(L, ST_DOWN, st);
+                if (!streamed) return fail(L, FFAI_ERR_UNSUPPORTED, "down projection does not fit the streamed decode kernel");
+                L->launches += 2;
+            }
+            if (cudaGetLastError() != cudaSuccess) return fail(L, FFAI_ERR_CUDA, "decode kernels launch failed");
+        }
+        if (!streamed) {
         Params p{};
         p.group_size = c.expert_group_size;
         p.offsets = L->offsets;
@@ -1503,6 +1594,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         L->launches += 1;
         stage_end(L, ST_DOWN, st);
         if (cudaGetLastError() != cudaSuccess) return fail(L, FFAI_ERR_CUDA, "decode kernels launch failed");
+        }
     } else
     if (tc_experts) {
         using namespace g100;
@@ -1520,7 +1612,6 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         p.offsets = L->offsets; p.tile_offsets = L->tile_offsets; p.group_rows = tc_group_rows(L);
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
         p.error_word = L->error_word;
-        p.debug_flags = L->opt_debug;
         p.timeline = L->timeline;
         if (L->timeline) cudaMemsetAsync(L->timeline, 0, sizeof(long long) * g100::TL_ROLES * g100::TL_SLOTS * g100::TL_EVENTS, st);
 

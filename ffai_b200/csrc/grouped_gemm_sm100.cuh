@@ -81,7 +81,6 @@ struct Params {
     int out_ld;
     int out_permute8;          // 1: store column n at (n & ~7) | {0,2,4,6,1,3,5,7}[n & 7]
     uint32_t* error_word;
-    int debug_flags;           // timing experiments only (results invalid): 1 no proxy fence, 2 no unpack/store, 4 no MMA
     long long* timeline;       // nullable: CTA 0 records clock64() per role / k block / event (TL_* layout)
 };
 
