@@ -157,6 +157,7 @@ SIGNATURES = {
     "ffai_moe_ep_export": (C.c_int, [_P, _P]),
     "ffai_moe_ep_import": (C.c_int, [_P, _P]),
     "ffai_moe_ep_release": (C.c_int, [_P]),
+    "ffai_moe_ep_skip_step": (C.c_int, [_P]),
     "ffai_ep_peer_layout": (C.c_int, [_P, _I, _I, _I, _P, _P]),
     "ffai_ep_get_unique_id": (C.c_int, [_P]),
     "ffai_ep_comm_create": (C.c_int, [_P, _I, _I, C.POINTER(_P)]),

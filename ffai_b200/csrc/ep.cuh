@@ -119,7 +119,7 @@ __global__ void copy_segments_kernel(const uint8_t* __restrict__ src, uint8_t* _
 // with a time limit; on expiry the kernel records an error word and returns.
 constexpr int EP_MAX_WORLD = 16;
 constexpr int EP_BARRIERS = 3;
-constexpr uint64_t EP_WAIT_LIMIT_NS = 2000000000ull;
+constexpr uint64_t EP_WAIT_LIMIT_NS = 2000000000ull;   // default limit of a barrier wait (a per-layer option overrides it)
 enum : uint32_t { EP_ERR_BARRIER_TIMEOUT = 16, EP_ERR_CAPACITY = 17 };
 
 struct PeerPtrs {
@@ -134,7 +134,7 @@ inline size_t win_words(int world, int n_experts) { return (size_t)EP_BARRIERS *
 // Tell every peer this rank reached `barrier` of step `epoch`, then wait (bounded) for all of them.
 // Called by one block; threads 0..world-1 take one peer each.  Writes before the call are made
 // visible system-wide first.
-FFAI_DEVINL void peer_barrier(const PeerPtrs& win, int me, int world, int barrier, uint32_t epoch, uint32_t* error_word) {
+FFAI_DEVINL void peer_barrier(const PeerPtrs& win, int me, int world, int barrier, uint32_t epoch, uint64_t limit_ns, uint32_t* error_word) {
     __threadfence_system();
     __syncthreads();
     if ((int)threadIdx.x < world) {
@@ -148,7 +148,7 @@ FFAI_DEVINL void peer_barrier(const PeerPtrs& win, int me, int world, int barrie
                 uint64_t now;
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
                 if (t0 == 0) t0 = now;
-                else if (now - t0 > EP_WAIT_LIMIT_NS) {
+                else if (now - t0 > limit_ns) {
                     atomicExch(error_word, EP_ERR_BARRIER_TIMEOUT);
                     break;
                 }
@@ -161,17 +161,17 @@ FFAI_DEVINL void peer_barrier(const PeerPtrs& win, int me, int world, int barrie
 
 __global__ void __launch_bounds__(256)
 ep_publish_counts_kernel(const uint32_t* __restrict__ counts, int n_experts, int me, int world, PeerPtrs win,
-                         uint32_t epoch, uint32_t* error_word) {
+                         uint32_t epoch, uint64_t limit_ns, uint32_t* error_word) {
     for (int d = 0; d < world; ++d) {
         uint32_t* row = win_matrix(win.p[d]) + (size_t)me * n_experts;
         for (int e = threadIdx.x; e < n_experts; e += blockDim.x) row[e] = counts[e];
     }
-    peer_barrier(win, me, world, 0, epoch, error_word);
+    peer_barrier(win, me, world, 0, epoch, limit_ns, error_word);
 }
 
 __global__ void __launch_bounds__(32)
-ep_barrier_kernel(int barrier, int me, int world, PeerPtrs win, uint32_t epoch, uint32_t* error_word) {
-    peer_barrier(win, me, world, barrier, epoch, error_word);
+ep_barrier_kernel(int barrier, int me, int world, PeerPtrs win, uint32_t epoch, uint64_t limit_ns, uint32_t* error_word) {
+    peer_barrier(win, me, world, barrier, epoch, limit_ns, error_word);
 }
 
 // From the counts matrix [world][n_experts] (identical on every rank after barrier 0): where rank `me`'s rows
@@ -196,11 +196,20 @@ __host__ __device__ inline uint32_t peer_local_offset(const uint32_t* matrix, in
 
 //   local_off[e_local+1]  row ranges of this rank's experts in its own row buffer (all sources, ascending rank)
 //   send_base[n_experts]  where this rank's rows for expert e start in the owner's row buffer
+// Offsets are clamped to the row buffer's capacity (and the error word raised) so that a matrix left half-updated
+// by a barrier that gave up cannot send the expert kernels past the buffer.
 __global__ void __launch_bounds__(256)
 ep_layout_kernel(const uint32_t* __restrict__ matrix, int n_experts, int e_local, int me, int world,
-                 uint32_t* __restrict__ local_off, uint32_t* __restrict__ send_base) {
+                 uint32_t* __restrict__ local_off, uint32_t* __restrict__ send_base, uint32_t capacity, uint32_t* error_word) {
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) send_base[e] = peer_send_base(matrix, n_experts, e_local, me, world, e);
-    for (int el = threadIdx.x; el <= e_local; el += blockDim.x) local_off[el] = peer_local_offset(matrix, n_experts, e_local, me, world, el);
+    for (int el = threadIdx.x; el <= e_local; el += blockDim.x) {
+        uint32_t v = peer_local_offset(matrix, n_experts, e_local, me, world, el);
+        if (v > capacity) {
+            v = capacity;
+            atomicExch(error_word, EP_ERR_CAPACITY);
+        }
+        local_off[el] = v;
+    }
 }
 
 // Gather fused with the dispatch: sorted row r of this rank (token perm[r]/k, expert indices[perm[r]])
@@ -240,7 +249,7 @@ combine_peer_kernel(PeerPtrs y_of, const uint32_t* __restrict__ inv_perm, const 
                     const uint32_t* __restrict__ offsets, const uint32_t* __restrict__ send_base, int e_local,
                     const float* __restrict__ weights, int k, const float* __restrict__ shared_y,
                     const float* __restrict__ shared_gate_logit, const uint16_t* __restrict__ residual,
-                    uint16_t* __restrict__ out, int hidden) {
+                    uint16_t* __restrict__ out, int hidden, uint32_t capacity, uint32_t* error_word) {
     const int t = blockIdx.x;
     __shared__ const uint16_t* row_s[32];
     __shared__ float w_s[32];
@@ -248,9 +257,15 @@ combine_peer_kernel(PeerPtrs y_of, const uint32_t* __restrict__ inv_perm, const 
     if ((int)threadIdx.x < k) {
         const size_t slot = (size_t)t * k + threadIdx.x;
         const uint32_t e = indices[slot];
-        const uint32_t pos = send_base[e] + (inv_perm[slot] - offsets[e]);
+        uint32_t pos = send_base[e] + (inv_perm[slot] - offsets[e]);
+        float w = weights[slot];
+        if (pos >= capacity) {   // only after a barrier gave up: the row is left out, the error word says so
+            atomicExch(error_word, EP_ERR_CAPACITY);
+            pos = 0;
+            w = 0.0f;
+        }
         row_s[threadIdx.x] = static_cast<const uint16_t*>(y_of.p[e / (uint32_t)e_local]) + (size_t)pos * hidden;
-        w_s[threadIdx.x] = weights[slot];
+        w_s[threadIdx.x] = w;
     }
     if (threadIdx.x == 0) {
         float sig = 1.0f;

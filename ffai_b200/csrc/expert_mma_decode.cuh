@@ -74,28 +74,6 @@ FFAI_DEVINL size_t src_row(const Params& p, int r) {
     return p.row_src ? (size_t)(__ldg(p.row_src + r) / (uint32_t)p.row_div) : (size_t)r;
 }
 
-// One packed word -> 4 bf16 pairs (128+n0,128+n4), (128+n1,128+n5), (128+n2,128+n6), (128+n3,128+n7).
-// The three right shifts are written as high halves of 32x32 multiplies (w >> s == mulhi(w, 2^(32-s))):
-// integer multiplies issue on the FMA pipe, which is nearly idle here, while shifts and logic ops
-// share the half-rate ALU pipe that bounds this kernel.
-FFAI_DEVINL uint32_t shr_mul(uint32_t w, uint32_t pow2) {
-    uint32_t r;
-    asm("mul.hi.u32 %0, %1, %2;" : "=r"(r) : "r"(w), "r"(pow2));
-    return r;
-}
-FFAI_DEVINL void unpack_word_128(uint32_t w, uint32_t* o) {
-    o[0] = (w & 0x000F000Fu) | 0x43004300u;
-    o[1] = (shr_mul(w, 1u << 28) & 0x000F000Fu) | 0x43004300u;
-    o[2] = (shr_mul(w, 1u << 24) & 0x000F000Fu) | 0x43004300u;
-    o[3] = (shr_mul(w, 1u << 20) & 0x000F000Fu) | 0x43004300u;
-}
-
-FFAI_DEVINL uint2 ld_stream_u2(const uint32_t* p) {
-    uint2 v;
-    asm volatile("ld.global.cs.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
-
 FFAI_DEVINL int permute8_col(int n) {
     const int k = n & 7;
     return (n & ~7) | (((k & 3) << 1) | (k >> 2));
@@ -165,17 +143,12 @@ FFAI_DEVINL uint32_t and_or(uint32_t w, uint32_t mask, uint32_t expo) {
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "r"(mask), "r"(expo));
     return r;
 }
-#ifndef FFAI_DM_ALU_SHIFTS
-#define FFAI_DM_ALU_SHIFTS 3   // how many of the three shifts per word go to the logic pipe instead of the multiplier
-#endif
+// One packed word -> 4 bf16 pairs (128+n0,128+n4), (128+n1,128+n5), (128+n2,128+n6), (128+n3,128+n7).
 FFAI_DEVINL void unpack_word_128r(uint32_t w, uint32_t* o, uint32_t mask, uint32_t expo) {
-#ifdef FFAI_DM_EXP_NOUNPACK
-    o[0] = w; o[1] = w ^ mask; o[2] = w ^ expo; o[3] = w; return;
-#endif
     o[0] = and_or(w, mask, expo);
-    o[1] = and_or(FFAI_DM_ALU_SHIFTS >= 1 ? (w >> 4) : shr_mul(w, 1u << 28), mask, expo);
-    o[2] = and_or(FFAI_DM_ALU_SHIFTS >= 2 ? (w >> 8) : shr_mul(w, 1u << 24), mask, expo);
-    o[3] = and_or(FFAI_DM_ALU_SHIFTS >= 3 ? (w >> 12) : shr_mul(w, 1u << 20), mask, expo);
+    o[1] = and_or(w >> 4, mask, expo);
+    o[2] = and_or(w >> 8, mask, expo);
+    o[3] = and_or(w >> 12, mask, expo);
 }
 // 16-byte asynchronous copy that reads `bytes` (16 or 0) from the source and zero-fills the rest.
 FFAI_DEVINL void cp_async16_zfill(uint32_t dst, const void* src, uint32_t bytes) {
@@ -258,7 +231,6 @@ FFAI_DEVINL void compute_run(const uint8_t* stage, const uint32_t* rd, const uin
                     else mma_bf16_16816(c, a, xb[w][2 * hp], xb[w][2 * hp + 1]);
                 }
                 if (G32 || w == 1) {
-                    constexpr int dummy = 0; (void)dummy;
                     const int hf = G32 ? w : 0;
                     tot[j][q][0] = fmaf(sc[hf][0], c[0], fmaf(bm[hf][0], sx[hf][j].x, tot[j][q][0]));
                     tot[j][q][1] = fmaf(sc[hf][0], c[1], fmaf(bm[hf][0], sx[hf][j].y, tot[j][q][1]));
@@ -333,9 +305,7 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
             cp_async16_zfill(job.sbdst + issue_slot, job.sbsrc + issue_off * (2 * SBW),
                              ((int)sb_run < issue_rem && !(job.sb_second && !job.second_ok)) ? 16u : 0u);
         cp_async_commit();
-#ifndef FFAI_DM_EXP_NOW
         issue_off += 64;
-#endif
         issue_rem -= STG_RUNS;
         issue_slot = issue_slot == (DEPTH - 1) * WS::STAGE ? 0u : issue_slot + WS::STAGE;
     };
@@ -368,14 +338,10 @@ FFAI_DEVINL void decode_pass(const Params& p, const WarpJob<FUSED>& job, uint8_t
         use_slot = use_slot == (DEPTH - 1) * WS::STAGE ? 0u : use_slot + WS::STAGE;
         // run 0 of the stage: its activations are in set 0; start fetching run 1's into set 1, and so on
         x_off = min(x_off + 128u, x_last);
-#ifndef FFAI_DM_EXP_NOX
         fetch_x(x_off, xbuf[1]);
-#endif
         compute_run<FUSED, NT, G32, 0>(stage, rd, xbuf[0], xs_run, mask, expo, g, tot);
         x_off = min(x_off + 128u, x_last);
-#ifndef FFAI_DM_EXP_NOX
         fetch_x(x_off, xbuf[0]);
-#endif
         compute_run<FUSED, NT, G32, 1>(stage, rd, xbuf[1], xs_run + 16 * SBW, mask, expo, g, tot);
         xs_run += STG_RUNS * 16 * SBW;
     }

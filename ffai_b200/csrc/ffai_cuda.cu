@@ -114,7 +114,8 @@ struct ffai_moe_layer {
     std::vector<void*> ep_opened;        // IPC mappings to close
     bool ep_peer_on = false;
     const uint32_t* ep_rows_dev = nullptr;   // set while the experts run on rows whose count only the device knows
-    uint32_t ep_epoch = 0;
+    uint32_t ep_epoch = 0;               // step counter of the peer exchange; never reset, so flags of earlier steps stay behind it
+    uint64_t ep_wait_ns = ep::EP_WAIT_LIMIT_NS;   // limit of a peer barrier wait (option "ep_wait_ms")
     uint32_t* ep_pin = nullptr;          // pinned: recv_counts | offsets[E+1] | plan upload staging
 
     // host-buffer entry point
@@ -976,8 +977,7 @@ extern "C" FFAI_API int ffai_moe_ep_import(ffai_moe_layer* L, const uint8_t* blo
         }
         L->ep_peer_win.p[r] = ptr[0]; L->ep_peer_rows.p[r] = ptr[1]; L->ep_peer_y.p[r] = ptr[2];
     }
-    L->ep_peer_on = true;
-    L->ep_epoch = 0;
+    L->ep_peer_on = true;   // the step counter keeps running: the flags a peer left in this window are all behind it
     return FFAI_OK;
 }
 
@@ -998,6 +998,13 @@ extern "C" FFAI_API int ffai_moe_ep_release(ffai_moe_layer* L) {
     for (void* p : L->ep_opened) cudaIpcCloseMemHandle(p);
     L->ep_opened.clear();
     L->ep_peer_on = false;
+    return FFAI_OK;
+}
+
+extern "C" FFAI_API int ffai_moe_ep_skip_step(ffai_moe_layer* L) {
+    if (!L) return FFAI_ERR_INVALID_ARG;
+    if (!L->ep_peer_on) return fail(L, FFAI_ERR_INVALID_ARG, "no peer buffers are imported");
+    L->ep_epoch += 1;
     return FFAI_OK;
 }
 
@@ -1059,6 +1066,11 @@ extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name,
     if (!strcmp(name, "ksplit")) {
         if (value != 0 && value != 1 && value != 2 && value != 4) return fail(L, FFAI_ERR_INVALID_ARG, "option ksplit must be 0, 1, 2 or 4");
         L->opt_ksplit = value;
+        return FFAI_OK;
+    }
+    if (!strcmp(name, "ep_wait_ms")) {
+        if (value < 1 || value > 60000) return fail(L, FFAI_ERR_INVALID_ARG, "option ep_wait_ms must be in 1..60000");
+        L->ep_wait_ns = (uint64_t)value * 1000000ull;
         return FFAI_OK;
     }
     if (!strcmp(name, "decode")) {
@@ -1420,13 +1432,13 @@ int forward_experts_ep_peer(ffai_moe_layer* L, const uint16_t* x, int T, cudaStr
     const uint32_t epoch = ++L->ep_epoch;
     int rc;
     stage_begin(L, ST_EXCHANGE, st);
-    ep::ep_publish_counts_kernel<<<1, 256, 0, st>>>(L->counts, E, me, W, L->ep_peer_win, epoch, L->error_word);
+    ep::ep_publish_counts_kernel<<<1, 256, 0, st>>>(L->counts, E, me, W, L->ep_peer_win, epoch, L->ep_wait_ns, L->error_word);
     uint32_t* local_off = L->ep_plan_dev;
-    ep::ep_layout_kernel<<<1, 256, 0, st>>>(ep::win_matrix(L->ep_win), E, El, me, W, local_off, L->ep_send_base);
+    ep::ep_layout_kernel<<<1, 256, 0, st>>>(ep::win_matrix(L->ep_win), E, El, me, W, local_off, L->ep_send_base, (uint32_t)L->mx_rows, L->error_word);
     if (M > 0)
         ep::ep_dispatch_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, L->indices, L->offsets, L->ep_send_base, K, El, M, H,
                                                             L->ep_peer_rows, (uint32_t)L->mx_rows, L->error_word);
-    ep::ep_barrier_kernel<<<1, 32, 0, st>>>(1, me, W, L->ep_peer_win, epoch, L->error_word);
+    ep::ep_barrier_kernel<<<1, 32, 0, st>>>(1, me, W, L->ep_peer_win, epoch, L->ep_wait_ns, L->error_word);
     L->launches += M > 0 ? 4 : 3;
     stage_end(L, ST_EXCHANGE, st);
     if (cudaGetLastError() != cudaSuccess) return fail(L, FFAI_ERR_CUDA, "exchange kernels launch failed");
@@ -1440,7 +1452,7 @@ int forward_experts_ep_peer(ffai_moe_layer* L, const uint16_t* x, int T, cudaStr
     L->ep_rows_dev = nullptr;
 
     stage_begin(L, ST_EXCHANGE, st);
-    ep::ep_barrier_kernel<<<1, 32, 0, st>>>(2, me, W, L->ep_peer_win, epoch, L->error_word);
+    ep::ep_barrier_kernel<<<1, 32, 0, st>>>(2, me, W, L->ep_peer_win, epoch, L->ep_wait_ns, L->error_word);
     L->launches += 1;
     stage_end(L, ST_EXCHANGE, st);
     return FFAI_OK;
@@ -1728,7 +1740,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     stage_begin(L, ST_COMBINE, st);
     if (ep_on && L->ep_peer_on)
         ep::combine_peer_kernel<<<T, 256, 0, st>>>(L->ep_peer_y, L->inv_perm, L->indices, L->offsets, L->ep_send_base, L->e_local,
-                                                   L->rweights, K, sh_y, sh_gate, residual, out, H);
+                                                   L->rweights, K, sh_y, sh_gate, residual, out, H, (uint32_t)L->mx_rows, L->error_word);
     else if (ep_on)
         combine_kernel<float, float><<<T, 256, 0, st>>>(L->ep_home_y, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
     else if (tc_experts)
@@ -1917,6 +1929,11 @@ int st_qproj(ffai_st_file* h, const std::string& base, int gs, ffai_qproj* q, in
     if (!valid_bits(bt)) return st_fail(h, base + ": shapes do not describe an affine-quantized tensor at this group size");
     for (size_t i = 0; i + 1 < r; ++i)
         if (w->shape[i] != s->shape[i]) return st_fail(h, base + ": leading dimensions differ");
+    // pointers into the mapping are handed out typed: the payload offsets must keep their natural alignment
+    if ((reinterpret_cast<uintptr_t>(h->f->data + w->begin) & 3u) || (reinterpret_cast<uintptr_t>(h->f->data + s->begin) & 1u) ||
+        (reinterpret_cast<uintptr_t>(h->f->data + b->begin) & 1u))
+        return st_fail(h, base + ": tensor data is not aligned to its element size");
+    if (r > 3) return st_fail(h, base + ": more than three dimensions");
     *n = r == 3 ? w->shape[0] : 1;
     *out_dim = w->shape[r - 2];
     *in_dim = scols * gs;
@@ -1933,6 +1950,8 @@ int st_linear(ffai_st_file* h, const std::string& base, int gs, ffai_linear* lin
     const ffai::st::Tensor* w = ffai::st::find(h->f, base + ".weight");
     if (!w || w->shape.size() != 2) return st_fail(h, "missing or non-2-D " + base + ".weight");
     *lin = ffai_linear{};
+    if (reinterpret_cast<uintptr_t>(h->f->data + w->begin) & (w->dtype == "BF16" ? 1u : 3u))
+        return st_fail(h, base + ".weight is not aligned to its element size");
     lin->weight = h->f->data + w->begin;
     *out_dim = w->shape[0];
     if (w->dtype == "F32") { *kind = FFAI_LINEAR_F32; *bits = 0; *in_dim = w->shape[1]; }
@@ -1941,6 +1960,10 @@ int st_linear(ffai_st_file* h, const std::string& base, int gs, ffai_linear* lin
         const ffai::st::Tensor* s = ffai::st::find(h->f, base + ".scales");
         const ffai::st::Tensor* b = ffai::st::find(h->f, base + ".biases");
         if (!s || !b || s->shape.size() != 2) return st_fail(h, base + ": packed weight without scales/biases");
+        if (s->dtype != "BF16" || b->dtype != "BF16" || s->shape != b->shape || s->shape[0] != w->shape[0])
+            return st_fail(h, base + ": scales/biases must be BF16 with the weight's row count");
+        if ((reinterpret_cast<uintptr_t>(h->f->data + s->begin) & 1u) || (reinterpret_cast<uintptr_t>(h->f->data + b->begin) & 1u))
+            return st_fail(h, base + ": scales/biases are not aligned to their element size");
         *bits = ffai_st_derive_bits(w->shape[1], s->shape[1], gs);
         if (!valid_bits(*bits)) return st_fail(h, base + ": shapes do not describe an affine-quantized tensor at this group size");
         *kind = FFAI_LINEAR_AFFINE;
@@ -1949,7 +1972,9 @@ int st_linear(ffai_st_file* h, const std::string& base, int gs, ffai_linear* lin
         lin->biases = reinterpret_cast<const uint16_t*>(h->f->data + b->begin);
     } else return st_fail(h, base + ".weight has an unsupported dtype " + w->dtype);
     if (const ffai::st::Tensor* bias = ffai::st::find(h->f, base + ".bias"))
-        if (bias->dtype == "BF16") lin->bias = reinterpret_cast<const uint16_t*>(h->f->data + bias->begin);
+        if (bias->dtype == "BF16" && bias->end - bias->begin == (uint64_t)w->shape[0] * 2 &&
+            !(reinterpret_cast<uintptr_t>(h->f->data + bias->begin) & 1u))
+            lin->bias = reinterpret_cast<const uint16_t*>(h->f->data + bias->begin);
     return FFAI_OK;
 }
 }  // namespace

@@ -12,6 +12,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <climits>
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
@@ -42,6 +43,8 @@ struct Cursor {
     const char* p;
     const char* end;
     bool ok = true;
+    int depth = 0;                     // nesting of skipped values (bounded: the walker recurses)
+    static constexpr int MAX_DEPTH = 32;
     void ws() { while (p < end && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r')) ++p; }
     bool eat(char c) { ws(); if (p < end && *p == c) { ++p; return true; } return false; }
     bool peek(char c) { ws(); return p < end && *p == c; }
@@ -56,7 +59,9 @@ struct Cursor {
                 switch (*p) {
                     case 'n': out += '\n'; break;
                     case 't': out += '\t'; break;
-                    case 'u': p += 4; out += '?'; break;   // names of interest are ASCII
+                    case 'u':                              // names of interest are ASCII
+                        if (end - p < 5) { ok = false; return out; }
+                        p += 4; out += '?'; break;
                     default: out += *p;
                 }
                 ++p;
@@ -68,28 +73,36 @@ struct Cursor {
         ++p;
         return out;
     }
-    int64_t integer() {
+    int64_t integer() {   // decimal digits with an optional sign; never reads at or past `end`
         ws();
-        char* e = nullptr;
-        const long long v = strtoll(p, &e, 10);
-        if (e == p) ok = false;
-        p = e;
-        return v;
+        bool neg = false;
+        if (p < end && (*p == '-' || *p == '+')) { neg = *p == '-'; ++p; }
+        if (p >= end || *p < '0' || *p > '9') { ok = false; return 0; }
+        uint64_t v = 0;
+        while (p < end && *p >= '0' && *p <= '9') {
+            if (v > (uint64_t)INT64_MAX / 10) { ok = false; return 0; }
+            v = v * 10 + (uint64_t)(*p - '0');
+            if (v > (uint64_t)INT64_MAX) { ok = false; return 0; }
+            ++p;
+        }
+        return neg ? -(int64_t)v : (int64_t)v;
     }
     void skip_value() {   // any JSON value
         ws();
         if (p >= end) { ok = false; return; }
         if (*p == '"') { str(); return; }
         if (*p == '{' || *p == '[') {
+            if (++depth > MAX_DEPTH) { ok = false; return; }
             const char open = *p, close = open == '{' ? '}' : ']';
             ++p;
-            if (eat(close)) return;
+            if (eat(close)) { --depth; return; }
             do {
-                if (open == '{') { str(); if (!eat(':')) { ok = false; return; } }
+                if (open == '{') { str(); if (!ok || !eat(':')) { ok = false; return; } }
                 skip_value();
                 if (!ok) return;
             } while (eat(','));
             if (!eat(close)) ok = false;
+            --depth;
             return;
         }
         while (p < end && *p != ',' && *p != '}' && *p != ']') ++p;   // number, true, false, null
@@ -131,6 +144,31 @@ inline bool parse_header(File& f, const char* json, size_t n) {
     return true;
 }
 
+// Bytes per element of the dtypes the container defines; 0 for a name this reader does not know.
+inline int dtype_bytes(const std::string& d) {
+    if (d == "F64" || d == "I64" || d == "U64") return 8;
+    if (d == "F32" || d == "I32" || d == "U32") return 4;
+    if (d == "F16" || d == "BF16" || d == "I16" || d == "U16") return 2;
+    if (d == "I8" || d == "U8" || d == "BOOL" || d == "F8_E4M3" || d == "F8_E5M2") return 1;
+    return 0;
+}
+
+// The byte range of a tensor must be exactly what its shape and dtype say (a header that declares a large
+// shape over a short range would otherwise send readers past the mapping).  False on a negative dimension,
+// an overflowing element count, or a size mismatch for a known dtype.
+inline bool shape_matches_range(const Tensor& t) {
+    uint64_t n = 1;
+    for (int64_t d : t.shape) {
+        if (d < 0) return false;
+        if (d != 0 && n > UINT64_MAX / (uint64_t)d) return false;
+        n *= (uint64_t)d;
+    }
+    const int eb = dtype_bytes(t.dtype);
+    if (eb == 0) return true;
+    if (n > UINT64_MAX / (uint64_t)eb) return false;
+    return n * (uint64_t)eb == t.end - t.begin;
+}
+
 inline File* open_file(const char* path, std::string* err) {
     File* f = new File();
     f->fd = ::open(path, O_RDONLY);
@@ -156,8 +194,9 @@ inline File* open_file(const char* path, std::string* err) {
     }
     const uint64_t payload = f->size - 8 - hlen;
     for (const auto& kv : f->tensors)
-        if (kv.second.end < kv.second.begin || kv.second.end > payload) {
-            *err = "tensor " + kv.first + " lies outside the file";
+        if (kv.second.end < kv.second.begin || kv.second.end > payload || !shape_matches_range(kv.second)) {
+            *err = "tensor " + kv.first + (kv.second.end > payload || kv.second.end < kv.second.begin
+                                               ? " lies outside the file" : ": shape and dtype do not match its byte range");
             munmap(m, f->size); ::close(f->fd); delete f;
             return nullptr;
         }

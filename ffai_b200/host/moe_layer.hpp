@@ -142,6 +142,11 @@ class MoELayer {
         int rc = ffai_moe_ep_release(h_);
         if (rc != FFAI_OK) throw Error(rc, std::string("ffai_moe_ep_release: ") + ffai_moe_last_error(h_));
     }
+    // This rank sits out one step of the peer-memory exchange: its step counter moves on without a forward.
+    void skipPeerStep() {
+        int rc = ffai_moe_ep_skip_step(h_);
+        if (rc != FFAI_OK) throw Error(rc, std::string("ffai_moe_ep_skip_step: ") + ffai_moe_last_error(h_));
+    }
     // Reads the device error word the bounded waits of the kernels write (0 = none).
     void checkDeviceStatus() {
         int rc = ffai_moe_check_device_status(h_);

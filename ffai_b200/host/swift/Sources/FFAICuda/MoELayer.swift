@@ -108,6 +108,12 @@ public final class MoELayer {
         if rc != 0 { throw FFAICudaError(status: rc, message: String(cString: ffai_moe_last_error(handle))) }
     }
 
+    /// This rank sits out one step of the peer-memory exchange: its step counter moves on without a forward.
+    public func skipPeerStep() throws {
+        let rc = ffai_moe_ep_skip_step(handle)
+        if rc != 0 { throw FFAICudaError(status: rc, message: String(cString: ffai_moe_last_error(handle))) }
+    }
+
     public func releasePeerBuffers() throws {
         let rc = ffai_moe_ep_release(handle)
         if rc != 0 { throw FFAICudaError(status: rc, message: String(cString: ffai_moe_last_error(handle))) }

@@ -114,6 +114,10 @@ class MoELayer:
     def ep_release(self) -> None:
         capi.check(self.lib.ffai_moe_ep_release(self.handle), "ffai_moe_ep_release", self.handle)
 
+    def ep_skip_step(self) -> None:
+        """This rank sits out one step of the peer-memory exchange (see ``ffai_moe_ep_skip_step``)."""
+        capi.check(self.lib.ffai_moe_ep_skip_step(self.handle), "ffai_moe_ep_skip_step", self.handle)
+
     def set_option(self, name: str, value: int) -> None:
         capi.check(self.lib.ffai_moe_set_option(self.handle, name.encode(), int(value)), "ffai_moe_set_option", self.handle)
 

@@ -208,7 +208,9 @@ FFAI_API const char* ffai_moe_last_error(const ffai_moe_layer* layer);
  * MoELayer.decodeMany (:677-969), GPTOSSMoELayer.decode (GPTOSSText.swift:1340-1392)
  * and Qwen35MoEFFN.forward / forwardMany (Qwen3xText.swift:928-1103).
  *   x, out, residual: device bf16 [T, H]; residual nullable; out complete when
- *   `stream` reaches the end of the call.  No allocation, no host sync.
+ *   `stream` reaches the end of the call.  No allocation.  No host synchronisation on one GPU and
+ *   under expert parallelism over peer memory; expert parallelism over NCCL waits for the stream once
+ *   per call (NCCL takes the exchange sizes from the host).
  */
 FFAI_API int ffai_moe_forward(ffai_moe_layer* layer, const uint16_t* x, int32_t n_tokens,
                      uint16_t* out, const uint16_t* residual,
@@ -218,6 +220,10 @@ FFAI_API int ffai_moe_forward(ffai_moe_layer* layer, const uint16_t* x, int32_t 
  * forward, copies out (and debug outputs) back, and waits.  This is what a
  * caller holding host tensors uses, as the reference's callers do with
  * shared-storage MTLBuffers (Sources/FFAI/Device.swift:23-64). */
+FFAI_API int ffai_moe_forward_host(ffai_moe_layer* layer, const uint16_t* x, int32_t n_tokens,
+                          uint16_t* out, const uint16_t* residual,
+                          const ffai_moe_debug* debug);
+
 /* As ffai_moe_forward / ffai_moe_forward_host, with the router reading its own input rows x_router
  * [T, hidden] while the experts (and the shared expert) read x: Gemma 4 normalises the two branches
  * differently (Gemma4Text.swift:929-933, 957).  x_router == NULL means x. */
@@ -225,9 +231,6 @@ FFAI_API int ffai_moe_forward_split(ffai_moe_layer* layer, const uint16_t* x, co
                                     uint16_t* out, const uint16_t* residual, const ffai_moe_debug* debug, void* stream);
 FFAI_API int ffai_moe_forward_host_split(ffai_moe_layer* layer, const uint16_t* x, const uint16_t* x_router, int32_t n_tokens,
                                          uint16_t* out, const uint16_t* residual, const ffai_moe_debug* debug);
-FFAI_API int ffai_moe_forward_host(ffai_moe_layer* layer, const uint16_t* x, int32_t n_tokens,
-                          uint16_t* out, const uint16_t* residual,
-                          const ffai_moe_debug* debug);
 
 /* Expert parallelism: attach an initialised ncclComm_t (one rank per GPU) before
  * the first forward when config.ep_world > 1.  No reference counterpart (the
@@ -251,8 +254,16 @@ FFAI_API int ffai_ep_comm_destroy(void* comm);
 FFAI_API int ffai_moe_ep_export(ffai_moe_layer* layer, uint8_t out_blob[FFAI_EP_EXPORT_BYTES]);
 FFAI_API int ffai_moe_ep_import(ffai_moe_layer* layer, const uint8_t* blobs /* [ep_world][FFAI_EP_EXPORT_BYTES] */);
 /* Unmaps the peers' buffers (after the last step; before any rank destroys its layer, so that no
- * exported buffer is freed while a peer still maps it). */
+ * exported buffer is freed while a peer still maps it).  The step counter that the flag barriers carry keeps
+ * running over a release and a later import, so flags left from earlier steps can never satisfy a new wait;
+ * ranks that import again must do so together, with layers that have run the same number of steps. */
 FFAI_API int ffai_moe_ep_release(ffai_moe_layer* layer);
+/* A rank that sits out one step of the peer-memory exchange (it learned on the host that the step is void for
+ * it) advances its step counter with this call instead of forward, so that it meets the others again at the
+ * next step.  The ranks that did run the step see their barriers give up after the wait limit (option
+ * "ep_wait_ms"), get FFAI_ERR_DEVICE_CHECK from ffai_moe_check_device_status / ffai_moe_forward_host, and discard
+ * that step's output.  No reference counterpart. */
+FFAI_API int ffai_moe_ep_skip_step(ffai_moe_layer* layer);
 /* The layout the peer-memory exchange derives on the device, computed on the host by the same code (for
  * tests; needs no GPU): from counts_matrix[world][n_experts] (rows every rank sends to every expert),
  * local_offsets[n_experts/world + 1] = row ranges of `rank`'s own experts in its row buffer, and
@@ -270,8 +281,17 @@ FFAI_API uint32_t ffai_ep_plan_exchange(const uint32_t* recv_counts, int32_t wor
 
 /* Execution options, replacing the reference's FFAI_MOE_* environment switches
  * (Sources/FFAI/Models/MoELayer.swift:486-497).  Names:
- *   "path"         0 automatic, 1 CUDA-core grouped GEMV only, 2 tcgen05 grouped GEMM whenever possible
- *   "tc_min_rows"  smallest T*k that takes the tcgen05 path under "path" = 0 (0: default) */
+ *   "path"         0 automatic, 1 CUDA-core grouped GEMV only, 2 tcgen05 grouped GEMM whenever possible,
+ *                  3 streaming decode kernels whenever possible
+ *   "tc_min_rows"  smallest T*k that takes the tcgen05 path under "path" = 0 (0: default)
+ *   "tc_weights"   tcgen05 path reads 0 the bf16 weight cache when the layer keeps one, 1 always the packed weights
+ *   "tc_pair"      1: a tcgen05 work item covers two 128-row token tiles of an expert
+ *   "ksplit"       cp.async decode kernels: slices of the reduction axis per 16-row block (0 automatic, 1, 2, 4)
+ *   "decode"       decode kernels: 0 automatic, 1 cp.async rings, 2 bulk-copy streams
+ *   "decode_team"  bulk-copy streams: warps that share one 16-row block (0 automatic, 1, 4, 16)
+ *   "nt2_cost"     bulk-copy streams: schedule weight of a block with more than 8 rows, 8 = as one with fewer (8..32)
+ *   "ep_wait_ms"   limit of a barrier wait of the peer-memory exchange, milliseconds (default 2000)
+ *   "timeline"     1: the gate/up tcgen05 kernel records its device timeline (builds with FFAI_G100_TIMELINE only) */
 FFAI_API int ffai_moe_set_option(ffai_moe_layer* layer, const char* name, int32_t value);
 
 /* Profiling aid for the tcgen05 grouped GEMM (the device-side counterpart of the reference's

@@ -41,6 +41,46 @@ CASES = [
 SAMPLED = {"cfg4_256_experts": 32}   # cases whose outputs are checked on this many sampled tokens (the oracle is scalar)
 
 
+def bounded_wait_case(rank, world, store, meet):
+    """One rank sits out a step of the peer-memory exchange; the others' barriers must give up within the (short)
+    limit and report it through the status call, nothing faults or waits for ever, and the next step that all
+    ranks run gives the same bits as the step before the gap.  The gap is made on the host, between steps."""
+    spec = synth.cfg3_qwen().with_(n_experts=32, name="qwen_32e_gap")
+    host = synth.make_layer(spec, seed=9)
+    T = 96
+    x = synth.make_tokens(T, spec.hidden, seed=2000 + rank)
+    lay = MoELayer(host, T, ep_rank=rank, ep_world=world)
+    rec = {"case": "bounded_wait", "tokens": 0, "bounded_wait": True}
+    try:
+        lay.set_option("ep_wait_ms", 50)
+        store.set(f"blob/gap/{rank}", lay.ep_export())
+        lay.ep_import([bytes(store.get(f"blob/gap/{r}")) for r in range(world)])
+        meet("gap/go0")
+        before, _ = lay.forward_host(x)
+        meet("gap/go1")
+        if rank == world - 1:
+            lay.ep_skip_step()                      # this rank sits the step out
+            rec["gave_up"] = None
+        else:
+            t0 = __import__("time").perf_counter()
+            try:
+                lay.forward_host(x)
+                rec["gave_up"] = False
+            except capi.FFAICudaError as err:
+                rec["gave_up"] = err.status == capi.FFAI_ERR_DEVICE_CHECK
+            rec["gave_up_after_s"] = __import__("time").perf_counter() - t0
+        meet("gap/go2")                             # everybody has left the void step
+        after, _ = lay.forward_host(x)
+        lay.check_device_status()
+        rec["same_bits_after_gap"] = bool(np.array_equal(before, after))
+        meet("gap/done")
+        lay.ep_release()
+        meet("gap/released")
+    finally:
+        lay.close()
+    return rec
+
+
 def main():
     rank, world, port, out_path = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), sys.argv[4]
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -114,6 +154,7 @@ def main():
                 lay.close()
                 one.close()
             results.append(rec)
+        results.append(bounded_wait_case(rank, world, store, meet))
         status = "ok"
     except Exception:
         status = traceback.format_exc()

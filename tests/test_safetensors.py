@@ -179,3 +179,62 @@ def test_layer_built_from_a_file_matches_the_layer_built_from_arrays(tmp_path, f
             ffai_lib.ffai_st_close(h)
         if layer:
             ffai_lib.ffai_moe_destroy(layer)
+
+
+def _open_raw(lib, tmp_path, name, header_bytes, payload=b""):
+    path = tmp_path / name
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(header_bytes)))
+        f.write(header_bytes)
+        f.write(payload)
+    h = C.c_void_p()
+    rc = lib.ffai_st_open(str(path).encode(), C.byref(h))
+    msg = lib.ffai_st_last_error(h).decode() if h else ""
+    if h:
+        lib.ffai_st_close(h)
+    return rc, msg
+
+
+def test_hostile_headers_are_rejected_not_followed(tmp_path):
+    """A header may not send a reader past the mapping: a shape larger than its byte range, a negative
+    dimension, a number that runs into the end of the file, an escape cut off by it, nesting without end."""
+    lib = capi.load()
+    # the declared shape needs 4 MiB, the byte range holds 16 bytes
+    hdr = json.dumps({"w": {"dtype": "U32", "shape": [64, 128, 128], "data_offsets": [0, 16]}}).encode()
+    rc, msg = _open_raw(lib, tmp_path, "short.safetensors", hdr, b"\0" * 16)
+    assert rc == capi.FFAI_ERR_INVALID_ARG and "byte range" in msg
+    hdr = json.dumps({"w": {"dtype": "F32", "shape": [-4, 2], "data_offsets": [0, 0]}}).encode()
+    assert _open_raw(lib, tmp_path, "neg.safetensors", hdr)[0] == capi.FFAI_ERR_INVALID_ARG
+    # the header (and the file) ends in the middle of a number
+    hdr = b'{"w":{"dtype":"F32","shape":[1],"data_offsets":[0,4'
+    assert _open_raw(lib, tmp_path, "digits.safetensors", hdr)[0] == capi.FFAI_ERR_INVALID_ARG
+    # ... in the middle of a \u escape inside a name
+    assert _open_raw(lib, tmp_path, "escape.safetensors", b'{"w\\u00')[0] == capi.FFAI_ERR_INVALID_ARG
+    # ... and metadata nested deeper than any real file
+    deep = b'{"__metadata__":' + b"[" * 5000 + b"]" * 5000 + b"}"
+    assert _open_raw(lib, tmp_path, "deep.safetensors", deep)[0] == capi.FFAI_ERR_INVALID_ARG
+    # a well-formed neighbour still opens
+    hdr = json.dumps({"w": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0, 16]}}).encode()
+    assert _open_raw(lib, tmp_path, "fine.safetensors", hdr, b"\0" * 16)[0] == capi.FFAI_OK
+
+
+def test_truncated_expert_tensor_is_rejected(tmp_path):
+    """A stacked projection whose scales tensor was cut short: the file no longer opens."""
+    spec = synth.LayerSpec("cut", 256, 128, 4, 2)
+    host = synth.make_layer(spec, 1)
+    t = checkpoint_tensors(host, "m.mlp", 0)
+    path = tmp_path / "cut.safetensors"
+    write_safetensors(path, t)
+    raw = path.read_bytes()
+    hlen = struct.unpack("<Q", raw[:8])[0]
+    header = json.loads(raw[8:8 + hlen])
+    name = "m.mlp.switch_mlp.down_proj.scales"
+    b, e = header[name]["data_offsets"]
+    header[name]["data_offsets"] = [b, b + (e - b) // 2]      # shape unchanged, half the bytes
+    hj = json.dumps(header).encode()
+    path.write_bytes(struct.pack("<Q", len(hj)) + hj + raw[8 + hlen:])
+    h = C.c_void_p()
+    lib = capi.load()
+    assert lib.ffai_st_open(str(path).encode(), C.byref(h)) == capi.FFAI_ERR_INVALID_ARG
+    assert name in lib.ffai_st_last_error(h).decode()
+    lib.ffai_st_close(h)
