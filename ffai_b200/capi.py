@@ -25,10 +25,12 @@ FFAI_ERR_DEVICE_CHECK = 6
 
 GATING_SOFTMAX_THEN_TOPK = 0
 GATING_TOPK_THEN_SOFTMAX = 1
+GATING_SIGMOID_TOPK = 2
 
 ACT_SWIGLU = 0
 ACT_CLAMPED_SWIGLU = 1
 ACT_GELU_GLU = 2
+ACT_RELU2 = 3
 
 LINEAR_NONE = 0
 LINEAR_F32 = 1
@@ -76,7 +78,8 @@ class MoEConfig(C.Structure):
         ("ep_world", C.c_int32),
         ("prefill_weight_cache", C.c_int32),
         ("router_logit_scale", C.c_float),
-        ("reserved", C.c_int32 * 6),
+        ("routed_scaling_factor", C.c_float),
+        ("reserved", C.c_int32 * 5),
     ]
 
     def __init__(self, **kw):

@@ -38,6 +38,7 @@ struct GemvParams {
     int n_rows;
     int activation;
     float limit, alpha;
+    int post_relu2;                // one-projection launches: out = relu(W x + b)^2 (experts without a gate projection)
 };
 
 template <typename TIn>
@@ -166,6 +167,9 @@ grouped_gemv_kernel(GemvParams p, const TIn* __restrict__ in, TOut* __restrict__
                 if (FUSED) {
                     if (p.row_bias2) a2 += bf16_bits_to_f32(p.row_bias2[r]);
                     v = glu_activation(a1, a2, p.activation, p.limit, p.alpha);
+                } else if (p.post_relu2) {
+                    v = fmaxf(v, 0.0f);
+                    v = v * v;
                 }
                 store_out(out + (size_t)(t0 + tt) * p.N + n, v);
             }

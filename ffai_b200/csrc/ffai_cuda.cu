@@ -75,6 +75,7 @@ struct ffai_moe_layer {
     float* inner_sum = nullptr;      // [M, I/64]  64-run sums of inner rows
     const uint16_t* router_x = nullptr;  // set for the duration of a split forward: the router's own input rows
     uint16_t* dev_xr = nullptr;          // host-buffer entry point: device copy of the router input
+    bool no_gate = false;            // experts without a gate projection (relu(up)^2): CUDA-core GEMV kernels only
     bool mma_ok = false;             // register-streaming decode kernels usable (4-bit, group 64/128)
     uint8_t* st_gate_up = nullptr;   // bulk-copy streams of the decode kernels: gate and up interleaved per 64-run, ...
     uint8_t* st_down = nullptr;      // ... and down (re-tiled copies of the packed experts, owned with the weights)
@@ -589,9 +590,9 @@ int validate_config(const ffai_moe_config* c, ffai_moe_layer* L) {
     if (c->n_experts <= 0 || c->n_experts > FFAI_MAX_EXPERTS) return fail(L, FFAI_ERR_INVALID_ARG, "n_experts must be in 1..%d", FFAI_MAX_EXPERTS);
     if (c->top_k <= 0 || c->top_k > c->n_experts || c->top_k > FFAI_MAX_TOP_K)
         return fail(L, FFAI_ERR_INVALID_ARG, "top_k (%d) must be in 1..min(n_experts=%d, %d)", c->top_k, c->n_experts, FFAI_MAX_TOP_K);
-    if (c->gating_mode != FFAI_GATING_SOFTMAX_THEN_TOPK && c->gating_mode != FFAI_GATING_TOPK_THEN_SOFTMAX)
+    if (c->gating_mode < FFAI_GATING_SOFTMAX_THEN_TOPK || c->gating_mode > FFAI_GATING_SIGMOID_TOPK)
         return fail(L, FFAI_ERR_INVALID_ARG, "unknown gating_mode %d", c->gating_mode);
-    if (c->activation < 0 || c->activation > FFAI_ACT_GELU_GLU) return fail(L, FFAI_ERR_INVALID_ARG, "unknown activation %d", c->activation);
+    if (c->activation < 0 || c->activation > FFAI_ACT_RELU2) return fail(L, FFAI_ERR_INVALID_ARG, "unknown activation %d", c->activation);
     if (c->router_kind < FFAI_LINEAR_F32 || c->router_kind > FFAI_LINEAR_AFFINE) return fail(L, FFAI_ERR_INVALID_ARG, "unknown router_kind %d", c->router_kind);
     if (c->router_kind == FFAI_LINEAR_AFFINE && (!valid_bits(c->router_bits) || !valid_gs(c->router_group_size)))
         return fail(L, FFAI_ERR_INVALID_ARG, "router bits/group_size (%d/%d) unsupported", c->router_bits, c->router_group_size);
@@ -660,6 +661,7 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
     const ffai_moe_config& c = L->cfg;
     const int world = c.ep_world <= 1 ? 1 : c.ep_world;
     L->e_local = c.n_experts / world;
+    L->no_gate = c.activation == FFAI_ACT_RELU2;
     *out_layer = L;
     if (ffai_cuda_device_count() <= 0) return fail(L, FFAI_ERR_CUDA, "no CUDA device available (there is no CPU fallback)");
     CUDA_TRY(L, cudaGetDevice(&L->device));
@@ -719,7 +721,7 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
     // tcgen05 grouped GEMM.  The tcgen05 path also needs every reduction length to hold at least one
     // 256-k packed TMA box.
     const bool tc_shapes = H >= 256 && I >= 256 && (c.shared_intermediate == 0 || c.shared_intermediate >= 256);
-    const bool want_tc = cc_major == 10 && tc_shapes;
+    const bool want_tc = cc_major == 10 && tc_shapes && !L->no_gate;
     {
         const double cache_bytes = 3.0 * (double)L->e_local * H * I * 2.0;
         const bool prefill_sized = (double)T * K / E >= 32.0;
@@ -736,7 +738,7 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
         if ((rc = ws_alloc(L, &L->inner_parts, (Mx + 1) * (size_t)(I / 16)))) return rc;
         if ((rc = ws_alloc(L, &L->x_tok, (T + 1) * H))) return rc;
         if ((rc = ws_alloc(L, &L->xsum_tok, (T + 1) * (size_t)((H / 32 + 3) & ~3)))) return rc;
-        L->mma_ok = c.expert_bits == 4;   // every group size the format allows (32, 64, 128)
+        L->mma_ok = c.expert_bits == 4 && !L->no_gate;   // every group size the format allows (32, 64, 128)
         if (want_tc) {
             if (world == 1 && (rc = ws_alloc(L, &L->y_bf, M * H))) return rc;
             if ((rc = ws_alloc(L, &L->tile_offsets, E + 1))) return rc;
@@ -793,15 +795,15 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
     if (w->router_per_expert_scale)
         if ((rc = upload(L, w->router_per_expert_scale, (size_t)c.n_experts * 4, loc, (const void**)&L->w.router_per_expert_scale))) return rc;
     const int El = L->e_local;
-    if ((rc = upload_qproj(L, w->gate_proj, El, c.intermediate, c.hidden, c.expert_bits, c.expert_group_size, loc, &L->w.gate_proj, "gate_proj"))) return rc;
+    if (!L->no_gate && (rc = upload_qproj(L, w->gate_proj, El, c.intermediate, c.hidden, c.expert_bits, c.expert_group_size, loc, &L->w.gate_proj, "gate_proj"))) return rc;
     if ((rc = upload_qproj(L, w->up_proj, El, c.intermediate, c.hidden, c.expert_bits, c.expert_group_size, loc, &L->w.up_proj, "up_proj"))) return rc;
     if ((rc = upload_qproj(L, w->down_proj, El, c.hidden, c.intermediate, c.expert_bits, c.expert_group_size, loc, &L->w.down_proj, "down_proj"))) return rc;
-    if (c.expert_row_bias && (!w->gate_proj.row_bias || !w->up_proj.row_bias || !w->down_proj.row_bias))
+    if (c.expert_row_bias && ((!L->no_gate && !w->gate_proj.row_bias) || !w->up_proj.row_bias || !w->down_proj.row_bias))
         return fail(L, FFAI_ERR_INVALID_ARG, "expert_row_bias set but a row_bias pointer is null");
     if (!c.expert_row_bias) L->w.gate_proj.row_bias = L->w.up_proj.row_bias = L->w.down_proj.row_bias = nullptr;
     if (c.shared_intermediate > 0) {
         const int Is = c.shared_intermediate;
-        if ((rc = upload_qproj(L, w->shared_gate_proj, 1, Is, c.hidden, c.shared_bits, c.shared_group_size, loc, &L->w.shared_gate_proj, "shared_gate_proj"))) return rc;
+        if (!L->no_gate && (rc = upload_qproj(L, w->shared_gate_proj, 1, Is, c.hidden, c.shared_bits, c.shared_group_size, loc, &L->w.shared_gate_proj, "shared_gate_proj"))) return rc;
         if ((rc = upload_qproj(L, w->shared_up_proj, 1, Is, c.hidden, c.shared_bits, c.shared_group_size, loc, &L->w.shared_up_proj, "shared_up_proj"))) return rc;
         if ((rc = upload_qproj(L, w->shared_down_proj, 1, c.hidden, Is, c.shared_bits, c.shared_group_size, loc, &L->w.shared_down_proj, "shared_down_proj"))) return rc;
         L->w.shared_gate_proj.row_bias = L->w.shared_up_proj.row_bias = L->w.shared_down_proj.row_bias = nullptr;
@@ -1176,6 +1178,7 @@ RouterParams router_params(const ffai_moe_layer* L) {
     p.logits_bf16 = c.router_logits_bf16;
     p.logit_scale = c.router_logit_scale != 0.0f ? c.router_logit_scale : 1.0f;
     p.per_expert_scale = L->w.router_per_expert_scale;
+    p.routed_scaling = c.routed_scaling_factor != 0.0f ? c.routed_scaling_factor : 1.0f;
     return p;
 }
 
@@ -1330,12 +1333,15 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         L->launches += 3;
     } else {
         int rc;
-        GemvParams p = gemv_params(L->w.gate_proj, &L->w.up_proj, I, H, c.expert_group_size, n_exp);
+        GemvParams p = L->no_gate ? gemv_params(L->w.up_proj, nullptr, I, H, c.expert_group_size, n_exp)
+                                  : gemv_params(L->w.gate_proj, &L->w.up_proj, I, H, c.expert_group_size, n_exp);
         p.offsets = offsets_dev;
         p.n_rows = n_rows;
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
+        p.post_relu2 = L->no_gate;
         stage_begin(L, ST_GATE_UP, st);
-        if ((rc = launch_grouped_gemv<uint16_t, float, true>(p, c.expert_bits, L->xg, L->inner, n_exp, st))) return fail(L, rc, "gate/up launch failed");
+        if ((rc = L->no_gate ? launch_grouped_gemv<uint16_t, float, false>(p, c.expert_bits, L->xg, L->inner, n_exp, st)
+                             : launch_grouped_gemv<uint16_t, float, true>(p, c.expert_bits, L->xg, L->inner, n_exp, st))) return fail(L, rc, "gate/up launch failed");
         stage_end(L, ST_GATE_UP, st);
         stage_begin(L, ST_DOWN, st);
         GemvParams d = gemv_params(L->w.down_proj, nullptr, H, I, c.expert_group_size, n_exp);
@@ -1653,13 +1659,16 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         // gate/up products + activation -> inner[M, I]; rows are read through the permutation
         stage_begin(L, ST_GATE_UP, st);
         {
-            GemvParams p = gemv_params(L->w.gate_proj, &L->w.up_proj, I, H, c.expert_group_size, E);
+            GemvParams p = L->no_gate ? gemv_params(L->w.up_proj, nullptr, I, H, c.expert_group_size, E)
+                                      : gemv_params(L->w.gate_proj, &L->w.up_proj, I, H, c.expert_group_size, E);
             p.offsets = L->offsets;
             p.in_row_ids = L->perm;
             p.in_row_div = K;
             p.n_rows = M;
             p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
-            if ((rc = launch_grouped_gemv<uint16_t, float, true>(p, c.expert_bits, x, L->inner, E, st)))
+            p.post_relu2 = L->no_gate;
+            if ((rc = L->no_gate ? launch_grouped_gemv<uint16_t, float, false>(p, c.expert_bits, x, L->inner, E, st)
+                                 : launch_grouped_gemv<uint16_t, float, true>(p, c.expert_bits, x, L->inner, E, st)))
                 return fail(L, rc, "gate/up launch failed: %s", cudaGetErrorString(cudaGetLastError()));
             L->launches += 1;
         }
@@ -1709,10 +1718,13 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
                 return fail(L, FFAI_ERR_CUDA, "shared down grouped GEMM launch failed");
             L->launches += 4;
         } else {
-            GemvParams p = gemv_params(L->w.shared_gate_proj, &L->w.shared_up_proj, Is, H, c.shared_group_size, 1);
+            GemvParams p = L->no_gate ? gemv_params(L->w.shared_up_proj, nullptr, Is, H, c.shared_group_size, 1)
+                                      : gemv_params(L->w.shared_gate_proj, &L->w.shared_up_proj, Is, H, c.shared_group_size, 1);
             p.n_rows = T;
             p.activation = FFAI_ACT_SWIGLU;
-            if ((rc = launch_grouped_gemv<uint16_t, float, true>(p, c.shared_bits, x, L->sh_inner, 1, st)))
+            p.post_relu2 = L->no_gate;   // beside gate-less experts the shared expert has their form (NemotronHText.swift:885-891)
+            if ((rc = L->no_gate ? launch_grouped_gemv<uint16_t, float, false>(p, c.shared_bits, x, L->sh_inner, 1, st)
+                                 : launch_grouped_gemv<uint16_t, float, true>(p, c.shared_bits, x, L->sh_inner, 1, st)))
                 return fail(L, rc, "shared gate/up launch failed");
             GemvParams d = gemv_params(L->w.shared_down_proj, nullptr, H, Is, c.shared_group_size, 1);
             d.n_rows = T;
@@ -2083,11 +2095,12 @@ extern "C" FFAI_API int ffai_op_moe_router_topk(const float* logits, uint32_t* i
                                        int32_t norm, const float* expert_bias, void* stream) {
     if (!logits || !indices || !weights || T <= 0) return FFAI_ERR_INVALID_ARG;
     if (E <= 0 || E > FFAI_MAX_EXPERTS || k <= 0 || k > E || k > FFAI_MAX_TOP_K) return FFAI_ERR_INVALID_ARG;
-    if (gating_mode != 0 && gating_mode != 1) return FFAI_ERR_INVALID_ARG;
+    if (gating_mode < 0 || gating_mode > FFAI_GATING_SIGMOID_TOPK) return FFAI_ERR_INVALID_ARG;
     int rc;
     if ((rc = need_device())) return rc;
     RouterParams p{};
     p.n_experts = E; p.top_k = k; p.gating_mode = gating_mode; p.norm_topk_prob = norm;
+    p.routed_scaling = 1.0f;
     p.expert_bias = expert_bias;
     const int warps = 4;
     route_only_kernel<<<(T + warps - 1) / warps, warps * 32, (size_t)warps * 2 * E * sizeof(float),

@@ -28,6 +28,7 @@ struct RouterParams {
     int logits_bf16;
     float logit_scale;               // logits are multiplied by this before routing (1 unless the model says otherwise)
     const float* per_expert_scale;   // nullable [E]: combine weight *= scale[expert]
+    float routed_scaling;            // sigmoid routing: factor on the combine weights (1 unless the model says otherwise)
 };
 
 // One 64-wide chunk of dot(x[t], W[e]) in ascending k with fused multiply-add.
@@ -145,6 +146,28 @@ FFAI_DEVINL void route_token_warp(const RouterParams& p, float* logits_s, float*
     if (p.logit_scale != 1.0f && p.logit_scale != 0.0f) {   // (0: unset) Gemma 4: hidden^-0.5 folded into the logits (Gemma4Text.swift:937-943)
         for (int e = lane; e < E; e += 32) logits_s[e] = __fmul_rn(logits_s[e], p.logit_scale);
         __syncwarp();
+    }
+    if (p.gating_mode == 2) {
+        // NemotronH routing (NemotronHText.swift:844-867): sigmoid scores; selection on score + bias; weights are the
+        // raw sigmoids of the selected, over (their sum + 1e-20) when k > 1 and renormalising, times the scaling factor
+        for (int e = lane; e < E; e += 32) {
+            const float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, det_expf(-logits_s[e])));
+            logits_s[e] = sg;
+            scratch[e] = p.expert_bias ? __fadd_rn(sg, p.expert_bias[e]) : sg;
+        }
+        __syncwarp();
+        warp_topk(scratch, E, K, lane, my_idx, my_val);
+        float w = (lane < K) ? logits_s[my_idx] : 0.0f;
+        if (K > 1 && p.norm_topk_prob) {
+            float sum = 0.0f;
+            for (int j = 0; j < K; ++j) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, w, j));
+            sum = __fadd_rn(sum, 1e-20f);
+            w = __fdiv_rn(w, sum);
+        }
+        w = __fmul_rn(w, p.routed_scaling);
+        if (p.per_expert_scale && lane < K) w = __fmul_rn(w, p.per_expert_scale[my_idx]);
+        if (lane < K) { idx_out[lane] = (uint32_t)my_idx; w_out[lane] = w; }
+        return;
     }
     const bool fast = (p.gating_mode == 1) ||
                       (p.gating_mode == 0 && p.norm_topk_prob && p.expert_bias == nullptr);

@@ -21,7 +21,8 @@ struct Error : std::runtime_error {
 };
 
 // MoEGatingMode — MoELayer.swift:71-78
-enum class MoEGatingMode { softmaxThenTopK = FFAI_GATING_SOFTMAX_THEN_TOPK, topKThenSoftmax = FFAI_GATING_TOPK_THEN_SOFTMAX };
+enum class MoEGatingMode { softmaxThenTopK = FFAI_GATING_SOFTMAX_THEN_TOPK, topKThenSoftmax = FFAI_GATING_TOPK_THEN_SOFTMAX,
+                           sigmoidTopK = FFAI_GATING_SIGMOID_TOPK /* NemotronHMoELayer routing */ };
 
 // MoERouter — MoELayer.swift:88-205.  A value type; routing itself runs on the device inside
 // MoELayer::decode / decodeMany (route() on a logits vector is ffai_op_moe_router_topk).

@@ -7,7 +7,14 @@ import CFFAICuda
 public enum MoEGatingMode: Sendable {
     case softmaxThenTopK
     case topKThenSoftmax
-    var raw: Int32 { self == .softmaxThenTopK ? 0 : 1 }
+    case sigmoidTopK          // NemotronHMoELayer routing
+    var raw: Int32 {
+        switch self {
+        case .softmaxThenTopK: return 0
+        case .topKThenSoftmax: return 1
+        case .sigmoidTopK: return 2
+        }
+    }
 }
 
 public struct FFAICudaError: Error, CustomStringConvertible {

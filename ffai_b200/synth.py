@@ -123,6 +123,7 @@ class LayerSpec:
     shared_gate_group_size: int = 0
     router_logit_scale: float = 0.0     # logits are multiplied by this before routing (0: no scaling)
     router_per_expert_scale: int = 0    # 1: a per-expert factor on the combine weights (Gemma 4)
+    routed_scaling_factor: float = 0.0  # sigmoid routing: factor on the combine weights (0: none)
     prefill_weight_cache: int = 0  # 0 automatic, 1 never, 2 always (bf16 copy of the experts for the tensor-core path)
     zipf_s: float = 0.0          # > 0: additive per-expert router bias with a Zipf profile
     zipf_strength: float = 1.0
@@ -137,7 +138,7 @@ class LayerSpec:
                   "router_bits", "router_group_size", "router_has_bias", "router_logits_bf16",
                   "expert_bits", "expert_group_size", "expert_row_bias", "shared_intermediate",
                   "shared_bits", "shared_group_size", "shared_gate_kind", "shared_gate_bits",
-                  "shared_gate_group_size", "prefill_weight_cache", "router_logit_scale"):
+                  "shared_gate_group_size", "prefill_weight_cache", "router_logit_scale", "routed_scaling_factor"):
             setattr(cfg, f, getattr(self, f))
         cfg.max_tokens = max_tokens
         cfg.ep_rank = ep_rank
@@ -199,6 +200,15 @@ def cfg5_skewed(bits: int) -> LayerSpec:
     """cfg3 shape with a Zipf(1.1) additive router bias and experts at `bits` bits."""
     return cfg3_qwen().with_(name=f"cfg5_skewed_{bits}bit", expert_bits=bits, router_has_bias=1,
                              zipf_s=1.1)
+
+
+def nemotronh_style() -> LayerSpec:
+    """NemotronH-style block: sigmoid routing with a selection bias and a routed scaling factor, experts
+    without a gate projection (relu(up)^2), an always-on shared expert of the same form
+    (NemotronHText.swift:696-912)."""
+    return LayerSpec("nemotronh_style", 512, 256, 16, 4, gating_mode=capi.GATING_SIGMOID_TOPK, router_expert_bias=1,
+                     activation=capi.ACT_RELU2, routed_scaling_factor=2.5, shared_intermediate=384,
+                     shared_bits=4, shared_group_size=64)
 
 
 def gemma4_style() -> LayerSpec:
@@ -318,15 +328,18 @@ def make_layer(spec: LayerSpec, seed: int = 0) -> HostLayer:
         a["gate.bias"] = f32_to_bf16(bias)
     if spec.router_expert_bias:
         a["gate.expert_bias"] = (0.02 * rng.standard_normal(E, dtype=np.float32)).astype(np.float32)
-    _rand_qproj(rng, E, I, H, spec.expert_bits, spec.expert_group_size, bool(spec.expert_row_bias),
-                "experts.gate_proj", a)
+    no_gate = spec.activation == capi.ACT_RELU2     # experts without a gate projection: the array is not made at all
+    if not no_gate:
+        _rand_qproj(rng, E, I, H, spec.expert_bits, spec.expert_group_size, bool(spec.expert_row_bias),
+                    "experts.gate_proj", a)
     _rand_qproj(rng, E, I, H, spec.expert_bits, spec.expert_group_size, bool(spec.expert_row_bias),
                 "experts.up_proj", a)
     _rand_qproj(rng, E, H, I, spec.expert_bits, spec.expert_group_size, bool(spec.expert_row_bias),
                 "experts.down_proj", a)
     if spec.shared_intermediate:
         Is = spec.shared_intermediate
-        _rand_qproj(rng, 1, Is, H, spec.shared_bits, spec.shared_group_size, False, "shared_expert.gate_proj", a)
+        if not no_gate:
+            _rand_qproj(rng, 1, Is, H, spec.shared_bits, spec.shared_group_size, False, "shared_expert.gate_proj", a)
         _rand_qproj(rng, 1, Is, H, spec.shared_bits, spec.shared_group_size, False, "shared_expert.up_proj", a)
         _rand_qproj(rng, 1, H, Is, spec.shared_bits, spec.shared_group_size, False, "shared_expert.down_proj", a)
         if spec.shared_gate_kind != capi.LINEAR_NONE:

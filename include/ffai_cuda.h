@@ -59,7 +59,12 @@ typedef enum ffai_status {
 /* MoEGatingMode — Sources/FFAI/Models/MoELayer.swift:71-78 */
 typedef enum ffai_gating_mode {
     FFAI_GATING_SOFTMAX_THEN_TOPK = 0,
-    FFAI_GATING_TOPK_THEN_SOFTMAX = 1
+    FFAI_GATING_TOPK_THEN_SOFTMAX = 1,
+    /* NemotronHMoELayer routing (Sources/FFAI/Models/Text/NemotronHText.swift:844-867): scores =
+     * sigmoid(logits); selection on scores + expert_bias (e_score_correction_bias; ties to the lower
+     * index); combine weights are the raw sigmoids of the selected, divided by (their sum + 1e-20) when
+     * top_k > 1 and norm_topk_prob, then multiplied by routed_scaling_factor. */
+    FFAI_GATING_SIGMOID_TOPK = 2
 } ffai_gating_mode;
 
 /* Expert activation.
@@ -67,11 +72,16 @@ typedef enum ffai_gating_mode {
  *   CLAMPED_SWIGLU  g=min(gate,L); u=clamp(up,-L,L);
  *                   (u+1) * g / (1+exp(-alpha*g))  Sources/FFAI/Models/Text/GPTOSSText.swift:1414-1431
  *   GELU_GLU        gelu_tanh(gate)*up             Sources/FFAI/Ops/OpsFused.swift:55-87
+ *   RELU2           relu(up)^2: experts WITHOUT a gate projection (NemotronHExpert,
+ *                   Sources/FFAI/Models/Text/NemotronHText.swift:741-763; Ops.relu, Ops.swift:209-212);
+ *                   gate_proj (and shared_gate_proj) are not read and may be null; a shared expert has
+ *                   the same form
  */
 typedef enum ffai_activation {
     FFAI_ACT_SWIGLU = 0,
     FFAI_ACT_CLAMPED_SWIGLU = 1,
-    FFAI_ACT_GELU_GLU = 2
+    FFAI_ACT_GELU_GLU = 2,
+    FFAI_ACT_RELU2 = 3
 } ffai_activation;
 
 /* Storage type of a dense-or-quantized projection (router, shared-expert gate). */
@@ -132,7 +142,9 @@ typedef struct ffai_moe_config {
                                /* batches always stream the packed weights.                         */
     float router_logit_scale;  /* the logits are multiplied by this (fp32) before top-k / softmax; 0 means 1.   */
                                /* Gemma 4 folds hidden^-0.5 into the logits here (Gemma4Text.swift:937-943). */
-    int32_t reserved[6];
+    float routed_scaling_factor; /* FFAI_GATING_SIGMOID_TOPK: factor on the combine weights; 0 means 1          */
+                               /* (NemotronHText.swift:263, 866).                                             */
+    int32_t reserved[5];
 } ffai_moe_config;
 
 /* One stacked quantized projection: weight [n, out, in*bits/32] u32,

@@ -52,14 +52,14 @@ def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 
 
-def route(logits, k, gating_mode, norm_topk_prob, expert_bias=None):
+def route(logits, k, gating_mode, norm_topk_prob, expert_bias=None, routed_scaling=1.0):
     """MoERouter.route on one logits vector → (indices int32[k], weights float32[k])."""
     logits = np.ascontiguousarray(logits, dtype=np.float32)
     idx = np.zeros(k, dtype=np.int32)
     w = np.zeros(k, dtype=np.float32)
     eb = None if expert_bias is None else np.ascontiguousarray(expert_bias, dtype=np.float32)
-    lib().orc_route(_p(logits), C.c_int(len(logits)), C.c_int(k), C.c_int(gating_mode),
-                    C.c_int(norm_topk_prob), _p(eb), _p(idx), _p(w))
+    lib().orc_route_scaled(_p(logits), C.c_int(len(logits)), C.c_int(k), C.c_int(gating_mode),
+                           C.c_int(norm_topk_prob), _p(eb), C.c_float(routed_scaling), _p(idx), _p(w))
     return idx, w
 
 

@@ -156,11 +156,48 @@ static void topk_indices(const float* x, int n, int k, int32_t* idx) {
     free(taken);
 }
 
-/* MoERouter.route — MoELayer.swift:140-205 (three branches, kept as written). */
+/* NemotronHMoELayer routing — Sources/FFAI/Models/Text/NemotronHText.swift:844-867: sigmoid of every logit,
+ * selection on sigmoid + bias (order: value desc, index asc), weights = raw sigmoid of the selected, divided by
+ * (their sum + 1e-20) when k > 1 and norm_topk_prob, times the routed scaling factor.  fp32 throughout, as the
+ * reference's Float arrays. */
+static void route_sigmoid(const float* logits, int n_experts, int k, int norm_topk_prob, const float* expert_bias,
+                          float routed_scaling, int32_t* indices, float* weights) {
+    float* orig = (float*)malloc(sizeof(float) * (size_t)n_experts);
+    float* sel = (float*)malloc(sizeof(float) * (size_t)n_experts);
+    for (int e = 0; e < n_experts; ++e) {
+        orig[e] = 1.0f / (1.0f + orc_expf(-logits[e]));
+        sel[e] = expert_bias ? orig[e] + expert_bias[e] : orig[e];
+    }
+    topk_indices(sel, n_experts, k, indices);
+    for (int j = 0; j < k; ++j) weights[j] = orig[indices[j]];
+    if (k > 1 && norm_topk_prob) {
+        float sum = 0.0f;
+        for (int j = 0; j < k; ++j) sum = sum + weights[j];
+        sum = sum + 1e-20f;
+        for (int j = 0; j < k; ++j) weights[j] = weights[j] / sum;
+    }
+    for (int j = 0; j < k; ++j) weights[j] = weights[j] * routed_scaling;
+    free(orig); free(sel);
+}
+
+/* MoERouter.route — MoELayer.swift:140-205 (three branches, kept as written); routed_scaling applies to the
+ * sigmoid mode only. */
+ORC_EXPORT void orc_route_scaled(const float* logits, int n_experts, int k, int gating_mode,
+                                 int norm_topk_prob, const float* expert_bias, float routed_scaling,
+                                 int32_t* indices, float* weights);
 ORC_EXPORT void orc_route(const float* logits, int n_experts, int k, int gating_mode,
                           int norm_topk_prob, const float* expert_bias, int32_t* indices,
                           float* weights) {
+    orc_route_scaled(logits, n_experts, k, gating_mode, norm_topk_prob, expert_bias, 1.0f, indices, weights);
+}
+ORC_EXPORT void orc_route_scaled(const float* logits, int n_experts, int k, int gating_mode,
+                                 int norm_topk_prob, const float* expert_bias, float routed_scaling,
+                                 int32_t* indices, float* weights) {
     float picked[FFAI_MAX_TOP_K];
+    if (gating_mode == FFAI_GATING_SIGMOID_TOPK) {
+        route_sigmoid(logits, n_experts, k, norm_topk_prob, expert_bias, routed_scaling, indices, weights);
+        return;
+    }
     if ((gating_mode == FFAI_GATING_SOFTMAX_THEN_TOPK && norm_topk_prob && !expert_bias) ||
         gating_mode == FFAI_GATING_TOPK_THEN_SOFTMAX) {
         topk_indices(logits, n_experts, k, indices);
@@ -373,11 +410,28 @@ static inline float proj_bias(const proj_view* v, int64_t e, int o) {
 static void run_expert(const ffai_moe_config* c, const proj_view* pg, const proj_view* pu,
                        const proj_view* pd, int64_t e, const float* const* xs, float* const* ys,
                        int cnt, int round_stages) {
-    const int H = pg->in_dim, I = pg->out_dim;
+    const int H = pu->in_dim, I = pu->out_dim;
+    /* experts without a gate projection (NemotronHExpert.forward, NemotronHText.swift:756-762): relu(up)^2 */
+    const int no_gate = c->activation == FFAI_ACT_RELU2;
     float* wg = (float*)malloc(sizeof(float) * (size_t)(H > I ? H : I));
     float* wu = (float*)malloc(sizeof(float) * (size_t)H);
     float* inner = (float*)malloc(sizeof(float) * (size_t)cnt * I);
     for (int n = 0; n < I; ++n) {
+        if (no_gate) {
+            proj_row(pu, e, n, wu);
+            float bu = proj_bias(pu, e, n);
+            for (int r = 0; r < cnt; ++r) {
+                float u = dot_seq(wu, xs[r], H);
+                if (round_stages) u = bf16r(u);
+                if (pu->p->row_bias) { u = u + bu; if (round_stages) u = bf16r(u); }
+                float a = u > 0.0f ? u : 0.0f;
+                if (round_stages) a = bf16r(a);
+                a = a * a;
+                if (round_stages) a = bf16r(a);
+                inner[(int64_t)r * I + n] = a;
+            }
+            continue;
+        }
         proj_row(pg, e, n, wg);
         proj_row(pu, e, n, wu);
         float bg = proj_bias(pg, e, n), bu = proj_bias(pu, e, n);
@@ -462,8 +516,9 @@ ORC_EXPORT int orc_moe_forward_split(const ffai_moe_config* c, const ffai_moe_we
 #pragma omp parallel for schedule(static)
     for (int t = 0; t < T; ++t) {
         int32_t idx[FFAI_MAX_TOP_K];
-        orc_route((scaled ? scaled : logits) + (int64_t)t * E, E, K, c->gating_mode, c->norm_topk_prob,
-                  c->router_expert_bias ? w->router_expert_bias : NULL, idx, rw + (int64_t)t * K);
+        orc_route_scaled((scaled ? scaled : logits) + (int64_t)t * E, E, K, c->gating_mode, c->norm_topk_prob,
+                         c->router_expert_bias ? w->router_expert_bias : NULL,
+                         c->routed_scaling_factor != 0.0f ? c->routed_scaling_factor : 1.0f, idx, rw + (int64_t)t * K);
         for (int s = 0; s < K; ++s) {
             indices[(int64_t)t * K + s] = (uint32_t)idx[s];
             if (w->router_per_expert_scale) rw[(int64_t)t * K + s] *= w->router_per_expert_scale[idx[s]];
@@ -519,7 +574,8 @@ ORC_EXPORT int orc_moe_forward_split(const ffai_moe_config* c, const ffai_moe_we
         proj_view su = {&w->shared_up_proj, c->shared_bits, c->shared_group_size, c->shared_intermediate, H};
         proj_view sd = {&w->shared_down_proj, c->shared_bits, c->shared_group_size, H, c->shared_intermediate};
         ffai_moe_config cs = *c;
-        cs.activation = FFAI_ACT_SWIGLU; /* the shared expert is a plain SwiGLU MLP */
+        /* the shared expert is a plain SwiGLU MLP, or, beside gate-less experts, of their form (NemotronHText.swift:885-891) */
+        cs.activation = c->activation == FFAI_ACT_RELU2 ? FFAI_ACT_RELU2 : FFAI_ACT_SWIGLU;
         int nthr = 1;
 #ifdef _OPENMP
         nthr = omp_get_max_threads();

@@ -428,3 +428,16 @@ def test_cfg5_at_its_full_size_with_requantized_experts(oracle_mod):
     mask = np.zeros(16384, dtype=np.uint8)
     mask[np.random.default_rng(55).choice(16384, size=32, replace=False)] = 1
     run_and_check(oracle_mod, host.spec, 16384, host=host, token_mask=mask)
+
+
+# ── NemotronH-style block: sigmoid routing with selection bias and scaling factor, experts without a gate projection ──
+
+@pytest.mark.parametrize("T", [1, 7, 64, 300])
+def test_nemotronh_style_block(oracle_mod, T):
+    spec = synth.nemotronh_style()
+    run_and_check(oracle_mod, spec, T, seed=6, residual=(T == 7))
+
+
+def test_nemotronh_style_block_other_widths(oracle_mod):
+    run_and_check(oracle_mod, synth.nemotronh_style().with_(name="nemotronh_8bit", expert_bits=8, shared_bits=8, norm_topk_prob=0), 33)
+    run_and_check(oracle_mod, synth.nemotronh_style().with_(name="nemotronh_no_shared", shared_intermediate=0, top_k=1), 20)

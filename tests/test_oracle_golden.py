@@ -193,3 +193,54 @@ def test_layer_matches_numpy_float64(oracle_mod):
     r2 = oracle_mod.moe_forward(layer, x, round_stages=True)
     rel2 = np.sqrt(((r2.out_f32 - r.out_f32) ** 2).mean()) / np.sqrt((r.out_f32 ** 2).mean())
     assert rel2 < 5e-3
+
+
+def test_sigmoid_routing_follows_the_reference_steps(oracle_mod):
+    """NemotronH routing (NemotronHText.swift:844-867) restated in numpy float32: sigmoid, selection on
+    sigmoid + bias with ties to the lower index, raw sigmoids of the selected over (sum + 1e-20), scaling."""
+    from ffai_b200 import capi
+    logits = np.array([0.0, 1.0, -1.0, 2.0, 1.0, -3.0], dtype=np.float32)
+    bias = np.array([0.5, 0.0, 0.0, -1.0, 0.0, 2.0], dtype=np.float32)
+    sig = (np.float32(1) / (np.float32(1) + np.exp(-logits).astype(np.float32))).astype(np.float32)
+    sel = sig + bias
+    order = sorted(range(len(sel)), key=lambda i: (-sel[i], i))
+    for k, norm, scale in ((2, 1, 2.5), (3, 1, 1.0), (3, 0, 0.5), (1, 1, 2.0)):
+        want_idx = order[:k]
+        w = sig[want_idx].astype(np.float32)
+        if k > 1 and norm:
+            w = (w / (np.float32(w.sum(dtype=np.float32)) + np.float32(1e-20))).astype(np.float32)
+        w = (w * np.float32(scale)).astype(np.float32)
+        idx, got = oracle_mod.route(logits, k, capi.GATING_SIGMOID_TOPK, norm, bias, routed_scaling=scale)
+        assert list(idx) == want_idx
+        assert np.allclose(got, w, rtol=3e-7, atol=0)
+    # experts 1 and 4 tie on the selection score: the lower index goes first
+    assert order.index(1) < order.index(4) and sel[1] == sel[4]
+    # without a bias the selection is on the sigmoid itself
+    idx, _ = oracle_mod.route(logits, 2, capi.GATING_SIGMOID_TOPK, 1, None)
+    assert list(idx) == [3, 1]
+
+
+def test_gateless_relu2_expert_matches_a_numpy_restatement(oracle_mod):
+    """down(relu(up x)^2) with an always-on shared expert of the same form (NemotronHText.swift:741-763, 885-899),
+    against a numpy float64 restatement on a small layer."""
+    from ffai_b200 import synth
+    spec = synth.nemotronh_style().with_(hidden=128, intermediate=64, n_experts=4, top_k=2, shared_intermediate=64)
+    host = synth.make_layer(spec, 3)
+    assert "experts.gate_proj.weight" not in host.arrays and "shared_expert.gate_proj.weight" not in host.arrays
+    x = synth.make_tokens(5, spec.hidden, 3)
+    r = oracle_mod.moe_forward(host, x)
+    a = host.arrays
+    xf = synth.bf16_to_f32(x).astype(np.float64)
+
+    def deq(name, e, n):
+        return synth.dequantize(a[name + ".weight"][e], a[name + ".scales"][e], a[name + ".biases"][e], 4, 64, n).astype(np.float64)
+
+    want = np.zeros((5, spec.hidden))
+    for t in range(5):
+        for s in range(spec.top_k):
+            e = int(r.indices[t, s])
+            inner = np.maximum(deq("experts.up_proj", e, spec.hidden) @ xf[t], 0.0) ** 2
+            want[t] += float(r.weights[t, s]) * (deq("experts.down_proj", e, spec.intermediate) @ inner)
+        inner = np.maximum(deq("shared_expert.up_proj", 0, spec.hidden) @ xf[t], 0.0) ** 2
+        want[t] += deq("shared_expert.down_proj", 0, spec.shared_intermediate) @ inner
+    assert np.allclose(r.out_f32, want, rtol=2e-4, atol=2e-4 * np.abs(want).max())
