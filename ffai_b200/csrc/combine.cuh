@@ -29,6 +29,7 @@ combine_kernel(const TY* __restrict__ y, const uint32_t* __restrict__ inv_perm,
     __shared__ uint32_t pos_s[32];
     __shared__ float w_s[32];
     __shared__ float sig_s;
+    pdl_wait();
     if (threadIdx.x < k) {
         pos_s[threadIdx.x] = inv_perm[(size_t)t * k + threadIdx.x];
         w_s[threadIdx.x] = weights[(size_t)t * k + threadIdx.x];

@@ -24,6 +24,13 @@ struct SmemOptIn {
     }
 };
 
+// Programmatic dependent launch (a kernel launched with the programmatic-stream-serialization attribute may start
+// while its predecessor in the stream is still running): `pdl_wait` blocks until the predecessor has completed and
+// its memory is visible; everything before it must not read what the predecessor writes.  `pdl_launch_dependents`
+// lets the successor's blocks be scheduled as this kernel's blocks retire.  Both are no-ops in a plain launch.
+FFAI_DEVINL void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+FFAI_DEVINL void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // bf16 bit pattern <-> fp32.  Same rule as FFAI's Tensor.swift:107-113,145-150
 // (round to nearest even on the bit pattern).
 FFAI_DEVINL float bf16_bits_to_f32(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }

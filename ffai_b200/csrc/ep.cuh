@@ -231,14 +231,27 @@ ep_dispatch_kernel(const uint16_t* __restrict__ x, const uint32_t* __restrict__ 
     }
     const uint4* s = reinterpret_cast<const uint4*>(x + (size_t)(pe / (uint32_t)k) * hidden);
     uint4* d = reinterpret_cast<uint4*>(static_cast<uint16_t*>(rows_of.p[e / (uint32_t)e_local]) + (size_t)pos * hidden);
-    for (int i = lane; i < hidden / 8; i += 32) {
-        const uint4 v = s[i];
-        uint4 o;
-        o.x = __byte_perm(v.x, v.z, 0x5410);
-        o.y = __byte_perm(v.x, v.z, 0x7632);
-        o.z = __byte_perm(v.y, v.w, 0x5410);
-        o.w = __byte_perm(v.y, v.w, 0x7632);
-        d[i] = o;
+    // four 16-byte pieces per lane in flight: all loads first, then the (possibly remote) stores
+    const int chunks = hidden / 8;
+    for (int i0 = 0; i0 < chunks; i0 += 128) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 32 + lane;
+            if (i < chunks) v[u] = s[i];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 32 + lane;
+            if (i < chunks) {
+                uint4 o;
+                o.x = __byte_perm(v[u].x, v[u].z, 0x5410);
+                o.y = __byte_perm(v[u].x, v[u].z, 0x7632);
+                o.z = __byte_perm(v[u].y, v[u].w, 0x5410);
+                o.w = __byte_perm(v[u].y, v[u].w, 0x7632);
+                d[i] = o;
+            }
+        }
     }
 }
 
@@ -273,26 +286,42 @@ combine_peer_kernel(PeerPtrs y_of, const uint32_t* __restrict__ inv_perm, const 
         sig_s = sig;
     }
     __syncthreads();
-    for (int h = threadIdx.x * 4; h < hidden; h += blockDim.x * 4) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s = 0; s < k; ++s) {
-            const float w = w_s[s];
-            const uint2 u = *reinterpret_cast<const uint2*>(row_s[s] + h);
-            acc.x += w * bf16lo(u.x); acc.y += w * bf16hi(u.x); acc.z += w * bf16lo(u.y); acc.w += w * bf16hi(u.y);
+    // a thread owns 8 consecutive hidden positions; the (remote) rows of up to 8 slots are loaded before the first use
+    for (int h = threadIdx.x * 8; h < hidden; h += blockDim.x * 8) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        for (int s0 = 0; s0 < k; s0 += 8) {
+            uint4 u[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (s0 + j < k) u[j] = *reinterpret_cast<const uint4*>(row_s[s0 + j] + h);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (s0 + j < k) {   // slot order: the sum does not depend on the launch geometry
+                    const float w = w_s[s0 + j];
+                    acc[0] += w * bf16lo(u[j].x); acc[1] += w * bf16hi(u[j].x); acc[2] += w * bf16lo(u[j].y); acc[3] += w * bf16hi(u[j].y);
+                    acc[4] += w * bf16lo(u[j].z); acc[5] += w * bf16hi(u[j].z); acc[6] += w * bf16lo(u[j].w); acc[7] += w * bf16hi(u[j].w);
+                }
         }
         if (shared_y) {
             const float sig = sig_s;
-            const float4 v = *reinterpret_cast<const float4*>(shared_y + (size_t)t * hidden + h);
-            acc.x += sig * v.x; acc.y += sig * v.y; acc.z += sig * v.z; acc.w += sig * v.w;
+            const float4 v0 = *reinterpret_cast<const float4*>(shared_y + (size_t)t * hidden + h);
+            const float4 v1 = *reinterpret_cast<const float4*>(shared_y + (size_t)t * hidden + h + 4);
+            acc[0] += sig * v0.x; acc[1] += sig * v0.y; acc[2] += sig * v0.z; acc[3] += sig * v0.w;
+            acc[4] += sig * v1.x; acc[5] += sig * v1.y; acc[6] += sig * v1.z; acc[7] += sig * v1.w;
         }
         if (residual) {
-            const uint2 u = *reinterpret_cast<const uint2*>(residual + (size_t)t * hidden + h);
-            acc.x += bf16lo(u.x); acc.y += bf16hi(u.x); acc.z += bf16lo(u.y); acc.w += bf16hi(u.y);
+            const uint4 r = *reinterpret_cast<const uint4*>(residual + (size_t)t * hidden + h);
+            acc[0] += bf16lo(r.x); acc[1] += bf16hi(r.x); acc[2] += bf16lo(r.y); acc[3] += bf16hi(r.y);
+            acc[4] += bf16lo(r.z); acc[5] += bf16hi(r.z); acc[6] += bf16lo(r.w); acc[7] += bf16hi(r.w);
         }
-        uint2 o;
-        o.x = (uint32_t)f32_to_bf16_bits(acc.x) | ((uint32_t)f32_to_bf16_bits(acc.y) << 16);
-        o.y = (uint32_t)f32_to_bf16_bits(acc.z) | ((uint32_t)f32_to_bf16_bits(acc.w) << 16);
-        *reinterpret_cast<uint2*>(out + (size_t)t * hidden + h) = o;
+        uint4 o;
+        o.x = (uint32_t)f32_to_bf16_bits(acc[0]) | ((uint32_t)f32_to_bf16_bits(acc[1]) << 16);
+        o.y = (uint32_t)f32_to_bf16_bits(acc[2]) | ((uint32_t)f32_to_bf16_bits(acc[3]) << 16);
+        o.z = (uint32_t)f32_to_bf16_bits(acc[4]) | ((uint32_t)f32_to_bf16_bits(acc[5]) << 16);
+        o.w = (uint32_t)f32_to_bf16_bits(acc[6]) | ((uint32_t)f32_to_bf16_bits(acc[7]) << 16);
+        *reinterpret_cast<uint4*>(out + (size_t)t * hidden + h) = o;
     }
 }
 

@@ -468,6 +468,8 @@ grouped_mma_decode_kernel(const Params p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    pdl_wait();                 // the routing tables and the activation rows come from the kernels before this one
+    pdl_launch_dependents();
     const int e = p.order ? (int)p.order[blockIdx.y] : (int)blockIdx.y;
     const int row0 = (int)p.offsets[e], cnt = (int)p.offsets[e + 1] - row0;
     if (cnt <= 0) return;

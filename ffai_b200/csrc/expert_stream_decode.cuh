@@ -69,6 +69,8 @@ struct Params {
     int activation;
     float limit, alpha;
     int nt2_cost;             // cost of an item with more than 8 rows relative to 8 for one with fewer (>= 8)
+    int tables_ready;         // 1: offsets / order were written two or more kernels back (a programmatic dependent launch
+                              // may build its schedule and start streaming weights before the kernel before it has ended)
     uint32_t* error_word;
 };
 
@@ -236,6 +238,7 @@ stream_decode_kernel(const Params p) {
     if (lane == 0)
         for (int d = 0; d < DEPTH; ++d) mbar_init(bar0 + d * 8, 1);
     if (threadIdx.x == 0) mbar_init(xbar, 1);
+    if (!p.tables_ready) pdl_wait();   // the routing tables come from the kernel right before this one
     // schedule tables: one warp scans the experts in hand-out order
     if (warp == 0) {
         uint32_t run_i = 0, run_c = 0;
@@ -318,6 +321,9 @@ stream_decode_kernel(const Params p) {
 #pragma unroll 1
     for (int d = 0; d < DEPTH; ++d) produce(ring_u + d * SLOT, bar0 + d * 8);
 
+    // The weights are in flight; the activation rows (and their sums) come from the kernel before this one.
+    if (p.tables_ready) pdl_wait();
+    pdl_launch_dependents();
     uint32_t c_off = 0, c_bar = bar0, c_phase = 0;   // slot cursor: byte offset into the ring, its mbarrier, the phase bit to wait for
     uint32_t x_phase = 0;
     int g_ord = 0;                      // expert cursor of the group builder (thread 0)

@@ -80,6 +80,7 @@ struct ffai_moe_layer {
     uint8_t* st_gate_up = nullptr;   // bulk-copy streams of the decode kernels: gate and up interleaved per 64-run, ...
     uint8_t* st_down = nullptr;      // ... and down (re-tiled copies of the packed experts, owned with the weights)
     int opt_decode = 0;              // decode kernels: 0 automatic, 1 per-lane cp.async rings, 2 bulk-copy streams
+    int opt_pdl = 1;                 // decode chain: programmatic dependent launches (0: plain launches)
     int opt_decode_team = 0;         // bulk-copy streams: warps per 16-row block (0 automatic, 1, 4, 16)
     int opt_nt2_cost = 12;           // bulk-copy streams: schedule weight of an item with more than 8 rows (8 = as one with fewer)
     uint32_t* sb_gate = nullptr;     // repacked (scale | bias << 16) words of the expert projections
@@ -261,6 +262,20 @@ void free_list(std::vector<void*>& v) {
         default: return FFAI_ERR_INVALID_ARG;                   \
     }
 
+// Launch with or without the programmatic-stream-serialization attribute (the kernel then calls pdl_wait before it
+// reads anything its predecessor in the stream writes).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename TIn, typename TOut, bool FUSED>
 int launch_grouped_gemv(const GemvParams& p, int bits, const TIn* in, TOut* out, int expert_slots,
                         cudaStream_t st) {
@@ -314,6 +329,26 @@ void launch_router_tiled(const RouterParams& p, const uint16_t* x, int T, float*
 int launch_router_batched(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w,
                           float* logits, float* partials, size_t partials_capacity, int n_sms, cudaStream_t st) {
     const int n_chunks = p.hidden / 64;
+    // long chunks: 128-token tiles with the next chunk's loads in flight behind the arithmetic (dense weights; a
+    // quantized router arrives here expanded to fp32).  Needs at least one tile per SM to pay.
+    if ((p.kind == FFAI_LINEAR_F32 || p.kind == FFAI_LINEAR_BF16) && p.hidden % 64 == 0 &&
+        ((T + RB_TOK - 1) / RB_TOK) * ((p.n_experts + RB_EXP - 1) / RB_EXP) >= n_sms) {
+        const dim3 grid((T + RB_TOK - 1) / RB_TOK, (p.n_experts + RB_EXP - 1) / RB_EXP);
+        static SmemOptIn opt1, opt2;
+        bool ok;
+        if (p.kind == FFAI_LINEAR_F32) {
+            ok = opt1.ensure(router_logits_big_kernel<1>, RB_SMEM);
+            if (ok) router_logits_big_kernel<1><<<grid, 256, RB_SMEM, st>>>(p, x, T, logits);
+        } else {
+            ok = opt2.ensure(router_logits_big_kernel<2>, RB_SMEM);
+            if (ok) router_logits_big_kernel<2><<<grid, 256, RB_SMEM, st>>>(p, x, T, logits);
+        }
+        if (ok) {
+            const int warps = 4;
+            route_only_kernel<<<(T + warps - 1) / warps, warps * 32, (size_t)warps * 2 * p.n_experts * sizeof(float), st>>>(p, logits, T, idx, w);
+            return cudaGetLastError() == cudaSuccess ? 2 : -1;
+        }
+    }
     const bool few_blocks = ((T + 63) / 64) * ((p.n_experts + 63) / 64) < 4 * n_sms;
     if (!(partials && few_blocks && (size_t)T * p.n_experts * n_chunks <= partials_capacity)) partials = nullptr;
     switch (p.kind) {
@@ -339,14 +374,18 @@ template <int KIND>
 int launch_router_rows(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w, float* logits,
                        uint32_t* tickets, const PlanOut& plan, uint16_t* x_perm8, float* x_sum64, int sum_pitch, cudaStream_t st) {
     const int wbytes = KIND == 1 ? 4 : 2;
-    const size_t smem = (size_t)ROUTER_ROWS * p.hidden * wbytes + (size_t)p.hidden * 2 +
-                        (size_t)ROUTER_ROWS * (p.hidden / 64) * 4 + 2 * (size_t)p.n_experts * 4;
+    // rows per block: 8, or fewer while the grid would leave most SMs without a block (a one-token step reads the
+    // router's weights through E / rows blocks only)
+    int rpb = ROUTER_ROWS;
+    while (rpb > 1 && ((p.n_experts + rpb - 1) / rpb) * T < 64) rpb >>= 1;
+    const size_t smem = (size_t)rpb * p.hidden * wbytes + (size_t)p.hidden * 2 +
+                        (size_t)rpb * (p.hidden / 64) * 4 + 2 * (size_t)p.n_experts * 4;
     if (smem > 200 * 1024 || p.hidden % 64 || T > ROUTER_BATCH_TICKET) return -1;
     auto k = router_rows_kernel<KIND>;
     static SmemOptIn opt_in;
     if (smem > 48 * 1024 && !opt_in.ensure(k, (int)smem)) return -1;
-    dim3 grid((p.n_experts + ROUTER_ROWS - 1) / ROUTER_ROWS, T);
-    k<<<grid, 256, smem, st>>>(p, x, T, idx, w, logits, tickets, plan, x_perm8, x_sum64, sum_pitch);
+    dim3 grid((p.n_experts + rpb - 1) / rpb, T);
+    k<<<grid, 256, smem, st>>>(p, x, T, idx, w, logits, tickets, plan, x_perm8, x_sum64, sum_pitch, rpb);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -395,7 +434,7 @@ int launch_plan(const uint32_t* indices, int n_rows, int E, uint32_t* counts, ui
 }
 
 template <bool FUSED, int NT, int KSPLIT, bool G32>
-void launch_mma_decode_k(const dmma::Params& p, int n_experts, cudaStream_t st) {
+void launch_mma_decode_k(const dmma::Params& p, int n_experts, cudaStream_t st, bool pdl) {
     using WS = dmma::WarpStage<FUSED, G32>;
     auto k = dmma::grouped_mma_decode_kernel<FUSED, NT, KSPLIT, G32>;
     const int smem = WS::smem_bytes(p.K / 64, KSPLIT);
@@ -404,49 +443,48 @@ void launch_mma_decode_k(const dmma::Params& p, int n_experts, cudaStream_t st) 
     const int rbw = 4 / KSPLIT;
     const int row_blocks = (FUSED && p.pair) ? (p.N + 31) / 32 : p.N / 16;   // 16-row blocks, or 32-row pairs
     dim3 grid((row_blocks + rbw - 1) / rbw, n_experts);
-    k<<<grid, 128, smem, st>>>(p);
+    launch_kernel(k, grid, dim3(128), (size_t)smem, st, pdl, p);
 }
 
 template <bool FUSED, bool G32>
-void launch_mma_decode_g(const dmma::Params& p, int n_experts, int nt, int ksplit, cudaStream_t st) {
+void launch_mma_decode_g(const dmma::Params& p, int n_experts, int nt, int ksplit, cudaStream_t st, bool pdl) {
     if (nt == 2) {
-        if (ksplit == 4) launch_mma_decode_k<FUSED, 2, 4, G32>(p, n_experts, st);
-        else if (ksplit == 2) launch_mma_decode_k<FUSED, 2, 2, G32>(p, n_experts, st);
-        else launch_mma_decode_k<FUSED, 2, 1, G32>(p, n_experts, st);
+        if (ksplit == 4) launch_mma_decode_k<FUSED, 2, 4, G32>(p, n_experts, st, pdl);
+        else if (ksplit == 2) launch_mma_decode_k<FUSED, 2, 2, G32>(p, n_experts, st, pdl);
+        else launch_mma_decode_k<FUSED, 2, 1, G32>(p, n_experts, st, pdl);
     } else {
-        if (ksplit == 4) launch_mma_decode_k<FUSED, 1, 4, G32>(p, n_experts, st);
-        else if (ksplit == 2) launch_mma_decode_k<FUSED, 1, 2, G32>(p, n_experts, st);
-        else launch_mma_decode_k<FUSED, 1, 1, G32>(p, n_experts, st);
+        if (ksplit == 4) launch_mma_decode_k<FUSED, 1, 4, G32>(p, n_experts, st, pdl);
+        else if (ksplit == 2) launch_mma_decode_k<FUSED, 1, 2, G32>(p, n_experts, st, pdl);
+        else launch_mma_decode_k<FUSED, 1, 1, G32>(p, n_experts, st, pdl);
     }
 }
 
 // nt: 8-row activation tiles per pass (1 or 2); ksplit: slices of the reduction axis per 16-row block (1, 2, 4);
 // the group size (p.group_size) picks the 32-run variant
 template <bool FUSED>
-void launch_mma_decode(const dmma::Params& p, int n_experts, int nt, int ksplit, cudaStream_t st) {
-    if (p.group_size == 32) launch_mma_decode_g<FUSED, true>(p, n_experts, nt, ksplit, st);
-    else launch_mma_decode_g<FUSED, false>(p, n_experts, nt, ksplit, st);
+void launch_mma_decode(const dmma::Params& p, int n_experts, int nt, int ksplit, cudaStream_t st, bool pdl = false) {
+    if (p.group_size == 32) launch_mma_decode_g<FUSED, true>(p, n_experts, nt, ksplit, st, pdl);
+    else launch_mma_decode_g<FUSED, false>(p, n_experts, nt, ksplit, st, pdl);
 }
 
 // Bulk-copy streamed decode kernels.  team: warps that share one 16-row block (4, or 16 for the smallest batches).
 // Returns false when the shape does not fit the kernel's shared memory (the caller then uses the cp.async kernels).
 template <bool FUSED, int TEAM, int CPU, int DEPTH>
-bool launch_stream_decode_t(const dstr::Params& p, int n_sms, cudaStream_t st) {
+bool launch_stream_decode_t(const dstr::Params& p, int n_sms, cudaStream_t st, bool pdl) {
     using LY = dstr::Layout<FUSED, TEAM, CPU, DEPTH>;
     const int smem = LY::total(p.n_experts, p.K);
     if (smem > 227 * 1024) return false;
     auto k = dstr::stream_decode_kernel<FUSED, TEAM, CPU, DEPTH>;
     static SmemOptIn opt_in;
     if (!opt_in.ensure(k, smem)) return false;
-    k<<<n_sms, dstr::THREADS, smem, st>>>(p);
-    return true;
+    return launch_kernel(k, dim3(n_sms), dim3(dstr::THREADS), (size_t)smem, st, pdl, p) == cudaSuccess;
 }
 template <bool FUSED>
-bool launch_stream_decode(const dstr::Params& p, int team, int n_sms, cudaStream_t st) {
+bool launch_stream_decode(const dstr::Params& p, int team, int n_sms, cudaStream_t st, bool pdl) {
     constexpr int CPU2 = FUSED ? 1 : 2;
-    if (team == 16) return launch_stream_decode_t<FUSED, 16, 1, 5>(p, n_sms, st) || launch_stream_decode_t<FUSED, 16, 1, 3>(p, n_sms, st);
-    if (team == 4) return launch_stream_decode_t<FUSED, 4, CPU2, 5>(p, n_sms, st) || launch_stream_decode_t<FUSED, 4, CPU2, 3>(p, n_sms, st);
-    return launch_stream_decode_t<FUSED, 1, CPU2, 6>(p, n_sms, st) || launch_stream_decode_t<FUSED, 1, CPU2, 3>(p, n_sms, st);
+    if (team == 16) return launch_stream_decode_t<FUSED, 16, 1, 5>(p, n_sms, st, pdl) || launch_stream_decode_t<FUSED, 16, 1, 3>(p, n_sms, st, pdl);
+    if (team == 4) return launch_stream_decode_t<FUSED, 4, CPU2, 5>(p, n_sms, st, pdl) || launch_stream_decode_t<FUSED, 4, CPU2, 3>(p, n_sms, st, pdl);
+    return launch_stream_decode_t<FUSED, 1, CPU2, 6>(p, n_sms, st, pdl) || launch_stream_decode_t<FUSED, 1, CPU2, 3>(p, n_sms, st, pdl);
 }
 
 // dense [1,H] projection per token (shared-expert gate stored as f32 / bf16)
@@ -1080,6 +1118,10 @@ extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name,
         L->opt_decode = value;
         return FFAI_OK;
     }
+    if (!strcmp(name, "pdl")) {
+        L->opt_pdl = value != 0;
+        return FFAI_OK;
+    }
     if (!strcmp(name, "decode_team")) {
         if (value != 0 && value != 1 && value != 4 && value != 16) return fail(L, FFAI_ERR_INVALID_ARG, "option decode_team must be 0, 1, 4 or 16");
         L->opt_decode_team = value;
@@ -1527,7 +1569,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
     //   CUDA-core grouped GEMV          any bit width / group size, and shapes the others do not take
     const double rows_per_expert = (double)M / E;
     const bool can_tc = tc_possible(L);
-    bool mma_experts = false, tc_experts = false;
+    bool mma_experts = false, tc_experts = false, decode_pdl = false;
     if (ep_on) { /* done above */ }
     else if (L->opt_path == 3) mma_experts = L->mma_ok;
     else if (L->opt_path == 2) tc_experts = can_tc;
@@ -1551,6 +1593,11 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         // Which decode kernels: the bulk-copy streamed ones (a warp owns a 16-row block; the batch sizes where they
         // measure faster on the GPT-OSS shape: more than 8 and at most 160 routed rows), else the cp.async ring kernels.
         const bool stream = L->st_gate_up && (L->opt_decode == 2 || (L->opt_decode == 0 && M > 8 && M <= 160));
+        // Programmatic dependent launches down the decode chain (gate/up after the router, down after gate/up, the
+        // combine after down): a kernel's blocks start as its predecessor's retire.  Stage events between the
+        // launches would serialise them again, so the chain is plain when timing is on.
+        const bool pdl = L->opt_pdl && !L->timing;
+        decode_pdl = pdl;
         bool streamed = false;
         if (stream) {
             dstr::Params q{};
@@ -1563,14 +1610,16 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
             q.wt = L->st_gate_up; q.rb1 = L->w.gate_proj.row_bias; q.rb2 = L->w.up_proj.row_bias;
             q.N = I; q.K = H; q.x = L->x_tok; q.row_src = L->perm; q.row_div = K; q.xsum = L->xsum_tok; q.xsum_pitch = xp_h;
             q.out = L->inner_bf; q.out_parts = L->inner_parts;
-            streamed = launch_stream_decode<true>(q, team, L->n_sms, st);
+            q.tables_ready = 0;
+            streamed = launch_stream_decode<true>(q, team, L->n_sms, st, pdl);
             stage_end(L, ST_GATE_UP, st);
             if (streamed) {
                 stage_begin(L, ST_DOWN, st);
                 q.wt = L->st_down; q.rb1 = L->w.down_proj.row_bias; q.rb2 = nullptr;
                 q.N = H; q.K = I; q.x = L->inner_bf; q.row_src = nullptr; q.row_div = 1; q.xsum = nullptr; q.xsum_parts = L->inner_parts;
                 q.out = L->y; q.out_parts = nullptr;
-                streamed = launch_stream_decode<false>(q, team, L->n_sms, st);
+                q.tables_ready = 1;   // routing tables were written before the gate/up kernel started
+                streamed = launch_stream_decode<false>(q, team, L->n_sms, st, pdl);
                 stage_end(L, ST_DOWN, st);
                 if (!streamed) return fail(L, FFAI_ERR_UNSUPPORTED, "down projection does not fit the streamed decode kernel");
                 L->launches += 2;
@@ -1594,7 +1643,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         p.N = I; p.K = H; p.x = L->x_tok; p.xsum = L->xsum_tok; p.xsum_pitch = xp_h; p.out = L->inner_bf;
         p.row_src = L->perm; p.row_div = K;
         p.out_parts = L->inner_parts;
-        launch_mma_decode<true>(p, E, nt, ksplit, st);
+        launch_mma_decode<true>(p, E, nt, ksplit, st, pdl);
         p.row_src = nullptr; p.row_div = 1;
         L->launches += 1;
         stage_end(L, ST_GATE_UP, st);
@@ -1607,8 +1656,8 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         p.out_parts = nullptr;
         // group 32: 32 rows per warp through the two-projection kernel (measured 9 % faster there; no gain at group 64)
         p.pair = c.expert_group_size == 32;
-        if (p.pair) launch_mma_decode<true>(p, E, nt, ksplit, st);
-        else launch_mma_decode<false>(p, E, nt, ksplit, st);
+        if (p.pair) launch_mma_decode<true>(p, E, nt, ksplit, st, pdl);
+        else launch_mma_decode<false>(p, E, nt, ksplit, st, pdl);
         L->launches += 1;
         stage_end(L, ST_DOWN, st);
         if (cudaGetLastError() != cudaSuccess) return fail(L, FFAI_ERR_CUDA, "decode kernels launch failed");
@@ -1757,8 +1806,9 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         combine_kernel<float, float><<<T, 256, 0, st>>>(L->ep_home_y, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
     else if (tc_experts)
         combine_kernel<uint16_t, float><<<T, 256, 0, st>>>(L->y_bf, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
-    else
-        combine_kernel<float, float><<<T, 256, 0, st>>>(L->y, L->inv_perm, L->rweights, K, sh_y, sh_gate, residual, out, H);
+    else if (launch_kernel(combine_kernel<float, float>, dim3(T), dim3(256), 0, st, decode_pdl && !sh_y, (const float*)L->y, (const uint32_t*)L->inv_perm,
+                           (const float*)L->rweights, K, sh_y, sh_gate, residual, out, H) != cudaSuccess)
+        return fail(L, FFAI_ERR_CUDA, "combine launch failed");
     L->launches += 1;
     stage_end(L, ST_COMBINE, st);
     if (cudaGetLastError() != cudaSuccess) return fail(L, FFAI_ERR_CUDA, "combine launch failed");

@@ -264,7 +264,7 @@ router_token_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens
 // the last slot of the ticket array) also builds the dispatch plan, which saves a launch per step.
 // Shared-memory rows are stored with the 16-byte pieces of each 64-value line XOR-swizzled by the
 // line index, so threads that read consecutive lines hit distinct banks.
-constexpr int ROUTER_ROWS = 8;
+constexpr int ROUTER_ROWS = 8;                // most weight rows a block stages (fewer when the batch is tiny, so that the grid still covers the SMs)
 constexpr int ROUTER_TICKETS = 96;             // per-token tickets; the last slot counts routed tokens of the batch
 constexpr int ROUTER_BATCH_TICKET = ROUTER_TICKETS - 1;
 
@@ -273,19 +273,19 @@ __global__ void __launch_bounds__(256)
 router_rows_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens,
                    uint32_t* __restrict__ indices, float* __restrict__ weights,
                    float* __restrict__ logits_out, uint32_t* __restrict__ tickets, PlanOut plan,
-                   uint16_t* __restrict__ x_perm8, float* __restrict__ x_sum64, int sum_pitch) {
+                   uint16_t* __restrict__ x_perm8, float* __restrict__ x_sum64, int sum_pitch, int rows_per_block) {
     constexpr int WBYTES = KIND == 1 ? 4 : 2;
     constexpr int LINE16 = 64 * WBYTES / 16;   // 16-byte pieces per 64-value line of a weight row
     extern __shared__ __align__(16) uint8_t rsm[];
     const int H = p.hidden, E = p.n_experts;
     const int nchunks = H / 64;
     const int t = blockIdx.y;
-    const int e0 = blockIdx.x * ROUTER_ROWS;
-    const int rows = min(ROUTER_ROWS, E - e0);
+    const int e0 = blockIdx.x * rows_per_block;
+    const int rows = min(rows_per_block, E - e0);
     uint8_t* wsm = rsm;                                          // [ROWS][H * WBYTES]
-    uint8_t* xsm = wsm + (size_t)ROUTER_ROWS * H * WBYTES;       // [H * 2]
+    uint8_t* xsm = wsm + (size_t)rows_per_block * H * WBYTES;    // [H * 2]
     float* partial = reinterpret_cast<float*>(xsm + (size_t)H * 2);  // [ROWS][nchunks]
-    float* lsm = partial + ROUTER_ROWS * nchunks;                // [2 * E] (routing, last block only)
+    float* lsm = partial + rows_per_block * nchunks;             // [2 * E] (routing, last block only)
     __shared__ uint32_t ticket_s;
     const uint32_t wsm_u = (uint32_t)__cvta_generic_to_shared(wsm), xsm_u = (uint32_t)__cvta_generic_to_shared(xsm);
 
@@ -530,6 +530,134 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
                 partials[((size_t)blockIdx.z * n_tokens + t) * E + e] = v;
                 continue;
             }
+            if (p.logits_bf16) v = bf16_round(v);
+            if (p.bias) {
+                v = __fadd_rn(v, bf16_bits_to_f32(p.bias[e]));
+                if (p.logits_bf16) v = bf16_round(v);
+            }
+            logits_out[(size_t)t * E + e] = v;
+        }
+    }
+}
+
+// Batched router projection for long prefill chunks: a 128-token x 64-expert tile per block of 256 threads, 8 x 4
+// outputs per thread, the hidden axis walked one 64-wide chunk at a time.  The global loads of chunk c+1 are issued
+// before the arithmetic of chunk c and parked in registers, so their latency hides behind 64 k-steps of fused
+// multiply-adds.  The running totals live in shared memory (touched once per chunk), which leaves the registers to
+// the 32 chunk accumulators and the parked loads.  Accumulation order is the fixed one (inside a chunk: ascending k
+// from 0 with fused multiply-add; chunk sums added in ascending order), so the logits equal those of every other
+// router kernel bit for bit.  KIND: 1 fp32 weights, 2 bf16 weights.
+constexpr int RB_TOK = 128, RB_EXP = 64, RB_XLD = 132, RB_WLD = 68;
+constexpr int RB_SMEM = (64 * (RB_XLD + RB_WLD) + 32 * 256) * 4;
+
+template <int KIND>
+__global__ void __launch_bounds__(256, 2)
+router_logits_big_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens, float* __restrict__ logits_out) {
+    extern __shared__ __align__(16) float rbsm[];
+    float* xs = rbsm;                          // [64 k][RB_XLD]
+    float* ws = rbsm + 64 * RB_XLD;            // [64 k][RB_WLD]
+    float* tot = ws + 64 * RB_WLD + threadIdx.x;   // [32 outputs][256 threads]
+    auto swz = [](int k) { return ((k >> 3) & 7) << 2; };
+    const int H = p.hidden, E = p.n_experts;
+    const int t0 = blockIdx.x * RB_TOK, e0 = blockIdx.y * RB_EXP;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    constexpr int WV = KIND == 1 ? 4 : 2;      // 16-byte pieces of weights per thread and chunk
+
+    uint4 xr[4];
+    uint4 wr[WV];
+    auto load_chunk = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int id = threadIdx.x + 256 * i, row = id >> 3, c8 = (id & 7) * 8;
+            const int t = t0 + row;
+            xr[i] = t < n_tokens ? *reinterpret_cast<const uint4*>(x + (size_t)t * H + k0 + c8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < WV; ++i) {
+            const int id = threadIdx.x + 256 * i;
+            if (KIND == 1) {
+                const int row = id >> 4, c4 = (id & 15) * 4;
+                const int e = e0 + row;
+                wr[i] = e < E ? *reinterpret_cast<const uint4*>((const float*)p.weight + (size_t)e * H + k0 + c4) : make_uint4(0, 0, 0, 0);
+            } else {
+                const int row = id >> 3, c8 = (id & 7) * 8;
+                const int e = e0 + row;
+                wr[i] = e < E ? *reinterpret_cast<const uint4*>((const uint16_t*)p.weight + (size_t)e * H + k0 + c8) : make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    auto store_chunk = [&]() {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int id = threadIdx.x + 256 * i, row = id >> 3, c8 = (id & 7) * 8;
+            const uint32_t w4[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                xs[(c8 + 2 * j) * RB_XLD + (row ^ swz(c8))] = bf16lo(w4[j]);
+                xs[(c8 + 2 * j + 1) * RB_XLD + (row ^ swz(c8))] = bf16hi(w4[j]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < WV; ++i) {
+            const int id = threadIdx.x + 256 * i;
+            if (KIND == 1) {
+                const int row = id >> 4, c4 = (id & 15) * 4;
+                const int col = row ^ swz(c4);
+                ws[(c4 + 0) * RB_WLD + col] = __uint_as_float(wr[i].x); ws[(c4 + 1) * RB_WLD + col] = __uint_as_float(wr[i].y);
+                ws[(c4 + 2) * RB_WLD + col] = __uint_as_float(wr[i].z); ws[(c4 + 3) * RB_WLD + col] = __uint_as_float(wr[i].w);
+            } else {
+                const int row = id >> 3, c8 = (id & 7) * 8;
+                const uint32_t w4[4] = {wr[i].x, wr[i].y, wr[i].z, wr[i].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    ws[(c8 + 2 * j) * RB_WLD + (row ^ swz(c8))] = bf16lo(w4[j]);
+                    ws[(c8 + 2 * j + 1) * RB_WLD + (row ^ swz(c8))] = bf16hi(w4[j]);
+                }
+            }
+        }
+    };
+
+#pragma unroll
+    for (int i = 0; i < 32; ++i) tot[i * 256] = 0.0f;
+
+    const int n_chunks = H / 64;
+    load_chunk(0);
+    for (int c = 0; c < n_chunks; ++c) {
+        store_chunk();
+        __syncthreads();
+        if (c + 1 < n_chunks) load_chunk((c + 1) * 64);
+        float part[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) part[i][j] = 0.0f;
+#pragma unroll 8
+        for (int k = 0; k < 64; ++k) {
+            const float4 xa = *reinterpret_cast<const float4*>(xs + k * RB_XLD + ((ty * 8) ^ swz(k)));
+            const float4 xc = *reinterpret_cast<const float4*>(xs + k * RB_XLD + ((ty * 8 + 4) ^ swz(k)));
+            const float4 wv = *reinterpret_cast<const float4*>(ws + k * RB_WLD + ((tx * 4) ^ swz(k)));
+            const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xc.x, xc.y, xc.z, xc.w};
+            const float wa[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) part[i][j] = __fmaf_rn(xv[i], wa[j], part[i][j]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tot[(i * 4 + j) * 256] = __fadd_rn(tot[(i * 4 + j) * 256], part[i][j]);
+        __syncthreads();   // the tiles are read: the next chunk may overwrite them
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int t = t0 + ty * 8 + i;
+        if (t >= n_tokens) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = e0 + tx * 4 + j;
+            if (e >= E) continue;
+            float v = tot[(i * 4 + j) * 256];
             if (p.logits_bf16) v = bf16_round(v);
             if (p.bias) {
                 v = __fadd_rn(v, bf16_bits_to_f32(p.bias[e]));
