@@ -80,6 +80,9 @@ struct ffai_moe_layer {
     uint8_t* st_gate_up = nullptr;   // bulk-copy streams of the decode kernels: gate and up interleaved per 64-run, ...
     uint8_t* st_down = nullptr;      // ... and down (re-tiled copies of the packed experts, owned with the weights)
     int opt_decode = 0;              // decode kernels: 0 automatic, 1 per-lane cp.async rings, 2 bulk-copy streams
+    int opt_overlap = 1;             // shared expert on a second stream beside router / plan / exchange (0: one stream)
+    cudaStream_t aux_stream = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     int opt_pdl = 1;                 // decode chain: programmatic dependent launches (0: plain launches)
     int opt_decode_team = 0;         // bulk-copy streams: warps per 16-row block (0 automatic, 1, 4, 16)
     int opt_nt2_cost = 12;           // bulk-copy streams: schedule weight of an item with more than 8 rows (8 = as one with fewer)
@@ -972,6 +975,7 @@ extern "C" FFAI_API int ffai_moe_destroy(ffai_moe_layer* L) {
     if (L->ev_made)
         for (auto& a : L->ev) for (auto& b : a) for (auto& e : b) cudaEventDestroy(e);
     if (L->own_stream) cudaStreamDestroy(L->own_stream);
+    if (L->aux_stream) { cudaStreamDestroy(L->aux_stream); cudaEventDestroy(L->ev_fork); cudaEventDestroy(L->ev_join); }
     delete L;
     return FFAI_OK;
 }
@@ -1116,6 +1120,10 @@ extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name,
     if (!strcmp(name, "decode")) {
         if (value < 0 || value > 2) return fail(L, FFAI_ERR_INVALID_ARG, "option decode must be 0 (automatic), 1 (cp.async rings) or 2 (bulk-copy streams)");
         L->opt_decode = value;
+        return FFAI_OK;
+    }
+    if (!strcmp(name, "overlap")) {
+        L->opt_overlap = value != 0;
         return FFAI_OK;
     }
     if (!strcmp(name, "pdl")) {
@@ -1520,6 +1528,86 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         return L->ep_peer_on ? forward_experts_ep_peer(L, x, 0, st) : forward_experts_ep(L, x, 0, st);
     }
 
+    // The shared expert reads only the layer's input.  With a prefill-sized batch (or under expert parallelism) it runs
+    // on a second stream beside router, plan, gather and the row exchange, which leave most of the GPU idle; the
+    // combine waits for it.  With stage events on, everything stays on one stream so the stage times mean something.
+    const float* sh_y = nullptr;
+    const float* sh_gate = nullptr;
+    const bool tc_shared = L->tc_ok && L->sh_x && L->opt_path != 1 && L->opt_path != 3 && (L->opt_path == 2 || T >= 16);
+    auto run_shared = [&](cudaStream_t ss) -> int {
+    if (c.shared_intermediate > 0) {
+            const int Is = c.shared_intermediate;
+            if (tc_shared) {
+                using namespace g100;
+                single_group_schedule_kernel<<<1, 32, 0, ss>>>(T, tc_group_rows(L), L->sh_sched);
+                gather_rows_perm8_kernel<<<(T + 7) / 8, 256, 0, ss>>>(x, nullptr, 1, L->sh_x, T, H);
+                Params p{};
+                p.n_experts = 1; p.group_size = c.shared_group_size;
+                p.offsets = L->sh_sched; p.tile_offsets = L->sh_sched + 2; p.group_rows = tc_group_rows(L);
+                p.activation = FFAI_ACT_SWIGLU;
+                p.error_word = L->error_word;
+                p.scales = L->w.shared_gate_proj.scales; p.biases = L->w.shared_gate_proj.biases;
+                p.scales2 = L->w.shared_up_proj.scales; p.biases2 = L->w.shared_up_proj.biases;
+                p.n_out = Is; p.K = H; p.m_tiles = (Is + BN / 2 - 1) / (BN / 2);
+                p.out = L->sh_inner_bf; p.out_ld = Is; p.out_permute8 = 1;
+                const bool wbf = L->sh_wbf[0] != nullptr;
+                if (wbf ? launch_grouped_gemm<true, uint16_t, true>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x, p, L->n_sms, ss)
+                        : launch_grouped_gemm<true, uint16_t>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x, p, L->n_sms, ss))
+                    return fail(L, FFAI_ERR_CUDA, "shared gate/up grouped GEMM launch failed");
+                p.scales = L->w.shared_down_proj.scales; p.biases = L->w.shared_down_proj.biases;
+                p.scales2 = nullptr; p.biases2 = nullptr;
+                p.n_out = H; p.K = Is; p.m_tiles = (H + BN - 1) / BN;
+                p.out = L->sh_y; p.out_ld = H; p.out_permute8 = 0;
+                if (wbf ? launch_grouped_gemm<false, float, true>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner, p, L->n_sms, ss)
+                        : launch_grouped_gemm<false, float>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner, p, L->n_sms, ss))
+                    return fail(L, FFAI_ERR_CUDA, "shared down grouped GEMM launch failed");
+                L->launches += 4;
+            } else {
+                GemvParams p = L->no_gate ? gemv_params(L->w.shared_up_proj, nullptr, Is, H, c.shared_group_size, 1)
+                                          : gemv_params(L->w.shared_gate_proj, &L->w.shared_up_proj, Is, H, c.shared_group_size, 1);
+                p.n_rows = T;
+                p.activation = FFAI_ACT_SWIGLU;
+                p.post_relu2 = L->no_gate;   // beside gate-less experts the shared expert has their form (NemotronHText.swift:885-891)
+                if ((rc = L->no_gate ? launch_grouped_gemv<uint16_t, float, false>(p, c.shared_bits, x, L->sh_inner, 1, ss)
+                                     : launch_grouped_gemv<uint16_t, float, true>(p, c.shared_bits, x, L->sh_inner, 1, ss)))
+                    return fail(L, rc, "shared gate/up launch failed");
+                GemvParams d = gemv_params(L->w.shared_down_proj, nullptr, H, Is, c.shared_group_size, 1);
+                d.n_rows = T;
+                if ((rc = launch_grouped_gemv<float, float, false>(d, c.shared_bits, L->sh_inner, L->sh_y, 1, ss)))
+                    return fail(L, rc, "shared down launch failed");
+                L->launches += 2;
+            }
+            sh_y = L->sh_y;
+            if (c.shared_gate_kind == FFAI_LINEAR_AFFINE) {
+                if ((rc = launch_affine_rowdot(L->w.shared_gate, c.shared_gate_bits, c.shared_gate_group_size, x, L->sh_gate, T, H, ss)))
+                    return fail(L, rc, "shared gate launch failed");
+                L->launches += 1;
+                sh_gate = L->sh_gate;
+            } else if (c.shared_gate_kind == FFAI_LINEAR_F32) {
+                dense_rowdot_kernel<float><<<(T + 3) / 4, 128, 0, ss>>>((const float*)L->w.shared_gate.weight, x, L->sh_gate, T, H);
+                L->launches += 1;
+                sh_gate = L->sh_gate;
+            } else if (c.shared_gate_kind == FFAI_LINEAR_BF16) {
+                dense_rowdot_kernel<uint16_t><<<(T + 3) / 4, 128, 0, ss>>>((const uint16_t*)L->w.shared_gate.weight, x, L->sh_gate, T, H);
+                L->launches += 1;
+                sh_gate = L->sh_gate;
+            }
+        }
+        return FFAI_OK;
+    };
+    const bool shared_beside = c.shared_intermediate > 0 && L->opt_overlap && !L->timing && (T >= 96 || c.ep_world > 1);
+    if (shared_beside) {
+        if (!L->aux_stream) {
+            CUDA_TRY(L, cudaStreamCreateWithFlags(&L->aux_stream, cudaStreamNonBlocking));
+            CUDA_TRY(L, cudaEventCreateWithFlags(&L->ev_fork, cudaEventDisableTiming));
+            CUDA_TRY(L, cudaEventCreateWithFlags(&L->ev_join, cudaEventDisableTiming));
+        }
+        CUDA_TRY(L, cudaEventRecord(L->ev_fork, st));
+        CUDA_TRY(L, cudaStreamWaitEvent(L->aux_stream, L->ev_fork, 0));
+        if ((rc = run_shared(L->aux_stream))) return rc;
+        CUDA_TRY(L, cudaEventRecord(L->ev_join, L->aux_stream));
+    }
+
     // stage 0: router (projection + bias + top-k + softmax)
     stage_begin(L, ST_ROUTER, st);
     RouterParams rp = router_params(L);
@@ -1578,7 +1666,6 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         if (!mma_experts && can_tc) tc_experts = M >= (L->opt_tc_min_rows > 0 ? L->opt_tc_min_rows : 64);
         if (!mma_experts && !tc_experts && L->mma_ok && rows_per_expert <= 48.0) mma_experts = true;
     }
-    const bool tc_shared = L->tc_ok && L->sh_x && L->opt_path != 1 && L->opt_path != 3 && (L->opt_path == 2 || T >= 16);
 
     if (mma_experts) {
         using namespace dmma;
@@ -1735,67 +1822,12 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         stage_end(L, ST_DOWN, st);
     }
 
-    // shared expert
-    const float* sh_y = nullptr;
-    const float* sh_gate = nullptr;
+    // shared expert (when it did not run beside the rest)
     stage_begin(L, ST_SHARED, st);
-    if (c.shared_intermediate > 0) {
-        const int Is = c.shared_intermediate;
-        if (tc_shared) {
-            using namespace g100;
-            single_group_schedule_kernel<<<1, 32, 0, st>>>(T, tc_group_rows(L), L->sh_sched);
-            gather_rows_perm8_kernel<<<(T + 7) / 8, 256, 0, st>>>(x, nullptr, 1, L->sh_x, T, H);
-            Params p{};
-            p.n_experts = 1; p.group_size = c.shared_group_size;
-            p.offsets = L->sh_sched; p.tile_offsets = L->sh_sched + 2; p.group_rows = tc_group_rows(L);
-            p.activation = FFAI_ACT_SWIGLU;
-            p.error_word = L->error_word;
-            p.scales = L->w.shared_gate_proj.scales; p.biases = L->w.shared_gate_proj.biases;
-            p.scales2 = L->w.shared_up_proj.scales; p.biases2 = L->w.shared_up_proj.biases;
-            p.n_out = Is; p.K = H; p.m_tiles = (Is + BN / 2 - 1) / (BN / 2);
-            p.out = L->sh_inner_bf; p.out_ld = Is; p.out_permute8 = 1;
-            const bool wbf = L->sh_wbf[0] != nullptr;
-            if (wbf ? launch_grouped_gemm<true, uint16_t, true>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x, p, L->n_sms, st)
-                    : launch_grouped_gemm<true, uint16_t>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x, p, L->n_sms, st))
-                return fail(L, FFAI_ERR_CUDA, "shared gate/up grouped GEMM launch failed");
-            p.scales = L->w.shared_down_proj.scales; p.biases = L->w.shared_down_proj.biases;
-            p.scales2 = nullptr; p.biases2 = nullptr;
-            p.n_out = H; p.K = Is; p.m_tiles = (H + BN - 1) / BN;
-            p.out = L->sh_y; p.out_ld = H; p.out_permute8 = 0;
-            if (wbf ? launch_grouped_gemm<false, float, true>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner, p, L->n_sms, st)
-                    : launch_grouped_gemm<false, float>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner, p, L->n_sms, st))
-                return fail(L, FFAI_ERR_CUDA, "shared down grouped GEMM launch failed");
-            L->launches += 4;
-        } else {
-            GemvParams p = L->no_gate ? gemv_params(L->w.shared_up_proj, nullptr, Is, H, c.shared_group_size, 1)
-                                      : gemv_params(L->w.shared_gate_proj, &L->w.shared_up_proj, Is, H, c.shared_group_size, 1);
-            p.n_rows = T;
-            p.activation = FFAI_ACT_SWIGLU;
-            p.post_relu2 = L->no_gate;   // beside gate-less experts the shared expert has their form (NemotronHText.swift:885-891)
-            if ((rc = L->no_gate ? launch_grouped_gemv<uint16_t, float, false>(p, c.shared_bits, x, L->sh_inner, 1, st)
-                                 : launch_grouped_gemv<uint16_t, float, true>(p, c.shared_bits, x, L->sh_inner, 1, st)))
-                return fail(L, rc, "shared gate/up launch failed");
-            GemvParams d = gemv_params(L->w.shared_down_proj, nullptr, H, Is, c.shared_group_size, 1);
-            d.n_rows = T;
-            if ((rc = launch_grouped_gemv<float, float, false>(d, c.shared_bits, L->sh_inner, L->sh_y, 1, st)))
-                return fail(L, rc, "shared down launch failed");
-            L->launches += 2;
-        }
-        sh_y = L->sh_y;
-        if (c.shared_gate_kind == FFAI_LINEAR_AFFINE) {
-            if ((rc = launch_affine_rowdot(L->w.shared_gate, c.shared_gate_bits, c.shared_gate_group_size, x, L->sh_gate, T, H, st)))
-                return fail(L, rc, "shared gate launch failed");
-            L->launches += 1;
-            sh_gate = L->sh_gate;
-        } else if (c.shared_gate_kind == FFAI_LINEAR_F32) {
-            dense_rowdot_kernel<float><<<(T + 3) / 4, 128, 0, st>>>((const float*)L->w.shared_gate.weight, x, L->sh_gate, T, H);
-            L->launches += 1;
-            sh_gate = L->sh_gate;
-        } else if (c.shared_gate_kind == FFAI_LINEAR_BF16) {
-            dense_rowdot_kernel<uint16_t><<<(T + 3) / 4, 128, 0, st>>>((const uint16_t*)L->w.shared_gate.weight, x, L->sh_gate, T, H);
-            L->launches += 1;
-            sh_gate = L->sh_gate;
-        }
+    if (shared_beside) {
+        CUDA_TRY(L, cudaStreamWaitEvent(st, L->ev_join, 0));
+    } else if ((rc = run_shared(st))) {
+        return rc;
     }
     stage_end(L, ST_SHARED, st);
     stage_begin(L, ST_COMBINE, st);

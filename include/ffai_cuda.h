@@ -302,6 +302,7 @@ FFAI_API uint32_t ffai_ep_plan_exchange(const uint32_t* recv_counts, int32_t wor
  *   "decode"       decode kernels: 0 automatic, 1 cp.async rings, 2 bulk-copy streams
  *   "decode_team"  bulk-copy streams: warps that share one 16-row block (0 automatic, 1, 4, 16)
  *   "nt2_cost"     bulk-copy streams: schedule weight of a block with more than 8 rows, 8 = as one with fewer (8..32)
+ *   "overlap"      shared expert on a second stream beside router, plan and row exchange (default 1; 0: one stream)
  *   "pdl"          decode chain launched as programmatic dependent launches (default 1; 0: plain launches)
  *   "ep_wait_ms"   limit of a barrier wait of the peer-memory exchange, milliseconds (default 2000)
  *   "timeline"     1: the gate/up tcgen05 kernel records its device timeline (builds with FFAI_G100_TIMELINE only) */
