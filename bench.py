@@ -535,6 +535,7 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # before any communicator exists: plain peer transports only
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     head = measure(name, args, rank, local_rank, world, dist, args.steps, with_clocks=True)

@@ -47,7 +47,7 @@ struct ffai_moe_layer {
     uint32_t* perm = nullptr;       // [M]
     uint32_t* inv_perm = nullptr;   // [M]
     uint32_t* block_hist = nullptr; // [nblocks,E]
-    float* router_partials = nullptr;  // [H/64][T][E] chunk sums of the split batched router (when it fits 64 MiB)
+    float* router_partials = nullptr;  // [H/64][T][E] chunk sums of the split batched router (when it fits 256 MiB)
     size_t router_partials_cap = 0;    // in floats
     uint32_t* tickets = nullptr;    // [min(T,96)] per-token arrival counters of the small-batch router (self-resetting)
     float* inner = nullptr;         // [M,I]
@@ -332,24 +332,41 @@ void launch_router_tiled(const RouterParams& p, const uint16_t* x, int T, float*
 int launch_router_batched(const RouterParams& p, const uint16_t* x, int T, uint32_t* idx, float* w,
                           float* logits, float* partials, size_t partials_capacity, int n_sms, cudaStream_t st) {
     const int n_chunks = p.hidden / 64;
-    // long chunks: 128-token tiles with the next chunk's loads in flight behind the arithmetic (dense weights; a
-    // quantized router arrives here expanded to fp32).  Needs at least one tile per SM to pay.
-    if ((p.kind == FFAI_LINEAR_F32 || p.kind == FFAI_LINEAR_BF16) && p.hidden % 64 == 0 &&
-        ((T + RB_TOK - 1) / RB_TOK) * ((p.n_experts + RB_EXP - 1) / RB_EXP) >= n_sms) {
-        const dim3 grid((T + RB_TOK - 1) / RB_TOK, (p.n_experts + RB_EXP - 1) / RB_EXP);
-        static SmemOptIn opt1, opt2;
-        bool ok;
-        if (p.kind == FFAI_LINEAR_F32) {
-            ok = opt1.ensure(router_logits_big_kernel<1>, RB_SMEM);
-            if (ok) router_logits_big_kernel<1><<<grid, 256, RB_SMEM, st>>>(p, x, T, logits);
-        } else {
-            ok = opt2.ensure(router_logits_big_kernel<2>, RB_SMEM);
-            if (ok) router_logits_big_kernel<2><<<grid, 256, RB_SMEM, st>>>(p, x, T, logits);
+    // 128-token x 64-expert tiles with the next chunk's loads in flight behind the arithmetic (dense weights; a
+    // quantized router arrives here expanded to fp32).  Long chunks give every SM a tile; mid-sized ones split the
+    // hidden axis into ranges of chunks as well and leave the ordered sum of the chunks to the routing kernel.
+    if ((p.kind == FFAI_LINEAR_F32 || p.kind == FFAI_LINEAR_BF16) && p.hidden % 64 == 0 && T >= 256) {
+        const int tiles = ((T + RB_TOK - 1) / RB_TOK) * ((p.n_experts + RB_EXP - 1) / RB_EXP);
+        int z = 1, per = n_chunks;
+        float* part = nullptr;
+        if (tiles < n_sms) {
+            if (partials && (size_t)T * p.n_experts * n_chunks <= partials_capacity) {
+                z = std::min(n_chunks, (2 * n_sms + tiles - 1) / tiles);
+                per = (n_chunks + z - 1) / z;
+                z = (n_chunks + per - 1) / per;
+                part = partials;
+            } else {
+                z = 0;   // no room for the chunk sums: the smaller tiles below
+            }
         }
-        if (ok) {
-            const int warps = 4;
-            route_only_kernel<<<(T + warps - 1) / warps, warps * 32, (size_t)warps * 2 * p.n_experts * sizeof(float), st>>>(p, logits, T, idx, w);
-            return cudaGetLastError() == cudaSuccess ? 2 : -1;
+        if (z > 0) {
+            const dim3 grid((T + RB_TOK - 1) / RB_TOK, (p.n_experts + RB_EXP - 1) / RB_EXP, z);
+            static SmemOptIn opt1, opt2;
+            bool ok;
+            if (p.kind == FFAI_LINEAR_F32) {
+                ok = opt1.ensure(router_logits_big_kernel<1>, RB_SMEM);
+                if (ok) router_logits_big_kernel<1><<<grid, 256, RB_SMEM, st>>>(p, x, T, logits, part, per);
+            } else {
+                ok = opt2.ensure(router_logits_big_kernel<2>, RB_SMEM);
+                if (ok) router_logits_big_kernel<2><<<grid, 256, RB_SMEM, st>>>(p, x, T, logits, part, per);
+            }
+            if (ok) {
+                const int warps = 4;
+                const size_t smem = (size_t)warps * 2 * p.n_experts * sizeof(float);
+                if (part) route_from_partials_kernel<<<(T + warps - 1) / warps, warps * 32, smem, st>>>(p, part, n_chunks, T, idx, w, logits);
+                else route_only_kernel<<<(T + warps - 1) / warps, warps * 32, smem, st>>>(p, logits, T, idx, w);
+                return cudaGetLastError() == cudaSuccess ? 2 : -1;
+            }
         }
     }
     const bool few_blocks = ((T + 63) / 64) * ((p.n_experts + 63) / 64) < 4 * n_sms;
@@ -719,7 +736,7 @@ extern "C" FFAI_API int ffai_moe_create(const ffai_moe_config* config, ffai_moe_
     if ((rc = ws_alloc(L, &L->perm, M))) return rc;
     if ((rc = ws_alloc(L, &L->inv_perm, M))) return rc;
     if ((rc = ws_alloc(L, &L->block_hist, (size_t)plan_num_blocks((int)M) * E))) return rc;
-    if (T >= 96 && T * E * (H / 64) * sizeof(float) <= (size_t)64 << 20) {
+    if (T >= 96 && T * E * (H / 64) * sizeof(float) <= (size_t)256 << 20) {
         L->router_partials_cap = T * E * (H / 64);
         if ((rc = ws_alloc(L, &L->router_partials, L->router_partials_cap))) return rc;
     }

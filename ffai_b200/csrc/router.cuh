@@ -550,9 +550,13 @@ router_logits_tiled_kernel(RouterParams p, const uint16_t* __restrict__ x, int n
 constexpr int RB_TOK = 128, RB_EXP = 64, RB_XLD = 132, RB_WLD = 68;
 constexpr int RB_SMEM = (64 * (RB_XLD + RB_WLD) + 32 * 256) * 4;
 
+// With `partials` the hidden axis is also split over blockIdx.z into ranges of `chunks_per_z` chunks: a block then
+// writes the sum of every chunk of its range to partials[chunk][token][expert] instead of keeping totals, and
+// route_from_partials_kernel adds the chunks in ascending order (same bits, enough blocks for mid-sized batches).
 template <int KIND>
 __global__ void __launch_bounds__(256, 2)
-router_logits_big_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens, float* __restrict__ logits_out) {
+router_logits_big_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_tokens, float* __restrict__ logits_out,
+                         float* __restrict__ partials, int chunks_per_z) {
     extern __shared__ __align__(16) float rbsm[];
     float* xs = rbsm;                          // [64 k][RB_XLD]
     float* ws = rbsm + 64 * RB_XLD;            // [64 k][RB_WLD]
@@ -620,9 +624,12 @@ router_logits_big_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_t
 #pragma unroll
     for (int i = 0; i < 32; ++i) tot[i * 256] = 0.0f;
 
-    const int n_chunks = H / 64;
-    load_chunk(0);
-    for (int c = 0; c < n_chunks; ++c) {
+    const int all_chunks = H / 64;
+    const int c_begin = partials ? (int)blockIdx.z * chunks_per_z : 0;
+    const int n_chunks = partials ? min(all_chunks, c_begin + chunks_per_z) : all_chunks;   // end of this block's range
+    if (c_begin >= n_chunks) return;
+    load_chunk(c_begin * 64);
+    for (int c = c_begin; c < n_chunks; ++c) {
         store_chunk();
         __syncthreads();
         if (c + 1 < n_chunks) load_chunk((c + 1) * 64);
@@ -643,12 +650,29 @@ router_logits_big_kernel(RouterParams p, const uint16_t* __restrict__ x, int n_t
 #pragma unroll
                 for (int j = 0; j < 4; ++j) part[i][j] = __fmaf_rn(xv[i], wa[j], part[i][j]);
         }
+        if (partials) {
+            float* dst = partials + (size_t)c * n_tokens * E;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < 8; ++i) {
+                const int t = t0 + ty * 8 + i, e = e0 + tx * 4;
+                if (t >= n_tokens) continue;
+                if (e + 3 < E && (E & 3) == 0) {
+                    *reinterpret_cast<float4*>(dst + (size_t)t * E + e) = make_float4(part[i][0], part[i][1], part[i][2], part[i][3]);
+                } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) tot[(i * 4 + j) * 256] = __fadd_rn(tot[(i * 4 + j) * 256], part[i][j]);
+                    for (int j = 0; j < 4; ++j)
+                        if (e + j < E) dst[(size_t)t * E + e + j] = part[i][j];
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) tot[(i * 4 + j) * 256] = __fadd_rn(tot[(i * 4 + j) * 256], part[i][j]);
+        }
         __syncthreads();   // the tiles are read: the next chunk may overwrite them
     }
+    if (partials) return;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int t = t0 + ty * 8 + i;
