@@ -18,6 +18,9 @@
 //                128-byte swizzle, ring "W".  bf16 weights (WBF16: expanded once at load time): two boxes of
 //                [128 rows x 64 k] per 64 k straight into the operand ring "B".
 //   warp 2       TMA producer of activations: [128 rows x 128 B] per 64 k, 128-byte swizzle, ring "X"
+//   warp 3       scheduler: finds the expert, row range and weight tile of each of the CTA's work items (a 32-way
+//                search over the tile prefix sums) and hands them to every other role through a small ring in
+//                shared memory, so no role waits on a chain of global loads at an item boundary
 //   warp 1       MMA issuer (one thread): 4 x tcgen05.mma (M128 N256 K16) per 64 k; owns TMEM
 //                (two accumulators of 256 columns, so the epilogue of a tile overlaps the next tile)
 //   warps 4-19   dequant (packed weights only): 512 threads, thread = (weight row, half of a 64-k block);
@@ -50,7 +53,9 @@ constexpr int SPF = 4;         // 64-k blocks of scale words a dequant thread fe
 constexpr int THREADS = 768;   // 24 warps
 constexpr int W_WARP = 0;      // packed-weight TMA producer
 constexpr int MMA_WARP = 1;    // MMA issuer, owns TMEM
-constexpr int X_WARP = 2;      // activation TMA producer (warp 3 idles: keeps the epilogue warps quadrant-aligned)
+constexpr int X_WARP = 2;      // activation TMA producer
+constexpr int SCHED_WARP = 3;  // work-item scheduler: resolves (expert, rows, weight tile) ahead of the other roles
+constexpr int NSCHED = 8;      // work items the scheduler may run ahead
 constexpr int DEQ_WARP0 = 4;   // first of the dequant warps
 constexpr int N_DEQ_WARPS = 16;
 constexpr int EPI_WARP0 = 20;  // four epilogue warps, warp % 4 = TMEM lane quadrant
@@ -272,29 +277,51 @@ FFAI_DEVINL int permute8_store_col(int n) {
     return (n & ~7) | (((k & 3) << 1) | (k >> 2));
 }
 
-// Work item index -> (expert, group of up to 256 routed rows, weight-row tile).  An item holds one or
-// two 128-row token tiles that are multiplied against the same dequantised weight tile (each weight
-// tile is produced once per item, not once per token tile).  Consecutive items share the rows so
-// the activation tiles stay hot in L2 across the CTAs that work on one expert.
-// n_cols_valid counts the item's rows (1..256); tiles = 1 + (n_cols_valid > 128).
+// A work item is (expert, group of up to 256 routed rows, weight-row tile).  An item holds one or two 128-row
+// token tiles that are multiplied against the same dequantised weight tile (each weight tile is produced once
+// per item, not once per token tile).  Consecutive items share the rows so the activation tiles stay hot in
+// L2 across the CTAs that work on one expert.  n_cols_valid counts the item's rows (1..256);
+// tiles = 1 + (n_cols_valid > 128).
 struct TileCoord {
     int expert, row_begin, n_cols_valid, m_tile;
 };
-FFAI_DEVINL TileCoord decode_tile(const Params& p, int tile, int ntok) {
-    const int g = tile / p.m_tiles;
-    int lo = 0, hi = p.n_experts;  // find e with tile_offsets[e] <= g < tile_offsets[e+1]
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if ((int)p.tile_offsets[mid] <= g) lo = mid; else hi = mid;
+
+// The scheduler warp's search: the last e in [0, n_experts) with tile_offsets[e] <= g, 32 candidates per round.
+FFAI_DEVINL int find_group_warp(const uint32_t* __restrict__ tile_offsets, int n_experts, int g, int lane) {
+    int lo = 0, n = n_experts;
+    while (n > 1) {
+        const int step = (n + 31) >> 5;
+        const int idx = lo + lane * step;
+        const bool le = idx < lo + n && (int)__ldg(tile_offsets + idx) <= g;
+        const int c = __popc(__ballot_sync(0xFFFFFFFFu, le));   // monotone: lanes 0..c-1 hold values <= g (c >= 1)
+        const int nlo = lo + (c - 1) * step;
+        n = min(step, lo + n - nlo);
+        lo = nlo;
     }
-    TileCoord c;
-    c.expert = lo;
-    const int nt = g - (int)p.tile_offsets[lo];
-    c.row_begin = (int)p.offsets[lo] + nt * ntok;
-    c.n_cols_valid = min(ntok, (int)p.offsets[lo + 1] - c.row_begin);
-    c.m_tile = tile - g * p.m_tiles;
-    return c;
+    return lo;
 }
+
+// A role's view of the scheduler ring: wait for the next item's coordinates, copy them, release the slot.
+struct ItemFeed {
+    uint32_t full0, empty0, coords0;   // shared-window addresses
+    uint32_t i;
+    // whole_warp: every lane of the warp calls (and reads); lane 0 releases the slot once all have read
+    FFAI_DEVINL bool take(TileCoord& c, volatile uint32_t* abort_flag, bool whole_warp) {
+        const uint32_t slot = i % NSCHED, phase = (i / NSCHED) & 1u;
+        ++i;
+        if (!mbar_wait<32>(full0 + 8u * slot, phase, abort_flag)) return false;
+        uint32_t a, b, d, e;
+        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(d), "=r"(e) : "r"(coords0 + 16u * slot));
+        c.expert = (int)a; c.row_begin = (int)b; c.n_cols_valid = (int)d; c.m_tile = (int)e;
+        if (whole_warp) {
+            __syncwarp();
+            if ((threadIdx.x & 31) == 0) mbar_arrive(empty0 + 8u * slot);
+        } else {
+            mbar_arrive(empty0 + 8u * slot);
+        }
+        return true;
+    }
+};
 
 // Ring depths.  Both TMA-fed rings must hold enough 64-k stages to cover the latency of a bulk copy
 // (a few thousand cycles) at one stage per ~540 cycles of tensor-pipe time, or the MMA issuer idles.
@@ -319,8 +346,10 @@ struct SmemLayout {
     static constexpr int OFF_W = OFF_B + NB * B_STAGE;
     static constexpr int OFF_X = OFF_W + NW * W_STAGE;
     static constexpr int OFF_BAR = OFF_X + NX * X_TILE;
-    static constexpr int N_BARS = 2 * NW + 2 * NX + 2 * NB + 4;
-    static constexpr int TOTAL = OFF_BAR + N_BARS * 8 + 16 + 1024;  // + alignment slack
+    static constexpr int N_BARS = 2 * NW + 2 * NX + 2 * NB + 4 + 2 * NSCHED;
+    static constexpr int OFF_SCHED = OFF_BAR + N_BARS * 8 + 16;     // NSCHED x 16 bytes of item coordinates
+    static constexpr int N_ITEM_READERS = 3 + (WBF16 ? 0 : N_DEQ_WARPS) + 4;   // warps that take every work item
+    static constexpr int TOTAL = OFF_SCHED + NSCHED * 16 + 1024;    // + alignment slack
     static constexpr int TMEM_COLS = 2 * BN;               // two accumulators of 256 fp32 columns
     static_assert(TOTAL <= 227 * 1024, "shared memory limit");
 };
@@ -352,6 +381,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     auto b_empty = [&](int s) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + NB + s); };
     auto acc_full = [&](int b) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + 2 * NB + b); };
     auto acc_empty = [&](int b) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + 2 * NB + 2 + b); };
+    auto s_full = [&](int s) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + 2 * NB + 4 + s); };
+    auto s_empty = [&](int s) { return bar0 + 8u * (2 * L::NW + 2 * L::NX + 2 * NB + 4 + NSCHED + s); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_BAR + L::N_BARS * 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -366,6 +397,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (int s = 0; s < L::NX; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 1); }
         for (int s = 0; s < NB; ++s) { mbar_init(b_full(s), WBF16 ? 1 : N_DEQ_WARPS); mbar_init(b_empty(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+        for (int s = 0; s < NSCHED; ++s) { mbar_init(s_full(s), 1); mbar_init(s_empty(s), L::N_ITEM_READERS); }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tm_w);
@@ -380,6 +412,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    ItemFeed feed{s_full(0), s_empty(0), sbase + (uint32_t)L::OFF_SCHED, 0u};
 
     if (warp == W_WARP && WBF16) {
         // ───────────── TMA producer, bf16 weights: two 128-row x 128-byte boxes per 64 k, into the operand ring ─────────────
@@ -388,7 +421,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             uint32_t issued = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileCoord c = decode_tile(p, tile, p.group_rows);
+                TileCoord c;
+                if (!feed.take(c, abort_flag, false)) { ok = false; break; }
                 const int wrow = c.expert * p.n_out + c.m_tile * ROWS_PER_TILE;
                 for (int kb = 0; kb < KB; ++kb) {
                     if (!mbar_wait<64>(b_empty(bp.stage), bp.phase ^ 1, abort_flag)) { ok = false; break; }
@@ -416,7 +450,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             uint32_t issued = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileCoord c = decode_tile(p, tile, p.group_rows);
+                TileCoord c;
+                if (!feed.take(c, abort_flag, false)) { ok = false; break; }
                 const int wrow = c.expert * p.n_out + c.m_tile * ROWS_PER_TILE;
                 for (int sb = 0; sb < SB; ++sb) {
                     tl_mark(p, TL_WPROD, (int)issued, 0);
@@ -448,7 +483,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             uint32_t issued = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileCoord c = decode_tile(p, tile, p.group_rows);
+                TileCoord c;
+                if (!feed.take(c, abort_flag, false)) { ok = false; break; }
                 const int nt = c.n_cols_valid > BM ? 2 : 1;
                 for (int kb = 0; kb < KB && ok; ++kb) {
                     for (int t = 0; t < nt; ++t) {
@@ -477,7 +513,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             bool ok = true;
             const uint32_t idesc = make_idesc_bf16(BM, BN);
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileCoord c = decode_tile(p, tile, p.group_rows);
+                TileCoord c;
+                if (!feed.take(c, abort_flag, false)) { ok = false; break; }
                 const int nt = c.n_cols_valid > BM ? 2 : 1;
                 // token tile t of the item accumulates in TMEM buffer (tcount + t) & 1
                 uint32_t d0[2];
@@ -489,6 +526,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                 if (!ok) break;
                 tc_fence_after();
                 for (int kb = 0; kb < KB && ok; ++kb, ++gk) {
+                    tl_mark(p, TL_MMA, gk, 2);
                     if (!mbar_wait<0>(b_full(bp.stage), bp.phase, abort_flag)) { ok = false; break; }
                     const uint64_t bd0 = make_kmajor_sw128_desc(sbase + L::OFF_B + bp.stage * L::B_STAGE);
                     for (int t = 0; t < nt; ++t) {
@@ -549,7 +587,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         int gk = 0;
         const bool tl_on = (warp == DEQ_WARP0 && lane == 0);
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const TileCoord c = decode_tile(p, tile, p.group_rows);
+            TileCoord c;
+            if (!feed.take(c, abort_flag, true)) break;
             int prow = c.m_tile * ROWS_PER_TILE + r_in_proj;        // row within the expert's projection
             if (prow >= p.n_out) prow = p.n_out - 1;                // rows past the projection: zero-filled by TMA, masked at store
             const long grow = (long)c.expert * p.n_out + prow;
@@ -630,9 +669,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
         uint32_t tcount = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+          TileCoord item;
+          if (!feed.take(item, abort_flag, true)) break;
           for (int tt = 0; tt < 2 && ok; ++tt) {
-            TileCoord c = decode_tile(p, tile, p.group_rows);
+            TileCoord c = item;
             if (tt == 1 && c.n_cols_valid <= BM) break;
             c.row_begin += tt * BM;                               // this token tile's rows
             c.n_cols_valid = min(BM, c.n_cols_valid - tt * BM);
@@ -720,6 +761,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             if (warp == EPI_WARP0 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 2);
             ++tcount;
           }
+        }
+    } else if (warp == SCHED_WARP) {
+        // ───────────── scheduler: coordinates of the CTA's work items, up to NSCHED items ahead ─────────────
+        bool ok = true;
+        uint32_t i = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++i) {
+            const uint32_t slot = i % NSCHED, phase = (i / NSCHED) & 1u;
+            if (!mbar_wait<64>(s_empty(slot), phase ^ 1u, abort_flag)) { ok = false; break; }
+            const int g = tile / p.m_tiles;
+            const int e = find_group_warp(p.tile_offsets, p.n_experts, g, lane);
+            if (lane == 0) {
+                const int nt = g - (int)__ldg(p.tile_offsets + e);
+                const int row_begin = (int)__ldg(p.offsets + e) + nt * p.group_rows;
+                const int n_valid = min(p.group_rows, (int)__ldg(p.offsets + e + 1) - row_begin);
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
+                             ::"r"(sbase + (uint32_t)L::OFF_SCHED + 16u * slot), "r"(e), "r"(row_begin), "r"(n_valid),
+                               "r"(tile - g * p.m_tiles) : "memory");
+                mbar_arrive(s_full(slot));   // release: the readers' wait acquires the coordinates
+            }
+            __syncwarp();
+        }
     }
 
     tc_fence_before();
