@@ -94,7 +94,6 @@ struct ffai_moe_layer {
     uint16_t* exp_wbf[3] = {nullptr, nullptr, nullptr}; // routed experts expanded to bf16 (prefill weight cache): gate, up, down
     bool cache_planned = false;
     CUtensorMap tm_gate_bf{}, tm_up_bf{}, tm_down_bf{};
-    int opt_tc_pair = 0;             // tensor-core path: 1 = two token tiles per pass over a weight tile (epilogues not overlapped)
     int opt_tc_weights = 0;          // tensor-core path reads: 0 the bf16 cache when there is one, 1 always the packed weights
     uint16_t* sh_wbf[3] = {nullptr, nullptr, nullptr};  // shared expert expanded to bf16 (bit widths other than 4): gate, up, down
     uint16_t* sh_inner_bf = nullptr; // [T,Is]
@@ -1115,10 +1114,6 @@ extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name,
         L->opt_tc_min_rows = value;
         return FFAI_OK;
     }
-    if (!strcmp(name, "tc_pair")) {
-        L->opt_tc_pair = value != 0;
-        return FFAI_OK;
-    }
     if (!strcmp(name, "tc_weights")) {
         if (value < 0 || value > 1) return fail(L, FFAI_ERR_INVALID_ARG, "tc_weights must be 0 (cache when present) or 1 (packed)");
         L->opt_tc_weights = value;
@@ -1302,7 +1297,7 @@ int ep_all_to_all(ffai_moe_layer* L, const uint8_t* send, const size_t* off_s, c
 
 // The two grouped GEMMs of the tensor-core path, from the bf16 weight cache when the layer keeps one,
 // else from the packed 4-bit weights with the in-kernel dequant stage.
-int tc_group_rows(const ffai_moe_layer* L) { return L->opt_tc_pair ? g100::PAIR : g100::BM; }
+int tc_group_rows(const ffai_moe_layer*) { return g100::BM; }
 bool tc_reads_cache(const ffai_moe_layer* L) { return L->exp_wbf[0] && (L->opt_tc_weights == 0 || L->cfg.expert_bits != 4); }
 bool tc_possible(const ffai_moe_layer* L) { return L->tc_ok && (L->cfg.expert_bits == 4 || L->exp_wbf[0]); }
 int tc_gate_up(ffai_moe_layer* L, const g100::Params& p, cudaStream_t st) {
@@ -1375,7 +1370,7 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         tile_schedule_kernel<<<1, 32, 0, st>>>(offsets_dev, n_exp, tc_group_rows(L), L->tile_offsets);
         Params p{};
         p.n_experts = n_exp; p.group_size = c.expert_group_size;
-        p.offsets = offsets_dev; p.tile_offsets = L->tile_offsets; p.group_rows = tc_group_rows(L);
+        p.offsets = offsets_dev; p.tile_offsets = L->tile_offsets;
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
         p.error_word = L->error_word;
         stage_begin(L, ST_GATE_UP, st);
@@ -1560,7 +1555,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
                 gather_rows_perm8_kernel<<<(T + 7) / 8, 256, 0, ss>>>(x, nullptr, 1, L->sh_x, T, H);
                 Params p{};
                 p.n_experts = 1; p.group_size = c.shared_group_size;
-                p.offsets = L->sh_sched; p.tile_offsets = L->sh_sched + 2; p.group_rows = tc_group_rows(L);
+                p.offsets = L->sh_sched; p.tile_offsets = L->sh_sched + 2;
                 p.activation = FFAI_ACT_SWIGLU;
                 p.error_word = L->error_word;
                 p.scales = L->w.shared_gate_proj.scales; p.biases = L->w.shared_gate_proj.biases;
@@ -1780,7 +1775,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
 
         Params p{};
         p.n_experts = E; p.group_size = c.expert_group_size;
-        p.offsets = L->offsets; p.tile_offsets = L->tile_offsets; p.group_rows = tc_group_rows(L);
+        p.offsets = L->offsets; p.tile_offsets = L->tile_offsets;
         p.activation = c.activation; p.limit = c.swiglu_limit; p.alpha = c.swiglu_alpha;
         p.error_word = L->error_word;
         p.timeline = L->timeline;

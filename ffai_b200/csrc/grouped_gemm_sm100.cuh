@@ -23,9 +23,9 @@
 //                shared memory, so no role waits on a chain of global loads at an item boundary
 //   warp 1       MMA issuer (one thread): 4 x tcgen05.mma (M128 N256 K16) per 64 k; owns TMEM
 //                (two accumulators of 256 columns, so the epilogue of a tile overlaps the next tile)
-//   warps 4-19   dequant (packed weights only): 512 threads, thread = (weight row, half of a 64-k block);
-//                unpack 4-bit to bf16 (w = fma(q, scale, bias) rounded once), store into the
-//                128-byte-swizzled K-major operand tile, ring "B"
+//   warps 4-19   dequant (packed weights only): two groups of 256 threads that take alternate 64-k blocks,
+//                thread = weight row; unpack 4-bit to bf16 (w = fma(q, scale, bias) rounded once), store into
+//                the 128-byte-swizzled K-major operand tile, ring "B"
 //   warps 20-23  epilogue: tcgen05.ld 8 or 16 columns at a time with the next chunk's load in flight,
 //                bias + activation (one special-function op per element), 16-byte stores
 // Every mbarrier wait is bounded (about one second); on expiry the kernel raises an error
@@ -44,7 +44,6 @@ namespace ffai {
 namespace g100 {
 
 constexpr int BM = 128;        // activation rows per tile (the MMA's M: one TMEM lane each)
-constexpr int PAIR = 2 * BM;   // activation rows per work item: up to two token tiles share one pass over the weights
 constexpr int BN = 256;        // weight rows per tile (the MMA's N: one fp32 TMEM column each)
 constexpr int BK = 64;         // k per MMA stage (one 128-byte swizzle row of bf16)
 constexpr int KS = 256;        // k per packed-weight TMA box (one 128-byte row of 4-bit values)
@@ -79,7 +78,6 @@ struct Params {
     const uint32_t* offsets;       // [E+1] row ranges per expert in the sorted row space
     const uint32_t* tile_offsets;  // [E+1] prefix sum of token tiles per expert
     int m_tiles;                   // ceil(n_out / 128)
-    int group_rows;                // routed rows per work item: BM (one token tile) or PAIR (two tiles share a pass over the weights)
     int activation;
     float limit, alpha;
     void* out;                 // [rows, out_ld]
@@ -277,11 +275,9 @@ FFAI_DEVINL int permute8_store_col(int n) {
     return (n & ~7) | (((k & 3) << 1) | (k >> 2));
 }
 
-// A work item is (expert, group of up to 256 routed rows, weight-row tile).  An item holds one or two 128-row
-// token tiles that are multiplied against the same dequantised weight tile (each weight tile is produced once
-// per item, not once per token tile).  Consecutive items share the rows so the activation tiles stay hot in
-// L2 across the CTAs that work on one expert.  n_cols_valid counts the item's rows (1..256);
-// tiles = 1 + (n_cols_valid > 128).
+// A work item is (expert, token tile of up to 128 routed rows, weight-row tile).  Consecutive items share
+// the rows so the activation tiles stay hot in L2 across the CTAs that work on one expert.
+// n_cols_valid counts the item's rows (1..128).
 struct TileCoord {
     int expert, row_begin, n_cols_valid, m_tile;
 };
@@ -395,7 +391,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     if (threadIdx.x == 0) {
         for (int s = 0; s < L::NW; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), N_DEQ_WARPS); }
         for (int s = 0; s < L::NX; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 1); }
-        for (int s = 0; s < NB; ++s) { mbar_init(b_full(s), WBF16 ? 1 : N_DEQ_WARPS); mbar_init(b_empty(s), 1); }
+        for (int s = 0; s < NB; ++s) { mbar_init(b_full(s), WBF16 ? 1 : N_DEQ_WARPS / 2); mbar_init(b_empty(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
         for (int s = 0; s < NSCHED; ++s) { mbar_init(s_full(s), 1); mbar_init(s_empty(s), L::N_ITEM_READERS); }
         *abort_flag = 0;
@@ -485,15 +481,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 TileCoord c;
                 if (!feed.take(c, abort_flag, false)) { ok = false; break; }
-                const int nt = c.n_cols_valid > BM ? 2 : 1;
-                for (int kb = 0; kb < KB && ok; ++kb) {
-                    for (int t = 0; t < nt; ++t) {
-                        if (!mbar_wait<32>(x_empty(xp.stage), xp.phase ^ 1, abort_flag)) { ok = false; break; }
-                        mbar_arrive_expect_tx(x_full(xp.stage), L::X_TILE);
-                        tma_load_2d(sbase + L::OFF_X + xp.stage * L::X_TILE, &tm_x, kb * BK, c.row_begin + t * BM, x_full(xp.stage));
-                        xp.advance(L::NX);
-                        ++issued;
-                    }
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!mbar_wait<32>(x_empty(xp.stage), xp.phase ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(x_full(xp.stage), L::X_TILE);
+                    tma_load_2d(sbase + L::OFF_X + xp.stage * L::X_TILE, &tm_x, kb * BK, c.row_begin, x_full(xp.stage));
+                    xp.advance(L::NX);
+                    ++issued;
                 }
             }
             if (!ok) {
@@ -515,55 +508,47 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 TileCoord c;
                 if (!feed.take(c, abort_flag, false)) { ok = false; break; }
-                const int nt = c.n_cols_valid > BM ? 2 : 1;
-                // token tile t of the item accumulates in TMEM buffer (tcount + t) & 1
-                uint32_t d0[2];
-                for (int t = 0; t < nt; ++t) {
-                    const uint32_t tc = tcount + t;
-                    if (!mbar_wait<32>(acc_empty(tc & 1), ((tc >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                    d0[t] = tmem_base + (uint32_t)((tc & 1) * BN);
-                }
-                if (!ok) break;
+                // the item accumulates in TMEM buffer tcount & 1
+                if (!mbar_wait<32>(acc_empty(tcount & 1), ((tcount >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                const uint32_t d0 = tmem_base + (uint32_t)((tcount & 1) * BN);
                 tc_fence_after();
                 for (int kb = 0; kb < KB && ok; ++kb, ++gk) {
                     tl_mark(p, TL_MMA, gk, 2);
                     if (!mbar_wait<0>(b_full(bp.stage), bp.phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait<0>(x_full(xp.stage), xp.phase, abort_flag)) { ok = false; break; }
+                    tl_mark(p, TL_MMA, gk, 0);
+                    tc_fence_after();
                     const uint64_t bd0 = make_kmajor_sw128_desc(sbase + L::OFF_B + bp.stage * L::B_STAGE);
-                    for (int t = 0; t < nt; ++t) {
-                        if (!mbar_wait<0>(x_full(xp.stage), xp.phase, abort_flag)) { ok = false; break; }
-                        if (t == 0) tl_mark(p, TL_MMA, gk, 0);
-                        tc_fence_after();
-                        const uint64_t ad0 = make_kmajor_sw128_desc(sbase + L::OFF_X + xp.stage * L::X_TILE);
+                    const uint64_t ad0 = make_kmajor_sw128_desc(sbase + L::OFF_X + xp.stage * L::X_TILE);
 #pragma unroll
-                        for (int k16 = 0; k16 < BK / 16; ++k16) {
-                            // advancing 16 k inside the swizzled row = +32 bytes = +2 in the (addr >> 4) field
-                            umma_bf16(d0[t], ad0 + 2 * k16, bd0 + 2 * k16, idesc, (kb | k16) != 0 ? 1u : 0u);
-                        }
-                        umma_commit(x_empty(xp.stage));
-                        xp.advance(L::NX);
+                    for (int k16 = 0; k16 < BK / 16; ++k16) {
+                        // advancing 16 k inside the swizzled row = +32 bytes = +2 in the (addr >> 4) field
+                        umma_bf16(d0, ad0 + 2 * k16, bd0 + 2 * k16, idesc, (kb | k16) != 0 ? 1u : 0u);
                     }
-                    if (!ok) break;
                     tl_mark(p, TL_MMA, gk, 1);
+                    umma_commit(x_empty(xp.stage));
                     umma_commit(b_empty(bp.stage));
                     tl_mark(p, TL_MMA, gk, 3);
+                    xp.advance(L::NX);
                     bp.advance(NB);
                 }
-                if (ok)
-                    for (int t = 0; t < nt; ++t) umma_commit(acc_full((tcount + t) & 1));
-                tcount += nt;
+                if (ok) umma_commit(acc_full(tcount & 1));
+                ++tcount;
             }
         }
     } else if (!WBF16 && warp >= DEQ_WARP0 && warp < DEQ_WARP0 + N_DEQ_WARPS) {
-        // ───────────── dequant: 512 threads, thread = (weight row r of 256, 32-k half of a 64-k block) ─────────────
-        // A warp covers 16 rows x 2 halves, eight consecutive rows per quarter-warp, so both the 16-byte
-        // reads of the 128-byte-swizzled packed tile and the 16-byte stores into the 128-byte-swizzled
-        // operand tile touch eight distinct chunk columns: no bank conflicts either way.
-        // Per 64-k block a thread turns 4 packed words into 32 bf16: per word 4 logic ops (mask and
-        // exponent held in registers so each pair is one instruction), 3 shifts, 4 subtract-128 and
-        // 4 fused multiply-adds on bf16 pairs, one 16-byte shared-space store.
+        // ───────────── dequant: two groups of 8 warps, a group takes every other 64-k block ─────────────
+        // Thread = one weight row of the 256-row stage; in a block of its group it turns the row's 8 packed words
+        // (two 16-byte reads) into 64 bf16 (eight 16-byte stores).  Eight consecutive rows per quarter-warp, so the
+        // reads of the 128-byte-swizzled packed tile and the stores into the 128-byte-swizzled operand tile
+        // touch eight distinct chunk columns: no bank conflicts either way.  Per word: 4 logic ops (mask and
+        // exponent held in registers so each pair is one instruction), 3 shifts, 4 subtract-128 and 4 fused
+        // multiply-adds on bf16 pairs.  The two groups work on different operand stages at the same time, so
+        // one group's waits and fences overlap the other group's arithmetic; blocks are counted over the CTA's
+        // whole run, so the alternation carries across work items whatever K is.
         const int dw = warp - DEQ_WARP0;
-        const int half = (lane >> 3) & 1;
-        const int r = dw * 16 + (lane & 7) + ((lane >> 4) << 3);   // 0..255
+        const uint32_t grp = (uint32_t)dw >> 3;
+        const int r = (dw & 7) * 32 + lane;                         // 0..255
         const int gpr = p.K / p.group_size;
         const int gshift = p.group_size == 32 ? 5 : (p.group_size == 64 ? 6 : 7);
         const bool second = FUSED && r >= BN / 2;                   // the up projection's half of the tile
@@ -574,95 +559,125 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         uint32_t mask, expo;
         asm volatile("mov.u32 %0, 0x000F000F;" : "=r"(mask));
         asm volatile("mov.u32 %0, 0x43004300;" : "=r"(expo));       // also the bf16 pair (128, 128)
-        // shared-window addresses of this thread's row in stage 0 of both rings, and its four swizzled chunks
-        const uint32_t w_row0 = sbase + L::OFF_W + r * (KS / 2);     // packed stage: 128-byte rows, 16-byte pieces XOR-swizzled by row
+        // shared-window addresses of this thread's row in stage 0 of both rings; a 16-byte piece c of the row
+        // sits at ((c << 4) ^ swz) in either ring
+        const uint32_t w_row0 = sbase + L::OFF_W + r * (KS / 2);
         const uint32_t b_row0 = sbase + L::OFF_B + r * 128;
-        uint32_t w_chunk[SUB], b_chunk[4];
-#pragma unroll
-        for (int j = 0; j < SUB; ++j) w_chunk[j] = (uint32_t)(((2 * j + half) ^ (r & 7)) << 4);
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) b_chunk[jj] = (uint32_t)(((half * 4 + jj) ^ (r & 7)) << 4);
+        const uint32_t swz = (uint32_t)(r & 7) << 4;
         RingPos wp{0, 0}, bp{0, 0};
+        if (grp) bp.advance(NB);                                    // the group's first block is block grp of the run
+        uint32_t blocks_before = 0;                                 // 64-k blocks of the work items so far
         bool ok = true;
         int gk = 0;
         const bool tl_on = (warp == DEQ_WARP0 && lane == 0);
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            TileCoord c;
-            if (!feed.take(c, abort_flag, true)) break;
+        // Where a row's scales and biases live, for one work item.
+        struct RowScales {
+            const uint16_t *sp, *bq;
+            const uint32_t* sw;
+            int j0;   // the group's blocks of a packed stage are j0 and j0 + 2
+        };
+        auto row_scales = [&](const TileCoord& c, uint32_t blocks_before_item) {
             int prow = c.m_tile * ROWS_PER_TILE + r_in_proj;        // row within the expert's projection
             if (prow >= p.n_out) prow = p.n_out - 1;                // rows past the projection: zero-filled by TMA, masked at store
             const long grow = (long)c.expert * p.n_out + prow;
-            const uint16_t* sp = sbase_ptr + grow * gpr;
-            const uint16_t* bq = bbase_ptr + grow * gpr;
-            const uint32_t* sw = sbw_ptr ? sbw_ptr + (((size_t)c.expert * (p.n_out >> 4) + (prow >> 4)) * KB) * 16 + (prow & 15) : nullptr;
-            // scale and bias per 64-k block, fetched one super block ahead.  The loaded values are left
-            // untouched until the next super block: an instruction that consumes a load stalls the warp
-            // until the data arrives, which would put the memory latency back on the critical path.
-            uint32_t s_nxt[SPF], b_nxt[SPF];
-            auto fetch_scales = [&](int kb0) {
+            RowScales rs;
+            rs.sp = sbase_ptr + grow * gpr;
+            rs.bq = bbase_ptr + grow * gpr;
+            rs.sw = sbw_ptr ? sbw_ptr + (((size_t)c.expert * (p.n_out >> 4) + (prow >> 4)) * KB) * 16 + (prow & 15) : nullptr;
+            rs.j0 = (int)((grp ^ blocks_before_item) & 1u);
+            return rs;
+        };
+        // (scale | bias << 16) of both 32-k halves of the group's two blocks of a packed stage, fetched one packed
+        // stage ahead - across work items too: the first stage of the next item is fetched during the last
+        // stage of this one, so no item starts by waiting for its scales.
+        uint32_t nxt[2][2];
+        auto fetch_scales = [&](const RowScales& rs, int kb0) {
 #pragma unroll
-                for (int j = 0; j < SPF; ++j) {
-                    const int kb = min(kb0 + j, KB - 1);
-                    if (sw) {
-                        s_nxt[j] = __ldg(sw + (size_t)kb * 16);
-                    } else {
-                        const int g = (kb * BK + half * 32) >> gshift;
-                        s_nxt[j] = sp[g];
-                        b_nxt[j] = bq[g];
+            for (int jj = 0; jj < 2; ++jj) {
+                const int kb = min(kb0 + rs.j0 + 2 * jj, KB - 1);
+                if (rs.sw) {
+                    nxt[jj][0] = __ldg(rs.sw + (size_t)kb * 16);
+                    nxt[jj][1] = nxt[jj][0];
+                } else {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int g = (kb * BK + h * 32) >> gshift;
+                        nxt[jj][h] = (uint32_t)rs.sp[g] | ((uint32_t)rs.bq[g] << 16);
                     }
                 }
-            };
-            fetch_scales(0);
-            for (int kb0 = 0; kb0 < KB && ok; kb0 += SPF) {
-                uint32_t sb_cur[SPF];
+            }
+        };
+        TileCoord c_next;
+        bool have_next = blockIdx.x < total_tiles && feed.take(c_next, abort_flag, true);
+        RowScales rs_next{};
+        if (have_next) {
+            rs_next = row_scales(c_next, 0u);
+            fetch_scales(rs_next, 0);
+        }
+        for (int tile = blockIdx.x; tile < total_tiles && ok && have_next; tile += gridDim.x) {
+            const RowScales rs = rs_next;
+            const int j0 = rs.j0;
+            have_next = tile + (int)gridDim.x < total_tiles && feed.take(c_next, abort_flag, true);
+            if (have_next) rs_next = row_scales(c_next, blocks_before + (uint32_t)KB);
+            else if (tile + (int)gridDim.x < total_tiles) ok = false;   // gave up waiting for the scheduler
+            for (int kb0 = 0; kb0 < KB && ok; kb0 += SUB) {
+                uint32_t cur[2][2];
 #pragma unroll
-                for (int j = 0; j < SPF; ++j) sb_cur[j] = sw ? s_nxt[j] : (s_nxt[j] | (b_nxt[j] << 16));
-                fetch_scales(kb0 + SPF);
-#pragma unroll
-                for (int ws = 0; ws < SPF / SUB; ++ws) {
-                    if (kb0 + ws * SUB >= KB) break;
-                    if (tl_on) tl_mark(p, TL_DEQ, gk, 0);
+                for (int jj = 0; jj < 2; ++jj) { cur[jj][0] = nxt[jj][0]; cur[jj][1] = nxt[jj][1]; }
+                if (kb0 + SUB < KB) fetch_scales(rs, kb0 + SUB);
+                else if (have_next) fetch_scales(rs_next, 0);
+                const int nblk = min(SUB, KB - kb0);
+                if (j0 < nblk) {
                     if (!mbar_wait<0>(w_full(wp.stage), wp.phase, abort_flag)) { ok = false; break; }
-                    if (tl_on) tl_mark(p, TL_DEQ, gk, 1);
                     const uint32_t w_row = w_row0 + wp.stage * L::W_STAGE;
 #pragma unroll
-                    for (int j = 0; j < SUB; ++j) {
-                        if (kb0 + ws * SUB + j >= KB) break;
-                        if (!mbar_wait<0>(b_empty(bp.stage), bp.phase ^ 1, abort_flag)) { ok = false; break; }
-                        if (tl_on) tl_mark(p, TL_DEQ, gk, 2);
-                        const uint32_t b_row = b_row0 + bp.stage * L::B_STAGE;
-                        uint32_t w4[4];
+                    for (int jj = 0; jj < 2; ++jj) {
+                        const int j = j0 + 2 * jj;
+                        if (j >= nblk) break;
+                        if (tl_on) tl_mark(p, TL_DEQ, gk, 0);
+                        uint32_t w8[8];
                         asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
-                                     : "=r"(w4[0]), "=r"(w4[1]), "=r"(w4[2]), "=r"(w4[3]) : "r"(w_row + w_chunk[j]));
-                        const uint32_t sbv = sb_cur[ws * SUB + j];
-                        const uint32_t s2 = __byte_perm(sbv, sbv, 0x1010), b2 = __byte_perm(sbv, sbv, 0x3232);
+                                     : "=r"(w8[0]), "=r"(w8[1]), "=r"(w8[2]), "=r"(w8[3]) : "r"(w_row + (((uint32_t)(2 * j) << 4) ^ swz)));
+                        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(w8[4]), "=r"(w8[5]), "=r"(w8[6]), "=r"(w8[7]) : "r"(w_row + (((uint32_t)(2 * j + 1) << 4) ^ swz)));
+                        if (!mbar_wait<0>(b_empty(bp.stage), bp.phase ^ 1, abort_flag)) { ok = false; break; }
+                        if (tl_on) tl_mark(p, TL_DEQ, gk, 1);
+                        const uint32_t b_row = b_row0 + bp.stage * L::B_STAGE;
 #pragma unroll
-                        for (int jj = 0; jj < 4; ++jj) {
-                            const uint32_t w = w4[jj];
-                            uint32_t o[4];
+                        for (int h = 0; h < 2; ++h) {
+                            const uint32_t sbv = cur[jj][h];
+                            const uint32_t s2 = __byte_perm(sbv, sbv, 0x1010), b2 = __byte_perm(sbv, sbv, 0x3232);
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                uint32_t t, q;
-                                asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(i == 0 ? w : (w >> (4 * i))), "r"(mask), "r"(expo));
-                                asm("sub.bf16x2 %0, %1, %2;" : "=r"(q) : "r"(t), "r"(expo));
-                                asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[i]) : "r"(q), "r"(s2), "r"(b2));
+                            for (int q4 = 0; q4 < 4; ++q4) {
+                                const uint32_t w = w8[h * 4 + q4];
+                                uint32_t o[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    uint32_t t, q;
+                                    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(i == 0 ? w : (w >> (4 * i))), "r"(mask), "r"(expo));
+                                    asm("sub.bf16x2 %0, %1, %2;" : "=r"(q) : "r"(t), "r"(expo));
+                                    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[i]) : "r"(q), "r"(s2), "r"(b2));
+                                }
+                                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
+                                             ::"r"(b_row + (((uint32_t)(h * 4 + q4) << 4) ^ swz)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
                             }
-                            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
-                                         ::"r"(b_row + b_chunk[jj]), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
                         }
+                        if (tl_on) tl_mark(p, TL_DEQ, gk, 2);
                         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
                         __syncwarp();
                         if (lane == 0) mbar_arrive(b_full(bp.stage));
                         if (tl_on) tl_mark(p, TL_DEQ, gk, 3);
                         ++gk;
                         bp.advance(NB);
+                        bp.advance(NB);
                     }
                     if (!ok) break;
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(w_empty(wp.stage));  // this warp is done reading the packed stage
-                    wp.advance(L::NW);
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(w_empty(wp.stage));  // this warp is done with the packed stage (or has no block in it)
+                wp.advance(L::NW);
             }
+            blocks_before += (uint32_t)KB;
         }
     } else if (warp >= EPI_WARP0) {
         // ───────────── epilogue: thread = activation row (TMEM lane), walks the 256 accumulator columns ─────────────
@@ -670,13 +685,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         uint32_t tcount = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-          TileCoord item;
-          if (!feed.take(item, abort_flag, true)) break;
-          for (int tt = 0; tt < 2 && ok; ++tt) {
-            TileCoord c = item;
-            if (tt == 1 && c.n_cols_valid <= BM) break;
-            c.row_begin += tt * BM;                               // this token tile's rows
-            c.n_cols_valid = min(BM, c.n_cols_valid - tt * BM);
+            TileCoord c;
+            if (!feed.take(c, abort_flag, true)) break;
             const int buf = tcount & 1;
             const uint32_t acc_ph = (tcount >> 1) & 1;
             if (warp == EPI_WARP0 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 0);
@@ -760,7 +770,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             if (lane == 0) mbar_arrive(acc_empty(buf));
             if (warp == EPI_WARP0 && lane == 0) tl_mark(p, TL_EPI, (int)tcount, 2);
             ++tcount;
-          }
         }
     } else if (warp == SCHED_WARP) {
         // ───────────── scheduler: coordinates of the CTA's work items, up to NSCHED items ahead ─────────────
@@ -773,8 +782,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             const int e = find_group_warp(p.tile_offsets, p.n_experts, g, lane);
             if (lane == 0) {
                 const int nt = g - (int)__ldg(p.tile_offsets + e);
-                const int row_begin = (int)__ldg(p.offsets + e) + nt * p.group_rows;
-                const int n_valid = min(p.group_rows, (int)__ldg(p.offsets + e + 1) - row_begin);
+                const int row_begin = (int)__ldg(p.offsets + e) + nt * BM;
+                const int n_valid = min(BM, (int)__ldg(p.offsets + e + 1) - row_begin);
                 asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
                              ::"r"(sbase + (uint32_t)L::OFF_SCHED + 16u * slot), "r"(e), "r"(row_begin), "r"(n_valid),
                                "r"(tile - g * p.m_tiles) : "memory");
