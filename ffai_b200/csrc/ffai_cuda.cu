@@ -1115,7 +1115,7 @@ extern "C" FFAI_API int ffai_moe_set_option(ffai_moe_layer* L, const char* name,
         return FFAI_OK;
     }
     if (!strcmp(name, "tc_weights")) {
-        if (value < 0 || value > 1) return fail(L, FFAI_ERR_INVALID_ARG, "tc_weights must be 0 (cache when present) or 1 (packed)");
+        if (value < 0 || value > 2) return fail(L, FFAI_ERR_INVALID_ARG, "tc_weights must be 0 (automatic), 1 (packed) or 2 (cache when present)");
         L->opt_tc_weights = value;
         return FFAI_OK;
     }
@@ -1298,10 +1298,16 @@ int ep_all_to_all(ffai_moe_layer* L, const uint8_t* send, const size_t* off_s, c
 // The two grouped GEMMs of the tensor-core path, from the bf16 weight cache when the layer keeps one,
 // else from the packed 4-bit weights with the in-kernel dequant stage.
 int tc_group_rows(const ffai_moe_layer*) { return g100::BM; }
-bool tc_reads_cache(const ffai_moe_layer* L) { return L->exp_wbf[0] && (L->opt_tc_weights == 0 || L->cfg.expert_bits != 4); }
+bool tc_reads_cache(const ffai_moe_layer* L) { return L->exp_wbf[0] && (L->opt_tc_weights != 1 || L->cfg.expert_bits != 4); }
 bool tc_possible(const ffai_moe_layer* L) { return L->tc_ok && (L->cfg.expert_bits == 4 || L->exp_wbf[0]); }
-int tc_gate_up(ffai_moe_layer* L, const g100::Params& p, cudaStream_t st) {
-    return tc_reads_cache(L) ? g100::launch_grouped_gemm<true, uint16_t, true>(L->tm_gate_bf, L->tm_up_bf, L->tm_xg, p, L->n_sms, st)
+// Gate/up with few rows per expert goes over the packed weights even when the layer keeps a cache: an expert
+// then has one or two token tiles, the dequant stage runs once or twice per weight tile, and the 4x smaller
+// weight read wins (cfg3: 160 us packed against 170 us cached; at 256 rows per expert the cache wins, 300
+// against 339 us).  Down keeps the cache: its reduction axis is short and the packed pipeline's start-up per
+// item weighs more.
+int tc_gate_up(ffai_moe_layer* L, const g100::Params& p, double rows_per_expert, cudaStream_t st) {
+    const bool packed_pays = L->cfg.expert_bits == 4 && L->opt_tc_weights == 0 && rows_per_expert <= 160.0;
+    return tc_reads_cache(L) && !packed_pays ? g100::launch_grouped_gemm<true, uint16_t, true>(L->tm_gate_bf, L->tm_up_bf, L->tm_xg, p, L->n_sms, st)
                              : g100::launch_grouped_gemm<true, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg, p, L->n_sms, st);
 }
 template <typename TOut>
@@ -1379,7 +1385,7 @@ int run_experts_on_rows(ffai_moe_layer* L, int n_rows, int n_exp, const uint32_t
         if (c.expert_group_size != 32) { p.sb = L->sb_gate; p.sb2 = L->sb_up; }
         p.n_out = I; p.K = H; p.m_tiles = (I + BN / 2 - 1) / (BN / 2);
         p.out = L->inner_bf; p.out_ld = I; p.out_permute8 = 1;
-        if (tc_gate_up(L, p, st))
+        if (tc_gate_up(L, p, rpe, st))
             return fail(L, FFAI_ERR_CUDA, "gate/up grouped GEMM launch failed");
         stage_end(L, ST_GATE_UP, st);
         stage_begin(L, ST_DOWN, st);
@@ -1787,7 +1793,7 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
         if (c.expert_group_size != 32) { p.sb = L->sb_gate; p.sb2 = L->sb_up; }
         p.n_out = I; p.K = H; p.m_tiles = (I + BN / 2 - 1) / (BN / 2);
         p.out = L->inner_bf; p.out_ld = I; p.out_permute8 = 1;
-        if (tc_gate_up(L, p, st))
+        if (tc_gate_up(L, p, rows_per_expert, st))
             return fail(L, FFAI_ERR_CUDA, "gate/up grouped GEMM launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += 1;
         stage_end(L, ST_GATE_UP, st);

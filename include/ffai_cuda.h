@@ -296,7 +296,8 @@ FFAI_API uint32_t ffai_ep_plan_exchange(const uint32_t* recv_counts, int32_t wor
  *   "path"         0 automatic, 1 CUDA-core grouped GEMV only, 2 tcgen05 grouped GEMM whenever possible,
  *                  3 streaming decode kernels whenever possible
  *   "tc_min_rows"  smallest T*k that takes the tcgen05 path under "path" = 0 (0: default)
- *   "tc_weights"   tcgen05 path reads 0 the bf16 weight cache when the layer keeps one, 1 always the packed weights
+ *   "tc_weights"   tcgen05 path reads 0 automatic (the bf16 weight cache when the layer keeps one, except gate/up
+ *                  with at most 160 routed rows per expert), 1 always the packed weights, 2 always the cache
  *   "ksplit"       cp.async decode kernels: slices of the reduction axis per 16-row block (0 automatic, 1, 2, 4)
  *   "decode"       decode kernels: 0 automatic, 1 cp.async rings, 2 bulk-copy streams
  *   "decode_team"  bulk-copy streams: warps that share one 16-row block (0 automatic, 1, 4, 16)

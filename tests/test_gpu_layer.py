@@ -230,12 +230,13 @@ def test_tc_cfg3_full_prefill_sampled(oracle_mod):
     run_and_check(oracle_mod, synth.cfg3_qwen(), 2048, token_mask=mask, path=TC)
 
 
-def test_tc_cfg3_full_prefill_packed_weights(oracle_mod):
-    """The same prefill with the tensor-core kernel dequantising the packed weights itself
-    (the automatic choice at this size is the bf16 weight cache)."""
+@pytest.mark.parametrize("tc_weights", [1, 2])
+def test_tc_cfg3_full_prefill_one_weight_source(oracle_mod, tc_weights):
+    """The same prefill with both grouped GEMMs dequantising the packed weights themselves (1) or both reading
+    the bf16 weight cache (2); the automatic choice at this size is packed gate/up and cached down."""
     mask = np.zeros(2048, dtype=np.uint8)
     mask[np.random.default_rng(2).choice(2048, size=64, replace=False)] = 1
-    run_and_check(oracle_mod, synth.cfg3_qwen(), 2048, token_mask=mask, path=TC, options={"tc_weights": 1})
+    run_and_check(oracle_mod, synth.cfg3_qwen(), 2048, token_mask=mask, path=TC, options={"tc_weights": tc_weights})
 
 
 @pytest.mark.parametrize("bits", [3, 4, 5, 6, 8])
@@ -253,13 +254,17 @@ def test_tc_cache_and_packed_weights_agree(oracle_mod):
     layer = MoELayer(host, 400)
     try:
         layer.set_option("path", TC)
+        layer.set_option("tc_weights", 2)
         a, _ = layer.forward_host(x)
         layer.set_option("tc_weights", 1)
         b, _ = layer.forward_host(x)
+        layer.set_option("tc_weights", 0)   # automatic: packed gate/up, cached down at this size
+        c, _ = layer.forward_host(x)
     finally:
         layer.close()
     # both round fma(q, scale, bias) to bf16 once and run the same MMA sequence
     assert np.array_equal(a, b)
+    assert np.array_equal(a, c)
 
 
 @pytest.mark.parametrize("gs", [32, 128])
