@@ -447,7 +447,10 @@ int launch_plan(const uint32_t* indices, int n_rows, int E, uint32_t* counts, ui
         }
     }
     plan_count_kernel<<<nb, 32, E * sizeof(uint32_t), st>>>(indices, n_rows, E, block_hist);
-    plan_scan_kernel<<<1, 256, (E + 1) * sizeof(uint32_t), st>>>(block_hist, nb, E, counts, offsets);
+    const bool tiles3 = tile_offsets != nullptr && tile_rows > 0;
+    plan_scan_kernel<<<1, 256, (E + 1) * sizeof(uint32_t), st>>>(block_hist, nb, E, counts, offsets, tile_rows,
+                                                                tiles3 ? tile_offsets : nullptr);
+    if (tiles3 && tiles_done) *tiles_done = true;
     plan_scatter_kernel<<<nb, 32, E * sizeof(uint32_t), st>>>(indices, n_rows, E, block_hist, perm, inv_perm);
     return cudaGetLastError() == cudaSuccess ? 3 : -1;
 }

@@ -802,18 +802,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     }
 }
 
-// Token tiles per expert and their prefix sum (one block).
+// Token tiles per expert and their prefix sum (one warp, 32 experts per round).
 __global__ void tile_schedule_kernel(const uint32_t* __restrict__ offsets, int n_experts, int ntok,
                                      uint32_t* __restrict__ tile_offsets) {
-    if (threadIdx.x == 0) {
-        uint32_t run = 0;
-        for (int e = 0; e < n_experts; ++e) {
-            tile_offsets[e] = run;
-            const uint32_t cnt = offsets[e + 1] - offsets[e];
-            run += (cnt + ntok - 1) / ntok;
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x >= 32) return;
+    uint32_t carry = 0;
+    for (int e0 = 0; e0 < n_experts; e0 += 32) {
+        const int e = e0 + lane;
+        const uint32_t t = e < n_experts ? (offsets[e + 1] - offsets[e] + ntok - 1) / ntok : 0u;
+        uint32_t incl = t;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += v;
         }
-        tile_offsets[n_experts] = run;
+        if (e < n_experts) tile_offsets[e] = carry + incl - t;
+        carry += __shfl_sync(0xFFFFFFFFu, incl, 31);
     }
+    if (lane == 0) tile_offsets[n_experts] = carry;
 }
 
 // Schedule of a single group of n_rows rows (the shared expert): sched = {0, n_rows, 0, n_tiles}.

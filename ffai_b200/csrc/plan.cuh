@@ -39,36 +39,68 @@ __global__ void plan_count_kernel(const uint32_t* __restrict__ indices, int n_ro
         block_hist[(size_t)blockIdx.x * n_experts + e] = hist[e];
 }
 
-// Pass 2 (one block): per expert, running sum over blocks -> block bases;
-// totals -> counts; exclusive scan over experts -> offsets; bases made absolute.
+// Pass 2 (one block): per expert, totals over blocks -> counts; exclusive scans over experts (rows and, when
+// tile_offsets is given, token tiles of tile_rows rows) by one warp with shuffles; then per expert the running
+// sum over blocks, offset by the expert's base -> absolute block bases.  The loads of a pass are issued in
+// batches before anything that depends on them, so a pass costs a few memory round trips, not one per block.
 __global__ void plan_scan_kernel(uint32_t* __restrict__ block_hist, int n_blocks, int n_experts,
-                                 uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets) {
+                                 uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets,
+                                 int tile_rows, uint32_t* __restrict__ tile_offsets) {
     extern __shared__ uint32_t totals[];  // [E+1]
+    constexpr int BATCH = 16;
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
         uint32_t run = 0;
-        for (int b = 0; b < n_blocks; ++b) {
-            uint32_t c = block_hist[(size_t)b * n_experts + e];
-            block_hist[(size_t)b * n_experts + e] = run;
-            run += c;
+        for (int b0 = 0; b0 < n_blocks; b0 += BATCH) {
+            uint32_t c[BATCH];
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) c[j] = b0 + j < n_blocks ? block_hist[(size_t)(b0 + j) * n_experts + e] : 0u;
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) run += c[j];
         }
         totals[e] = run;
         counts[e] = run;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t run = 0;
-        for (int e = 0; e < n_experts; ++e) {
-            uint32_t c = totals[e];
-            totals[e] = run;
-            offsets[e] = run;
-            run += c;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        uint32_t carry = 0, tcarry = 0;
+        for (int e0 = 0; e0 < n_experts; e0 += 32) {
+            const int e = e0 + lane;
+            const uint32_t c = (e < n_experts) ? totals[e] : 0u;
+            const uint32_t t = tile_offsets ? (c + tile_rows - 1) / tile_rows : 0u;
+            uint32_t incl = c, tincl = t;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                const uint32_t tv = __shfl_up_sync(0xFFFFFFFFu, tincl, d);
+                if (lane >= d) { incl += v; tincl += tv; }
+            }
+            if (e < n_experts) {
+                totals[e] = carry + incl - c;
+                offsets[e] = carry + incl - c;
+                if (tile_offsets) tile_offsets[e] = tcarry + tincl - t;
+            }
+            carry += __shfl_sync(0xFFFFFFFFu, incl, 31);
+            tcarry += __shfl_sync(0xFFFFFFFFu, tincl, 31);
         }
-        offsets[n_experts] = run;
+        if (lane == 0) {
+            offsets[n_experts] = carry;
+            if (tile_offsets) tile_offsets[n_experts] = tcarry;
+        }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-        const uint32_t off = totals[e];
-        for (int b = 0; b < n_blocks; ++b) block_hist[(size_t)b * n_experts + e] += off;
+        uint32_t run = totals[e];
+        for (int b0 = 0; b0 < n_blocks; b0 += BATCH) {
+            uint32_t c[BATCH];
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) c[j] = b0 + j < n_blocks ? block_hist[(size_t)(b0 + j) * n_experts + e] : 0u;
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) {
+                if (b0 + j < n_blocks) block_hist[(size_t)(b0 + j) * n_experts + e] = run;
+                run += c[j];
+            }
+        }
     }
 }
 
