@@ -298,6 +298,9 @@ FFAI_API uint32_t ffai_ep_plan_exchange(const uint32_t* recv_counts, int32_t wor
  *   "tc_min_rows"  smallest T*k that takes the tcgen05 path under "path" = 0 (0: default)
  *   "tc_weights"   tcgen05 path reads 0 automatic (the bf16 weight cache when the layer keeps one, except gate/up
  *                  with at most 160 routed rows per expert), 1 always the packed weights, 2 always the cache
+ *   "host_chunks"  host entry points: 0 = a batch of 4096 tokens or more goes through in up to 3 chunks whose copies
+ *                  overlap the compute (same bits: tokens are independent), 1 = always as one piece, 2..4 = at
+ *                  most that many chunks
  *   "ksplit"       cp.async decode kernels: slices of the reduction axis per 16-row block (0 automatic, 1, 2, 4)
  *   "decode"       decode kernels: 0 automatic, 1 cp.async rings, 2 bulk-copy streams
  *   "decode_team"  bulk-copy streams: warps that share one 16-row block (0 automatic, 1, 4, 16)
