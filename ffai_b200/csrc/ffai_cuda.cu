@@ -2404,8 +2404,10 @@ extern "C" FFAI_API int ffai_op_moe_unpermute(const uint16_t* expert_out, const 
 
 extern "C" FFAI_API int ffai_op_add_rmsnorm(const uint16_t* a, const uint16_t* b, const uint16_t* weight, float eps,
                                             int32_t n_rows, int32_t n, uint16_t* residual_out, uint16_t* normed_out, void* stream) {
-    if (!a || !b || !weight || !residual_out || !normed_out || n_rows <= 0 || n <= 0 || n % 4) return FFAI_ERR_INVALID_ARG;
-    if (!aligned16(a) || !aligned16(b) || !aligned16(residual_out) || !aligned16(normed_out) || (n % 8)) return FFAI_ERR_INVALID_ARG;
+    if (!a || !weight || !normed_out || n_rows <= 0 || n <= 0 || n % 4) return FFAI_ERR_INVALID_ARG;
+    if (b && !residual_out) return FFAI_ERR_INVALID_ARG;   // the sum is the caller's next residual: it must have a home
+    if (!aligned16(a) || (b && !aligned16(b)) || (residual_out && !aligned16(residual_out)) || !aligned16(normed_out) || (n % 8))
+        return FFAI_ERR_INVALID_ARG;
     int rc;
     if ((rc = need_device())) return rc;
     prep::add_rmsnorm_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(a, b, weight, eps, n, residual_out, normed_out);

@@ -135,11 +135,12 @@ add_rmsnorm_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ 
                    float eps, int n, uint16_t* __restrict__ residual_out, uint16_t* __restrict__ normed_out) {
     const size_t row = blockIdx.x;
     const uint16_t* ar = a + row * n;
-    const uint16_t* br = b + row * n;
+    const uint16_t* br = b ? b + row * n : nullptr;   // no second addend: a plain RMSNorm of a
     __shared__ float red[8];
     float ssq = 0.0f;
     for (int h = threadIdx.x * 4; h < n; h += blockDim.x * 4) {
-        const uint2 ua = *reinterpret_cast<const uint2*>(ar + h), ub = *reinterpret_cast<const uint2*>(br + h);
+        const uint2 ua = *reinterpret_cast<const uint2*>(ar + h);
+        const uint2 ub = br ? *reinterpret_cast<const uint2*>(br + h) : make_uint2(0u, 0u);
         const float s0 = bf16lo(ua.x) + bf16lo(ub.x), s1 = bf16hi(ua.x) + bf16hi(ub.x);
         const float s2 = bf16lo(ua.y) + bf16lo(ub.y), s3 = bf16hi(ua.y) + bf16hi(ub.y);
         ssq += (s0 * s0 + s1 * s1) + (s2 * s2 + s3 * s3);
@@ -152,7 +153,8 @@ add_rmsnorm_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ 
     for (int w = 0; w < 8; ++w) total += red[w];
     const float inv_rms = 1.0f / sqrtf(total / (float)n + eps);
     for (int h = threadIdx.x * 4; h < n; h += blockDim.x * 4) {
-        const uint2 ua = *reinterpret_cast<const uint2*>(ar + h), ub = *reinterpret_cast<const uint2*>(br + h);
+        const uint2 ua = *reinterpret_cast<const uint2*>(ar + h);
+        const uint2 ub = br ? *reinterpret_cast<const uint2*>(br + h) : make_uint2(0u, 0u);
         const uint2 uw = *reinterpret_cast<const uint2*>(weight + h);
         const float s0 = bf16lo(ua.x) + bf16lo(ub.x), s1 = bf16hi(ua.x) + bf16hi(ub.x);
         const float s2 = bf16lo(ua.y) + bf16lo(ub.y), s3 = bf16hi(ua.y) + bf16hi(ub.y);
@@ -161,7 +163,7 @@ add_rmsnorm_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ 
         r.y = (uint32_t)f32_to_bf16_bits(s2) | ((uint32_t)f32_to_bf16_bits(s3) << 16);
         o.x = (uint32_t)f32_to_bf16_bits(s0 * inv_rms * bf16lo(uw.x)) | ((uint32_t)f32_to_bf16_bits(s1 * inv_rms * bf16hi(uw.x)) << 16);
         o.y = (uint32_t)f32_to_bf16_bits(s2 * inv_rms * bf16lo(uw.y)) | ((uint32_t)f32_to_bf16_bits(s3 * inv_rms * bf16hi(uw.y)) << 16);
-        *reinterpret_cast<uint2*>(residual_out + row * n + h) = r;
+        if (residual_out) *reinterpret_cast<uint2*>(residual_out + row * n + h) = r;
         *reinterpret_cast<uint2*>(normed_out + row * n + h) = o;
     }
 }

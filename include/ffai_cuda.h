@@ -448,7 +448,10 @@ FFAI_API int ffai_st_moe_weights(ffai_st_file* file, const char* prefix, int32_t
  *   layout this library reads (QuantizedOps.swift:229-388); bits in {2,3,4,5,6,8}, gs in {32,64,128}. */
 /* The step in front of the block (Ops.addAndRmsNorm, Ops.swift:658-760; called right before the MoE
  * block in GPTOSSText.swift:700-716): residual_out = a + b, normed_out = RMSNorm(a + b) * weight, rows of
- * n bf16 (n a multiple of 8; no upper limit, unlike the reference's 4096), fp32 arithmetic inside. */
+ * n bf16 (n a multiple of 8; no upper limit, unlike the reference's 4096), fp32 arithmetic inside.
+ * With b = NULL it is the plain row-wise RMSNorm (Ops.rmsNorm / Ops.rmsNormRows, Ops.swift:515-578): the norm a
+ * Gemma 4 block applies to the router's input rows and to the experts' input rows (Gemma4Text.swift:932-960)
+ * before ffai_moe_forward_split; residual_out may then be NULL. */
 FFAI_API int ffai_op_add_rmsnorm(const uint16_t* a, const uint16_t* b, const uint16_t* weight, float eps,
                                  int32_t n_rows, int32_t n, uint16_t* residual_out, uint16_t* normed_out, void* stream);
 FFAI_API int ffai_op_mxfp4_to_affine_int4(const uint32_t* packed, const uint8_t* e8m0, int64_t n_groups,

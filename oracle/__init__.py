@@ -145,15 +145,15 @@ def affine_quantize(w_bf16, bits, gs):
 
 
 def add_rmsnorm(a, b, weight, eps):
-    """bf16 bit patterns [rows, n], [rows, n], [n] -> (residual bf16, normed bf16, normed f32)."""
+    """bf16 bit patterns [rows, n], [rows, n] or None (plain RMSNorm), [n] -> (residual bf16, normed bf16, normed f32)."""
     a = np.ascontiguousarray(a, dtype=np.uint16)
-    b = np.ascontiguousarray(b, dtype=np.uint16)
+    b = None if b is None else np.ascontiguousarray(b, dtype=np.uint16)
     weight = np.ascontiguousarray(weight, dtype=np.uint16)
     rows, n = a.shape
     res = np.zeros((rows, n), dtype=np.uint16)
     nrm = np.zeros((rows, n), dtype=np.uint16)
     nf = np.zeros((rows, n), dtype=np.float32)
-    lib().orc_add_rmsnorm(_p(a), _p(b), _p(weight), C.c_float(eps), C.c_int(rows), C.c_int(n), _p(res), _p(nrm), _p(nf))
+    lib().orc_add_rmsnorm(_p(a), _p(b) if b is not None else None, _p(weight), C.c_float(eps), C.c_int(rows), C.c_int(n), _p(res), _p(nrm), _p(nf))
     return res, nrm, nf
 
 

@@ -761,20 +761,21 @@ ORC_EXPORT void orc_affine_quantize(const uint16_t* w, int64_t rows, int K, int 
 
 /* residual = a + b; normed = (a + b) / sqrt(mean((a + b)^2) + eps) * weight, per row of n values.
  * Follows the CPU check of the reference's own test (OpsTests.swift:1042-1052): the sum of squares is
- * accumulated sequentially in float, the norm uses the unrounded sum.  bf16 bit patterns in and out. */
+ * accumulated sequentially in float, the norm uses the unrounded sum.  bf16 bit patterns in and out.
+ * b = NULL: the plain RMSNorm y = x / rms(x) * weight (LayersTests.swift:101-128 holds its CPU check). */
 ORC_EXPORT void orc_add_rmsnorm(const uint16_t* a, const uint16_t* b, const uint16_t* weight, float eps, int n_rows, int n,
                                 uint16_t* residual_out, uint16_t* normed_out, float* normed_f32) {
     for (int r = 0; r < n_rows; ++r) {
         float ssq = 0.0f;
         for (int d = 0; d < n; ++d) {
-            const float s = orc_bf16_to_f32(a[(size_t)r * n + d]) + orc_bf16_to_f32(b[(size_t)r * n + d]);
+            const float s = orc_bf16_to_f32(a[(size_t)r * n + d]) + (b ? orc_bf16_to_f32(b[(size_t)r * n + d]) : 0.0f);
             ssq += s * s;
         }
         const float rms = sqrtf(ssq / (float)n + eps);
         for (int d = 0; d < n; ++d) {
-            const float s = orc_bf16_to_f32(a[(size_t)r * n + d]) + orc_bf16_to_f32(b[(size_t)r * n + d]);
+            const float s = orc_bf16_to_f32(a[(size_t)r * n + d]) + (b ? orc_bf16_to_f32(b[(size_t)r * n + d]) : 0.0f);
             const float v = s / rms * orc_bf16_to_f32(weight[d]);
-            residual_out[(size_t)r * n + d] = orc_f32_to_bf16(s);
+            if (residual_out) residual_out[(size_t)r * n + d] = orc_f32_to_bf16(s);
             normed_out[(size_t)r * n + d] = orc_f32_to_bf16(v);
             if (normed_f32) normed_f32[(size_t)r * n + d] = v;
         }

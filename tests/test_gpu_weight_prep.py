@@ -103,3 +103,23 @@ def test_add_rmsnorm_matches_oracle(ffai_lib, oracle_mod, rows, n):
     got = synth.bf16_to_f32(from_dev(nrm, np.uint16)).reshape(rows, n)
     # the sum of squares is reduced in another order: at most one bf16 step from the fp32 oracle value
     assert np.all(np.abs(got - onf) <= 2.0 ** -7 * np.abs(onf) + 1e-6)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,n", [(1, 2816), (33, 2048)])
+def test_plain_rmsnorm_matches_oracle(ffai_lib, oracle_mod, rows, n):
+    """b = NULL: the row-wise RMSNorm in front of a Gemma 4 router and its experts; no residual output needed."""
+    import torch
+    rng = np.random.default_rng(rows + n)
+    a = synth.f32_to_bf16(rng.standard_normal((rows, n)).astype(np.float32) * 2)
+    w = synth.f32_to_bf16((1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32))
+    da, dw = to_dev(a.reshape(-1)), to_dev(w)
+    nrm = torch.zeros(rows * n, dtype=torch.int16, device="cuda")
+    capi.check(ffai_lib.ffai_op_add_rmsnorm(da.data_ptr(), None, dw.data_ptr(), 1e-6, rows, n, None, nrm.data_ptr(), None),
+               "ffai_op_add_rmsnorm")
+    torch.cuda.synchronize()
+    _, _, onf = oracle_mod.add_rmsnorm(a, None, w, 1e-6)
+    got = synth.bf16_to_f32(from_dev(nrm, np.uint16)).reshape(rows, n)
+    assert np.all(np.abs(got - onf) <= 2.0 ** -7 * np.abs(onf) + 1e-6)
+    # a second addend without a place for the sum is refused
+    assert ffai_lib.ffai_op_add_rmsnorm(da.data_ptr(), da.data_ptr(), dw.data_ptr(), 1e-6, rows, n, None, nrm.data_ptr(), None) == capi.FFAI_ERR_INVALID_ARG

@@ -132,3 +132,17 @@ def test_add_rmsnorm_oracle_on_the_reference_pattern(oracle_mod):
     assert np.abs(synth.bf16_to_f32(res) - s).max() < 1e-3 * 32      # the reference's 1e-3, widened for bf16 storage
     assert np.abs(nf - ref).max() < 1e-5
     assert np.abs(synth.bf16_to_f32(nrm) - ref).max() < 1e-2
+
+
+def test_plain_rmsnorm_oracle_on_the_reference_check(oracle_mod):
+    """Without a second addend the op is the reference's RMSNorm; its own check (LayersTests.swift:101-128):
+    x = 1..128, weight = 1, eps = 1e-6, y = x / sqrt(mean(x^2)) within 1e-2 (bf16 storage here: within 0.5 %)."""
+    n = 128
+    xs = np.arange(1, n + 1, dtype=np.float32)
+    xb = synth.f32_to_bf16(xs.reshape(1, n))
+    wb = synth.f32_to_bf16(np.ones(n, dtype=np.float32))
+    res, nrm, nf = oracle_mod.add_rmsnorm(xb, None, wb, 1e-6)
+    expected = xs / np.sqrt((xs.astype(np.float64) ** 2).mean())
+    assert np.array_equal(res, xb)                       # the "sum" is the input itself
+    assert np.abs(nf[0] - expected).max() < 1e-2
+    assert np.abs(synth.bf16_to_f32(nrm)[0] - expected).max() < 5e-3 * expected.max()
