@@ -93,7 +93,6 @@ struct ffai_moe_layer {
     uint16_t* sh_x = nullptr;        // [T,H]  shared expert input (8-run permuted)
     uint16_t* exp_wbf[3] = {nullptr, nullptr, nullptr}; // routed experts expanded to bf16 (prefill weight cache): gate, up, down
     bool cache_planned = false;
-    CUtensorMap tm_gate_bf{}, tm_up_bf{}, tm_down_bf{};
     int opt_tc_weights = 0;          // tensor-core path reads: 0 the bf16 cache when there is one, 1 always the packed weights
     uint16_t* sh_wbf[3] = {nullptr, nullptr, nullptr};  // shared expert expanded to bf16 (bit widths other than 4): gate, up, down
     uint16_t* sh_inner_bf = nullptr; // [T,Is]
@@ -547,12 +546,16 @@ __global__ void expand_router_f32_kernel(const uint32_t* __restrict__ weight, co
     out[i] = __fmaf_rn(bf16_bits_to_f32(scales[g]), (float)unpack_at<BITS>(w, k), bf16_bits_to_f32(biases[g]));
 }
 
-// One projection expanded to bf16 in the tensor-core operand's K order: w = fma(q, scale, bias) rounded
-// once, every 8-run stored as 0,4,1,5,2,6,3,7.  One thread per 8-run.  Runs once, at load time.
+// One projection expanded to bf16 as the tensor-core kernel's operand tiles: w = fma(q, scale, bias) rounded
+// once, every 8-run stored as 0,4,1,5,2,6,3,7 (one 16-byte chunk).  The cache is tile-major: for every
+// (expert, block of 128 rows, 64-k block) the 16 KB operand tile sits contiguously and already 128-byte
+// swizzled (row r of the block at r * 128 bytes, chunk c at ((c ^ (r & 7)) * 16)), so the kernel's weight
+// producer brings a tile in with one contiguous bulk copy.  blocks_per_expert may exceed ceil(n_out / 128):
+// rows past n_out stay zero (the buffer is cleared first).  One thread per 8-run.  Runs once, at load time.
 template <int BITS>
-__global__ void expand_to_bf16_perm8_kernel(const uint32_t* __restrict__ weight, const uint16_t* __restrict__ scales,
+__global__ void expand_to_bf16_tiles_kernel(const uint32_t* __restrict__ weight, const uint16_t* __restrict__ scales,
                                             const uint16_t* __restrict__ biases, uint16_t* __restrict__ out,
-                                            size_t rows, int K, int group_size) {
+                                            size_t rows, int n_out, int blocks_per_expert, int K, int group_size) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int runs = K / 8;
     if (i >= rows * runs) return;
@@ -570,19 +573,36 @@ __global__ void expand_to_bf16_perm8_kernel(const uint32_t* __restrict__ weight,
     o.y = (uint32_t)v[1] | ((uint32_t)v[5] << 16);
     o.z = (uint32_t)v[2] | ((uint32_t)v[6] << 16);
     o.w = (uint32_t)v[3] | ((uint32_t)v[7] << 16);
-    *reinterpret_cast<uint4*>(out + row * K + run * 8) = o;
+    const size_t e = row / n_out;
+    const int rp = (int)(row - e * n_out);
+    const int rb = rp >> 7, r = rp & 127, kb = run >> 3, c = run & 7;
+    const size_t tile = (e * blocks_per_expert + rb) * (size_t)(K / 64) + kb;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(out) + tile * 16384 + (size_t)r * 128 + (size_t)((c ^ (r & 7)) << 4);
+    *reinterpret_cast<uint4*>(dst) = o;
 }
 
-int launch_expand_to_bf16(const ffai_qproj& q, uint16_t* out, size_t rows, int K, int bits, int gs) {
+// 128-row blocks per expert in a tile-major cache: a gate/up stage takes block m of each projection, a down
+// stage takes blocks 2m and 2m+1, so down rounds its count up to an even number (the extra block stays zero).
+int cache_blocks(int n_out, bool fused) { return fused ? (n_out + 127) / 128 : 2 * ((n_out + 255) / 256); }
+
+// Size in bytes of a tile-major cache.
+size_t cache_tiles_bytes(size_t n_groups, int blocks_per_expert, int K) {
+    return n_groups * blocks_per_expert * (size_t)(K / 64) * 16384;
+}
+
+int launch_expand_to_bf16(const ffai_qproj& q, uint16_t* out, size_t n_groups, int n_out, int blocks_per_expert, int K,
+                          int bits, int gs) {
+    const size_t rows = n_groups * n_out;
     const size_t n = rows * (K / 8);
     const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (cudaMemset(out, 0, cache_tiles_bytes(n_groups, blocks_per_expert, K)) != cudaSuccess) return FFAI_ERR_CUDA;
     switch (bits) {
-        case 2: expand_to_bf16_perm8_kernel<2><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
-        case 3: expand_to_bf16_perm8_kernel<3><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
-        case 4: expand_to_bf16_perm8_kernel<4><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
-        case 5: expand_to_bf16_perm8_kernel<5><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
-        case 6: expand_to_bf16_perm8_kernel<6><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
-        case 8: expand_to_bf16_perm8_kernel<8><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, K, gs); break;
+        case 2: expand_to_bf16_tiles_kernel<2><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, n_out, blocks_per_expert, K, gs); break;
+        case 3: expand_to_bf16_tiles_kernel<3><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, n_out, blocks_per_expert, K, gs); break;
+        case 4: expand_to_bf16_tiles_kernel<4><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, n_out, blocks_per_expert, K, gs); break;
+        case 5: expand_to_bf16_tiles_kernel<5><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, n_out, blocks_per_expert, K, gs); break;
+        case 6: expand_to_bf16_tiles_kernel<6><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, n_out, blocks_per_expert, K, gs); break;
+        case 8: expand_to_bf16_tiles_kernel<8><<<blocks, 256>>>(q.weight, q.scales, q.biases, out, rows, n_out, blocks_per_expert, K, gs); break;
         default: return FFAI_ERR_INVALID_ARG;
     }
     return cudaGetLastError() == cudaSuccess ? FFAI_OK : FFAI_ERR_CUDA;
@@ -890,20 +910,18 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
         }
         if (L->cache_planned) {
             const ffai_qproj* q[3] = {&L->w.gate_proj, &L->w.up_proj, &L->w.down_proj};
-            const size_t rows[3] = {(size_t)El * c.intermediate, (size_t)El * c.intermediate, (size_t)El * c.hidden};
+            const int n_out[3] = {c.intermediate, c.intermediate, c.hidden};
             const int kk[3] = {c.hidden, c.hidden, c.intermediate};
             for (int i = 0; i < 3; ++i) {
+                const int blocks = cache_blocks(n_out[i], i < 2);
                 void* buf = nullptr;
-                CUDA_TRY(L, cudaMalloc(&buf, rows[i] * kk[i] * 2));
+                CUDA_TRY(L, cudaMalloc(&buf, cache_tiles_bytes((size_t)El, blocks, kk[i])));
                 L->owned_weights.push_back(buf);
                 L->exp_wbf[i] = static_cast<uint16_t*>(buf);
-                if ((rc = launch_expand_to_bf16(*q[i], L->exp_wbf[i], rows[i], kk[i], c.expert_bits, c.expert_group_size)))
+                if ((rc = launch_expand_to_bf16(*q[i], L->exp_wbf[i], (size_t)El, n_out[i], blocks, kk[i], c.expert_bits, c.expert_group_size)))
                     return fail(L, rc, "expanding the experts to bf16 failed");
             }
             CUDA_TRY(L, cudaDeviceSynchronize());
-            ok = ok && make_act_map(&L->tm_gate_bf, L->exp_wbf[0], rows[0], c.hidden, BM);
-            ok = ok && make_act_map(&L->tm_up_bf, L->exp_wbf[1], rows[1], c.hidden, BM);
-            ok = ok && make_act_map(&L->tm_down_bf, L->exp_wbf[2], rows[2], c.intermediate, BM);
             if (c.expert_bits != 4) {
                 ok = ok && make_act_map(&L->tm_xg, L->xg, Mcap, c.hidden, BM);
                 ok = ok && make_act_map(&L->tm_inner, L->inner_bf, Mcap, c.intermediate, BM);
@@ -919,20 +937,18 @@ extern "C" FFAI_API int ffai_moe_set_weights(ffai_moe_layer* L, const ffai_moe_w
                 // other bit widths: expand the one shared expert to bf16 once (2 bytes per weight) and let the
                 // tensor-core kernel read it without a dequant stage
                 const ffai_qproj* q[3] = {&L->w.shared_gate_proj, &L->w.shared_up_proj, &L->w.shared_down_proj};
-                const size_t rows[3] = {(size_t)Is, (size_t)Is, (size_t)c.hidden};
+                const int n_out[3] = {Is, Is, c.hidden};
                 const int kk[3] = {c.hidden, c.hidden, Is};
                 for (int i = 0; i < 3; ++i) {
+                    const int blocks = cache_blocks(n_out[i], i < 2);
                     void* buf = nullptr;
-                    CUDA_TRY(L, cudaMalloc(&buf, rows[i] * kk[i] * 2));
+                    CUDA_TRY(L, cudaMalloc(&buf, cache_tiles_bytes(1, blocks, kk[i])));
                     L->owned_weights.push_back(buf);
                     L->sh_wbf[i] = static_cast<uint16_t*>(buf);
-                    if ((rc = launch_expand_to_bf16(*q[i], L->sh_wbf[i], rows[i], kk[i], c.shared_bits, c.shared_group_size)))
+                    if ((rc = launch_expand_to_bf16(*q[i], L->sh_wbf[i], 1, n_out[i], blocks, kk[i], c.shared_bits, c.shared_group_size)))
                         return fail(L, rc, "expanding the shared expert to bf16 failed");
                 }
                 CUDA_TRY(L, cudaDeviceSynchronize());
-                ok = ok && make_act_map(&L->tm_sh_gate, L->sh_wbf[0], Is, c.hidden, BM);
-                ok = ok && make_act_map(&L->tm_sh_up, L->sh_wbf[1], Is, c.hidden, BM);
-                ok = ok && make_act_map(&L->tm_sh_down, L->sh_wbf[2], c.hidden, Is, BM);
             }
             ok = ok && make_act_map(&L->tm_sh_x, L->sh_x, Tcap, c.hidden, BM);
             ok = ok && make_act_map(&L->tm_sh_inner, L->sh_inner_bf, Tcap, Is, BM);
@@ -1324,13 +1340,21 @@ bool tc_possible(const ffai_moe_layer* L) { return L->tc_ok && (L->cfg.expert_bi
 // item weighs more.
 int tc_gate_up(ffai_moe_layer* L, const g100::Params& p, double rows_per_expert, cudaStream_t st) {
     const bool packed_pays = L->cfg.expert_bits == 4 && L->opt_tc_weights == 0 && rows_per_expert <= 160.0;
-    return tc_reads_cache(L) && !packed_pays ? g100::launch_grouped_gemm<true, uint16_t, true>(L->tm_gate_bf, L->tm_up_bf, L->tm_xg, p, L->n_sms, st)
-                             : g100::launch_grouped_gemm<true, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg, p, L->n_sms, st);
+    if (tc_reads_cache(L) && !packed_pays) {
+        g100::Params pc = p;
+        pc.wcache = L->exp_wbf[0]; pc.wcache2 = L->exp_wbf[1]; pc.cache_blocks = cache_blocks(p.n_out, true);
+        return g100::launch_grouped_gemm<true, uint16_t, true>(L->tm_xg, L->tm_xg, L->tm_xg, pc, L->n_sms, st);
+    }
+    return g100::launch_grouped_gemm<true, uint16_t>(L->tm_gate, L->tm_up, L->tm_xg, p, L->n_sms, st);
 }
 template <typename TOut>
 int tc_down(ffai_moe_layer* L, const g100::Params& p, cudaStream_t st) {
-    return tc_reads_cache(L) ? g100::launch_grouped_gemm<false, TOut, true>(L->tm_down_bf, L->tm_down_bf, L->tm_inner, p, L->n_sms, st)
-                             : g100::launch_grouped_gemm<false, TOut>(L->tm_down, L->tm_down, L->tm_inner, p, L->n_sms, st);
+    if (tc_reads_cache(L)) {
+        g100::Params pc = p;
+        pc.wcache = L->exp_wbf[2]; pc.wcache2 = nullptr; pc.cache_blocks = cache_blocks(p.n_out, false);
+        return g100::launch_grouped_gemm<false, TOut, true>(L->tm_inner, L->tm_inner, L->tm_inner, pc, L->n_sms, st);
+    }
+    return g100::launch_grouped_gemm<false, TOut>(L->tm_down, L->tm_down, L->tm_inner, p, L->n_sms, st);
 }
 
 // Whether rows travel 8-run permuted (the layout both 4-bit kernels read).  Every rank must agree, so
@@ -1586,14 +1610,16 @@ int forward_device(ffai_moe_layer* L, const uint16_t* x, int T, uint16_t* out, c
                 p.n_out = Is; p.K = H; p.m_tiles = (Is + BN / 2 - 1) / (BN / 2);
                 p.out = L->sh_inner_bf; p.out_ld = Is; p.out_permute8 = 1;
                 const bool wbf = L->sh_wbf[0] != nullptr;
-                if (wbf ? launch_grouped_gemm<true, uint16_t, true>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x, p, L->n_sms, ss)
+                if (wbf) { p.wcache = L->sh_wbf[0]; p.wcache2 = L->sh_wbf[1]; p.cache_blocks = cache_blocks(Is, true); }
+                if (wbf ? launch_grouped_gemm<true, uint16_t, true>(L->tm_sh_x, L->tm_sh_x, L->tm_sh_x, p, L->n_sms, ss)
                         : launch_grouped_gemm<true, uint16_t>(L->tm_sh_gate, L->tm_sh_up, L->tm_sh_x, p, L->n_sms, ss))
                     return fail(L, FFAI_ERR_CUDA, "shared gate/up grouped GEMM launch failed");
                 p.scales = L->w.shared_down_proj.scales; p.biases = L->w.shared_down_proj.biases;
                 p.scales2 = nullptr; p.biases2 = nullptr;
                 p.n_out = H; p.K = Is; p.m_tiles = (H + BN - 1) / BN;
                 p.out = L->sh_y; p.out_ld = H; p.out_permute8 = 0;
-                if (wbf ? launch_grouped_gemm<false, float, true>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner, p, L->n_sms, ss)
+                if (wbf) { p.wcache = L->sh_wbf[2]; p.wcache2 = nullptr; p.cache_blocks = cache_blocks(H, false); }
+                if (wbf ? launch_grouped_gemm<false, float, true>(L->tm_sh_inner, L->tm_sh_inner, L->tm_sh_inner, p, L->n_sms, ss)
                         : launch_grouped_gemm<false, float>(L->tm_sh_down, L->tm_sh_down, L->tm_sh_inner, p, L->n_sms, ss))
                     return fail(L, FFAI_ERR_CUDA, "shared down grouped GEMM launch failed");
                 L->launches += 4;

@@ -14,9 +14,9 @@
 // issuing thread 80-100 clk whatever its N; only N = 256 keeps the tensor pipe busy that long.)
 //
 // Warp roles in a 768-thread CTA (persistent; work items are (expert, 128 routed rows, weight-row tile)):
-//   warp 0       TMA producer of weights.  Packed 4-bit: two boxes of [128 rows x 128 B] (256 k) per stage,
-//                128-byte swizzle, ring "W".  bf16 weights (WBF16: expanded once at load time): two boxes of
-//                [128 rows x 64 k] per 64 k straight into the operand ring "B".
+//   warp 0       producer of weights.  Packed 4-bit: two TMA boxes of [128 rows x 128 B] (256 k) per stage,
+//                128-byte swizzle, ring "W".  bf16 weights (WBF16: expanded once at load time into tile-major,
+//                pre-swizzled 16 KB tiles): two contiguous bulk copies per 64 k straight into the operand ring "B".
 //   warp 2       TMA producer of activations: [128 rows x 128 B] per 64 k, 128-byte swizzle, ring "X"
 //   warp 3       scheduler: finds the expert, row range and weight tile of each of the CTA's work items (a 32-way
 //                search over the tile prefix sums) and hands them to every other role through a small ring in
@@ -69,6 +69,9 @@ struct Params {
     const uint16_t* scales2;   // second projection (fused gate/up)
     const uint16_t* biases2;
     const uint16_t* row_bias2;
+    const uint16_t* wcache;    // WBF16: the projection's tile-major bf16 cache, [E, cache_blocks, K/64] tiles of 16 KB
+    const uint16_t* wcache2;   // WBF16, fused gate/up: the up projection's cache
+    int cache_blocks;          // 128-row blocks per expert in a cache
     const uint32_t* sb;        // nullable: (scale | bias << 16) words re-tiled [E, n_out/16, K/64, 16] (group 64 or 128)
     const uint32_t* sb2;
     int n_out;                 // output rows per expert
@@ -166,6 +169,11 @@ FFAI_DEVINL void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
+}
+// Contiguous bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion on the mbarrier.
+FFAI_DEVINL void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 FFAI_DEVINL void prefetch_tmap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -354,9 +362,9 @@ struct SmemLayout {
 // FUSED:  the 256 weight rows are 128 gate rows and the 128 matching up rows of one expert;
 //         out[row, n] = act(Wg[e][n]·x[row] + bg, Wu[e][n]·x[row] + bu), bf16, optionally 8-run permuted
 // !FUSED: 256 consecutive rows of one projection;  out[row, n] = W[e][n]·x[row] + b, TOut
-// WBF16: the weights are already bf16 in the operand's K order ([rows, K], 8-runs permuted like the
-//         activations): the weight producer copies them by TMA straight into the operand ring and the
-//         dequant warps have nothing to do.  Used for projections that were expanded once at load time
+// WBF16: the weights are already bf16 operand tiles (tile-major cache, 8-runs permuted like the
+//         activations, 128-byte swizzle applied): the weight producer copies them straight into the operand
+//         ring and the dequant warps have nothing to do.  Used for projections that were expanded once at load time
 //         (bit widths other than 4).
 template <bool FUSED, typename TOut, bool WBF16>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -396,8 +404,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (int s = 0; s < NSCHED; ++s) { mbar_init(s_full(s), 1); mbar_init(s_empty(s), L::N_ITEM_READERS); }
         *abort_flag = 0;
         fence_barrier_init();
-        prefetch_tmap(&tm_w);
-        if (FUSED) prefetch_tmap(&tm_w2);
+        if (!WBF16) {
+            prefetch_tmap(&tm_w);
+            if (FUSED) prefetch_tmap(&tm_w2);
+        }
         prefetch_tmap(&tm_x);
     }
     if (warp == MMA_WARP) {
@@ -411,22 +421,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     ItemFeed feed{s_full(0), s_empty(0), sbase + (uint32_t)L::OFF_SCHED, 0u};
 
     if (warp == W_WARP && WBF16) {
-        // ───────────── TMA producer, bf16 weights: two 128-row x 128-byte boxes per 64 k, into the operand ring ─────────────
+        // ───────────── producer, bf16 weights: two contiguous 16 KB tiles per 64 k, into the operand ring ─────────────
+        // The cache holds every (expert, 128-row block, 64-k block) tile contiguously and already swizzled, so a
+        // tile is one bulk copy of consecutive bytes: full DRAM pages instead of 128 rows of 128 bytes 4 KB apart.
         if (lane == 0) {
             RingPos bp{0, 0};
             uint32_t issued = 0;
             bool ok = true;
+            constexpr uint32_t TILE = BM * BK * 2;   // 16 KB
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 TileCoord c;
                 if (!feed.take(c, abort_flag, false)) { ok = false; break; }
-                const int wrow = c.expert * p.n_out + c.m_tile * ROWS_PER_TILE;
+                const size_t blk = (size_t)c.expert * p.cache_blocks + (FUSED ? c.m_tile : 2 * c.m_tile);
+                const uint8_t* src0 = reinterpret_cast<const uint8_t*>(p.wcache) + blk * KB * TILE;
+                const uint8_t* src1 = FUSED ? reinterpret_cast<const uint8_t*>(p.wcache2) + blk * KB * TILE
+                                            : src0 + (size_t)KB * TILE;   // the next 128-row block of the projection
                 for (int kb = 0; kb < KB; ++kb) {
                     if (!mbar_wait<64>(b_empty(bp.stage), bp.phase ^ 1, abort_flag)) { ok = false; break; }
                     const uint32_t stage = sbase + L::OFF_B + bp.stage * L::B_STAGE;
                     mbar_arrive_expect_tx(b_full(bp.stage), L::B_STAGE);
-                    tma_load_2d(stage, &tm_w, kb * BK, wrow, b_full(bp.stage));
-                    if (FUSED) tma_load_2d(stage + L::B_STAGE / 2, &tm_w2, kb * BK, wrow, b_full(bp.stage));
-                    else tma_load_2d(stage + L::B_STAGE / 2, &tm_w, kb * BK, wrow + BN / 2, b_full(bp.stage));
+                    bulk_load_1d(stage, src0 + (size_t)kb * TILE, TILE, b_full(bp.stage));
+                    bulk_load_1d(stage + L::B_STAGE / 2, src1 + (size_t)kb * TILE, TILE, b_full(bp.stage));
                     bp.advance(NB);
                     ++issued;
                 }
