@@ -247,6 +247,25 @@ def test_tc_bf16_weight_cache_any_bit_width(oracle_mod, bits):
     run_and_check(oracle_mod, spec, 300)          # automatic choice
 
 
+def test_tc_weight_cache_with_ragged_row_blocks(oracle_mod):
+    """2880 output rows are 22.5 blocks of 128: the tile-major cache pads the last block of gate/up with zero
+    rows and gives down an even block count; both weight sources must still give the same bits."""
+    spec = synth.cfg2_gptoss().with_(prefill_weight_cache=2, expert_row_bias=1)
+    host = synth.make_layer(spec, 9)
+    x = synth.make_tokens(600, spec.hidden, 9)
+    layer = MoELayer(host, 600)
+    try:
+        layer.set_option("path", TC)
+        layer.set_option("tc_weights", 2)
+        cached, _ = layer.forward_host(x)
+        layer.set_option("tc_weights", 1)
+        packed, _ = layer.forward_host(x)
+    finally:
+        layer.close()
+    assert np.array_equal(cached, packed)
+    run_and_check(oracle_mod, spec, 600, seed=9, host=host, path=TC, options={"tc_weights": 2})
+
+
 def test_tc_cache_and_packed_weights_agree(oracle_mod):
     spec = synth.LayerSpec("cache_vs_packed", 512, 256, 16, 4, prefill_weight_cache=2)
     host = synth.make_layer(spec, 3)
