@@ -159,16 +159,6 @@ FFAI_DEVINL void peer_barrier(const PeerPtrs& win, int me, int world, int barrie
     __threadfence_system();
 }
 
-__global__ void __launch_bounds__(256)
-ep_publish_counts_kernel(const uint32_t* __restrict__ counts, int n_experts, int me, int world, PeerPtrs win,
-                         uint32_t epoch, uint64_t limit_ns, uint32_t* error_word) {
-    for (int d = 0; d < world; ++d) {
-        uint32_t* row = win_matrix(win.p[d]) + (size_t)me * n_experts;
-        for (int e = threadIdx.x; e < n_experts; e += blockDim.x) row[e] = counts[e];
-    }
-    peer_barrier(win, me, world, 0, epoch, limit_ns, error_word);
-}
-
 __global__ void __launch_bounds__(32)
 ep_barrier_kernel(int barrier, int me, int world, PeerPtrs win, uint32_t epoch, uint64_t limit_ns, uint32_t* error_word) {
     peer_barrier(win, me, world, barrier, epoch, limit_ns, error_word);
@@ -198,18 +188,74 @@ __host__ __device__ inline uint32_t peer_local_offset(const uint32_t* matrix, in
 //   send_base[n_experts]  where this rank's rows for expert e start in the owner's row buffer
 // Offsets are clamped to the row buffer's capacity (and the error word raised) so that a matrix left half-updated
 // by a barrier that gave up cannot send the expert kernels past the buffer.
-__global__ void __launch_bounds__(256)
-ep_layout_kernel(const uint32_t* __restrict__ matrix, int n_experts, int e_local, int me, int world,
-                 uint32_t* __restrict__ local_off, uint32_t* __restrict__ send_base, uint32_t capacity, uint32_t* error_word) {
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) send_base[e] = peer_send_base(matrix, n_experts, e_local, me, world, e);
-    for (int el = threadIdx.x; el <= e_local; el += blockDim.x) {
-        uint32_t v = peer_local_offset(matrix, n_experts, e_local, me, world, el);
+FFAI_DEVINL void ep_layout_block(const uint32_t* __restrict__ matrix, int n_experts, int e_local, int me, int world,
+                                 uint32_t* __restrict__ local_off, uint32_t* __restrict__ send_base, uint32_t capacity,
+                                 uint32_t* error_word) {
+    // The same numbers as peer_send_base / peer_local_offset, by prefix sums: per expert the rows of all sources,
+    // an exclusive scan of those totals inside every owner's range (one warp per owner at a time, 32 experts per
+    // round), plus the rows of the sources below this rank.  (Evaluating the two functions per expert walks up
+    // to e_local * world matrix words in a dependent chain per thread: 50 us at 256 experts.)
+    extern __shared__ uint32_t lay_sm[];     // [n_experts] totals, then [n_experts] exclusive scans
+    uint32_t* tot = lay_sm;
+    uint32_t* excl = lay_sm + n_experts;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        uint32_t t = 0;
+        for (int s = 0; s < world; ++s) t += __ldcg(matrix + (size_t)s * n_experts + e);   // written by the peers: read from L2
+        tot[e] = t;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int owner = warp; owner < world; owner += n_warps) {
+        uint32_t carry = 0;
+        for (int e0 = 0; e0 < e_local; e0 += 32) {
+            const int el = e0 + lane;
+            const uint32_t c = el < e_local ? tot[owner * e_local + el] : 0u;
+            uint32_t incl = c;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                if (lane >= d) incl += v;
+            }
+            if (el < e_local) excl[owner * e_local + el] = carry + incl - c;
+            carry += __shfl_sync(0xFFFFFFFFu, incl, 31);
+        }
+        if (owner == me && lane == 0) {
+            uint32_t v = carry;              // all rows this rank's experts receive
+            if (v > capacity) {
+                v = capacity;
+                atomicExch(error_word, EP_ERR_CAPACITY);
+            }
+            local_off[e_local] = v;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        uint32_t below = 0;
+        for (int s = 0; s < me; ++s) below += __ldcg(matrix + (size_t)s * n_experts + e);
+        send_base[e] = excl[e] + below;
+    }
+    for (int el = threadIdx.x; el < e_local; el += blockDim.x) {
+        uint32_t v = excl[me * e_local + el];
         if (v > capacity) {
             v = capacity;
             atomicExch(error_word, EP_ERR_CAPACITY);
         }
         local_off[el] = v;
     }
+}
+
+// Counts to every peer, barrier 0, then the layout - one launch (one block of 256 threads, 2 * n_experts words of
+// dynamic shared memory).
+__global__ void __launch_bounds__(256)
+ep_publish_and_layout_kernel(const uint32_t* __restrict__ counts, int n_experts, int e_local, int me, int world, PeerPtrs win,
+                             uint32_t epoch, uint64_t limit_ns, uint32_t* __restrict__ local_off,
+                             uint32_t* __restrict__ send_base, uint32_t capacity, uint32_t* error_word) {
+    for (int d = 0; d < world; ++d) {
+        uint32_t* row = win_matrix(win.p[d]) + (size_t)me * n_experts;
+        for (int e = threadIdx.x; e < n_experts; e += blockDim.x) row[e] = counts[e];
+    }
+    peer_barrier(win, me, world, 0, epoch, limit_ns, error_word);
+    ep_layout_block(win_matrix(win.p[me]), n_experts, e_local, me, world, local_off, send_base, capacity, error_word);
 }
 
 // Gather fused with the dispatch: sorted row r of this rank (token perm[r]/k, expert indices[perm[r]])

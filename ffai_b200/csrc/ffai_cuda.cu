@@ -137,7 +137,7 @@ struct ffai_moe_layer {
 
     // stage timing
     bool timing = false;
-    cudaEvent_t ev[FFAI_N_STAGES][2][2]{};  // [stage][segment][begin/end]
+    cudaEvent_t ev[FFAI_N_STAGES][3][2]{};  // [stage][segment][begin/end]
     bool ev_made = false;
     int ev_segments[FFAI_N_STAGES]{};
     int launches = 0;
@@ -653,13 +653,13 @@ int launch_affine_rowdot(const ffai_linear& g, int bits, int gs, const uint16_t*
 
 enum Stage { ST_ROUTER = 0, ST_PLAN, ST_GATHER, ST_GATE_UP, ST_DOWN, ST_COMBINE, ST_SHARED, ST_EXCHANGE };
 
-// A stage may run in up to two segments per forward (the exchange does).
+// A stage may run in up to three segments per forward (the exchange does).
 void stage_begin(ffai_moe_layer* L, int stage, cudaStream_t st) {
-    if (!L->timing || L->ev_segments[stage] >= 2) return;
+    if (!L->timing || L->ev_segments[stage] >= 3) return;
     cudaEventRecord(L->ev[stage][L->ev_segments[stage]][0], st);
 }
 void stage_end(ffai_moe_layer* L, int stage, cudaStream_t st) {
-    if (!L->timing || L->ev_segments[stage] >= 2) return;
+    if (!L->timing || L->ev_segments[stage] >= 3) return;
     cudaEventRecord(L->ev[stage][L->ev_segments[stage]][1], st);
     L->ev_segments[stage] += 1;
 }
@@ -1547,14 +1547,20 @@ int forward_experts_ep_peer(ffai_moe_layer* L, const uint16_t* x, int T, cudaStr
     const uint32_t epoch = ++L->ep_epoch;
     int rc;
     stage_begin(L, ST_EXCHANGE, st);
-    ep::ep_publish_counts_kernel<<<1, 256, 0, st>>>(L->counts, E, me, W, L->ep_peer_win, epoch, L->ep_wait_ns, L->error_word);
     uint32_t* local_off = L->ep_plan_dev;
-    ep::ep_layout_kernel<<<1, 256, 0, st>>>(ep::win_matrix(L->ep_win), E, El, me, W, local_off, L->ep_send_base, (uint32_t)L->mx_rows, L->error_word);
+    ep::ep_publish_and_layout_kernel<<<1, 256, 2 * E * sizeof(uint32_t), st>>>(L->counts, E, El, me, W, L->ep_peer_win, epoch, L->ep_wait_ns,
+                                                                                local_off, L->ep_send_base, (uint32_t)L->mx_rows, L->error_word);
+    stage_end(L, ST_EXCHANGE, st);
+    // the dispatch is the row gather with its stores going to the owners' buffers: timed as the gather stage,
+    // so the exchange stage shows what the counts, the layout and the barriers cost by themselves
+    stage_begin(L, ST_GATHER, st);
     if (M > 0)
         ep::ep_dispatch_kernel<<<(M + 7) / 8, 256, 0, st>>>(x, L->perm, L->indices, L->offsets, L->ep_send_base, K, El, M, H,
                                                             L->ep_peer_rows, (uint32_t)L->mx_rows, L->error_word);
+    stage_end(L, ST_GATHER, st);
+    stage_begin(L, ST_EXCHANGE, st);
     ep::ep_barrier_kernel<<<1, 32, 0, st>>>(1, me, W, L->ep_peer_win, epoch, L->ep_wait_ns, L->error_word);
-    L->launches += M > 0 ? 4 : 3;
+    L->launches += M > 0 ? 3 : 2;
     stage_end(L, ST_EXCHANGE, st);
     if (cudaGetLastError() != cudaSuccess) return fail(L, FFAI_ERR_CUDA, "exchange kernels launch failed");
 
