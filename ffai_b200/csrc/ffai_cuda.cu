@@ -340,7 +340,9 @@ int launch_router_batched(const RouterParams& p, const uint16_t* x, int T, uint3
         const int tiles = ((T + RB_TOK - 1) / RB_TOK) * ((p.n_experts + RB_EXP - 1) / RB_EXP);
         int z = 1, per = n_chunks;
         float* part = nullptr;
-        if (tiles < n_sms) {
+        // measured at 256 experts: 128 tiles take 156 us un-split (one block per SM) against 169 us split three ways
+        // with their 134 MB of chunk sums; 64 tiles take 87 us split and would take the same 156 us un-split
+        if (tiles * 4 < n_sms * 3) {
             if (partials && (size_t)T * p.n_experts * n_chunks <= partials_capacity) {
                 z = std::min(n_chunks, (2 * n_sms + tiles - 1) / tiles);
                 per = (n_chunks + z - 1) / z;
